@@ -1,0 +1,221 @@
+"""CUDA kernels against the fp32 PyTorch references of the same ops."""
+import math
+
+import pytest
+import torch
+
+from tokenweave_b200 import ops
+from tokenweave_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+def rnd(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(BF)
+
+
+def close(a, b, atol=2e-2, rtol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    bound = atol + rtol * b.abs()
+    bad = (err > bound).sum().item()
+    assert bad == 0, f"{bad}/{a.numel()} elements off, max err {err.max().item():.4g} (ref max {b.abs().max().item():.4g})"
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    ops.reset_status()
+    yield
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (300, 1280, 1024), (1000, 1000, 200),
+                                   (4096, 7168, 1024), (77, 8, 512), (2048, 8192, 3584)])
+def test_gemm_plain(M, N, K):
+    a, w = rnd(M, K), rnd(N, K, scale=1 / math.sqrt(K))
+    out = ops.gemm(a, w)
+    close(out, ref.gemm(a, w))
+
+
+def test_gemm_bias_rowscale_strided_out():
+    M, N, K = 513, 1280, 1024
+    a, w, bias = rnd(M, K), rnd(N, K, scale=1 / math.sqrt(K)), rnd(N)
+    rs = torch.rand(M, device=DEV)
+    big = torch.zeros(M, N + 64, device=DEV, dtype=BF)
+    out = big[:, 32:32 + N]
+    ops.gemm(a, w, out=out, bias=bias, row_scale=rs)
+    close(out, ref.gemm(a, w, bias, rs))
+    assert big[:, :32].abs().max().item() == 0 and big[:, 32 + N:].abs().max().item() == 0
+
+
+def test_gemm_strided_a():
+    M, N, K = 256, 512, 256
+    big = rnd(M, 3 * K)
+    a = big[:, K:2 * K]
+    w = rnd(N, K, scale=1 / math.sqrt(K))
+    close(ops.gemm(a, w), ref.gemm(a.contiguous(), w))
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 3584, 1024), (1000, 200, 256), (4096, 3696, 512)])
+def test_gemm_swiglu(M, I, K):
+    a, w = rnd(M, K), rnd(2 * I, K, scale=1 / math.sqrt(K))
+    out = ops.gemm(a, w, swiglu=True)
+    assert out.shape == (M, I)
+    close(out, ref.gemm_swiglu(a, w))
+
+
+def test_gemm_max_ctas():
+    M, N, K = 2048, 2048, 512
+    a, w = rnd(M, K), rnd(N, K, scale=1 / math.sqrt(K))
+    close(ops.gemm(a, w, max_ctas=7), ref.gemm(a, w))
+
+
+@pytest.mark.parametrize("T,H", [(7, 256), (83, 8192), (1000, 6144), (64, 4096)])
+def test_norms(T, H):
+    x, r, w = rnd(T, H), rnd(T, H), (1 + 0.1 * torch.randn(H, device=DEV)).to(BF)
+    close(ops.rmsnorm(x, w, 1e-5), ref.rmsnorm(x, w, 1e-5))
+    x1, r1 = x.clone(), r.clone()
+    x2, r2 = x.clone(), r.clone()
+    ops.add_rmsnorm_(x1, r1, w, 1e-5)
+    ref.add_rmsnorm_(x2, r2, w, 1e-5)
+    close(x1, x2)
+    assert torch.equal(r1, r2)
+    x1, x2 = x.clone(), x.clone()
+    ro1, ro2 = torch.empty_like(x), torch.empty_like(x)
+    ops.rmsnorm_copy_(x1, ro1, w, 1e-5, max_ctas=5)
+    ref.rmsnorm_copy_(x2, ro2, w, 1e-5)
+    close(x1, x2)
+    assert torch.equal(ro1, ro2)
+
+
+@pytest.mark.parametrize("hq,hkv,D,page", [(8, 2, 128, 16), (64, 8, 128, 128), (4, 2, 64, 32)])
+def test_rope_kv_write(hq, hkv, D, page):
+    T, blocks = 333, 40
+    qkv = rnd(T + 5, (hq + 2 * hkv) * D)
+    pos = torch.randint(0, 4000, (T,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(blocks * page, device=DEV)[:T].to(torch.int32)
+    slots[5] = -1
+    cs = ref.build_cos_sin_cache(D, 4096, 500000.0, device=DEV)
+    kc, vc = torch.zeros(blocks, page, hkv, D, device=DEV, dtype=BF), torch.zeros(blocks, page, hkv, D, device=DEV, dtype=BF)
+    kc2, vc2 = kc.clone(), vc.clone()
+    q1, q2 = qkv.clone(), qkv.clone()
+    ops.rope_kv_write_(q1, pos, slots, cs, kc, vc, hq, hkv, D, write_k_back=True)
+    ref.rope_kv_write_(q2[:T], pos, slots, cs, kc2, vc2, hq, hkv, D)
+    close(q1, q2, atol=1e-2)
+    close(kc, kc2, atol=1e-2)
+    assert torch.equal(vc, vc2)
+
+
+def test_swiglu_embedding_argmax():
+    x = rnd(300, 2 * 3584)
+    close(ops.swiglu(x), ref.swiglu(x))
+    table = rnd(1000, 512)
+    ids = torch.randint(0, 2000, (257,), device=DEV, dtype=torch.int32)
+    out = ops.embedding(ids, table, vocab_start=500, vocab_end=1500)
+    assert torch.equal(out, ref.embedding(ids, table, 500, 1500))
+    logits = torch.randn(33, 128256, device=DEV)
+    assert torch.equal(ops.argmax(logits).long(), torch.argmax(logits, -1))
+
+
+def _make_paged(seqs, hkv, D, page, extra_blocks=3):
+    """seqs: list of (q_len, kv_len). Returns caches filled with random data + metadata."""
+    n_blocks = sum((kv + page - 1) // page for _, kv in seqs) + extra_blocks
+    kc, vc = rnd(n_blocks, page, hkv, D), rnd(n_blocks, page, hkv, D)
+    perm = torch.randperm(n_blocks).tolist()
+    max_blocks = max((kv + page - 1) // page for _, kv in seqs) + 1
+    bt = torch.zeros(len(seqs), max_blocks, dtype=torch.int32)
+    cur = 0
+    for b, (_, kv) in enumerate(seqs):
+        n = (kv + page - 1) // page
+        bt[b, :n] = torch.tensor(perm[cur:cur + n], dtype=torch.int32)
+        cur += n
+    cu = [0]
+    for ql, _ in seqs:
+        cu.append(cu[-1] + ql)
+    return kc, vc, bt.to(DEV), cu, [kv for _, kv in seqs]
+
+
+@pytest.mark.parametrize("hq,hkv,D,page,seqs", [
+    (4, 2, 128, 16, [(128, 128)]),
+    (8, 1, 128, 128, [(300, 300), (17, 17), (129, 129)]),
+    (8, 2, 128, 16, [(200, 1000), (1, 77), (128, 640), (5, 5)]),
+    (4, 4, 64, 32, [(333, 333), (64, 500)]),
+    (16, 2, 128, 64, [(1024, 1024), (700, 2048)]),
+])
+def test_attn_prefill(hq, hkv, D, page, seqs):
+    kc, vc, bt, cu, kv_lens = _make_paged(seqs, hkv, D, page)
+    T = cu[-1]
+    q = rnd(T, hq * D)
+    scale = D ** -0.5
+    expect = ref.paged_attention(q, kc, vc, cu, kv_lens, bt, hq, hkv, D, scale)
+    tile_seq, tile_q0 = [], []
+    for b, (ql, _) in enumerate(seqs):
+        for q0 in range(0, ql, 128):
+            tile_seq.append(b)
+            tile_q0.append(q0)
+    out = torch.zeros_like(q)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    ops.attn_prefill(q, kc, vc, out, i32(cu), i32(kv_lens), bt, i32(tile_seq), i32(tile_q0), len(tile_seq), hq,
+                     hkv, D, scale)
+    torch.cuda.synchronize()
+    close(out, expect, atol=2e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("hq,hkv,D,page,kvs", [
+    (8, 1, 128, 16, [1, 31, 32, 33, 700]),
+    (64, 8, 128, 128, [5000, 77]),
+    (6, 1, 128, 64, [300] * 40),
+    (4, 2, 64, 16, [129, 4096]),
+])
+def test_attn_decode(hq, hkv, D, page, kvs):
+    seqs = [(1, kv) for kv in kvs]
+    kc, vc, bt, cu, kv_lens = _make_paged(seqs, hkv, D, page)
+    T = len(kvs)
+    q = rnd(T, hq * D)
+    scale = D ** -0.5
+    expect = ref.paged_attention(q, kc, vc, cu, kv_lens, bt, hq, hkv, D, scale)
+    out = torch.zeros_like(q)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    ops.attn_decode(q, kc, vc, out, i32(list(range(T))), i32(list(range(T))), i32(kv_lens), T, bt, hq, hkv, D,
+                    scale, max(kvs))
+    close(out, expect, atol=2e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("T,H,I,E", [(64, 512, 256, 8), (1000, 1024, 512, 8), (300, 6144, 2048, 8)])
+def test_moe_pipeline(T, H, I, E):
+    topk = 2
+    x = rnd(T, H)
+    gate = rnd(E, H, scale=1 / math.sqrt(H))
+    w13 = rnd(E, 2 * I, H, scale=1 / math.sqrt(H))
+    w2 = rnd(E, H, I, scale=1 / math.sqrt(I))
+    tw, ids, logits = ops.moe_router(x, gate, topk, want_logits=True)
+    rw, rids, rlogits = ref.moe_router(x, gate, topk)
+    close(logits, rlogits, atol=1e-2)
+    # top-k ids may differ only where probabilities are nearly tied
+    same = (ids.long() == rids.long()).all(dim=-1)
+    assert same.float().mean().item() > 0.98
+    close(tw[same], rw[same], atol=1e-3)
+    expect = ref.moe_experts(x, w13, w2, tw, ids)
+
+    n_pairs = T * topk
+    max_rows = n_pairs + E * 127
+    max_tiles = (max_rows + 127) // 128
+    i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=DEV)
+    offs, cursor, tile_expert, meta = i32(E + 1), i32(E), i32(max_tiles), i32(2)
+    ops.moe_align(ids, E, 128, offs, cursor, tile_expert, meta)
+    a_sorted = torch.zeros(max_tiles * 128, H, device=DEV, dtype=BF)
+    row_scale = torch.zeros(max_tiles * 128, device=DEV)
+    sorted_pos = i32(T, topk)
+    ops.moe_scatter(x, ids, tw, offs, cursor, a_sorted, row_scale, sorted_pos, E)
+    counts = torch.bincount(ids.flatten().long(), minlength=E)
+    padded = ((counts + 127) // 128 * 128)
+    assert meta[1].item() == padded.sum().item() and meta[0].item() == padded.sum().item() // 128
+    act = ops.gemm(a_sorted, w13.view(E * 2 * I, H), swiglu=True, tile_expert=tile_expert, num_m_tiles=meta[:1],
+                   n_per_expert=2 * I)
+    y = ops.gemm(act, w2.view(E * H, I), row_scale=row_scale, tile_expert=tile_expert, num_m_tiles=meta[:1],
+                 n_per_expert=H)
+    out = torch.empty(T, H, device=DEV, dtype=BF)
+    ops.moe_combine(y, sorted_pos, out, topk)
+    close(out, expect, atol=3e-2, rtol=3e-2)

@@ -1,0 +1,425 @@
+// Causal variable-length attention over a paged KV cache for sm_100a (prefill and chunked
+// prefill). Replaces the FlashAttention-2 varlen call the reference falls back to on Blackwell
+// (vllm/v1/attention/backends/flash_attn.py:713-733, vllm/attention/utils/fa_utils.py:29-34).
+//
+// One CTA per (128-query tile, query head), 192 threads:
+//   warp 0      TMA producer: the Q tile once, then K and V tiles of 128 keys, one
+//               cp.async.bulk.tensor.4d per cache page and 64-column half, straight from the
+//               paged cache [blocks, page, kv_heads, D] through the request's block table
+//   warp 1      MMA issuer (tcgen05, accumulators in TMEM):
+//                 S[j&1] = Q K_j^T     (M=128, N=128, K=D, both operands K-major)
+//                 O     += P_j V_j      (M=128, N=D,   K=128, V is an MN-major operand)
+//               S is double-buffered, so Q K_{j+1}^T runs while the softmax of tile j does.
+//   warps 2..5  softmax: thread r owns query row r. Pass 1 reads S from TMEM for the row
+//               maximum, pass 2 re-reads it, exponentiates (exp2, scale folded in), writes bf16
+//               P into shared memory in the swizzled K-major operand layout. O stays in TMEM
+//               across tiles and is rescaled only when the running maximum grows by more than
+//               2^8 (the stale maximum is a valid softmax reference; P stays below 256).
+// Every wait is bounded; a timeout reports TW_ERR_MBAR_TIMEOUT and leaves by the tear-down.
+#include "tw_common.cuh"
+#include "tw_host.h"
+#include "tw_kernels.h"
+
+namespace tw {
+
+constexpr int ATT_BM = 128;      // query rows per CTA
+constexpr int ATT_BN = 128;      // keys per tile
+constexpr int ATT_THREADS = 192;
+constexpr int ATT_HALF_BYTES = 128 * 128;  // a [128 rows x 64 bf16] swizzled half tile
+
+struct AttnParams {
+  __nv_bfloat16* out;
+  long long ldo;
+  const int* cu_q;         // [B+1] first query row of each sequence
+  const int* kv_lens;      // [B] keys visible to the last query of the sequence
+  const int* block_table;  // [B, max_blocks]
+  const int* tile_seq;     // [num_tiles] sequence of each query tile
+  const int* tile_q0;      // [num_tiles] first query (within the sequence) of the tile
+  int max_blocks;
+  int page;                // tokens per cache page
+  int hq, hkv;
+  float scale_log2;        // softmax scale * log2(e)
+  uint32_t* status;
+};
+
+template <int D>
+struct AttnSmem {
+  static constexpr int HALVES = D / 64;
+  static constexpr int Q_BYTES = HALVES * ATT_HALF_BYTES;
+  static constexpr int KV_BYTES = HALVES * ATT_HALF_BYTES;  // one K or V tile
+  static constexpr int P_BYTES = 2 * ATT_HALF_BYTES;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
+  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  using S = AttnSmem<D>;
+  constexpr int HALVES = S::HALVES;
+  constexpr uint32_t IDESC_QK = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);
+  constexpr uint32_t IDESC_PV = make_idesc_bf16(ATT_BM, D, 0, 1);
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t COL_S = 0;    // two S buffers: [0,128) and [128,256)
+  constexpr uint32_t COL_O = 256;  // O accumulator: D columns
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;   // [2]
+  uint64_t* k_empty = bars + 3;  // [2]
+  uint64_t* v_full = bars + 5;   // [2]
+  uint64_t* v_empty = bars + 7;  // [2]
+  uint64_t* s_full = bars + 9;   // [2]
+  uint64_t* p_ready = bars + 11;
+  uint64_t* o_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.x;
+  const int tile = blockIdx.y;
+  const int kvh = head / (p.hq / p.hkv);
+
+  const int seq = p.tile_seq[tile];
+  const int q0 = p.tile_q0[tile];
+  const int q_begin = p.cu_q[seq];
+  const int q_len = p.cu_q[seq + 1] - q_begin;
+  const int kv_len = p.kv_lens[seq];
+  const int rows_valid = min(ATT_BM, q_len - q0);
+  // absolute position of query i of the sequence: kv_len - q_len + i
+  const int pos0 = kv_len - q_len + q0;
+  const int kv_end = min(kv_len, pos0 + rows_valid);  // keys [0, kv_end) are needed
+  const int n_tiles = (kv_end + ATT_BN - 1) / ATT_BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+    }
+    mbar_init(p_ready, 128);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0 && n_tiles > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, S::Q_BYTES);
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h)
+        tma_load_2d(smem + S::OFF_Q + h * ATT_HALF_BYTES, &tmQ, q_full, head * D + h * 64, q_begin + q0);
+      const int pages_per_tile = ATT_BN / p.page;
+      const int last_page = (kv_len - 1) / p.page;
+      const int* table = p.block_table + static_cast<long long>(seq) * p.max_blocks;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        // K tile
+        if (!mbar_wait(&k_empty[st], ph ^ 1)) { report_error(p.status, TW_ERR_MBAR_TIMEOUT); *abort_flag = 1; break; }
+        mbar_expect_tx(&k_full[st], S::KV_BYTES);
+        for (int pg = 0; pg < pages_per_tile; ++pg) {
+          const int block = table[min(j * pages_per_tile + pg, last_page)];
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h)
+            tma_load_4d(smem + S::OFF_K + st * S::KV_BYTES + h * ATT_HALF_BYTES + pg * p.page * 128, &tmK,
+                        &k_full[st], h * 64, kvh, 0, block);
+        }
+        // V tile
+        if (!mbar_wait(&v_empty[st], ph ^ 1)) { report_error(p.status, TW_ERR_MBAR_TIMEOUT); *abort_flag = 1; break; }
+        mbar_expect_tx(&v_full[st], S::KV_BYTES);
+        for (int pg = 0; pg < pages_per_tile; ++pg) {
+          const int block = table[min(j * pages_per_tile + pg, last_page)];
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h)
+            tma_load_4d(smem + S::OFF_V + st * S::KV_BYTES + h * ATT_HALF_BYTES + pg * p.page * 128, &tmV,
+                        &v_full[st], h * 64, kvh, 0, block);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t q_addr = smem_u32(smem + S::OFF_Q);
+      const uint32_t p_addr = smem_u32(smem + S::OFF_P);
+      bool ok = mbar_wait(q_full, 0);
+      auto issue_qk = [&](int j) {
+        const int st = j & 1;
+        if (!mbar_wait(&k_full[st], (j >> 1) & 1)) return false;
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(smem + S::OFF_K + st * S::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * ATT_HALF_BYTES + (k & 3) * 32;
+          umma_ss(tmem_base + COL_S + st * ATT_BN, make_smem_desc_sw128(q_addr + off, 16, 1024),
+                  make_smem_desc_sw128(k_addr + off, 16, 1024), IDESC_QK, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&k_empty[st]);
+        umma_commit(&s_full[st]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) {
+          ok = issue_qk(j + 1);
+          if (!ok) break;
+        }
+        const int st = j & 1;
+        if (!mbar_wait(p_ready, j & 1)) { ok = false; break; }
+        if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(smem + S::OFF_V + st * S::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < ATT_BN / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * ATT_HALF_BYTES + (k & 3) * 32;
+          umma_ss(tmem_base + COL_O, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
+                  make_smem_desc_sw128(v_addr + k * 16 * 128, ATT_HALF_BYTES, 1024), IDESC_PV,
+                  (j | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&v_empty[st]);
+        umma_commit(o_done);
+      }
+      if (!ok) {
+        report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+        *abort_flag = 1;
+      }
+    }
+  } else if (n_tiles > 0) {
+    // ---------------- softmax + epilogue (warps 2..5) ----------------
+    const int qr = warp & 3;
+    const int r = qr * 32 + lane;                   // row within the tile
+    const int pos = pos0 + min(r, rows_valid - 1);  // padding rows copy the last valid row's mask
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(qr * 32) << 16);
+    uint8_t* p_row = smem + S::OFF_P + r * 128;
+    float m_ref = -INFINITY;  // softmax reference (a stale running maximum), log2 domain
+    float l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int sb = j & 1;
+      if (!mbar_wait(&s_full[sb], (j >> 1) & 1)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t t_s = t_lane + COL_S + sb * ATT_BN;
+      const int k_base = j * ATT_BN;
+      // warp-uniform: lane 0 holds the smallest position of the warp
+      const bool need_mask = (k_base + ATT_BN - 1) > __shfl_sync(0xffffffffu, pos, 0);
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < ATT_BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + c * 32, v);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (k_base + c * 32 + i <= pos) mx = fmaxf(mx, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+      }
+      mx *= p.scale_log2;
+      float alpha = 1.f;
+      bool rescale = false;
+      if (j == 0) {
+        m_ref = mx;
+      } else if (mx > m_ref + 8.f) {
+        alpha = exp2f(m_ref - mx);
+        m_ref = mx;
+        rescale = true;
+      }
+      if (j > 0) {
+        // P buffer and O are free once P_{j-1} V_{j-1} has completed.
+        if (!mbar_wait(o_done, (j - 1) & 1)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, rescale)) {
+          l_sum *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(t_lane + COL_O + c * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(t_lane + COL_O + c * 32, v);
+          }
+          tmem_wait_st();
+        }
+      }
+      // pass 2: probabilities -> shared memory (bf16, swizzled K-major operand layout)
+#pragma unroll 1
+      for (int c = 0; c < ATT_BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + c * 32, v);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float a = exp2f(__uint_as_float(v[2 * i]) * p.scale_log2 - m_ref);
+          float b = exp2f(__uint_as_float(v[2 * i + 1]) * p.scale_log2 - m_ref);
+          if (need_mask) {
+            if (k_base + c * 32 + 2 * i > pos) a = 0.f;
+            if (k_base + c * 32 + 2 * i + 1 > pos) b = 0.f;
+          }
+          l_sum += a + b;
+          pk[i] = pack_bf16x2(a, b);
+        }
+        // columns c*32 .. c*32+31 of the row: key half (c >> 1), 16-byte chunks (c & 1)*4 .. +3
+        uint8_t* dst = p_row + (c >> 1) * ATT_HALF_BYTES;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
+          *reinterpret_cast<uint4*>(dst + chunk * 16) =
+              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        }
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      mbar_arrive(p_ready);
+    }
+    if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1);
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv = 1.f / l_sum;
+      __nv_bfloat16* orow = p.out + static_cast<long long>(q_begin + q0 + r) * p.ldo + head * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_lane + COL_O + c * 32, v);
+        tmem_wait_ld();
+        if (r < rows_valid) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[8 * q4 + 0]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = o;
+          }
+        }
+      }
+    } else {
+      report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+      *abort_flag = 1;
+    }
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int D>
+static int launch_prefill(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                          const AttnParams& p, int num_tiles, cudaStream_t stream) {
+  using S = AttnSmem<D>;
+  auto kern = attn_prefill_kernel<D>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) {
+      set_last_error("attn_prefill: cudaFuncSetAttribute(smem=%d) failed: %s", S::TOTAL,
+                     cudaGetErrorString(e));
+      return 1;
+    }
+    configured_dev = dev;
+  }
+  dim3 grid(p.hq, num_tiles);
+  kern<<<grid, ATT_THREADS, S::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error("attn_prefill launch failed: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
+
+}  // namespace tw
+
+using namespace tw;
+
+// q: [T, hq*D] rows with stride ldq (may alias a packed qkv buffer). Caches:
+// [num_blocks, page, hkv, D]. tile_seq/tile_q0 list the 128-query tiles (device arrays).
+extern "C" int tw_attn_prefill(const void* q, long long ldq, int T, const void* k_cache, const void* v_cache,
+                               int num_blocks, int page, void* out, long long ldo, const int* cu_q,
+                               const int* kv_lens, const int* block_table, int max_blocks,
+                               const int* tile_seq, const int* tile_q0, int num_tiles, int hq, int hkv,
+                               int D, float scale, uint32_t* status, cudaStream_t stream) {
+  if (num_tiles <= 0 || T <= 0) return 0;
+  if (D != 128 && D != 64) {
+    set_last_error("attn_prefill: head_dim must be 64 or 128 (got %d)", D);
+    return 1;
+  }
+  if (page < 8 || page > 128 || (128 % page) != 0) {
+    set_last_error("attn_prefill: page size must divide 128 and be >= 8 (got %d)", page);
+    return 1;
+  }
+  if (hq % hkv != 0 || ldq % 8 != 0 || ldo % 8 != 0) {
+    set_last_error("attn_prefill: bad head counts or strides");
+    return 1;
+  }
+  CUtensorMap tmQ, tmK, tmV;
+  {
+    uint64_t dims[2] = {(uint64_t)hq * D, (uint64_t)T};
+    uint64_t strides[1] = {(uint64_t)ldq * 2};
+    uint32_t box[2] = {64, ATT_BM};
+    if (!make_tensor_map_bf16(&tmQ, q, 2, dims, strides, box)) return 1;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)hkv, (uint64_t)page, (uint64_t)num_blocks};
+    uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)hkv * D * 2, (uint64_t)page * hkv * D * 2};
+    uint32_t box[4] = {64, 1, (uint32_t)page, 1};
+    if (!make_tensor_map_bf16(&tmK, k_cache, 4, dims, strides, box)) return 1;
+    if (!make_tensor_map_bf16(&tmV, v_cache, 4, dims, strides, box)) return 1;
+  }
+  AttnParams p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.cu_q = cu_q;
+  p.kv_lens = kv_lens;
+  p.block_table = block_table;
+  p.tile_seq = tile_seq;
+  p.tile_q0 = tile_q0;
+  p.max_blocks = max_blocks;
+  p.page = page;
+  p.hq = hq;
+  p.hkv = hkv;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  return D == 128 ? launch_prefill<128>(tmQ, tmK, tmV, p, num_tiles, stream)
+                  : launch_prefill<64>(tmQ, tmK, tmV, p, num_tiles, stream);
+}

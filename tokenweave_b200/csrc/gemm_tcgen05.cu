@@ -1,0 +1,373 @@
+// bf16 GEMM for sm_100a: C[M,N] = A[M,K] * B[N,K]^T  (nn.Linear layout, fp32 accumulate).
+//
+// Replaces the cuBLAS calls of the reference's linear layers
+// (vllm/model_executor/layers/linear.py:196-230) and, in grouped mode, its Triton fused-MoE
+// GEMM (vllm/model_executor/layers/fused_moe/fused_moe.py:255-463).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: A tile 128x64 and B tile BNx64 per pipeline stage
+//               (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//   warp 1      MMA issuer: tcgen05.mma kind::f16, M=128, N=BN, K=16, operands from shared
+//               memory descriptors, accumulators in TMEM (two buffers, so the epilogue of
+//               tile i overlaps the main loop of tile i+1)
+//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns -> registers -> bf16 -> global
+// Epilogues: plain, +bias[n], *row_scale[m], and SwiGLU (the B tile holds 128 "gate" rows and
+// 128 "up" rows; the stored value is silu(gate)*up, N/2 output columns per tile).
+// Grouped mode: each 128-row tile of A belongs to one expert (tile_expert[m_tile]); the B rows
+// are offset by expert * n_per_expert; the number of valid tiles is read from device memory.
+//
+// Every mbarrier wait is bounded; on a timeout the CTA reports TW_ERR_MBAR_TIMEOUT, waits for
+// its copies in flight, frees its TMEM and returns.
+#include "tw_common.cuh"
+#include "tw_host.h"
+#include "tw_kernels.h"
+
+namespace tw {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_GROUP_M = 16;
+
+struct GemmParams {
+  __nv_bfloat16* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  const float* row_scale;
+  int M, N, K;
+  int num_m_tiles, num_n_tiles;
+  const int* tile_expert;
+  const int* num_m_tiles_dev;
+  int n_per_expert;
+  int up_row_offset;
+  uint32_t* status;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_tile, int& n_tile) {
+  const int group_span = GEMM_GROUP_M * num_n;
+  const int group = t / group_span;
+  const int first_m = group * GEMM_GROUP_M;
+  const int rows = min(num_m - first_m, GEMM_GROUP_M);
+  const int in_group = t - group * group_span;
+  m_tile = first_m + in_group % rows;
+  n_tile = in_group / rows;
+}
+
+template <int BN, bool SWIGLU>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int STAGES = S::STAGES;
+  constexpr int OUT_COLS = SWIGLU ? BN / 2 : BN;
+  constexpr uint32_t IDESC = make_idesc_bf16(GEMM_BM, BN, 0, 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  int num_m = p.num_m_tiles;
+  if (p.num_m_tiles_dev != nullptr) num_m = min(num_m, *p.num_m_tiles_dev);
+  const int num_n = p.num_n_tiles;
+  const int total_tiles = num_m * num_n;
+  const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+        int m_tile, n_tile;
+        tile_coords(t, num_m, num_n, m_tile, n_tile);
+        const int m0 = m_tile * GEMM_BM;
+        int b_row0 = n_tile * OUT_COLS;
+        if (p.tile_expert != nullptr) b_row0 += p.tile_expert[m_tile] * p.n_per_expert;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+            *abort_flag = 1;
+            break;
+          }
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+          tma_load_2d(sa, &tmA, &full_bar[stage], kb * GEMM_BK, m0);
+          if (SWIGLU) {
+            tma_load_2d(sb, &tmB, &full_bar[stage], kb * GEMM_BK, b_row0);
+            tma_load_2d(sb + (BN / 2) * GEMM_BK * 2, &tmB, &full_bar[stage], kb * GEMM_BK,
+                        b_row0 + p.up_row_offset);
+          } else {
+#pragma unroll
+            for (int h = 0; h < BN / 128; ++h)
+              tma_load_2d(sb + h * 128 * GEMM_BK * 2, &tmB, &full_bar[stage], kb * GEMM_BK,
+                          b_row0 + h * 128);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+          report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sb = sa + S::A_BYTES;
+          const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t b_desc = make_smem_desc_sw128(sb, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            // 16 bf16 = 32 bytes further along K: +2 in the descriptor's 16-byte address units
+            umma_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) {
+          report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+          *abort_flag = 1;
+          break;
+        }
+        umma_commit(&acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+      int m_tile, n_tile;
+      tile_coords(t, num_m, num_n, m_tile, n_tile);
+      if (!mbar_wait(&acc_full[acc], acc_phase)) {
+        report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = m_tile * GEMM_BM + q * 32 + lane;
+      const int n0 = n_tile * OUT_COLS;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const float rs = (p.row_scale != nullptr && row < p.M) ? p.row_scale[row] : 1.f;
+      __nv_bfloat16* crow = p.C + static_cast<long long>(row) * p.ldc + n0;
+#pragma unroll 1
+      for (int c = 0; c < OUT_COLS / 32; ++c) {
+        uint32_t v[32];
+        uint32_t packed[16];
+        tmem_ld_32x32(taddr + c * 32, v);
+        if (SWIGLU) {
+          uint32_t u[32];
+          tmem_ld_32x32(taddr + BN / 2 + c * 32, u);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float g0 = __uint_as_float(v[2 * j]), g1 = __uint_as_float(v[2 * j + 1]);
+            float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            float s0 = g0 / (1.f + __expf(-g0)) * u0;
+            float s1 = g1 / (1.f + __expf(-g1)) * u1;
+            packed[j] = pack_bf16x2(s0 * rs, s1 * rs);
+          }
+        } else {
+          tmem_wait_ld();
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int n = n0 + c * 32 + j;
+              const float b = (n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+              v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            packed[j] = pack_bf16x2(__uint_as_float(v[2 * j]) * rs, __uint_as_float(v[2 * j + 1]) * rs);
+        }
+        if (row < p.M) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = n0 + c * 32 + j * 8;
+            if (n + 8 <= p.N) {
+              *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) =
+                  make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+            } else if (n < p.N) {
+              uint16_t* c16 = reinterpret_cast<uint16_t*>(crow + c * 32 + j * 8);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const uint32_t w = packed[4 * j + (e >> 1)];
+                if (n + e < p.N) c16[e] = (e & 1) ? static_cast<uint16_t>(w >> 16) : static_cast<uint16_t>(w & 0xffffu);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  // ---------------- tear-down ----------------
+  if (*abort_flag) {
+    // Give copies that may still be in flight time to land before shared memory is released.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+template <int BN, bool SWIGLU>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
+                       cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  auto kern = gemm_bf16_kernel<BN, SWIGLU>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) {
+      set_last_error("cudaFuncSetAttribute(smem=%d) failed: %s", S::TOTAL, cudaGetErrorString(e));
+      return 1;
+    }
+    configured_dev = dev;
+  }
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error("gemm launch failed: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
+
+}  // namespace tw
+
+using namespace tw;
+
+// C launcher. `mode` bit 0: SwiGLU epilogue. A is [M,K] with row stride lda, B is
+// [rows_b, K] with row stride ldb (rows_b = N, 2*N for SwiGLU, or experts * n_per_expert).
+extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
+                            void* C, long long ldc, const void* bias, const float* row_scale, int M,
+                            int N, int K, int swiglu, int up_row_offset, const int* tile_expert,
+                            const int* num_m_tiles_dev, int n_per_expert, int max_ctas,
+                            uint32_t* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldc % 8) != 0) {
+    set_last_error("tw_gemm_bf16: K, lda, ldb, ldc must be multiples of 8 (got %d, %lld, %lld, %lld)", K,
+                   lda, ldb, ldc);
+    return 1;
+  }
+  // Tile width: 256 accumulator columns unless that leaves most SMs idle.
+  int sms = device_sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
+  const int out_cols_256 = swiglu ? 128 : 256;
+  const int tiles_256 = num_m * ((N + out_cols_256 - 1) / out_cols_256);
+  const bool use_256 = tiles_256 >= sms;
+  const int BN = use_256 ? 256 : 128;
+  const int out_cols = swiglu ? BN / 2 : BN;
+  const int num_n = (N + out_cols - 1) / out_cols;
+
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t strides[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {GEMM_BK, GEMM_BM};
+    if (!make_tensor_map_bf16(&tmA, A, 2, dims, strides, box)) return 1;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows_b};
+    uint64_t strides[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {GEMM_BK, (uint32_t)(swiglu ? BN / 2 : 128)};
+    if (!make_tensor_map_bf16(&tmB, B, 2, dims, strides, box)) return 1;
+  }
+  GemmParams p;
+  p.C = reinterpret_cast<__nv_bfloat16*>(C);
+  p.ldc = ldc;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.row_scale = row_scale;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.num_m_tiles = num_m;
+  p.num_n_tiles = num_n;
+  p.tile_expert = tile_expert;
+  p.num_m_tiles_dev = num_m_tiles_dev;
+  p.n_per_expert = n_per_expert;
+  p.up_row_offset = up_row_offset;
+  p.status = status;
+  int grid = num_m * num_n;
+  if (grid > sms) grid = sms;
+  if (use_256) {
+    return swiglu ? launch_gemm<256, true>(tmA, tmB, p, grid, stream)
+                  : launch_gemm<256, false>(tmA, tmB, p, grid, stream);
+  }
+  return swiglu ? launch_gemm<128, true>(tmA, tmB, p, grid, stream)
+                : launch_gemm<128, false>(tmA, tmB, p, grid, stream);
+}

@@ -1,0 +1,295 @@
+"""Operator layer: one Python function per hot op.
+
+CUDA tensors go to the hand-written sm_100a kernels in ``_C.so`` (through :mod:`._native`; a missing
+library raises). CPU tensors go to the PyTorch references in :mod:`.reference`, which are also the
+oracle the kernels are tested against.
+
+Reference counterpart of this layer: vllm/_custom_ops.py:184-221 and csrc/torch_bindings.cpp:146-196.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _native, reference
+
+__all__ = [
+    "gemm", "rmsnorm", "rmsnorm_copy_", "add_rmsnorm_", "rope_kv_write_", "swiglu", "embedding", "argmax",
+    "attn_prefill", "attn_decode", "moe_router", "moe_align", "moe_scatter", "moe_combine", "status_word",
+    "check_status", "reset_status", "STATUS_CODES", "KernelStatusError",
+]
+
+STATUS_CODES = {1: "mbarrier wait timed out", 2: "peer signal wait timed out", 4: "bad argument",
+                8: "tile-ready flag wait timed out"}
+
+
+class KernelStatusError(RuntimeError):
+    """A kernel gave up on a bounded wait (or failed a device-side check) and said so."""
+
+    def __init__(self, code: int):
+        self.code = code
+        what = ", ".join(v for k, v in STATUS_CODES.items() if code & k) or "unknown"
+        super().__init__(f"device status word = {code:#x}: {what}")
+
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """The int32 word kernels OR their error codes into (one per device, zero when healthy)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    """Synchronising read of the status word; raises :class:`KernelStatusError` if it is non-zero."""
+    code = int(status_word(device).item())
+    if code != 0:
+        raise KernelStatusError(code)
+
+
+def reset_status(device=None) -> None:
+    status_word(device).zero_()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _check_bf16(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and t.dtype != torch.bfloat16:
+            raise TypeError(f"the sm_100a kernels take bfloat16 tensors, got {t.dtype}")
+
+
+def _row_stride(t: torch.Tensor) -> int:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError("expected a 2-D tensor with contiguous rows")
+    return t.stride(0)
+
+
+# ---------------------------------------------------------------------------------------------
+def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *,
+         bias: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None, swiglu: bool = False,
+         max_ctas: int = 0, tile_expert: Optional[torch.Tensor] = None,
+         num_m_tiles: Optional[torch.Tensor] = None, n_per_expert: int = 0) -> torch.Tensor:
+    """``out = a @ w.T`` (+bias, *row_scale); with ``swiglu`` the weight is ``[gate; up]`` and the
+    output is ``silu(a@gate.T) * (a@up.T)``. Grouped mode (``tile_expert`` given): every 128-row tile
+    of ``a`` multiplies the weight block of its expert, ``w`` being ``[E * n_per_expert, K]``."""
+    M, K = a.shape
+    rows_b = w.shape[0]
+    per_expert = n_per_expert if tile_expert is not None else rows_b
+    N = per_expert // 2 if swiglu else per_expert
+    if out is None:
+        out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+    if not a.is_cuda:
+        if tile_expert is not None:
+            raise NotImplementedError("grouped GEMM on CPU goes through reference.moe_experts")
+        res = reference.gemm_swiglu(a, w, row_scale) if swiglu else reference.gemm(a, w, bias, row_scale)
+        out.copy_(res)
+        return out
+    _check_bf16(a, w, out, bias)
+    _native.call("tw_gemm_bf16", a.data_ptr(), _row_stride(a), w.data_ptr(), _row_stride(w), rows_b,
+                 out.data_ptr(), _row_stride(out), _p(bias), _p(row_scale), M, N, K, int(swiglu),
+                 per_expert // 2 if swiglu else 0, _p(tile_expert), _p(num_m_tiles), per_expert, max_ctas,
+                 status_word(a.device).data_ptr(), _stream())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None,
+            max_ctas: int = 0) -> torch.Tensor:
+    if out is None:
+        out = torch.empty_like(x)
+    if not x.is_cuda:
+        out.copy_(reference.rmsnorm(x, weight, eps))
+        return out
+    _check_bf16(x, weight, out)
+    T, H = x.shape
+    _native.call("tw_rmsnorm", x.data_ptr(), out.data_ptr(), weight.data_ptr(), T, H, _row_stride(x),
+                 _row_stride(out), eps, max_ctas, _stream())
+    return out
+
+
+def rmsnorm_copy_(x: torch.Tensor, residual_out: torch.Tensor, weight: torch.Tensor, eps: float,
+                  max_ctas: int = 0) -> None:
+    """``residual_out = x; x = rmsnorm(x) * w`` (first-layer helper)."""
+    if not x.is_cuda:
+        reference.rmsnorm_copy_(x, residual_out, weight, eps)
+        return
+    _check_bf16(x, weight, residual_out)
+    T, H = x.shape
+    _native.call("tw_rmsnorm_copy", x.data_ptr(), residual_out.data_ptr(), weight.data_ptr(), T, H,
+                 _row_stride(x), _row_stride(residual_out), eps, max_ctas, _stream())
+
+
+def add_rmsnorm_(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                 max_ctas: int = 0) -> None:
+    """``x += residual; residual = x; x = rmsnorm(x) * w`` in place."""
+    if not x.is_cuda:
+        reference.add_rmsnorm_(x, residual, weight, eps)
+        return
+    _check_bf16(x, weight, residual)
+    T, H = x.shape
+    _native.call("tw_add_rmsnorm", x.data_ptr(), residual.data_ptr(), weight.data_ptr(), T, H, _row_stride(x),
+                 _row_stride(residual), eps, max_ctas, _stream())
+
+
+def rope_kv_write_(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor],
+                   cos_sin: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                   hq: int, hkv: int, head_dim: int, write_k_back: bool = False) -> None:
+    """Rotate q (and k) of the first ``len(positions)`` rows of ``qkv`` and write k, v to the cache."""
+    T = positions.shape[0]
+    if T == 0:
+        return
+    if not qkv.is_cuda:
+        reference.rope_kv_write_(qkv[:T], positions, slots, cos_sin, k_cache, v_cache, hq, hkv, head_dim,
+                                 write_k_back=True)
+        return
+    _check_bf16(qkv, k_cache, v_cache)
+    assert positions.dtype == torch.int32 and (slots is None or slots.dtype == torch.int32)
+    assert cos_sin.dtype == torch.float32 and cos_sin.shape[1] == head_dim
+    _native.call("tw_rope_kv_write", qkv.data_ptr(), _row_stride(qkv), positions.data_ptr(), _p(slots),
+                 cos_sin.data_ptr(), _p(k_cache), _p(v_cache), T, hq, hkv, head_dim, int(write_k_back),
+                 _stream())
+
+
+def swiglu(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T, d2 = x.shape
+    d = d2 // 2
+    if out is None:
+        out = torch.empty(T, d, dtype=x.dtype, device=x.device)
+    if not x.is_cuda:
+        out.copy_(reference.swiglu(x))
+        return out
+    _check_bf16(x, out)
+    _native.call("tw_swiglu", x.data_ptr(), _row_stride(x), out.data_ptr(), _row_stride(out), T, d, _stream())
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, vocab_start: int = 0,
+              vocab_end: Optional[int] = None) -> torch.Tensor:
+    T = ids.shape[0]
+    H = table.shape[1]
+    vocab_end = vocab_start + table.shape[0] if vocab_end is None else vocab_end
+    if out is None:
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    if not table.is_cuda:
+        out.copy_(reference.embedding(ids, table, vocab_start, vocab_end))
+        return out
+    _check_bf16(table, out)
+    assert ids.dtype == torch.int32
+    _native.call("tw_embedding", ids.data_ptr(), table.data_ptr(), out.data_ptr(), _row_stride(out), T, H,
+                 vocab_start, vocab_end, _stream())
+    return out
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Row-wise argmax of fp32 logits -> int32 ids."""
+    if not logits.is_cuda:
+        return torch.argmax(logits, dim=-1).to(torch.int32)
+    assert logits.dtype == torch.float32
+    rows, V = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _native.call("tw_argmax", logits.data_ptr(), _row_stride(logits), out.data_ptr(), rows, V, _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                 cu_q: torch.Tensor, kv_lens: torch.Tensor, block_table: torch.Tensor, tile_seq: torch.Tensor,
+                 tile_q0: torch.Tensor, num_tiles: int, hq: int, hkv: int, head_dim: int, scale: float) -> None:
+    """Tensor-core causal attention for the 128-query tiles listed in (tile_seq, tile_q0)."""
+    if num_tiles == 0:
+        return
+    _check_bf16(q, k_cache, v_cache, out)
+    num_blocks, page = k_cache.shape[0], k_cache.shape[1]
+    _native.call("tw_attn_prefill", q.data_ptr(), _row_stride(q), q.shape[0], k_cache.data_ptr(),
+                 v_cache.data_ptr(), num_blocks, page, out.data_ptr(), _row_stride(out), cu_q.data_ptr(),
+                 kv_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], tile_seq.data_ptr(),
+                 tile_q0.data_ptr(), num_tiles, hq, hkv, head_dim, scale, status_word(q.device).data_ptr(),
+                 _stream())
+
+
+_decode_ws: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                tok_row: torch.Tensor, tok_seq: torch.Tensor, tok_kvlen: torch.Tensor, n_tok: int,
+                block_table: torch.Tensor, hq: int, hkv: int, head_dim: int, scale: float, max_kv_len: int,
+                sm_count: int = 148) -> None:
+    """Single-query attention for the listed tokens; splits the keys when the grid would be small."""
+    if n_tok == 0:
+        return
+    _check_bf16(q, k_cache, v_cache, out)
+    page = k_cache.shape[1]
+    ctas = n_tok * hkv
+    splits = 1
+    if ctas < 2 * sm_count and max_kv_len > 512:
+        splits = min(32, max(1, (2 * sm_count) // ctas), (max_kv_len + 255) // 256)
+    part_o = part_ml = None
+    if splits > 1:
+        key = (q.device.index, n_tok * hq * splits * head_dim)
+        ws = _decode_ws.get(key)
+        if ws is None:
+            ws = (torch.empty(n_tok * hq * splits * head_dim, dtype=torch.float32, device=q.device),
+                  torch.empty(n_tok * hq * splits * 2, dtype=torch.float32, device=q.device))
+            if len(_decode_ws) > 64:
+                _decode_ws.clear()
+            _decode_ws[key] = ws
+        part_o, part_ml = ws
+    _native.call("tw_attn_decode", q.data_ptr(), _row_stride(q), k_cache.data_ptr(), v_cache.data_ptr(), page,
+                 out.data_ptr(), _row_stride(out), tok_row.data_ptr(), tok_seq.data_ptr(), tok_kvlen.data_ptr(),
+                 n_tok, block_table.data_ptr(), block_table.shape[1], hq, hkv, head_dim, scale, splits,
+                 _p(part_o), _p(part_ml), _stream())
+
+
+# ---------------------------------------------------------------------------------------------
+def moe_router(x: torch.Tensor, gate_w: torch.Tensor, topk: int, renormalize: bool = True,
+               want_logits: bool = False):
+    """Gate GEMV + softmax + top-k (+ renormalise). Returns (weights fp32 [T,k], ids int32 [T,k], logits|None)."""
+    if not x.is_cuda:
+        w, ids, logits = reference.moe_router(x, gate_w, topk, renormalize)
+        return w, ids, (logits if want_logits else None)
+    _check_bf16(x, gate_w)
+    T, H = x.shape
+    E = gate_w.shape[0]
+    w = torch.empty(T, topk, dtype=torch.float32, device=x.device)
+    ids = torch.empty(T, topk, dtype=torch.int32, device=x.device)
+    logits = torch.empty(T, E, dtype=torch.float32, device=x.device) if want_logits else None
+    _native.call("tw_moe_router", x.data_ptr(), _row_stride(x), gate_w.data_ptr(), w.data_ptr(), ids.data_ptr(),
+                 _p(logits), T, H, E, topk, int(renormalize), _stream())
+    return w, ids, logits
+
+
+def moe_align(topk_ids: torch.Tensor, num_experts: int, tile_rows: int, expert_offsets: torch.Tensor,
+              expert_cursor: torch.Tensor, tile_expert: torch.Tensor, meta: torch.Tensor) -> None:
+    """Counting sort bookkeeping: padded expert offsets, expert per row tile, meta = [tiles, padded rows]."""
+    _native.call("tw_moe_align", topk_ids.data_ptr(), topk_ids.numel(), num_experts, tile_rows,
+                 expert_offsets.data_ptr(), expert_cursor.data_ptr(), tile_expert.data_ptr(),
+                 tile_expert.numel(), meta.data_ptr(), _stream())
+
+
+def moe_scatter(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, expert_offsets: torch.Tensor,
+                expert_cursor: torch.Tensor, a_sorted: torch.Tensor, row_scale: torch.Tensor,
+                sorted_pos: torch.Tensor, num_experts: int) -> None:
+    T, H = x.shape
+    topk = topk_ids.shape[1]
+    _native.call("tw_moe_scatter", x.data_ptr(), _row_stride(x), topk_ids.data_ptr(), topk_w.data_ptr(),
+                 expert_offsets.data_ptr(), expert_cursor.data_ptr(), a_sorted.data_ptr(), row_scale.data_ptr(),
+                 sorted_pos.data_ptr(), T * topk, topk, H, num_experts, _stream())
+
+
+def moe_combine(y_sorted: torch.Tensor, sorted_pos: torch.Tensor, out: torch.Tensor, topk: int) -> None:
+    T, H = out.shape
+    _native.call("tw_moe_combine", y_sorted.data_ptr(), sorted_pos.data_ptr(), out.data_ptr(), _row_stride(out),
+                 T, topk, H, _stream())

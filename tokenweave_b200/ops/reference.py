@@ -1,0 +1,217 @@
+"""Plain PyTorch reference implementations of every op in :mod:`tokenweave_b200.ops`.
+
+These are the oracle for the CUDA kernels (computed in fp32, rounded where the kernels round) and
+the execution path on CPU, where the engine runs for tests and for the fp32 correctness
+configuration. They follow the numerics order of the reference kernels
+(csrc/layernorm_kernels.cu:87-113, csrc/tokenweave_fused_kernels.cu:127-151): the residual add is
+done in the storage dtype, the sum of squares in fp32 over the rounded sums, the normalised value
+is rounded to the storage dtype before the weight multiply.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+
+# ---------------------------------------------------------------------------------------------
+# norms
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    inv = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return (xf * inv).to(x.dtype) * weight.to(x.dtype)
+
+
+def add_rmsnorm_(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """In place: ``x += residual; residual = x; x = rmsnorm(x) * w``."""
+    s = x + residual
+    residual.copy_(s)
+    x.copy_(rmsnorm(s, weight, eps))
+
+
+def rmsnorm_copy_(x: torch.Tensor, residual_out: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """In place: ``residual_out = x; x = rmsnorm(x) * w``."""
+    residual_out.copy_(x)
+    x.copy_(rmsnorm(x, weight, eps))
+
+
+# ---------------------------------------------------------------------------------------------
+# linear algebra
+def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+         row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a @ w.T`` with fp32 accumulation, optional bias (per column) and row scale."""
+    out = a.float() @ w.float().t()
+    if bias is not None:
+        out = out + bias.float()
+    if row_scale is not None:
+        out = out * row_scale.float().unsqueeze(-1)
+    return out.to(a.dtype)
+
+
+def swiglu(x: torch.Tensor) -> torch.Tensor:
+    d = x.shape[-1] // 2
+    xf = x.float()
+    return (F.silu(xf[..., :d]) * xf[..., d:]).to(x.dtype)
+
+
+def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(a @ Wg.T) * (a @ Wu.T)`` where ``w_gate_up = [Wg; Wu]``, rounded once at the end."""
+    inter = w_gate_up.shape[0] // 2
+    y = a.float() @ w_gate_up.float().t()
+    out = F.silu(y[:, :inter]) * y[:, inter:]
+    if row_scale is not None:
+        out = out * row_scale.float().unsqueeze(-1)
+    return out.to(a.dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+# rotary embedding and KV cache
+def build_cos_sin_cache(head_dim: int, max_pos: int, theta: float,
+                        rope_scaling: Optional[dict] = None, device="cpu") -> torch.Tensor:
+    """fp32 table ``[max_pos, head_dim]``: cos in the first half of each row, sin in the second.
+
+    ``rope_scaling`` supports the Llama-3 frequency rescaling
+    (vllm/model_executor/layers/rotary_embedding.py:808-851) and plain linear scaling.
+    """
+    half = head_dim // 2
+    inv_freq = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim))
+    if rope_scaling:
+        kind = rope_scaling.get("rope_type", rope_scaling.get("type", ""))
+        if kind == "llama3":
+            factor = float(rope_scaling["factor"])
+            low = float(rope_scaling.get("low_freq_factor", 1.0))
+            high = float(rope_scaling.get("high_freq_factor", 4.0))
+            orig = float(rope_scaling.get("original_max_position_embeddings", 8192))
+            wavelen = 2 * math.pi / inv_freq
+            smooth = (orig / wavelen - low) / (high - low)
+            scaled = torch.where(
+                wavelen < orig / high, inv_freq,
+                torch.where(wavelen > orig / low, inv_freq / factor,
+                            (1 - smooth) * inv_freq / factor + smooth * inv_freq))
+            inv_freq = scaled
+        elif kind == "linear":
+            inv_freq = inv_freq / float(rope_scaling["factor"])
+    t = torch.arange(max_pos, dtype=torch.float64)
+    freqs = torch.outer(t, inv_freq)
+    return torch.cat([freqs.cos(), freqs.sin()], dim=-1).float().to(device)
+
+
+def rope_kv_write_(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor],
+                   cos_sin: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                   hq: int, hkv: int, head_dim: int, write_k_back: bool = True) -> None:
+    """NeoX rotary on the q and k heads of ``qkv`` ([T, (hq+2*hkv)*D]) in place, then scatter the
+    rotated k and the v rows into the paged caches ([blocks, page, hkv, D]) at ``slots``
+    (negative slots are skipped)."""
+    T = qkv.shape[0]
+    if T == 0:
+        return
+    D = head_dim
+    half = D // 2
+    cs = cos_sin.index_select(0, positions.long())
+    cos = cs[:, :half].unsqueeze(1)
+    sin = cs[:, half:].unsqueeze(1)
+    qk = qkv[:, : (hq + hkv) * D].reshape(T, hq + hkv, D).float()
+    x, y = qk[..., :half], qk[..., half:]
+    rot = torch.cat([x * cos - y * sin, y * cos + x * sin], dim=-1).to(qkv.dtype)
+    k_rot = rot[:, hq:]
+    qkv[:, : hq * D] = rot[:, :hq].reshape(T, hq * D)
+    if write_k_back:
+        qkv[:, hq * D: (hq + hkv) * D] = k_rot.reshape(T, hkv * D)
+    if slots is not None and k_cache is not None:
+        valid = slots >= 0
+        idx = slots[valid].long()
+        kc = k_cache.view(-1, hkv, D)
+        vc = v_cache.view(-1, hkv, D)
+        kc[idx] = k_rot[valid]
+        vc[idx] = qkv[:, (hq + hkv) * D:].reshape(T, hkv, D)[valid]
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, vocab_start: int = 0,
+              vocab_end: Optional[int] = None) -> torch.Tensor:
+    vocab_end = vocab_start + table.shape[0] if vocab_end is None else vocab_end
+    ok = (ids >= vocab_start) & (ids < vocab_end)
+    local = torch.where(ok, ids - vocab_start, torch.zeros_like(ids)).long()
+    out = table.index_select(0, local)
+    return out * ok.unsqueeze(-1).to(out.dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+# attention
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: Sequence[int],
+                    kv_lens: Sequence[int], block_table: torch.Tensor, hq: int, hkv: int, head_dim: int,
+                    scale: float) -> torch.Tensor:
+    """Causal varlen attention over a paged cache. ``q``: [T, hq*D]; caches [blocks, page, hkv, D];
+    sequence b owns query rows ``cu_q[b]:cu_q[b+1]`` whose last row sees ``kv_lens[b]`` keys."""
+    T = q.shape[0]
+    D = head_dim
+    page = k_cache.shape[1]
+    out = torch.zeros(T, hq * D, dtype=q.dtype, device=q.device)
+    group = hq // hkv
+    for b in range(len(kv_lens)):
+        qs, qe = int(cu_q[b]), int(cu_q[b + 1])
+        q_len = qe - qs
+        if q_len <= 0:
+            continue
+        kv_len = int(kv_lens[b])
+        n_pages = (kv_len + page - 1) // page
+        blocks = block_table[b, :n_pages].long()
+        k = k_cache.index_select(0, blocks).reshape(-1, hkv, D)[:kv_len].float()
+        v = v_cache.index_select(0, blocks).reshape(-1, hkv, D)[:kv_len].float()
+        qb = q[qs:qe].reshape(q_len, hq, D).float()
+        k = k.repeat_interleave(group, dim=1)
+        v = v.repeat_interleave(group, dim=1)
+        s = torch.einsum("qhd,khd->hqk", qb, k) * scale
+        qpos = torch.arange(kv_len - q_len, kv_len, device=q.device).unsqueeze(-1)
+        kpos = torch.arange(kv_len, device=q.device).unsqueeze(0)
+        s = s.masked_fill((kpos > qpos).unsqueeze(0), float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        o = torch.einsum("hqk,khd->qhd", p, v)
+        out[qs:qe] = o.reshape(q_len, hq * D).to(q.dtype)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# mixture of experts
+def moe_router(x: torch.Tensor, gate_w: torch.Tensor, topk: int, renormalize: bool = True):
+    """Returns (weights [T, k] fp32, ids [T, k] int32, logits [T, E] fp32)."""
+    logits = x.float() @ gate_w.float().t()
+    probs = torch.softmax(logits, dim=-1)
+    w, ids = torch.topk(probs, topk, dim=-1)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w, ids.to(torch.int32), logits
+
+
+def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor,
+                topk_ids: torch.Tensor) -> torch.Tensor:
+    """Loop-over-experts MoE MLP: ``sum_k w_k * W2[e_k] (silu(W1[e_k] x) * W3[e_k] x)``.
+    ``w13``: [E, 2*I, H] (gate rows first), ``w2``: [E, H, I]. The activation and the weighted
+    expert output are rounded to the storage dtype, the top-k sum runs in fp32."""
+    T, H = x.shape
+    E = w13.shape[0]
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    for e in range(E):
+        sel = (topk_ids == e)
+        tok, slot = sel.nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        xe = x.index_select(0, tok)
+        act = gemm_swiglu(xe, w13[e])
+        ye = gemm(act, w2[e], row_scale=topk_w[tok, slot])
+        out.index_add_(0, tok, ye.float())
+    return out.to(x.dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+# fused collective (single-process emulation over a list of per-rank tensors)
+def fused_allreduce_add_rmsnorm(partials: Sequence[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor,
+                                eps: float):
+    """Reference of the fused RS + add + RMSNorm + AG: returns (normed [T,H], new residual [T,H]).
+    The cross-rank sum accumulates in fp32 and is rounded to the storage dtype before the add."""
+    acc = torch.zeros_like(partials[0], dtype=torch.float32)
+    for p in partials:
+        acc += p.float()
+    s = acc.to(partials[0].dtype) + residual
+    return rmsnorm(s, weight, eps), s
