@@ -2,3 +2,16 @@
 token-split compute/communication overlap and fused all-reduce + RMSNorm."""
 
 __version__ = "0.1.0"
+
+from .sampling_params import SamplingParams  # noqa: E402,F401
+from .outputs import CompletionOutput, RequestOutput  # noqa: E402,F401
+
+
+def __getattr__(name):
+    if name == "LLM":
+        from .entrypoints.llm import LLM
+        return LLM
+    if name == "EngineArgs":
+        from .config import EngineArgs
+        return EngineArgs
+    raise AttributeError(name)

@@ -1,0 +1,292 @@
+"""Configuration dataclasses and the flag system.
+
+Three tiers, as in the reference (vllm/config.py:201-3619, vllm/engine/arg_utils.py, vllm/envs.py):
+``EngineArgs`` (constructor / CLI flags) folds into ``EngineConfig`` (model, cache, parallel,
+scheduler and TokenWeave sections); environment variables ``TW_*`` are read lazily through
+:mod:`tokenweave_b200.envs`; per-model TokenWeave JSON files map a token count to a split point and
+communication-SM budget (:mod:`tokenweave_b200.tokenweave.config`).
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Optional
+
+import torch
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           "float16": torch.float16, "half": torch.float16, "auto": None}
+
+
+@dataclass
+class ModelConfig:
+    """Architecture of a decoder-only transformer (Llama-3.x, Qwen2.5, Mixtral layouts)."""
+    name: str = "tiny-llama"
+    architecture: str = "llama"          # "llama" | "qwen2" | "mixtral"
+    hidden_size: int = 256
+    num_layers: int = 2
+    num_q_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 64
+    intermediate_size: int = 688
+    vocab_size: int = 1024
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    rope_scaling: Optional[dict] = None
+    qkv_bias: bool = False
+    num_experts: int = 0                 # 0 = dense MLP
+    num_experts_per_tok: int = 2
+    max_model_len: int = 8192
+    tie_word_embeddings: bool = False
+    dtype: torch.dtype = torch.bfloat16
+    eos_token_id: Optional[int] = None
+    init_std: float = 0.02
+    path: Optional[str] = None           # checkpoint directory (None: random init)
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def num_params(self) -> int:
+        h, l = self.hidden_size, self.num_layers
+        attn = h * (self.num_q_heads + 2 * self.num_kv_heads) * self.head_dim + self.num_q_heads * self.head_dim * h
+        mlp = 3 * h * self.intermediate_size * max(1, self.num_experts)
+        emb = self.vocab_size * h * (1 if self.tie_word_embeddings else 2)
+        return l * (attn + mlp + 2 * h) + emb + h
+
+    @staticmethod
+    def from_hf_dict(cfg: dict, name: str = "", path: Optional[str] = None) -> "ModelConfig":
+        archs = cfg.get("architectures") or [cfg.get("model_type", "llama")]
+        a = archs[0].lower()
+        arch = "mixtral" if "mixtral" in a else "qwen2" if "qwen2" in a else "llama"
+        heads = cfg["num_attention_heads"]
+        head_dim = cfg.get("head_dim") or cfg["hidden_size"] // heads
+        dt = _DTYPES.get(str(cfg.get("torch_dtype", "bfloat16")), torch.bfloat16) or torch.bfloat16
+        eos = cfg.get("eos_token_id")
+        if isinstance(eos, list):
+            eos = eos[0]
+        return ModelConfig(
+            name=name or cfg.get("_name_or_path", arch), architecture=arch, hidden_size=cfg["hidden_size"],
+            num_layers=cfg["num_hidden_layers"], num_q_heads=heads,
+            num_kv_heads=cfg.get("num_key_value_heads", heads), head_dim=head_dim,
+            intermediate_size=cfg["intermediate_size"], vocab_size=cfg["vocab_size"],
+            rms_norm_eps=cfg.get("rms_norm_eps", 1e-6 if arch == "qwen2" else 1e-5),
+            rope_theta=cfg.get("rope_theta", 1e6 if arch in ("qwen2", "mixtral") else 10000.0),
+            rope_scaling=cfg.get("rope_scaling"), qkv_bias=cfg.get("attention_bias", arch == "qwen2"),
+            num_experts=cfg.get("num_local_experts", 0), num_experts_per_tok=cfg.get("num_experts_per_tok", 2),
+            max_model_len=cfg.get("max_position_embeddings", 8192),
+            tie_word_embeddings=cfg.get("tie_word_embeddings", False), dtype=dt, eos_token_id=eos, path=path)
+
+    @staticmethod
+    def from_pretrained(path: str) -> "ModelConfig":
+        p = Path(path)
+        with open(p / "config.json") as f:
+            return ModelConfig.from_hf_dict(json.load(f), name=p.name, path=str(p))
+
+
+def _preset(**kw) -> ModelConfig:
+    return ModelConfig(**kw)
+
+
+MODEL_PRESETS: dict[str, dict[str, Any]] = {
+    # correctness configuration: fp32 on CPU, split path must equal the unsplit path
+    "tiny-llama": dict(architecture="llama", hidden_size=256, num_layers=2, num_q_heads=4, num_kv_heads=2,
+                       head_dim=64, intermediate_size=688, vocab_size=1024, rms_norm_eps=1e-5,
+                       rope_theta=500000.0, max_model_len=2048),
+    "tiny-llama-d128": dict(architecture="llama", hidden_size=512, num_layers=2, num_q_heads=4, num_kv_heads=2,
+                            head_dim=128, intermediate_size=1024, vocab_size=2048, rms_norm_eps=1e-5,
+                            rope_theta=500000.0, max_model_len=4096),
+    "tiny-qwen2": dict(architecture="qwen2", hidden_size=512, num_layers=2, num_q_heads=4, num_kv_heads=2,
+                       head_dim=128, intermediate_size=1024, vocab_size=2048, rms_norm_eps=1e-6,
+                       rope_theta=1e6, qkv_bias=True, max_model_len=4096),
+    "tiny-mixtral": dict(architecture="mixtral", hidden_size=512, num_layers=2, num_q_heads=4, num_kv_heads=2,
+                         head_dim=128, intermediate_size=512, vocab_size=2048, rms_norm_eps=1e-5, rope_theta=1e6,
+                         num_experts=8, num_experts_per_tok=2, max_model_len=4096),
+    "llama-3.3-70b": dict(architecture="llama", hidden_size=8192, num_layers=80, num_q_heads=64, num_kv_heads=8,
+                          head_dim=128, intermediate_size=28672, vocab_size=128256, rms_norm_eps=1e-5,
+                          rope_theta=500000.0, max_model_len=131072,
+                          rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+                                            high_freq_factor=4.0, original_max_position_embeddings=8192)),
+    "llama-3.1-8b": dict(architecture="llama", hidden_size=4096, num_layers=32, num_q_heads=32, num_kv_heads=8,
+                         head_dim=128, intermediate_size=14336, vocab_size=128256, rms_norm_eps=1e-5,
+                         rope_theta=500000.0, max_model_len=131072,
+                         rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+                                           high_freq_factor=4.0, original_max_position_embeddings=8192)),
+    "qwen2.5-72b": dict(architecture="qwen2", hidden_size=8192, num_layers=80, num_q_heads=64, num_kv_heads=8,
+                        head_dim=128, intermediate_size=29568, vocab_size=152064, rms_norm_eps=1e-6,
+                        rope_theta=1e6, qkv_bias=True, max_model_len=32768),
+    "mixtral-8x22b": dict(architecture="mixtral", hidden_size=6144, num_layers=56, num_q_heads=48, num_kv_heads=8,
+                          head_dim=128, intermediate_size=16384, vocab_size=32768, rms_norm_eps=1e-5,
+                          rope_theta=1e6, num_experts=8, num_experts_per_tok=2, max_model_len=65536),
+}
+_ALIASES = {"meta-llama/llama-3.3-70b-instruct": "llama-3.3-70b", "qwen/qwen2.5-72b-instruct": "qwen2.5-72b",
+            "mistralai/mixtral-8x22b-instruct-v0.1": "mixtral-8x22b", "meta-llama/llama-3.1-8b-instruct": "llama-3.1-8b"}
+
+
+def resolve_model_config(model: "str | ModelConfig", dtype: Optional[str] = None,
+                         max_model_len: Optional[int] = None, num_layers: Optional[int] = None) -> ModelConfig:
+    """A preset name, a HuggingFace-style name of a supported model, or a checkpoint directory."""
+    if isinstance(model, ModelConfig):
+        cfg = dataclasses.replace(model)
+    else:
+        key = _ALIASES.get(model.lower(), model.lower())
+        if key in MODEL_PRESETS:
+            cfg = ModelConfig(name=key, **MODEL_PRESETS[key])
+        elif Path(model).is_dir() and (Path(model) / "config.json").exists():
+            cfg = ModelConfig.from_pretrained(model)
+        else:
+            raise ValueError(f"unknown model {model!r}: not a preset ({sorted(MODEL_PRESETS)}) nor a checkpoint directory")
+    if dtype and _DTYPES.get(dtype) is not None:
+        cfg.dtype = _DTYPES[dtype]
+    if max_model_len:
+        cfg.max_model_len = max_model_len
+    if num_layers:
+        cfg.num_layers = num_layers
+    return cfg
+
+
+@dataclass
+class CacheConfig:
+    block_size: int = 128                 # tokens per KV page (TMA-friendly; the reference uses 16)
+    gpu_memory_utilization: float = 0.90
+    num_gpu_blocks: Optional[int] = None  # override the profiled value
+    enable_prefix_caching: bool = False
+
+
+@dataclass
+class ParallelConfig:
+    tensor_parallel_size: int = 1
+    # "uni": in-process worker; "mp": one spawned worker process per GPU;
+    # "external_launcher": this process is one rank of a torchrun job (SPMD, deterministic scheduling)
+    distributed_executor_backend: str = "auto"
+    disable_custom_all_reduce: bool = True
+    nvls: bool = True                     # allow multimem transport when the hardware offers it
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_batched_tokens: int = 8192
+    max_num_seqs: int = 256
+    enable_chunked_prefill: bool = True
+    max_model_len: int = 8192
+
+
+@dataclass
+class TokenWeaveConfig:
+    """How the tensor-parallel all-reduce of every layer is executed.
+
+    mode:
+      "overlap"           token split + fused RS/add/RMSNorm/AG on a second stream (the product path)
+      "fuse_only"         fused kernel, no split
+      "baseline_multimem" in-kernel all-reduce, separate add+RMSNorm kernel
+      "baseline_nccl"     NCCL all-reduce, separate add+RMSNorm kernel
+      "no_ar"             communication deleted (numerically wrong upper bound)
+    """
+    mode: str = "overlap"
+    config_path: Optional[str] = None     # JSON: tokens -> {attention_ctas, mlp_ctas, split_offset}
+    overlap_threshold: Optional[int] = None  # tokens; None: 1024 (llama, qwen2) / 2048 (mixtral)
+    fuse_only_ctas: int = 16
+    transport: str = "auto"               # "auto" | "multimem" | "p2p"
+    split_offset: Optional[int] = None    # overrides the file (and TW_SPLIT_OFFSET)
+    attention_ctas: Optional[int] = None
+    mlp_ctas: Optional[int] = None
+    use_cuda_graphs: bool = False
+    wait_budget_ms: int = 2000            # budget of every cross-GPU wait inside a kernel
+
+
+@dataclass
+class EngineConfig:
+    model: ModelConfig = field(default_factory=ModelConfig)
+    cache: CacheConfig = field(default_factory=CacheConfig)
+    parallel: ParallelConfig = field(default_factory=ParallelConfig)
+    scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
+    tokenweave: TokenWeaveConfig = field(default_factory=TokenWeaveConfig)
+    load_format: str = "auto"             # "auto" | "dummy" | "safetensors"
+    seed: int = 0
+    device: str = "auto"                  # "auto" | "cuda" | "cpu"
+    enforce_eager: bool = True
+    tokenizer: Optional[str] = None
+    skip_tokenizer_init: bool = False
+    disable_log_stats: bool = True
+
+    def resolved_device(self) -> str:
+        if self.device != "auto":
+            return self.device
+        return "cuda" if torch.cuda.is_available() else "cpu"
+
+
+@dataclass
+class EngineArgs:
+    """Constructor / command-line flags (subset of vllm/engine/arg_utils.py that TokenWeave runs use)."""
+    model: Any = "tiny-llama"
+    tokenizer: Optional[str] = None
+    skip_tokenizer_init: bool = False
+    dtype: str = "auto"
+    seed: int = 0
+    max_model_len: Optional[int] = None
+    tensor_parallel_size: int = 1
+    distributed_executor_backend: str = "auto"
+    block_size: int = 128
+    gpu_memory_utilization: float = 0.90
+    num_gpu_blocks_override: Optional[int] = None
+    enable_prefix_caching: bool = False
+    max_num_batched_tokens: Optional[int] = None
+    max_num_seqs: int = 256
+    enable_chunked_prefill: bool = True
+    enforce_eager: bool = True
+    disable_custom_all_reduce: bool = True
+    load_format: str = "auto"
+    device: str = "auto"
+    num_hidden_layers_override: Optional[int] = None
+    disable_log_stats: bool = True
+    # TokenWeave
+    tokenweave_mode: str = "overlap"
+    tokenweave_config: Optional[str] = None
+    tokenweave_threshold: Optional[int] = None
+    tokenweave_transport: str = "auto"
+    tokenweave_cuda_graphs: bool = False
+    fuse_only_ctas: int = 16
+
+    def create_engine_config(self) -> EngineConfig:
+        model = resolve_model_config(self.model, None if self.dtype == "auto" else self.dtype,
+                                     self.max_model_len, self.num_hidden_layers_override)
+        max_len = model.max_model_len
+        budget = self.max_num_batched_tokens or (8192 if self.enable_chunked_prefill else max(max_len, 8192))
+        load_format = self.load_format
+        if load_format == "auto":
+            load_format = "safetensors" if model.path else "dummy"
+        return EngineConfig(
+            model=model,
+            cache=CacheConfig(self.block_size, self.gpu_memory_utilization, self.num_gpu_blocks_override,
+                              self.enable_prefix_caching),
+            parallel=ParallelConfig(self.tensor_parallel_size, self.distributed_executor_backend,
+                                    self.disable_custom_all_reduce),
+            scheduler=SchedulerConfig(budget, self.max_num_seqs, self.enable_chunked_prefill, max_len),
+            tokenweave=TokenWeaveConfig(mode=self.tokenweave_mode, config_path=self.tokenweave_config,
+                                        overlap_threshold=self.tokenweave_threshold,
+                                        transport=self.tokenweave_transport,
+                                        use_cuda_graphs=self.tokenweave_cuda_graphs,
+                                        fuse_only_ctas=self.fuse_only_ctas),
+            load_format=load_format, seed=self.seed, device=self.device, enforce_eager=self.enforce_eager,
+            tokenizer=self.tokenizer, skip_tokenizer_init=self.skip_tokenizer_init,
+            disable_log_stats=self.disable_log_stats)
+
+    @staticmethod
+    def add_cli_args(parser: argparse.ArgumentParser) -> argparse.ArgumentParser:
+        for f in dataclasses.fields(EngineArgs):
+            flag = "--" + f.name.replace("_", "-")
+            if f.type in ("bool", bool):
+                parser.add_argument(flag, action=argparse.BooleanOptionalAction, default=f.default)
+            else:
+                typ = {"int": int, "float": float, "Optional[int]": int, "str": str, "Optional[str]": str}.get(
+                    str(f.type), str)
+                parser.add_argument(flag, type=typ, default=f.default)
+        return parser
+
+    @staticmethod
+    def from_cli_args(ns: argparse.Namespace) -> "EngineArgs":
+        names = {f.name for f in dataclasses.fields(EngineArgs)}
+        return EngineArgs(**{k: v for k, v in vars(ns).items() if k in names})

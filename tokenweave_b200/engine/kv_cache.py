@@ -1,0 +1,131 @@
+"""Paged KV-cache bookkeeping: a ref-counted block pool with an LRU free queue, optional
+prefix-cache hashing, and the per-request slot allocator.
+
+Counterpart of vllm/v1/core/kv_cache_manager.py:105-324 and block_pool.py. Pure CPU. The default
+page is 128 tokens (one TMA box per page and 64-column half in the attention kernel) instead of the
+reference's 16; any power of two from 8 to 128 works.
+"""
+from __future__ import annotations
+
+import hashlib
+from collections import OrderedDict
+from typing import Optional
+
+from .request import Request
+
+
+class BlockPool:
+    def __init__(self, num_blocks: int, enable_caching: bool = False):
+        if num_blocks < 2:
+            raise ValueError("the KV cache needs at least 2 blocks")
+        self.num_blocks = num_blocks
+        self.enable_caching = enable_caching
+        self.ref = [0] * num_blocks
+        # block 0 is reserved: out-of-range page-table entries point at it
+        self.free: "OrderedDict[int, None]" = OrderedDict((i, None) for i in range(1, num_blocks))
+        self.hash_of: dict[int, bytes] = {}
+        self.block_of: dict[bytes, int] = {}
+
+    @property
+    def num_free(self) -> int:
+        return len(self.free)
+
+    def usage(self) -> float:
+        return 1.0 - self.num_free / max(1, self.num_blocks - 1)
+
+    def allocate(self, n: int) -> list[int]:
+        if n > len(self.free):
+            raise RuntimeError("out of KV blocks")
+        out = []
+        for _ in range(n):
+            b, _ = self.free.popitem(last=False)
+            h = self.hash_of.pop(b, None)
+            if h is not None and self.block_of.get(h) == b:
+                del self.block_of[h]
+            self.ref[b] = 1
+            out.append(b)
+        return out
+
+    def touch(self, b: int) -> None:
+        """Take a reference on a cached block (removing it from the free queue if it was evictable)."""
+        if self.ref[b] == 0:
+            self.free.pop(b, None)
+        self.ref[b] += 1
+
+    def release(self, blocks: list[int]) -> None:
+        # freed in reverse so that the tail of a sequence is evicted before its head
+        for b in reversed(blocks):
+            self.ref[b] -= 1
+            if self.ref[b] == 0:
+                self.free[b] = None
+
+    def cache_block(self, b: int, h: bytes) -> None:
+        if self.enable_caching and h not in self.block_of:
+            self.block_of[h] = b
+            self.hash_of[b] = h
+
+    def lookup(self, h: bytes) -> Optional[int]:
+        return self.block_of.get(h) if self.enable_caching else None
+
+
+def block_hashes(token_ids: list[int], block_size: int) -> list[bytes]:
+    """Chained hash of every full block of a token sequence."""
+    out = []
+    prev = b""
+    for i in range(0, len(token_ids) - block_size + 1, block_size):
+        m = hashlib.sha256(prev)
+        m.update(b",".join(str(t).encode() for t in token_ids[i:i + block_size]))
+        prev = m.digest()
+        out.append(prev)
+    return out
+
+
+class KVCacheManager:
+    def __init__(self, num_blocks: int, block_size: int, enable_caching: bool = False):
+        self.block_size = block_size
+        self.pool = BlockPool(num_blocks, enable_caching)
+        self.enable_caching = enable_caching
+
+    def get_computed_blocks(self, req: Request) -> tuple[list[int], int]:
+        """Longest cached prefix of the request's prompt: (block ids, number of tokens)."""
+        if not self.enable_caching:
+            return [], 0
+        blocks = []
+        # never reuse the whole prompt: the last token must be recomputed to produce logits
+        usable = (req.num_tokens - 1) // self.block_size
+        for h in block_hashes(req.all_token_ids, self.block_size)[:usable]:
+            b = self.pool.lookup(h)
+            if b is None:
+                break
+            blocks.append(b)
+        return blocks, len(blocks) * self.block_size
+
+    def allocate_slots(self, req: Request, num_new_tokens: int, cached_blocks: Optional[list[int]] = None) -> bool:
+        """Make sure ``req`` owns enough blocks for ``num_computed_tokens + num_new_tokens`` tokens.
+        Returns False (and changes nothing) if the pool cannot provide them."""
+        cached_blocks = cached_blocks or []
+        have = len(req.block_ids) + len(cached_blocks)
+        need_total = (req.num_computed_tokens + len(cached_blocks) * 0 + num_new_tokens + self.block_size - 1) // self.block_size
+        need = max(0, need_total - have)
+        evictable_cached = sum(1 for b in cached_blocks if self.pool.ref[b] == 0)
+        if need > self.pool.num_free - evictable_cached:
+            return False
+        for b in cached_blocks:
+            self.pool.touch(b)
+        req.block_ids.extend(cached_blocks)
+        req.block_ids.extend(self.pool.allocate(need))
+        return True
+
+    def cache_full_blocks(self, req: Request) -> None:
+        if not self.enable_caching:
+            return
+        full = req.num_computed_tokens // self.block_size
+        for i, h in enumerate(block_hashes(req.all_token_ids[:full * self.block_size], self.block_size)):
+            self.pool.cache_block(req.block_ids[i], h)
+
+    def free(self, req: Request) -> None:
+        self.pool.release(req.block_ids)
+        req.block_ids = []
+
+    def usage(self) -> float:
+        return self.pool.usage()

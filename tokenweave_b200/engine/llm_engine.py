@@ -1,0 +1,153 @@
+"""Engine front end: tokenises requests, drives the core, turns tokens back into ``RequestOutput``s.
+
+Counterpart of vllm/v1/engine/llm_engine.py:41-231, processor.py and output_processor.py (n > 1 fan-out,
+incremental detokenisation, stop strings).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional, Union
+
+from ..config import EngineArgs, EngineConfig
+from ..outputs import CompletionOutput, RequestMetrics, RequestOutput
+from ..sampling_params import SamplingParams
+from ..utils.logging import init_logger
+from ..utils.metrics import LoggingStatLogger
+from .core import EngineCore
+from .request import Request, RequestStatus
+from .tokenizer import IncrementalDetokenizer, load_tokenizer
+
+logger = init_logger(__name__)
+
+
+@dataclass
+class _Parent:
+    request_id: str
+    prompt: Optional[str]
+    prompt_token_ids: list[int]
+    params: SamplingParams
+    children: list[Request] = field(default_factory=list)
+    detoks: list[Optional[IncrementalDetokenizer]] = field(default_factory=list)
+    logprobs: list[list] = field(default_factory=list)
+    cum_logprob: list[float] = field(default_factory=list)
+    arrival: float = field(default_factory=time.monotonic)
+
+
+class LLMEngine:
+    def __init__(self, config: EngineConfig, executor=None):
+        self.config = config
+        self.tokenizer = None if config.skip_tokenizer_init else load_tokenizer(config.tokenizer or
+                                                                               (config.model.path if config.model.path else "byte"))
+        self.core = EngineCore(config, executor)
+        self.parents: dict[str, _Parent] = {}
+        self.child_to_parent: dict[str, tuple[str, int]] = {}
+        self.stat_logger = None if config.disable_log_stats else LoggingStatLogger()
+        eos = config.model.eos_token_id
+        if eos is None and self.tokenizer is not None:
+            eos = getattr(self.tokenizer, "eos_token_id", None)
+        self.eos_token_id = eos
+
+    @classmethod
+    def from_engine_args(cls, args: EngineArgs) -> "LLMEngine":
+        return cls(args.create_engine_config())
+
+    # ---- requests ---------------------------------------------------------------------------
+    def add_request(self, request_id: str, prompt: Union[str, list[int], dict], params: SamplingParams) -> None:
+        text: Optional[str] = None
+        if isinstance(prompt, dict):
+            text = prompt.get("prompt")
+            ids = prompt.get("prompt_token_ids")
+            if ids is None:
+                ids = self._encode(text)
+        elif isinstance(prompt, str):
+            text, ids = prompt, self._encode(prompt)
+        else:
+            ids = list(prompt)
+        vocab = self.config.model.vocab_size
+        if any((t < 0 or t >= vocab) for t in ids):
+            raise ValueError(f"request {request_id}: token id outside [0, {vocab})")
+        parent = _Parent(request_id, text, list(ids), params)
+        for i in range(params.n):
+            sp = params
+            if params.n > 1:
+                sp = params.clone()
+                sp.n = 1
+                if sp.seed is not None:
+                    sp.seed = sp.seed + i
+            cid = request_id if params.n == 1 else f"{i}_{request_id}"
+            child = Request(cid, list(ids), sp, eos_token_id=self.eos_token_id, prompt=text)
+            parent.children.append(child)
+            detok = None
+            if self.tokenizer is not None and params.detokenize:
+                detok = IncrementalDetokenizer(self.tokenizer, ids, params.skip_special_tokens, params.stop)
+            parent.detoks.append(detok)
+            parent.logprobs.append([])
+            parent.cum_logprob.append(0.0)
+            self.child_to_parent[cid] = (request_id, i)
+            self.core.add_request(child)
+        self.parents[request_id] = parent
+
+    def _encode(self, text: str) -> list[int]:
+        if self.tokenizer is None:
+            raise ValueError("text prompts need a tokenizer (skip_tokenizer_init is set)")
+        return list(self.tokenizer.encode(text))
+
+    def abort_request(self, request_id: str) -> None:
+        parent = self.parents.pop(request_id, None)
+        if parent:
+            for c in parent.children:
+                self.core.abort_request(c.request_id)
+                self.child_to_parent.pop(c.request_id, None)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.core.has_unfinished_requests()
+
+    def get_num_unfinished_requests(self) -> int:
+        return self.core.scheduler.num_unfinished()
+
+    # ---- stepping ---------------------------------------------------------------------------
+    def step(self) -> list[RequestOutput]:
+        touched = self.core.step()
+        if self.stat_logger is not None and self.core.last_stats is not None:
+            self.stat_logger.record(self.core.last_stats)
+        lps = getattr(self.core, "_last_logprobs", {})
+        outputs: dict[str, RequestOutput] = {}
+        for child in touched:
+            pid, idx = self.child_to_parent[child.request_id]
+            parent = self.parents[pid]
+            lp = lps.get(child.request_id)
+            if lp is not None:
+                parent.logprobs[idx].append(lp)
+                parent.cum_logprob[idx] += lp.get(child.output_token_ids[-1], 0.0)
+            detok = parent.detoks[idx]
+            if detok is not None and not child.status == RequestStatus.FINISHED_ABORTED:
+                hit = detok.update(child.output_token_ids[len(detok.token_ids):])
+                if hit is not None and not child.status.finished:
+                    self.core.scheduler.finish_request(child, RequestStatus.FINISHED_STOPPED, hit)
+            outputs[pid] = self._make_output(parent)
+        done = [pid for pid, out in outputs.items() if out.finished]
+        for pid in done:
+            parent = self.parents.pop(pid)
+            for c in parent.children:
+                self.child_to_parent.pop(c.request_id, None)
+        return list(outputs.values())
+
+    def _make_output(self, parent: _Parent) -> RequestOutput:
+        comps = []
+        for i, c in enumerate(parent.children):
+            detok = parent.detoks[i]
+            comps.append(CompletionOutput(
+                index=i, text=detok.text if detok is not None else "", token_ids=list(c.output_token_ids),
+                cumulative_logprob=parent.cum_logprob[i] if parent.params.logprobs is not None else None,
+                logprobs=list(parent.logprobs[i]) if parent.params.logprobs is not None else None,
+                finish_reason=c.finish_reason, stop_reason=c.stop_reason))
+        finished = all(c.status.finished for c in parent.children)
+        first = [c.first_token_time for c in parent.children if c.first_token_time is not None]
+        metrics = RequestMetrics(parent.arrival, min((c.first_scheduled_time or parent.arrival) for c in parent.children),
+                                 min(first) if first else None,
+                                 max((c.finished_time or 0.0) for c in parent.children) if finished else None)
+        return RequestOutput(parent.request_id, parent.prompt, parent.prompt_token_ids, comps, finished, metrics)
+
+    def shutdown(self) -> None:
+        self.core.shutdown()

@@ -1,0 +1,200 @@
+"""Continuous-batching scheduler with a per-step token budget (chunked prefill by construction).
+
+Counterpart of vllm/v1/core/sched/scheduler.py:133-498 (schedule) and :609-735 (update_from_output):
+running requests are served first, then waiting ones, each capped by what is left of
+``max_num_batched_tokens``; a request whose prompt does not fit is prefetched in chunks; when the
+KV pool is exhausted the most recently admitted running request is preempted and recomputed later.
+The schedule is a pure function of the request stream, so SPMD ranks that replay the same calls
+stay in lockstep without exchanging messages.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Optional
+
+from ..config import SchedulerConfig
+from .kv_cache import KVCacheManager
+from .request import Request, RequestStatus
+
+
+@dataclass
+class ScheduledRequest:
+    request: Request
+    num_new_tokens: int
+    num_computed_tokens: int     # before this step
+    is_new: bool                 # first time (or resumed after preemption) on the workers
+
+
+@dataclass
+class SchedulerOutput:
+    scheduled: list[ScheduledRequest] = field(default_factory=list)
+    total_num_tokens: int = 0
+    finished_req_ids: list[str] = field(default_factory=list)
+    preempted_req_ids: list[str] = field(default_factory=list)
+    step_id: int = 0
+
+    @property
+    def empty(self) -> bool:
+        return self.total_num_tokens == 0
+
+
+@dataclass
+class ModelRunnerOutput:
+    req_ids: list[str]
+    sampled_token_ids: list[Optional[int]]        # None for requests still prefilling
+    logprobs: Optional[list] = None
+
+
+class Scheduler:
+    def __init__(self, config: SchedulerConfig, kv: KVCacheManager):
+        self.config = config
+        self.kv = kv
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.requests: dict[str, Request] = {}
+        self._finished_since_last: list[str] = []
+        self._step = 0
+
+    # ---- request lifecycle -------------------------------------------------------------
+    def add_request(self, req: Request) -> None:
+        if req.num_prompt_tokens == 0:
+            raise ValueError("empty prompt")
+        if req.num_prompt_tokens >= self.config.max_model_len:
+            raise ValueError(f"prompt of {req.num_prompt_tokens} tokens does not fit max_model_len "
+                             f"{self.config.max_model_len}")
+        self.requests[req.request_id] = req
+        self.waiting.append(req)
+
+    def abort_request(self, request_id: str) -> None:
+        req = self.requests.get(request_id)
+        if req is None or req.status.finished:
+            return
+        if req in self.running:
+            self.running.remove(req)
+        elif req in self.waiting:
+            self.waiting.remove(req)
+        self._finish(req, RequestStatus.FINISHED_ABORTED)
+
+    def has_unfinished_requests(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def num_unfinished(self) -> int:
+        return len(self.waiting) + len(self.running)
+
+    # ---- scheduling ---------------------------------------------------------------------
+    def schedule(self) -> SchedulerOutput:
+        out = SchedulerOutput(step_id=self._step)
+        self._step += 1
+        budget = self.config.max_num_batched_tokens
+        preempted: list[Request] = []
+
+        # running requests first (decode tokens and prefill continuations)
+        i = 0
+        while i < len(self.running) and budget > 0:
+            req = self.running[i]
+            n = min(req.num_tokens - req.num_computed_tokens, budget)
+            if not self.config.enable_chunked_prefill and n < req.num_tokens - req.num_computed_tokens:
+                i += 1
+                continue
+            while not self.kv.allocate_slots(req, n):
+                victim = self.running.pop()     # most recently admitted
+                self._preempt(victim)
+                preempted.append(victim)
+                if victim is req:
+                    n = 0
+                    break
+            if n == 0:
+                break
+            out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, False))
+            budget -= n
+            i += 1
+
+        # then admit waiting requests
+        if not preempted:
+            while self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
+                req = self.waiting[0]
+                cached, n_cached = ([], 0)
+                if req.num_computed_tokens == 0:
+                    cached, n_cached = self.kv.get_computed_blocks(req)
+                remaining = req.num_tokens - req.num_computed_tokens - n_cached
+                n = min(remaining, budget)
+                if n < remaining and not self.config.enable_chunked_prefill:
+                    break
+                req.num_computed_tokens += n_cached
+                if not self.kv.allocate_slots(req, n, cached):
+                    req.num_computed_tokens -= n_cached
+                    break
+                self.waiting.popleft()
+                req.status = RequestStatus.RUNNING
+                if req.first_scheduled_time is None:
+                    req.first_scheduled_time = time.monotonic()
+                self.running.append(req)
+                out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, True))
+                budget -= n
+
+        out.total_num_tokens = sum(s.num_new_tokens for s in out.scheduled)
+        out.finished_req_ids = self._finished_since_last
+        self._finished_since_last = []
+        out.preempted_req_ids = [r.request_id for r in preempted]
+        return out
+
+    def _preempt(self, req: Request) -> None:
+        self.kv.free(req)
+        req.status = RequestStatus.PREEMPTED
+        req.num_computed_tokens = 0
+        self.waiting.appendleft(req)
+
+    # ---- results ------------------------------------------------------------------------
+    def update_from_output(self, sched: SchedulerOutput, result: ModelRunnerOutput) -> list[Request]:
+        """Advance every scheduled request; returns the requests that produced a token or finished."""
+        sampled = dict(zip(result.req_ids, result.sampled_token_ids))
+        touched: list[Request] = []
+        for s in sched.scheduled:
+            req = s.request
+            if req.status.finished:
+                continue
+            req.num_computed_tokens = s.num_computed_tokens + s.num_new_tokens
+            self.kv.cache_full_blocks(req)
+            tok = sampled.get(req.request_id)
+            if req.num_computed_tokens < req.num_tokens or tok is None:
+                continue                       # still prefilling: the sampled token (if any) is discarded
+            req.output_token_ids.append(int(tok))
+            if req.first_token_time is None:
+                req.first_token_time = time.monotonic()
+            touched.append(req)
+            self._check_stop(req)
+        return touched
+
+    def _check_stop(self, req: Request) -> None:
+        sp = req.sampling_params
+        last = req.output_token_ids[-1]
+        n_out = len(req.output_token_ids)
+        if n_out >= sp.min_tokens:
+            if not sp.ignore_eos and req.eos_token_id is not None and last == req.eos_token_id:
+                self._stop_running(req, RequestStatus.FINISHED_STOPPED, None)
+                return
+            if last in sp.stop_token_ids:
+                self._stop_running(req, RequestStatus.FINISHED_STOPPED, last)
+                return
+        if (sp.max_tokens is not None and n_out >= sp.max_tokens) or req.num_tokens >= self.config.max_model_len:
+            self._stop_running(req, RequestStatus.FINISHED_LENGTH, None)
+
+    def finish_request(self, req: Request, status: RequestStatus, stop_reason=None) -> None:
+        """Used by the front end for stop strings detected after detokenisation."""
+        if not req.status.finished:
+            self._stop_running(req, status, stop_reason)
+
+    def _stop_running(self, req: Request, status: RequestStatus, stop_reason) -> None:
+        if req in self.running:
+            self.running.remove(req)
+        req.stop_reason = stop_reason
+        self._finish(req, status)
+
+    def _finish(self, req: Request, status: RequestStatus) -> None:
+        req.status = status
+        req.finished_time = time.monotonic()
+        self.kv.free(req)
+        self._finished_since_last.append(req.request_id)
+        self.requests.pop(req.request_id, None)

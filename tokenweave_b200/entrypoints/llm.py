@@ -1,0 +1,99 @@
+"""Offline inference API: ``LLM(model, tensor_parallel_size=..., ...).generate(prompts, sampling_params)``.
+
+Counterpart of vllm/entrypoints/llm.py:162-471 and the ``_run_engine`` loop at :1404-1446. Keyword
+arguments are the reference's engine flags that TokenWeave runs use (``tensor_parallel_size``,
+``enforce_eager``, ``enable_chunked_prefill``, ``max_num_batched_tokens``, ``disable_custom_all_reduce``,
+``enable_prefix_caching``, ``load_format``, ``max_model_len``, ``gpu_memory_utilization``, ``seed``,
+``dtype``...), plus ``tokenweave_*`` options.
+"""
+from __future__ import annotations
+
+import itertools
+from typing import Any, Optional, Sequence, Union
+
+from ..config import EngineArgs, ModelConfig
+from ..engine.llm_engine import LLMEngine
+from ..outputs import RequestOutput
+from ..sampling_params import SamplingParams
+from ..utils.logging import init_logger
+
+logger = init_logger(__name__)
+
+PromptType = Union[str, list[int], dict]
+
+
+class LLM:
+    def __init__(self, model: Union[str, ModelConfig] = "tiny-llama", tokenizer: Optional[str] = None,
+                 tensor_parallel_size: int = 1, dtype: str = "auto", seed: int = 0, **kwargs: Any):
+        if "no_enable_prefix_caching" in kwargs:
+            kwargs["enable_prefix_caching"] = not kwargs.pop("no_enable_prefix_caching")
+        kwargs.pop("trust_remote_code", None)
+        kwargs.pop("tokenizer_mode", None)
+        self.engine_args = EngineArgs(model=model, tokenizer=tokenizer, tensor_parallel_size=tensor_parallel_size,
+                                      dtype=dtype, seed=seed, **kwargs)
+        self.llm_engine = LLMEngine.from_engine_args(self.engine_args)
+        self._counter = itertools.count()
+
+    def get_tokenizer(self):
+        return self.llm_engine.tokenizer
+
+    # ---- generation ---------------------------------------------------------------------------
+    def generate(self, prompts: Union[PromptType, Sequence[PromptType], None] = None,
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 prompt_token_ids: Optional[Sequence[list[int]]] = None, use_tqdm: bool = False) -> list[RequestOutput]:
+        """Generate completions; results come back in prompt order. A prompt is text, a list of token
+        ids, or ``{"prompt": ..., "prompt_token_ids": [...]}``."""
+        if prompts is None:
+            if prompt_token_ids is None:
+                raise ValueError("give prompts or prompt_token_ids")
+            prompts = [list(p) for p in prompt_token_ids]
+        elif isinstance(prompts, (str, dict)) or (isinstance(prompts, list) and prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        prompts = list(prompts)
+        if sampling_params is None:
+            sampling_params = SamplingParams()
+        if isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params] * len(prompts)
+        if len(sampling_params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt (or a single one for all)")
+        ids = []
+        for p, sp in zip(prompts, sampling_params):
+            rid = str(next(self._counter))
+            self.llm_engine.add_request(rid, p, sp)
+            ids.append(rid)
+        return self._run_engine(ids, use_tqdm)
+
+    def _run_engine(self, request_ids: list[str], use_tqdm: bool = False) -> list[RequestOutput]:
+        final: dict[str, RequestOutput] = {}
+        bar = None
+        if use_tqdm:
+            from tqdm import tqdm
+            bar = tqdm(total=len(request_ids), desc="Processed prompts")
+        while self.llm_engine.has_unfinished_requests():
+            for out in self.llm_engine.step():
+                if out.finished:
+                    final[out.request_id] = out
+                    if bar is not None:
+                        bar.update(1)
+        if bar is not None:
+            bar.close()
+        return [final[r] for r in request_ids if r in final]
+
+    # ---- utilities ------------------------------------------------------------------------------
+    def collective_rpc(self, method: str, *args, **kwargs) -> list[Any]:
+        return self.llm_engine.core.executor.collective_rpc(method, *args, **kwargs)
+
+    def start_profile(self) -> None:
+        self.llm_engine.core.executor.profile(True)
+
+    def stop_profile(self) -> None:
+        self.llm_engine.core.executor.profile(False)
+
+    def shutdown(self) -> None:
+        self.llm_engine.shutdown()
+
+    def __del__(self):
+        try:
+            self.shutdown()
+        except Exception:
+            pass

@@ -1,0 +1,102 @@
+"""Token sampling from fp32 logits: greedy, temperature, top-k / top-p / min-p, repetition / presence /
+frequency penalties, per-request seeded generators, optional log-probabilities.
+
+Counterpart of vllm/v1/sample/sampler.py:17-270 and ops/topk_topp_sampler.py:170-262. Random draws use
+the exponential-race form ``argmax(p / Exp(1))`` so that no host synchronisation is needed; the
+all-greedy batch (the latency benchmarks) takes a single argmax kernel.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..sampling_params import SamplingParams
+
+
+@dataclass
+class SamplerOutput:
+    token_ids: torch.Tensor                      # [B] int32 (device)
+    logprobs: Optional[list] = None              # per request: dict token -> logprob (top-n + sampled)
+
+
+def apply_penalties(logits: torch.Tensor, params: Sequence[SamplingParams], prompt_tokens: Sequence[Sequence[int]],
+                    output_tokens: Sequence[Sequence[int]]) -> torch.Tensor:
+    V = logits.shape[1]
+    for i, sp in enumerate(params):
+        if not sp.needs_penalties:
+            continue
+        out_ids = torch.as_tensor(list(output_tokens[i]), dtype=torch.long, device=logits.device)
+        if sp.repetition_penalty != 1.0:
+            seen = torch.as_tensor(list(prompt_tokens[i]) + list(output_tokens[i]), dtype=torch.long, device=logits.device)
+            seen = seen[seen < V].unique()
+            row = logits[i, seen]
+            logits[i, seen] = torch.where(row > 0, row / sp.repetition_penalty, row * sp.repetition_penalty)
+        if out_ids.numel() and (sp.frequency_penalty != 0.0 or sp.presence_penalty != 0.0):
+            counts = torch.bincount(out_ids[out_ids < V], minlength=V).to(logits.dtype)
+            logits[i] -= sp.frequency_penalty * counts
+            logits[i] -= sp.presence_penalty * (counts > 0).to(logits.dtype)
+    return logits
+
+
+def _filter_top_k_top_p(logits: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor, min_p: torch.Tensor) -> torch.Tensor:
+    """Sort-based joint top-k / top-p mask (ascending sort, as in the reference)."""
+    V = logits.shape[1]
+    if bool((top_k < V).any()) or bool((top_p < 1.0).any()):
+        sorted_logits, idx = logits.sort(dim=-1, descending=False)
+        kth = sorted_logits.gather(1, (V - top_k.clamp(max=V)).unsqueeze(1).long())
+        sorted_logits = sorted_logits.masked_fill(sorted_logits < kth, float("-inf"))
+        probs = sorted_logits.softmax(dim=-1)
+        cum = probs.cumsum(dim=-1)
+        mask = cum <= (1.0 - top_p).unsqueeze(1)
+        mask[:, -1] = False
+        sorted_logits = sorted_logits.masked_fill(mask, float("-inf"))
+        logits = torch.empty_like(logits).scatter_(1, idx, sorted_logits)
+    if bool((min_p > 0).any()):
+        probs = logits.softmax(dim=-1)
+        thresh = probs.max(dim=-1, keepdim=True).values * min_p.unsqueeze(1)
+        logits = logits.masked_fill(probs < thresh, float("-inf"))
+    return logits
+
+
+class Sampler:
+    def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                 generators: Sequence[Optional[torch.Generator]], prompt_tokens=None, output_tokens=None) -> SamplerOutput:
+        B, V = logits.shape
+        want_logprobs = any(sp.logprobs is not None for sp in params)
+        if any(sp.needs_penalties for sp in params):
+            logits = apply_penalties(logits.clone(), params, prompt_tokens, output_tokens)
+        raw_logprobs = torch.log_softmax(logits, dim=-1) if want_logprobs else None
+        if all(sp.greedy for sp in params):
+            ids = ops.argmax(logits)
+        else:
+            dev = logits.device
+            temp = torch.tensor([1.0 if sp.greedy else sp.temperature for sp in params], dtype=torch.float32, device=dev)
+            top_k = torch.tensor([V if sp.top_k <= 0 else min(sp.top_k, V) for sp in params], dtype=torch.long, device=dev)
+            top_p = torch.tensor([sp.top_p for sp in params], dtype=torch.float32, device=dev)
+            min_p = torch.tensor([sp.min_p for sp in params], dtype=torch.float32, device=dev)
+            scaled = _filter_top_k_top_p(logits / temp.unsqueeze(1), top_k, top_p, min_p)
+            probs = scaled.softmax(dim=-1)
+            noise = torch.empty_like(probs)
+            for i, g in enumerate(generators):
+                noise[i].exponential_(generator=g)
+            sampled = (probs / noise).argmax(dim=-1)
+            greedy = torch.tensor([sp.greedy for sp in params], dtype=torch.bool, device=dev)
+            ids = torch.where(greedy, logits.argmax(dim=-1), sampled).to(torch.int32)
+        lp_out = None
+        if want_logprobs:
+            lp_out = []
+            ids_l = ids.long()
+            for i, sp in enumerate(params):
+                if sp.logprobs is None:
+                    lp_out.append(None)
+                    continue
+                row = raw_logprobs[i]
+                d = {int(ids_l[i]): float(row[ids_l[i]])}
+                if sp.logprobs > 0:
+                    vals, toks = row.topk(min(sp.logprobs, V))
+                    d.update({int(t): float(v) for t, v in zip(toks.tolist(), vals.tolist())})
+                lp_out.append(d)
+        return SamplerOutput(ids, lp_out)

@@ -1,0 +1,268 @@
+"""Decoder-only transformer shared by the Llama, Qwen2 and Mixtral families.
+
+Counterparts: vllm/model_executor/models/llama.py:99-590, qwen2.py, mixtral.py (with the TokenWeave
+edits). Differences by design:
+
+* the residual stream lives in one symmetric staging buffer ``[max_tokens + 512, H]`` per rank that
+  o_proj / down_proj / the MoE write their partial sums into and the fused collective reduces and
+  normalises in place (same aliasing as llama.py:537,568);
+* the gate_up projection and SwiGLU are one GEMM (epilogue), RoPE and the KV-cache write one kernel;
+* every activation workspace is allocated once for ``max_tokens`` (no allocator traffic in a step, so a
+  step can be captured in a CUDA graph);
+* the embedding table is replicated (see layers/embedding.py) unless ``embedding_parallel`` is set.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Iterable, Optional
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..config import EngineConfig, ModelConfig
+from ..layers.attention import Attention, AttentionMetadata
+from ..layers.embedding import ParallelLMHead, VocabEmbedding
+from ..layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
+from ..layers.moe import FusedMoE
+from ..ops import reference
+from ..parallel.comm import TPCommunicator
+from ..parallel.state import get_tp
+from ..parallel.symm_mem import SymmetricBuffer, create_symmetric_buffer
+from ..tokenweave import schedule
+from ..tokenweave.config import SplitPlan
+
+STAGING_EXTRA_ROWS = 512   # room for the 256-row padding plus a split offset (llama.py:437 uses +512)
+
+
+@dataclass
+class StepInput:
+    """Everything one forward pass needs besides the weights."""
+    input_ids: torch.Tensor                   # [T] int32
+    plan: SplitPlan
+    meta: Optional[AttentionMetadata] = None  # unsplit batch
+    meta0: Optional[AttentionMetadata] = None  # token subset 0 / 1 of the overlap schedule
+    meta1: Optional[AttentionMetadata] = None
+    logits_indices: Optional[torch.Tensor] = None   # rows whose logits are needed (last token of each request)
+
+
+class Runtime:
+    """Per-rank buffers and streams shared by all layers."""
+
+    def __init__(self, cfg: ModelConfig, max_tokens: int, device: torch.device, tw_cfg, provider: Optional[str] = None):
+        tp = get_tp()
+        self.device = device
+        self.max_tokens = max_tokens
+        rows = max_tokens + STAGING_EXTRA_ROWS
+        H, D = cfg.hidden_size, cfg.head_dim
+        dt = cfg.dtype
+        hq = cfg.num_q_heads // tp.world_size
+        hkv = max(1, cfg.num_kv_heads // tp.world_size)
+        allow_mc = tw_cfg.transport in ("auto", "multimem")
+        self.staging: SymmetricBuffer = create_symmetric_buffer(rows, H, dt, tp, provider, allow_mc)
+        self.hidden = self.staging.tensor
+        self.residual = torch.zeros(rows, H, dtype=dt, device=device)
+        self.qkv = torch.zeros(rows, (hq + 2 * hkv) * D, dtype=dt, device=device)
+        self.attn_out = torch.zeros(rows, hq * D, dtype=dt, device=device)
+        inter = cfg.intermediate_size // tp.world_size
+        self.act = None if cfg.is_moe else torch.zeros(rows, inter, dtype=dt, device=device)
+        self.comm = TPCommunicator(self.staging, tp, tw_cfg.wait_budget_ms, tw_cfg.transport)
+        if device.type == "cuda":
+            self.comm_stream = torch.cuda.Stream(device=device, priority=-1)
+            self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+        else:
+            self.comm_stream = None
+            self.sm_count = 0
+        self.cos_sin = reference.build_cos_sin_cache(D, cfg.max_model_len, cfg.rope_theta, cfg.rope_scaling, device)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, *, device):
+        super().__init__()
+        tp = get_tp()
+        dt = cfg.dtype
+        H, D = cfg.hidden_size, cfg.head_dim
+        self.qkv_proj = QKVParallelLinear(H, D, cfg.num_q_heads, cfg.num_kv_heads, cfg.qkv_bias, dtype=dt, device=device)
+        self.o_proj = RowParallelLinear(cfg.num_q_heads * D, H, False, dtype=dt, device=device)
+        self.attn = Attention(self.qkv_proj.q_heads, self.qkv_proj.kv_heads, D)
+        self.input_norm_w = nn.Parameter(torch.ones(H, dtype=dt, device=device), requires_grad=False)
+        self.post_norm_w = nn.Parameter(torch.ones(H, dtype=dt, device=device), requires_grad=False)
+        if cfg.is_moe:
+            self.moe = FusedMoE(cfg.num_experts, cfg.num_experts_per_tok, H, cfg.intermediate_size, dtype=dt, device=device)
+            self.gate_up_proj = self.down_proj = None
+        else:
+            self.moe = None
+            self.gate_up_proj = MergedColumnParallelLinear(H, [cfg.intermediate_size] * 2, False, dtype=dt, device=device)
+            self.down_proj = RowParallelLinear(cfg.intermediate_size, H, False, dtype=dt, device=device)
+
+    def attn_block(self, rows: torch.Tensor, n: int, meta: AttentionMetadata, rt: Runtime, max_ctas: int) -> None:
+        """rows[:n] (normalised activations) -> this rank's partial o_proj output, in place."""
+        if n == 0:
+            return
+        qkv = self.qkv_proj(rows[:n], out=rt.qkv[:n], max_ctas=max_ctas)
+        attn_out = self.attn(qkv, rt.cos_sin, meta, rt.attn_out[:n])
+        self.o_proj(attn_out, out=rows[:n], max_ctas=max_ctas)
+
+    def mlp_block(self, rows: torch.Tensor, n: int, rt: Runtime, max_ctas: int) -> None:
+        if n == 0:
+            return
+        if self.moe is not None:
+            self.moe(rows[:n], out=rows[:n], max_ctas=max_ctas)
+            return
+        act = self.gate_up_proj.forward_swiglu(rows[:n], out=rt.act[:n], max_ctas=max_ctas)
+        self.down_proj(act, out=rows[:n], max_ctas=max_ctas)
+
+
+class DecoderModel(nn.Module):
+    architecture = "llama"
+
+    def __init__(self, cfg: ModelConfig, *, device, embedding_parallel: bool = False):
+        super().__init__()
+        self.cfg = cfg
+        dt = cfg.dtype
+        self.embed_tokens = VocabEmbedding(cfg.vocab_size, cfg.hidden_size, embedding_parallel, dtype=dt, device=device)
+        self.layers = nn.ModuleList([DecoderLayer(cfg, device=device) for _ in range(cfg.num_layers)])
+        self.norm_w = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dt, device=device), requires_grad=False)
+        self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, dtype=dt, device=device)
+        self.rt: Optional[Runtime] = None
+        self.tw_mode = "overlap"
+
+    # ---- runtime -------------------------------------------------------------------------
+    def setup_runtime(self, max_tokens: int, tw_cfg, provider: Optional[str] = None) -> Runtime:
+        device = self.norm_w.device
+        self.rt = Runtime(self.cfg, max_tokens, device, tw_cfg, provider)
+        self.tw_mode = tw_cfg.mode
+        return self.rt
+
+    def kv_cache_bytes_per_block(self, block_size: int) -> int:
+        l0 = self.layers[0]
+        return 2 * block_size * l0.attn.hkv * l0.attn.head_dim * self.cfg.dtype.itemsize * len(self.layers)
+
+    def init_kv_cache(self, num_blocks: int, block_size: int) -> None:
+        dev = self.norm_w.device
+        for layer in self.layers:
+            a = layer.attn
+            k = torch.zeros(num_blocks, block_size, a.hkv, a.head_dim, dtype=self.cfg.dtype, device=dev)
+            v = torch.zeros_like(k)
+            a.bind_kv_cache(k, v)
+
+    # ---- forward -------------------------------------------------------------------------
+    @torch.inference_mode()
+    def forward(self, step: StepInput) -> torch.Tensor:
+        """Runs the decoder stack; returns the final-norm hidden rows ``[T, H]`` (a view of the staging buffer)."""
+        rt, plan, cfg = self.rt, step.plan, self.cfg
+        T, Tp = plan.num_tokens, plan.padded_tokens
+        assert Tp <= rt.hidden.shape[0], "step exceeds the staging buffer"
+        hidden, residual = rt.hidden, rt.residual
+        eps = cfg.rms_norm_eps
+        if Tp > T:
+            hidden[T:Tp].zero_()
+        self.embed_tokens(step.input_ids, out=hidden[:T])
+        pending = self.embed_tokens.parallel and self.tw_mode != "no_ar"
+        if pending:
+            residual[:Tp].zero_()
+        else:
+            if Tp > T:
+                residual[T:Tp].zero_()
+            ops.rmsnorm_copy_(hidden[:T], residual[:T], self.layers[0].input_norm_w, eps)
+        if plan.overlap:
+            schedule.run_overlap(self.layers, self.norm_w, hidden, residual, step.meta0, step.meta1, plan, rt.comm,
+                                 rt, eps, pending)
+        elif self.tw_mode in ("overlap", "fuse_only"):
+            schedule.run_fuse_only(self.layers, self.norm_w, hidden, residual, step.meta, plan, rt.comm, rt, eps,
+                                   pending)
+        else:
+            schedule.run_baseline(self.layers, self.norm_w, hidden, residual, step.meta, plan, rt.comm, rt, eps,
+                                  self.tw_mode, pending)
+        return hidden[:T]
+
+    @torch.inference_mode()
+    def compute_logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
+        return self.lm_head(hidden_rows)
+
+    # ---- weights -------------------------------------------------------------------------
+    def init_dummy_weights(self, seed: int = 0) -> None:
+        """Random weights of the checkpoint's statistics (the reference's DummyModelLoader,
+        vllm/model_executor/model_loader/loader.py:476-500). Every rank draws the full-size tensor
+        stream from the same seed and keeps its shard, so TP runs are comparable across sizes only
+        statistically; for exact TP-vs-single comparisons load a checkpoint instead."""
+        std = self.cfg.init_std
+        gen_dev = self.norm_w.device
+        g = torch.Generator(device=gen_dev)
+        g.manual_seed(seed + 1234567 * (get_tp().rank + 1))
+        for name, p in self.named_parameters():
+            if name.endswith("norm_w"):
+                p.data.fill_(1.0)
+            elif p.dim() == 1:
+                p.data.zero_()
+            else:
+                p.data.normal_(0.0, std, generator=g)
+        if self.embed_tokens.parallel is False and get_tp().world_size > 1:
+            # a replicated table must be identical on all ranks
+            g2 = torch.Generator(device=gen_dev)
+            g2.manual_seed(seed + 99)
+            self.embed_tokens.weight.data.normal_(0.0, std, generator=g2)
+        if get_tp().world_size > 1:
+            for layer in self.layers:
+                if layer.moe is not None:
+                    g3 = torch.Generator(device=gen_dev)
+                    g3.manual_seed(seed + 7)
+                    layer.moe.gate.data.normal_(0.0, std, generator=g3)
+
+    # HuggingFace name -> (module path, shard id)
+    STACKED = [(".q_proj", ".qkv_proj", "q"), (".k_proj", ".qkv_proj", "k"), (".v_proj", ".qkv_proj", "v"),
+               (".gate_proj", ".gate_up_proj", 0), (".up_proj", ".gate_up_proj", 1)]
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        """Load HuggingFace-layout tensors (``model.layers.N.self_attn.q_proj.weight`` ...), sharding on
+        the fly. Returns the names that were consumed."""
+        loaded: set[str] = set()
+        saw_lm_head = False
+        for name, tensor in weights:
+            if "rotary_emb.inv_freq" in name:
+                continue
+            n = name[len("model."):] if name.startswith("model.") else name
+            if n == "embed_tokens.weight":
+                self.embed_tokens.weight_loader(self.embed_tokens.weight, tensor)
+                if self.cfg.tie_word_embeddings:
+                    self.lm_head.weight_loader(self.lm_head.weight, tensor)
+            elif n == "norm.weight":
+                self.norm_w.data.copy_(tensor)
+            elif n == "lm_head.weight":
+                saw_lm_head = True
+                self.lm_head.weight_loader(self.lm_head.weight, tensor)
+            elif n.startswith("layers."):
+                _, idx, rest = n.split(".", 2)
+                if int(idx) >= len(self.layers):
+                    continue
+                self._load_layer_weight(self.layers[int(idx)], rest, tensor)
+            else:
+                continue
+            loaded.add(name)
+        return loaded
+
+    def _load_layer_weight(self, layer: DecoderLayer, rest: str, t: torch.Tensor) -> None:
+        if rest == "input_layernorm.weight":
+            layer.input_norm_w.data.copy_(t)
+            return
+        if rest == "post_attention_layernorm.weight":
+            layer.post_norm_w.data.copy_(t)
+            return
+        if rest.startswith("block_sparse_moe."):
+            sub = rest[len("block_sparse_moe."):]
+            if sub == "gate.weight":
+                layer.moe.gate.data.copy_(t)
+            else:                                   # experts.{e}.w{1,2,3}.weight
+                _, e, which, _ = sub.split(".")
+                layer.moe.load_expert_weight(int(e), which, t)
+            return
+        rest = rest.replace("self_attn.", "").replace("mlp.", "")
+        kind = "bias" if rest.endswith(".bias") else "weight"
+        stem = "." + rest[: -len(kind) - 1]
+        for hf, ours, shard in self.STACKED:
+            if stem == hf:
+                mod = getattr(layer, ours[1:])
+                mod.weight_loader(getattr(mod, kind), t, shard)
+                return
+        mod = getattr(layer, stem[1:])
+        mod.weight_loader(getattr(mod, kind), t)

@@ -1,0 +1,72 @@
+"""Weight loading: HuggingFace safetensors checkpoints (sharded, with or without an index file),
+``.bin``/``.pt`` state dicts, and random initialisation for performance runs.
+
+Counterpart of vllm/model_executor/model_loader/loader.py:330-500. Tensors are streamed file by file
+and narrowed to this rank's shard by each parameter's ``weight_loader`` before they reach the GPU, so
+peak host memory is one checkpoint shard.
+"""
+from __future__ import annotations
+
+import glob
+import json
+import os
+from typing import Iterator
+
+import torch
+
+from ..config import EngineConfig
+from ..utils.logging import init_logger
+
+logger = init_logger(__name__)
+
+
+def iter_checkpoint(path: str) -> Iterator[tuple[str, torch.Tensor]]:
+    st_files = sorted(glob.glob(os.path.join(path, "*.safetensors")))
+    index = os.path.join(path, "model.safetensors.index.json")
+    if os.path.exists(index):
+        with open(index) as f:
+            wanted = set(json.load(f)["weight_map"].values())
+        st_files = [f for f in st_files if os.path.basename(f) in wanted]
+    if st_files:
+        from safetensors import safe_open
+        for fname in st_files:
+            with safe_open(fname, framework="pt", device="cpu") as f:
+                for key in f.keys():
+                    yield key, f.get_tensor(key)
+        return
+    pt_files = sorted(glob.glob(os.path.join(path, "*.bin")) + glob.glob(os.path.join(path, "*.pt")))
+    if not pt_files:
+        raise FileNotFoundError(f"no *.safetensors, *.bin or *.pt weights under {path}")
+    for fname in pt_files:
+        state = torch.load(fname, map_location="cpu", weights_only=True)
+        yield from state.items()
+        del state
+
+
+def load_model_weights(model, config: EngineConfig) -> None:
+    fmt = config.load_format
+    if fmt == "dummy" or (fmt == "auto" and not config.model.path):
+        model.init_dummy_weights(config.seed)
+        return
+    if not config.model.path:
+        raise ValueError(f"load_format={fmt!r} needs a checkpoint directory")
+    loaded = model.load_weights(iter_checkpoint(config.model.path))
+    logger.info("loaded %d tensors from %s", len(loaded), config.model.path)
+
+
+def save_hf_checkpoint(state: dict[str, torch.Tensor], hf_config: dict, path: str, shards: int = 1) -> None:
+    """Write tensors in HuggingFace layout (used by tests and by the sharded-state export)."""
+    from safetensors.torch import save_file
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(hf_config, f)
+    names = sorted(state)
+    per = (len(names) + shards - 1) // shards
+    weight_map = {}
+    for s in range(shards):
+        part = {n: state[n].contiguous() for n in names[s * per:(s + 1) * per]}
+        fname = f"model-{s + 1:05d}-of-{shards:05d}.safetensors"
+        save_file(part, os.path.join(path, fname))
+        weight_map.update({n: fname for n in part})
+    with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {}, "weight_map": weight_map}, f)

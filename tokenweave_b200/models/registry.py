@@ -1,0 +1,25 @@
+"""Architecture name -> model class, and model construction + weight loading."""
+from __future__ import annotations
+
+import torch
+
+from ..config import EngineConfig, ModelConfig
+
+
+def get_model_class(architecture: str):
+    from .llama import LlamaForCausalLM
+    from .mixtral import MixtralForCausalLM
+    from .qwen2 import Qwen2ForCausalLM
+    table = {"llama": LlamaForCausalLM, "qwen2": Qwen2ForCausalLM, "mixtral": MixtralForCausalLM}
+    if architecture not in table:
+        raise ValueError(f"unsupported architecture {architecture!r} (supported: {sorted(table)})")
+    return table[architecture]
+
+
+def build_model(config: EngineConfig, device: torch.device, embedding_parallel: bool = False):
+    """Instantiate on ``device`` and fill the weights (checkpoint or random init)."""
+    from .loader import load_model_weights
+    cls = get_model_class(config.model.architecture)
+    model = cls(config.model, device=device, embedding_parallel=embedding_parallel)
+    load_model_weights(model, config)
+    return model

@@ -87,8 +87,18 @@ class OptionalSymbols:
     """Entry points that newer builds of the library export; bound when present."""
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of launcher calls made so far by this process (each is at least one kernel launch)."""
+    return _launches
+
+
 def call(name: str, *args) -> None:
+    global _launches
     lib = load()
+    _launches += 1
     rc = getattr(lib, name)(*args)
     if rc != 0:
         msg = lib.tw_last_error()

@@ -1,0 +1,38 @@
+"""Result types returned by ``LLM.generate`` (counterpart of vllm/outputs.py)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+
+@dataclass
+class CompletionOutput:
+    index: int
+    text: str
+    token_ids: list[int]
+    cumulative_logprob: Optional[float] = None
+    logprobs: Optional[list[dict[int, float]]] = None
+    finish_reason: Optional[str] = None   # "stop" | "length" | "abort"
+    stop_reason: Optional[object] = None
+
+    @property
+    def finished(self) -> bool:
+        return self.finish_reason is not None
+
+
+@dataclass
+class RequestMetrics:
+    arrival_time: float = 0.0
+    first_scheduled_time: Optional[float] = None
+    first_token_time: Optional[float] = None
+    finished_time: Optional[float] = None
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt: Optional[str]
+    prompt_token_ids: list[int]
+    outputs: list[CompletionOutput]
+    finished: bool
+    metrics: RequestMetrics = field(default_factory=RequestMetrics)

@@ -1,0 +1,131 @@
+"""Tensor-parallel communicator: the fused reduce-scatter + residual-add + RMSNorm + all-gather and
+the stand-alone collectives, over three transports.
+
+* in-kernel NVLS multimem or peer loads/stores on a symmetric buffer (``csrc/comm_fused.cu``),
+* NCCL through ``torch.distributed`` (the baseline the reference calls "ring"),
+* gloo on CPU, where the fused op is emulated as all-reduce followed by add+RMSNorm (used by tests and
+  by the fp32 correctness configuration).
+
+Reference call sites: ``fused_allreduce_layernorm`` (vllm/model_executor/models/tokenweave_utils.py:24-92),
+``multimem_all_reduce / reduce_scatter / all_gather`` (vllm/distributed/triton_comm/triton_comm.py:240-386),
+``pytorch_all_reduce`` (vllm/distributed/communication_op.py:15-20).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import _native
+from .state import TPState, get_tp
+from .symm_mem import SymmetricBuffer
+
+# signal-pad slot ranges: independent call sites never share barrier slots
+CHANNEL_FUSED = 0
+CHANNEL_COLLECTIVE = 0
+OP_ALL_REDUCE, OP_REDUCE_SCATTER, OP_ALL_GATHER = 0, 1, 2
+
+
+class TPCommunicator:
+    def __init__(self, buf: Optional[SymmetricBuffer], tp: Optional[TPState] = None, wait_budget_ms: int = 2000,
+                 transport: str = "auto"):
+        self.tp = tp or get_tp()
+        self.buf = buf
+        self.budget_ns = int(wait_budget_ms) * 1_000_000
+        self.in_kernel = (buf is not None and buf.provider != "local" and self.tp.world_size > 1)
+        self.use_mc = self.in_kernel and buf.has_multicast and transport in ("auto", "multimem")
+        if transport == "multimem" and self.in_kernel and not buf.has_multicast:
+            raise RuntimeError("multimem transport requested but the symmetric buffer has no multicast mapping")
+
+    @property
+    def world(self) -> int:
+        return self.tp.world_size
+
+    def _mc(self) -> Optional[int]:
+        return self.buf.multicast_ptr if self.use_mc else None
+
+    # ---- the product op -----------------------------------------------------------------
+    def fused_allreduce_add_rmsnorm_(self, x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
+                                     eps: float, max_ctas: int = 16, mode: int = 0, rows_in_flight: int = 0) -> None:
+        """``x`` ([T, H] rows of the symmetric buffer holding this rank's partial sums) becomes
+        ``rmsnorm(sum_ranks(x) + residual) * weight`` on every rank; ``residual`` ([T, H], same row
+        indexing as ``x``) is updated on this rank's shard of the rows only."""
+        T, H = x.shape
+        if self.world == 1:
+            ops.add_rmsnorm_(x, residual, weight, eps, max_ctas=0)
+            return
+        if T % self.world != 0:
+            raise ValueError(f"token count {T} must be a multiple of the TP size {self.world}")
+        if not self.in_kernel:
+            dist.all_reduce(x, group=self.tp.group)
+            ops.add_rmsnorm_(x, residual, weight, eps)
+            return
+        rpr = T // self.world
+        shard_res = residual[self.tp.rank * rpr:(self.tp.rank + 1) * rpr]
+        _native.call("tw_fused_rs_norm_ag", self._mc(), self.buf.peer_ptrs_dev, self.buf.signal_pads_dev,
+                     self.tp.rank, self.world, CHANNEL_FUSED, self.budget_ns,
+                     ops.status_word(x.device).data_ptr(), self.buf.byte_offset(x), shard_res.data_ptr(),
+                     shard_res.stride(0), weight.data_ptr(), T, H, eps, max_ctas, mode, rows_in_flight,
+                     torch.cuda.current_stream().cuda_stream)
+
+    # ---- stand-alone collectives on rows of the symmetric buffer ---------------------------
+    def _collective(self, x: torch.Tensor, op: int, max_ctas: int) -> None:
+        _native.call("tw_collective", self._mc(), self.buf.peer_ptrs_dev, self.buf.signal_pads_dev, self.tp.rank,
+                     self.world, CHANNEL_COLLECTIVE, self.budget_ns, ops.status_word(x.device).data_ptr(),
+                     self.buf.byte_offset(x), x.numel() * x.element_size(), op, max_ctas,
+                     torch.cuda.current_stream().cuda_stream)
+
+    def all_reduce_(self, x: torch.Tensor, max_ctas: int = 16) -> None:
+        if self.world == 1:
+            return
+        if self.in_kernel:
+            self._collective(x, OP_ALL_REDUCE, max_ctas)
+        else:
+            dist.all_reduce(x, group=self.tp.group)
+
+    def reduce_scatter_(self, x: torch.Tensor, max_ctas: int = 16) -> None:
+        """In place: this rank's 1/world slice of ``x`` (by flat offset) becomes the reduced slice."""
+        if self.world == 1:
+            return
+        if self.in_kernel:
+            self._collective(x, OP_REDUCE_SCATTER, max_ctas)
+        else:
+            flat = x.view(-1)
+            n = flat.numel() // self.world
+            out = torch.empty(n, dtype=x.dtype, device=x.device)
+            dist.reduce_scatter_tensor(out, flat, group=self.tp.group)
+            flat[self.tp.rank * n:(self.tp.rank + 1) * n] = out
+
+    def all_gather_(self, x: torch.Tensor, max_ctas: int = 16) -> None:
+        """In place: every rank's slice of ``x`` is broadcast to all ranks."""
+        if self.world == 1:
+            return
+        if self.in_kernel:
+            self._collective(x, OP_ALL_GATHER, max_ctas)
+        else:
+            flat = x.view(-1)
+            n = flat.numel() // self.world
+            mine = flat[self.tp.rank * n:(self.tp.rank + 1) * n].clone()
+            dist.all_gather_into_tensor(flat, mine, group=self.tp.group)
+
+    def oneshot_all_reduce(self, x: torch.Tensor, out: torch.Tensor, max_ctas: int = 36) -> torch.Tensor:
+        """Small-message peer all-reduce: every rank pulls the whole message from every peer."""
+        if self.world == 1:
+            out.copy_(x)
+            return out
+        if not self.in_kernel:
+            out.copy_(x)
+            dist.all_reduce(out, group=self.tp.group)
+            return out
+        _native.call("tw_oneshot_allreduce", self.buf.peer_ptrs_dev, self.buf.signal_pads_dev, self.tp.rank,
+                     self.world, CHANNEL_COLLECTIVE, self.budget_ns, ops.status_word(x.device).data_ptr(),
+                     self.buf.byte_offset(x), x.numel() * x.element_size(), out.data_ptr(), max_ctas,
+                     torch.cuda.current_stream().cuda_stream)
+        return out
+
+    # ---- NCCL baseline ------------------------------------------------------------------
+    def nccl_all_reduce_(self, x: torch.Tensor) -> None:
+        if self.world > 1:
+            dist.all_reduce(x, group=self.tp.group)

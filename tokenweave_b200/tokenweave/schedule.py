@@ -1,0 +1,132 @@
+"""Layer schedules: how the attention / MLP blocks of a decoder stack and the collectives between
+them are ordered on the GPU.
+
+* ``run_fuse_only``  one token set; every all-reduce is the fused RS+add+RMSNorm+AG kernel
+                     (reference: tokenweave_with_fuse_only, tokenweave_utils.py:95-172).
+* ``run_overlap``    two token subsets; the compute stream runs one subset's attention / MLP while the
+                     communication stream runs the other subset's fused kernel on a few SMs
+                     (reference: tokenweave_overlap, tokenweave_utils.py:175-340).
+* ``run_baseline``   all-reduce (NCCL or in-kernel multimem) followed by a separate add+RMSNorm kernel,
+                     or no communication at all (the artifact's baseline_ring / baseline_multimem /
+                     no_ar variants, artifact/llama_src_files/pl_*.py).
+
+On entry the rows of ``hidden`` hold ``rmsnorm(x) * input_layernorm[0]`` and ``residual`` holds ``x``
+(or ``hidden`` holds vocab-parallel partial embeddings and ``residual`` zeros, with ``first_pending``
+set): on exit ``hidden`` holds the final-norm output.
+
+Unlike the reference, compute kernels are told how many SMs to use (``sm_count - comm_ctas``): their
+persistent grids leave the communication CTAs a guaranteed place to run instead of relying on stream
+priority alone.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from .. import envs, ops
+from ..parallel.comm import TPCommunicator
+from .config import SplitPlan
+
+
+def _nvtx(name: str):
+    if envs.TW_NVTX and torch.cuda.is_available():
+        return torch.cuda.nvtx.range(name)
+    import contextlib
+    return contextlib.nullcontext()
+
+
+def run_fuse_only(layers: Sequence, final_norm_w: torch.Tensor, hidden: torch.Tensor, residual: torch.Tensor,
+                  meta, plan: SplitPlan, comm: TPCommunicator, rt, eps: float, first_pending: bool = False) -> None:
+    T, Tp = plan.num_tokens, plan.padded_tokens
+    h, r = hidden[:Tp], residual[:Tp]
+    ctas = plan.attention_ctas
+    if first_pending:
+        comm.fused_allreduce_add_rmsnorm_(h, r, layers[0].input_norm_w, eps, ctas)
+    for i, layer in enumerate(layers):
+        next_w = layers[i + 1].input_norm_w if i + 1 < len(layers) else final_norm_w
+        layer.attn_block(h, T, meta, rt, 0)
+        comm.fused_allreduce_add_rmsnorm_(h, r, layer.post_norm_w, eps, ctas)
+        layer.mlp_block(h, T, rt, 0)
+        comm.fused_allreduce_add_rmsnorm_(h, r, next_w, eps, ctas)
+
+
+def run_baseline(layers: Sequence, final_norm_w: torch.Tensor, hidden: torch.Tensor, residual: torch.Tensor,
+                 meta, plan: SplitPlan, comm: TPCommunicator, rt, eps: float, mode: str,
+                 first_pending: bool = False) -> None:
+    T, Tp = plan.num_tokens, plan.padded_tokens
+    h, r = hidden[:Tp], residual[:Tp]
+
+    def reduce_norm(w):
+        if mode == "baseline_nccl":
+            comm.nccl_all_reduce_(hidden[:T])
+        elif mode == "baseline_multimem":
+            comm.all_reduce_(h, plan.attention_ctas)
+        ops.add_rmsnorm_(h, r, w, eps)
+
+    if first_pending:
+        reduce_norm(layers[0].input_norm_w)
+    for i, layer in enumerate(layers):
+        next_w = layers[i + 1].input_norm_w if i + 1 < len(layers) else final_norm_w
+        layer.attn_block(h, T, meta, rt, 0)
+        reduce_norm(layer.post_norm_w)
+        layer.mlp_block(h, T, rt, 0)
+        reduce_norm(next_w)
+
+
+def run_overlap(layers: Sequence, final_norm_w: torch.Tensor, hidden: torch.Tensor, residual: torch.Tensor,
+                meta0, meta1, plan: SplitPlan, comm: TPCommunicator, rt, eps: float,
+                first_pending: bool = False) -> None:
+    """Steady state of layer l (C = compute stream, X = communication stream):
+
+        C: attention(S0)   | X: fused(S1, input_norm[l])        (skipped for l = 0 unless first_pending)
+        C: attention(S1)   | X: fused(S0, post_attn_norm[l])
+        C: mlp(S0)         | X: fused(S1, post_attn_norm[l])
+        C: mlp(S1)         | X: fused(S0, input_norm[l+1] or final norm)
+        after the last layer, on C alone: fused(S1, final norm)
+
+    Split 1's attention sees split 0's keys because both run on C and split 0 writes the cache first.
+    """
+    split, Tp = plan.split, plan.padded_tokens
+    s0, s1 = hidden[:split], hidden[split:Tp]
+    r0, r1 = residual[:split], residual[split:Tp]
+    n0, n1 = plan.tokens_0, plan.tokens_1
+    on_gpu = hidden.is_cuda
+    C = torch.cuda.current_stream() if on_gpu else None
+    X = rt.comm_stream if on_gpu else None
+    sms = rt.sm_count
+    a_ctas, m_ctas = plan.attention_ctas, plan.mlp_ctas
+    a_sms = max(1, sms - a_ctas) if on_gpu and comm.world > 1 else 0
+    m_sms = max(1, sms - m_ctas) if on_gpu and comm.world > 1 else 0
+
+    def comm_async(x, r, w, ctas):
+        if on_gpu:
+            X.wait_stream(C)
+            with torch.cuda.stream(X):
+                comm.fused_allreduce_add_rmsnorm_(x, r, w, eps, ctas)
+        else:
+            comm.fused_allreduce_add_rmsnorm_(x, r, w, eps, ctas)
+
+    def join():
+        if on_gpu:
+            C.wait_stream(X)
+
+    if first_pending:
+        comm.fused_allreduce_add_rmsnorm_(s0, r0, layers[0].input_norm_w, eps, a_ctas)
+    for i, layer in enumerate(layers):
+        next_w = layers[i + 1].input_norm_w if i + 1 < len(layers) else final_norm_w
+        with _nvtx(f"layer{i}"):
+            if i > 0 or first_pending:
+                comm_async(s1, r1, layer.input_norm_w, a_ctas)
+            layer.attn_block(s0, n0, meta0, rt, a_sms)
+            join()
+            comm_async(s0, r0, layer.post_norm_w, a_ctas)
+            layer.attn_block(s1, n1, meta1, rt, a_sms)
+            join()
+            comm_async(s1, r1, layer.post_norm_w, m_ctas)
+            layer.mlp_block(s0, n0, rt, m_sms)
+            join()
+            comm_async(s0, r0, next_w, m_ctas)
+            layer.mlp_block(s1, n1, rt, m_sms)
+            join()
+    comm.fused_allreduce_add_rmsnorm_(s1, r1, final_norm_w, eps, plan.tail_ctas)

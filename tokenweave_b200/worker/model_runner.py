@@ -1,0 +1,217 @@
+"""Model runner: turns the scheduler's decision for one step into device inputs, runs the model and
+samples.
+
+Counterpart of vllm/v1/worker/gpu_model_runner.py:532-746 (input preparation incl. the TokenWeave split
+metadata) and :1117-1380 (execute_model). Request state (token ids, block ids, sampling parameters,
+generators) is cached on the worker so a running request costs a few integers per step on the wire.
+All integer inputs of a step are packed into pinned staging memory and reach the device in two
+``non_blocking`` copies (token ids; attention metadata).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..config import EngineConfig
+from ..layers.attention import AttentionMetadata, build_attention_metadata
+from ..layers.sampler import Sampler
+from ..models.decoder import DecoderModel, StepInput
+from ..parallel.state import get_tp
+from ..sampling_params import SamplingParams
+from ..tokenweave.config import TokenWeavePlanner
+from ..utils.logging import init_logger
+from .split_metadata import split_batch
+
+logger = init_logger(__name__)
+
+
+@dataclass
+class NewRequestData:
+    req_id: str
+    token_ids: list[int]             # prompt (+ outputs generated before a preemption)
+    num_prompt_tokens: int
+    sampling_params: SamplingParams
+    block_ids: list[int]
+
+
+@dataclass
+class StepData:
+    """What the scheduler sends to the workers for one step (picklable)."""
+    step_id: int
+    new_requests: list[NewRequestData] = field(default_factory=list)
+    # (req_id, num_computed_tokens, num_new_tokens, block ids appended since the last step)
+    scheduled: list[tuple[str, int, int, list[int]]] = field(default_factory=list)
+    finished_req_ids: list[str] = field(default_factory=list)
+    preempted_req_ids: list[str] = field(default_factory=list)
+    total_num_tokens: int = 0
+
+
+@dataclass
+class StepResult:
+    req_ids: list[str]
+    sampled_token_ids: list[Optional[int]]
+    logprobs: Optional[list] = None
+    device_time_ms: Optional[float] = None
+
+
+@dataclass
+class _CachedRequest:
+    token_ids: list[int]
+    num_prompt_tokens: int
+    sampling_params: SamplingParams
+    block_ids: list[int]
+    generator: Optional[torch.Generator] = None
+
+
+class ModelRunner:
+    def __init__(self, config: EngineConfig, device: torch.device):
+        self.config = config
+        self.device = device
+        self.tp = get_tp()
+        self.model: Optional[DecoderModel] = None
+        self.requests: dict[str, _CachedRequest] = {}
+        self.sampler = Sampler()
+        self.block_size = config.cache.block_size
+        self.max_tokens = config.scheduler.max_num_batched_tokens
+        tw = config.tokenweave
+        self.planner = TokenWeavePlanner(
+            config.model.architecture, self.tp.world_size, tw.mode, tw.config_path, tw.overlap_threshold,
+            tw.fuse_only_ctas, tw.split_offset, tw.attention_ctas, tw.mlp_ctas,
+            force_overlap=getattr(tw, "force_overlap", False))
+        pin = device.type == "cuda"
+        self._ids_host = torch.zeros(self.max_tokens, dtype=torch.int32, pin_memory=pin)
+        self._ids_dev = torch.zeros(self.max_tokens, dtype=torch.int32, device=device)
+        self._meta_host = [torch.zeros(1 << 20, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self.h2d_bytes_last_step = 0
+        self.d2h_bytes_last_step = 0
+        self.timing_events = None
+        self._h2d_done = torch.cuda.Event() if pin else None   # guards reuse of the pinned staging buffers
+
+    # ---- set-up -----------------------------------------------------------------------------
+    def load_model(self, embedding_parallel: bool = False) -> None:
+        from ..models.registry import build_model
+        t0 = time.monotonic()
+        self.model = build_model(self.config, self.device, embedding_parallel)
+        self.model.setup_runtime(self.max_tokens, self.config.tokenweave)
+        logger.info("model %s ready on %s in %.1fs (%.2f GB of weights on this rank)", self.config.model.name,
+                    self.device, time.monotonic() - t0,
+                    sum(p.numel() * p.element_size() for p in self.model.parameters()) / 1e9)
+
+    def init_kv_cache(self, num_blocks: int) -> None:
+        self.model.init_kv_cache(num_blocks, self.block_size)
+
+    # ---- one step ---------------------------------------------------------------------------
+    def _update_states(self, step: StepData) -> None:
+        for rid in step.finished_req_ids:
+            self.requests.pop(rid, None)
+        for rid in step.preempted_req_ids:
+            self.requests.pop(rid, None)
+        for nr in step.new_requests:
+            gen = None
+            sp = nr.sampling_params
+            if sp.seed is not None:
+                gen = torch.Generator(device=self.device)
+                gen.manual_seed(sp.seed)
+            self.requests[nr.req_id] = _CachedRequest(list(nr.token_ids), nr.num_prompt_tokens, sp, list(nr.block_ids), gen)
+
+    def _build_metadata(self, entries, tokens_base: int, positions: np.ndarray, slots: np.ndarray,
+                        tables: dict[int, list[int]], which: int) -> AttentionMetadata:
+        """entries: list of (seq_index, q_len, kv_len) laid out back to back starting at row tokens_base."""
+        q_lens = [e[1] for e in entries]
+        kv_lens = [e[2] for e in entries]
+        n = sum(q_lens)
+        max_blocks = max((len(tables[e[0]]) for e in entries), default=1)
+        bt = np.zeros((len(entries), max(1, max_blocks)), dtype=np.int32)
+        for i, e in enumerate(entries):
+            t = tables[e[0]]
+            bt[i, : len(t)] = t
+        return build_attention_metadata(q_lens, kv_lens, positions[tokens_base:tokens_base + n],
+                                        slots[tokens_base:tokens_base + n], bt, self.device, self._meta_host[which])
+
+    @torch.inference_mode()
+    def execute_model(self, step: StepData) -> StepResult:
+        self._update_states(step)
+        if not step.scheduled:
+            return StepResult([], [])
+        T = step.total_num_tokens
+        assert T <= self.max_tokens, f"step of {T} tokens exceeds max_num_batched_tokens={self.max_tokens}"
+        if self._h2d_done is not None:
+            self._h2d_done.synchronize()      # the previous step's copies have left the staging buffers
+        ids = self._ids_host.numpy()
+        positions = np.empty(T, dtype=np.int32)
+        slots = np.empty(T, dtype=np.int32)
+        q_lens, kv_lens, tables = [], [], {}
+        logits_rows, sample_reqs = [], []
+        row = 0
+        bs = self.block_size
+        for b, (rid, computed, n_new, new_blocks) in enumerate(step.scheduled):
+            req = self.requests[rid]
+            req.block_ids.extend(new_blocks)
+            ids[row:row + n_new] = req.token_ids[computed:computed + n_new]
+            pos = np.arange(computed, computed + n_new, dtype=np.int32)
+            positions[row:row + n_new] = pos
+            blocks = np.asarray(req.block_ids, dtype=np.int32)
+            slots[row:row + n_new] = blocks[pos // bs] * bs + pos % bs
+            q_lens.append(n_new)
+            kv_lens.append(computed + n_new)
+            tables[b] = req.block_ids
+            if computed + n_new >= len(req.token_ids):
+                logits_rows.append(row + n_new - 1)
+                sample_reqs.append(rid)
+            row += n_new
+
+        plan = self.planner.plan(T)
+        ids_dev = self._ids_dev[:T]
+        ids_dev.copy_(self._ids_host[:T], non_blocking=True)
+        h2d = T * 4
+        if plan.overlap:
+            first, second = split_batch(q_lens, kv_lens, plan.split)
+            meta0 = self._build_metadata(first, 0, positions, slots, tables, 0)
+            meta1 = self._build_metadata(second, plan.split, positions, slots, tables, 1)
+            step_in = StepInput(ids_dev, plan, meta0=meta0, meta1=meta1)
+        else:
+            entries = [(b, q_lens[b], kv_lens[b]) for b in range(len(q_lens))]
+            step_in = StepInput(ids_dev, plan, meta=self._build_metadata(entries, 0, positions, slots, tables, 0))
+        for m in (step_in.meta, step_in.meta0, step_in.meta1):
+            if m is not None:
+                h2d += 4 * (2 * m.num_actual_tokens + 2 * m.num_seqs + 1 + m.block_table.numel() + 2 * m.num_tiles + 3 * m.num_single)
+
+        if self._h2d_done is not None:
+            self._h2d_done.record()
+        ev = None
+        if self.timing_events is not None:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
+        hidden = self.model(step_in)
+        sampled: dict[str, int] = {}
+        lp = None
+        d2h = 0
+        if logits_rows:
+            idx = torch.as_tensor(logits_rows, dtype=torch.long, device=self.device)
+            logits = self.model.compute_logits(hidden.index_select(0, idx))
+            reqs = [self.requests[r] for r in sample_reqs]
+            out = self.sampler(logits, [r.sampling_params for r in reqs], [r.generator for r in reqs],
+                               [r.token_ids[: r.num_prompt_tokens] for r in reqs],
+                               [r.token_ids[r.num_prompt_tokens:] for r in reqs])
+            if ev is not None:
+                ev[1].record()
+            toks = out.token_ids.tolist()            # the device -> host synchronisation point of the step
+            d2h = len(toks) * 4
+            lp = out.logprobs
+            for rid, tok in zip(sample_reqs, toks):
+                sampled[rid] = int(tok)
+                self.requests[rid].token_ids.append(int(tok))
+        elif ev is not None:
+            ev[1].record()
+        if ev is not None:
+            self.timing_events.append(ev)
+        self.h2d_bytes_last_step, self.d2h_bytes_last_step = h2d, d2h
+        req_ids = [s[0] for s in step.scheduled]
+        lp_by_req = dict(zip(sample_reqs, lp)) if lp is not None else None
+        return StepResult(req_ids, [sampled.get(r) for r in req_ids],
+                          [lp_by_req.get(r) for r in req_ids] if lp_by_req is not None else None)

@@ -1,0 +1,105 @@
+"""Worker: one per GPU. Binds the device, joins the process group, loads the model, sizes and allocates
+the KV cache, and executes steps.
+
+Counterpart of vllm/v1/worker/gpu_worker.py:91-252.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from .. import envs, ops
+from ..config import EngineConfig
+from ..parallel import state as pstate
+from ..utils.logging import init_logger
+from .model_runner import ModelRunner, StepData, StepResult
+
+logger = init_logger(__name__)
+
+
+class Worker:
+    def __init__(self, config: EngineConfig, rank: int = 0, local_rank: Optional[int] = None,
+                 init_method: Optional[str] = None):
+        self.config = config
+        self.rank = rank
+        self.local_rank = rank if local_rank is None else local_rank
+        self.init_method = init_method
+        self.runner: Optional[ModelRunner] = None
+        self.profiler = None
+
+    def init_device(self) -> None:
+        world = self.config.parallel.tensor_parallel_size
+        dev_kind = self.config.resolved_device()
+        if world > 1:
+            tp = pstate.init_distributed(self.rank, world, self.local_rank, dev_kind, self.init_method)
+        else:
+            if dev_kind == "cuda":
+                torch.cuda.set_device(self.local_rank)
+                dev = torch.device("cuda", self.local_rank)
+            else:
+                dev = torch.device("cpu")
+            tp = pstate.set_single_process(dev)
+        self.device = tp.device
+        torch.manual_seed(self.config.seed)
+        self.runner = ModelRunner(self.config, self.device)
+
+    def load_model(self) -> None:
+        self.runner.load_model(embedding_parallel=bool(int(os.getenv("TW_EMBEDDING_PARALLEL", "0"))))
+
+    def determine_num_blocks(self) -> int:
+        """KV blocks that fit in what is left of ``gpu_memory_utilization`` after weights and workspaces."""
+        cache = self.config.cache
+        if cache.num_gpu_blocks is not None:
+            return cache.num_gpu_blocks
+        per_block = self.runner.model.kv_cache_bytes_per_block(cache.block_size)
+        if self.device.type != "cuda":
+            want = self.config.scheduler.max_num_batched_tokens * 4 // cache.block_size + 16
+            return max(16, want)
+        torch.cuda.synchronize()
+        free, total = torch.cuda.mem_get_info(self.device)
+        used_by_others = total - free - torch.cuda.memory_reserved(self.device)
+        budget = total * cache.gpu_memory_utilization - torch.cuda.memory_reserved(self.device) - max(0, used_by_others)
+        budget -= 2 << 30     # logits, sampler temporaries, NCCL buffers
+        n = int(budget // per_block)
+        if n < 4:
+            raise RuntimeError(f"not enough GPU memory for the KV cache ({budget / 1e9:.1f} GB left, "
+                               f"{per_block / 1e6:.1f} MB per block)")
+        max_useful = (self.config.scheduler.max_model_len * self.config.scheduler.max_num_seqs) // cache.block_size + 64
+        return min(n, max_useful)
+
+    def init_kv_cache(self, num_blocks: int) -> None:
+        self.runner.init_kv_cache(num_blocks)
+        logger.info("KV cache: %d blocks of %d tokens", num_blocks, self.config.cache.block_size)
+
+    def execute_model(self, step: StepData) -> StepResult:
+        return self.runner.execute_model(step)
+
+    def check_health(self) -> bool:
+        if self.device.type == "cuda":
+            ops.check_status(self.device)
+        return True
+
+    # ---- profiling hooks (LLM.start_profile / stop_profile) ----
+    def profile(self, start: bool) -> None:
+        trace_dir = envs.TW_TORCH_PROFILER_DIR
+        if trace_dir is None:
+            raise RuntimeError("set TW_TORCH_PROFILER_DIR to enable the torch profiler")
+        if start:
+            acts = [torch.profiler.ProfilerActivity.CPU]
+            if self.device.type == "cuda":
+                acts.append(torch.profiler.ProfilerActivity.CUDA)
+            self.profiler = torch.profiler.profile(
+                activities=acts, with_stack=True,
+                on_trace_ready=torch.profiler.tensorboard_trace_handler(trace_dir, use_gzip=True))
+            self.profiler.start()
+        elif self.profiler is not None:
+            self.profiler.stop()
+            self.profiler = None
+
+    def shutdown(self) -> None:
+        self.runner = None
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        pstate.destroy_distributed()
