@@ -195,6 +195,7 @@ class TokenWeaveConfig:
     mlp_ctas: Optional[int] = None
     use_cuda_graphs: bool = False
     wait_budget_ms: int = 2000            # budget of every cross-GPU wait inside a kernel
+    force_overlap: bool = False           # take the split schedule even at TP=1 (tests, ablations)
 
 
 @dataclass
@@ -248,6 +249,10 @@ class EngineArgs:
     tokenweave_threshold: Optional[int] = None
     tokenweave_transport: str = "auto"
     tokenweave_cuda_graphs: bool = False
+    tokenweave_force_overlap: bool = False
+    tokenweave_split_offset: Optional[int] = None
+    tokenweave_attention_ctas: Optional[int] = None
+    tokenweave_mlp_ctas: Optional[int] = None
     fuse_only_ctas: int = 16
 
     def create_engine_config(self) -> EngineConfig:
@@ -269,7 +274,11 @@ class EngineArgs:
                                         overlap_threshold=self.tokenweave_threshold,
                                         transport=self.tokenweave_transport,
                                         use_cuda_graphs=self.tokenweave_cuda_graphs,
-                                        fuse_only_ctas=self.fuse_only_ctas),
+                                        fuse_only_ctas=self.fuse_only_ctas,
+                                        force_overlap=self.tokenweave_force_overlap,
+                                        split_offset=self.tokenweave_split_offset,
+                                        attention_ctas=self.tokenweave_attention_ctas,
+                                        mlp_ctas=self.tokenweave_mlp_ctas),
             load_format=load_format, seed=self.seed, device=self.device, enforce_eager=self.enforce_eager,
             tokenizer=self.tokenizer, skip_tokenizer_init=self.skip_tokenizer_init,
             disable_log_stats=self.disable_log_stats)

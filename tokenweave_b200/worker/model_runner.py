@@ -82,7 +82,7 @@ class ModelRunner:
         self.planner = TokenWeavePlanner(
             config.model.architecture, self.tp.world_size, tw.mode, tw.config_path, tw.overlap_threshold,
             tw.fuse_only_ctas, tw.split_offset, tw.attention_ctas, tw.mlp_ctas,
-            force_overlap=getattr(tw, "force_overlap", False))
+            force_overlap=tw.force_overlap)
         pin = device.type == "cuda"
         self._ids_host = torch.zeros(self.max_tokens, dtype=torch.int32, pin_memory=pin)
         self._ids_dev = torch.zeros(self.max_tokens, dtype=torch.int32, device=device)
@@ -90,6 +90,8 @@ class ModelRunner:
         self.h2d_bytes_last_step = 0
         self.d2h_bytes_last_step = 0
         self.timing_events = None
+        self.capture_logits = False          # tests: keep the fp32 logits of every step
+        self.captured_logits: list = []
         self._h2d_done = torch.cuda.Event() if pin else None   # guards reuse of the pinned staging buffers
 
     # ---- set-up -----------------------------------------------------------------------------
@@ -194,6 +196,8 @@ class ModelRunner:
         if logits_rows:
             idx = torch.as_tensor(logits_rows, dtype=torch.long, device=self.device)
             logits = self.model.compute_logits(hidden.index_select(0, idx))
+            if self.capture_logits:
+                self.captured_logits.append((list(sample_reqs), logits.detach().float().cpu().clone()))
             reqs = [self.requests[r] for r in sample_reqs]
             out = self.sampler(logits, [r.sampling_params for r in reqs], [r.generator for r in reqs],
                                [r.token_ids[: r.num_prompt_tokens] for r in reqs],
