@@ -1,0 +1,110 @@
+"""End-to-end model correctness on CPU in fp32: the engine (paged cache, chunked prefill, token-split
+schedule, HF checkpoint loading) against a naive dense forward of the same weights."""
+import os
+
+import pytest
+import torch
+
+from tokenweave_b200 import LLM, SamplingParams
+from tokenweave_b200.config import MODEL_PRESETS, ModelConfig
+from tokenweave_b200.models.loader import save_hf_checkpoint
+
+from tw_testing import hf_config_dict, make_hf_state, naive_logits
+
+
+def _engine(path_or_name, **kw):
+    args = dict(dtype="float32", device="cpu", skip_tokenizer_init=True, block_size=16, max_num_batched_tokens=512)
+    args.update(kw)
+    return LLM(path_or_name, **args)
+
+
+def _runner(llm):
+    return llm.llm_engine.core.executor.worker.runner
+
+
+def _prompts(vocab, lens, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+
+
+@pytest.mark.parametrize("arch", ["tiny-llama", "tiny-qwen2", "tiny-mixtral"])
+def test_engine_matches_naive_forward(tmp_path, arch):
+    preset = dict(MODEL_PRESETS[arch])
+    if arch != "tiny-llama":
+        preset.update(hidden_size=128, head_dim=32, intermediate_size=96, vocab_size=300, max_model_len=512)
+    cfg = ModelConfig(name=arch, **preset)
+    st = make_hf_state(cfg, seed=1)
+    save_hf_checkpoint(st, hf_config_dict(cfg), str(tmp_path), shards=2)
+    llm = _engine(str(tmp_path), max_num_batched_tokens=64)      # forces chunked prefill of the long prompt
+    r = _runner(llm)
+    r.capture_logits = True
+    prompts = _prompts(cfg.vocab_size, [100, 7, 33])
+    outs = llm.generate(prompts, SamplingParams(temperature=0, max_tokens=3))
+    # first logits of every request = logits at the last prompt position of the naive forward
+    first = {}
+    for reqs, logits in r.captured_logits:
+        for rid, row in zip(reqs, logits):
+            first.setdefault(rid, row)
+    for i, p in enumerate(prompts):
+        ref = naive_logits(cfg, st, p)[-1]
+        torch.testing.assert_close(first[str(i)], ref, atol=2e-4, rtol=2e-4)
+    # greedy continuation equals the naive model's
+    for i, p in enumerate(prompts):
+        seq = list(p)
+        for _ in range(3):
+            seq.append(int(naive_logits(cfg, st, seq)[-1].argmax()))
+        assert outs[i].outputs[0].token_ids == seq[len(p):]
+
+
+def test_split_path_equals_unsplit_path():
+    """Tiny Llama-style decoder, fp32, 4 prompts of 64 tokens, greedy 16 tokens: the two-subset schedule
+    must reproduce the unsplit path."""
+    prompts = _prompts(1024, [64] * 4, seed=0)
+    sp = SamplingParams(temperature=0, max_tokens=16)
+    results = {}
+    for name, kw in (("unsplit", dict(tokenweave_mode="fuse_only")),
+                     ("split", dict(tokenweave_mode="overlap", tokenweave_force_overlap=True, tokenweave_threshold=128)),
+                     ("split_off", dict(tokenweave_mode="overlap", tokenweave_force_overlap=True, tokenweave_threshold=128,
+                                        tokenweave_split_offset=32))):
+        llm = _engine("tiny-llama", seed=0, **kw)
+        r = _runner(llm)
+        r.capture_logits = True
+        outs = llm.generate(prompts, sp)
+        plan = r.planner.plan(256)
+        assert plan.overlap == (name != "unsplit")
+        if name == "split_off":
+            assert plan.split == 160        # the cut falls inside the third prompt: a straddling request
+        results[name] = ([o.outputs[0].token_ids for o in outs], torch.cat([l for _, l in r.captured_logits]))
+        llm.shutdown()
+    for name in ("split", "split_off"):
+        assert results[name][0] == results["unsplit"][0]
+        torch.testing.assert_close(results[name][1], results["unsplit"][1], atol=1e-5, rtol=1e-5)
+
+
+def test_sampling_seeded_and_n():
+    llm = _engine("tiny-llama")
+    p = _prompts(1024, [20])
+    sp = SamplingParams(temperature=0.8, top_p=0.9, top_k=50, max_tokens=8, seed=7, n=2, logprobs=2)
+    a = llm.generate(p, sp)[0]
+    b = llm.generate(p, sp)[0]
+    assert [c.token_ids for c in a.outputs] == [c.token_ids for c in b.outputs]
+    assert len(a.outputs) == 2 and a.outputs[0].token_ids != a.outputs[1].token_ids
+    assert len(a.outputs[0].logprobs) == 8 and a.outputs[0].cumulative_logprob < 0
+
+
+def test_text_prompt_and_stop_string():
+    llm = LLM("tiny-llama", dtype="float32", device="cpu", tokenizer="byte", block_size=16, max_num_batched_tokens=256)
+    out = llm.generate("hello world", SamplingParams(temperature=0, max_tokens=12))[0]
+    assert out.prompt == "hello world" and len(out.outputs[0].token_ids) == 12
+    assert isinstance(out.outputs[0].text, str)
+
+
+def test_preemption_recompute_keeps_outputs():
+    """With a KV pool too small for both requests one is preempted and recomputed; results must not change."""
+    prompts = _prompts(1024, [60, 50], seed=3)
+    sp = SamplingParams(temperature=0, max_tokens=24)
+    big = _engine("tiny-llama", num_gpu_blocks_override=64)
+    expect = [o.outputs[0].token_ids for o in big.generate(prompts, sp)]
+    small = _engine("tiny-llama", num_gpu_blocks_override=10)     # 9 usable blocks = 144 tokens < 60+50+48
+    got = [o.outputs[0].token_ids for o in small.generate(prompts, sp)]
+    assert got == expect
