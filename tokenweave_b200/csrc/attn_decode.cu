@@ -237,3 +237,98 @@ extern "C" int tw_attn_decode(const void* q, long long ldq, const void* k_cache,
   }
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant (see tw_noalloc.h): the split-KV partial results go to a fixed array in
+// the library's device data segment instead of a caller-provided workspace.
+#include <mutex>
+
+#include "tw_noalloc.h"
+
+namespace tw {
+
+constexpr size_t NOALLOC_SCRATCH_FLOATS = TW_NOALLOC_SCRATCH_BYTES / sizeof(float);
+constexpr int NOALLOC_MAX_DEVICES = 64;
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_decode_scratch[NOALLOC_SCRATCH_FLOATS];
+
+static float* g_scratch_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+static std::mutex g_scratch_mutex;
+
+// Device address of the scratch array on the current device; looked up once per device.
+static int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+    set_last_error("attn_decode_noalloc: cannot identify the current device (%s)", cudaGetErrorString(e));
+    return 1;
+  }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_last_error("attn_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
+                     cudaGetErrorString(e));
+      return 1;
+    }
+    g_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_scratch_addr[dev];
+  return 0;
+}
+
+}  // namespace tw
+
+extern "C" int tw_attn_decode_noalloc(const void* q, long long ldq, const void* k_cache, const void* v_cache,
+                                      int page, void* out, long long ldo, const int* tok_row,
+                                      const int* tok_seq, const int* tok_kvlen, int n_tok,
+                                      const int* block_table, int max_blocks, int hq, int hkv, int D,
+                                      float scale, int splits, cudaStream_t stream) {
+  if (n_tok <= 0) return 0;
+  if ((D != 128 && D != 64) || hkv <= 0 || hq % hkv != 0 || hq / hkv > DEC_GMAX) {
+    set_last_error("attn_decode_noalloc: unsupported shape (D=%d, hq=%d, hkv=%d)", D, hq, hkv);
+    return 1;
+  }
+  if (splits < 1) splits = 1;
+  const unsigned long long partials = static_cast<unsigned long long>(n_tok) * hq * splits;
+  const unsigned long long need = partials * (static_cast<unsigned long long>(D) + 2ull);
+  if (need > NOALLOC_SCRATCH_FLOATS) {
+    set_last_error("attn_decode_noalloc: %llu tokens x heads x splits need %llu bytes of scratch, the built-in "
+                   "array holds %u; lower `splits` or the batch, or use tw_attn_decode with your own workspace",
+                   partials, need * 4ull, TW_NOALLOC_SCRATCH_BYTES);
+    return 1;
+  }
+  float* scratch = nullptr;
+  if (noalloc_scratch(&scratch) != 0) return 1;
+  float* part_o = scratch;
+  float* part_ml = scratch + partials * D;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(n_tok, hkv, splits);
+  auto qb = reinterpret_cast<const __nv_bfloat16*>(q);
+  auto kb = reinterpret_cast<const __nv_bfloat16*>(k_cache);
+  auto vb = reinterpret_cast<const __nv_bfloat16*>(v_cache);
+  auto ob = reinterpret_cast<__nv_bfloat16*>(out);
+  if (D == 128) {
+    attn_decode_kernel<128><<<grid, DEC_WARPS * 32, 0, stream>>>(qb, ldq, kb, vb, tok_row, tok_seq, tok_kvlen,
+                                                                 block_table, max_blocks, page, hq, hkv,
+                                                                 scale_log2, splits, ob, ldo, part_o, part_ml);
+    if (splits > 1)
+      attn_decode_merge_kernel<128><<<dim3(n_tok, hq), 128, 0, stream>>>(part_o, part_ml, tok_row, hq, splits,
+                                                                         ob, ldo);
+  } else {
+    attn_decode_kernel<64><<<grid, DEC_WARPS * 32, 0, stream>>>(qb, ldq, kb, vb, tok_row, tok_seq, tok_kvlen,
+                                                                block_table, max_blocks, page, hq, hkv,
+                                                                scale_log2, splits, ob, ldo, part_o, part_ml);
+    if (splits > 1)
+      attn_decode_merge_kernel<64><<<dim3(n_tok, hq), 64, 0, stream>>>(part_o, part_ml, tok_row, hq, splits,
+                                                                       ob, ldo);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error("attn_decode_noalloc launch failed: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
