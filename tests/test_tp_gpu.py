@@ -1,0 +1,87 @@
+"""Tensor-parallel engine on 2 GPUs (NCCL + in-kernel collectives): every schedule must agree with the
+single-GPU engine on the same checkpoint within bf16 tolerance."""
+import os
+
+import pytest
+import torch
+
+from tokenweave_b200.config import MODEL_PRESETS, ModelConfig
+from tokenweave_b200.models.loader import save_hf_checkpoint
+
+from tw_testing import hf_config_dict, make_hf_state, run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _prompts(vocab, lens, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+
+
+def _generate(path, prompts, **kw):
+    from tokenweave_b200 import LLM, SamplingParams, ops
+    args = dict(device="cuda", skip_tokenizer_init=True, block_size=128, max_num_batched_tokens=2048,
+                num_gpu_blocks_override=64)
+    args.update(kw)
+    llm = LLM(path, **args)
+    runner = llm.llm_engine.core.executor.worker.runner
+    runner.capture_logits = True
+    outs = llm.generate(prompts, SamplingParams(temperature=0, max_tokens=4))
+    torch.cuda.synchronize()
+    ops.check_status()
+    first = {}
+    for reqs, logits in runner.captured_logits:
+        for rid, row in zip(reqs, logits):
+            first.setdefault(rid, row)
+    res = torch.stack([first[str(i)] for i in range(len(prompts))])
+    return res, llm
+
+
+def _rank(rank, world, path, prompts, mode, expect_path, transport):
+    import torch.distributed as dist
+    if transport == "p2p":
+        os.environ["TW_DISABLE_NVLS"] = "1"
+    err = None
+    try:
+        logits, llm = _generate(path, prompts, tensor_parallel_size=world,
+                                distributed_executor_backend="external_launcher", tokenweave_mode=mode,
+                                tokenweave_threshold=1024)
+        expect = torch.load(expect_path)
+        d = (logits - expect).abs().max().item()
+        if d > 0.08 * max(1.0, expect.abs().max().item()):
+            err = f"rank {rank} mode {mode}: first-token logits differ by {d} (max |logit| {expect.abs().max().item()})"
+        if (logits.argmax(-1) != expect.argmax(-1)).float().mean().item() > 0.34:
+            err = (err or "") + f" rank {rank}: argmax disagrees"
+    except Exception:
+        import traceback
+        err = traceback.format_exc()
+    torch.cuda.synchronize()
+    if dist.is_initialized():
+        dist.barrier()
+    try:
+        llm.shutdown()
+    except Exception:
+        pass
+    assert err is None, err
+
+
+@pytest.mark.parametrize("arch,mode,transport", [("tiny-llama-d128", "overlap", "multimem"),
+                                                 ("tiny-llama-d128", "fuse_only", "p2p"),
+                                                 ("tiny-llama-d128", "baseline_nccl", "multimem"),
+                                                 ("tiny-llama-d128", "baseline_multimem", "multimem"),
+                                                 ("tiny-qwen2", "overlap", "p2p"),
+                                                 ("tiny-mixtral", "overlap", "multimem")])
+def test_tp2_matches_single_gpu(tmp_path, arch, mode, transport):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cfg = ModelConfig(name=arch, **MODEL_PRESETS[arch])
+    st = make_hf_state(cfg, seed=5, dtype=torch.bfloat16)
+    hf = hf_config_dict(cfg)
+    hf["torch_dtype"] = "bfloat16"
+    save_hf_checkpoint(st, hf, str(tmp_path))
+    prompts = _prompts(cfg.vocab_size, [700, 300, 333, 40])      # 1373 tokens: overlap schedule, straddling request
+    expect, llm = _generate(str(tmp_path), prompts)
+    llm.shutdown()
+    ep = str(tmp_path / "expect.pt")
+    torch.save(expect, ep)
+    run_ranks(_rank, 2, str(tmp_path), prompts, mode, ep, transport, timeout=300)

@@ -72,9 +72,10 @@ class ParallelLMHead(nn.Module):
         tp = get_tp()
         local = ops.gemm(hidden, self.weight)
         if tp.world_size > 1:
-            gathered = torch.empty(tp.world_size, *local.shape, dtype=local.dtype, device=local.device)
+            rows, cols = local.shape
+            gathered = torch.empty(tp.world_size * rows, cols, dtype=local.dtype, device=local.device)
             dist.all_gather_into_tensor(gathered, local.contiguous(), group=tp.group)
-            local = gathered.permute(1, 0, 2).reshape(local.shape[0], -1)
+            local = gathered.view(tp.world_size, rows, cols).permute(1, 0, 2).reshape(rows, -1)
         return local[:, : self.vocab_size].float()
 
     def weight_loader(self, param: nn.Parameter, loaded: torch.Tensor, shard_id=None) -> None:
