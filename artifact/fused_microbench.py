@@ -1,0 +1,127 @@
+#!/usr/bin/env python
+"""Fused all-reduce + residual-add + RMSNorm microbenchmark (figures 4 and 10 of the paper;
+reference: artifact/figure_4_10/bench.py:63-237).
+
+Launch: ``python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 artifact/fused_microbench.py``.
+Per rank: a bf16 partial-sum tensor [T, 8192] and residual [T, 8192] ~ N(0,1), RMSNorm weight ~ N(1, 0.1),
+eps 1e-5, seed per rank. Columns (microseconds, median, cold L2, max over ranks):
+
+  norm_full      add+RMSNorm on all T rows (what follows an unfused all-reduce)
+  norm_shard     add+RMSNorm on this rank's T/N rows
+  nccl_ar        NCCL all-reduce
+  nccl_ar_norm   NCCL all-reduce + add+RMSNorm (the baseline the fused kernel replaces)
+  mm_ar / mm_rs / mm_ag   in-kernel all-reduce / reduce-scatter / all-gather
+  simple_fusion  RS, norm, AG as three phases of one kernel
+  fused[c]       the product kernel on c CTAs, c in --ctas ("fused_best" = min over c)
+  roofline_us    T*H*2 bytes over the measured 770 GB/s per direction; frac = roofline / fused_best
+Each fused result is checked against NCCL all-reduce + reference RMSNorm with atol = rtol = 4e-2.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from common import NVLINK_GBS_MEASURED, finish_ranks, init_ranks, time_us, write_rows  # noqa: E402
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, nargs="+", default=[64, 256, 1024, 4096, 8192, 16384])
+    ap.add_argument("--ctas", type=int, nargs="+", default=[2, 4, 8, 16, 32])
+    ap.add_argument("--hidden", type=int, default=8192)
+    ap.add_argument("--iters", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--transport", default="auto", choices=["auto", "multimem", "p2p"])
+    ap.add_argument("--out", default=os.path.join("gpurun_out", "fused_microbench"))
+    args = ap.parse_args()
+    if args.transport == "p2p":
+        os.environ["TW_DISABLE_NVLS"] = "1"
+    tp = init_ranks()
+    from tokenweave_b200 import ops
+    from tokenweave_b200.ops import reference as ref
+    from tokenweave_b200.parallel.comm import TPCommunicator
+    from tokenweave_b200.parallel.symm_mem import create_symmetric_buffer
+
+    H, W, rank = args.hidden, tp.world_size, tp.rank
+    Tmax = max(args.tokens)
+    buf = create_symmetric_buffer(Tmax, H, torch.bfloat16, tp)
+    comm = TPCommunicator(buf, tp, wait_budget_ms=5000)
+    g = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    gw = torch.Generator(device="cuda").manual_seed(7)
+    w = (1 + 0.1 * torch.randn(H, device="cuda", generator=gw)).to(torch.bfloat16)
+    rows = []
+    for T in args.tokens:
+        if T % W:
+            continue
+        x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+        res0 = torch.randn(T, H, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)).to(torch.bfloat16)
+        res = res0.clone()
+        view = buf.tensor[:T]
+        scratch = torch.empty_like(x)
+        rpr = T // W
+
+        def refill():
+            view.copy_(x)
+
+        # correctness of the product kernel for this T
+        xs = x.float()
+        if W > 1:
+            dist.all_reduce(xs)
+        expect_res = xs.to(torch.bfloat16) + res0
+        expect = ref.rmsnorm(expect_res, w, 1e-5)
+        refill()
+        res.copy_(res0)
+        torch.cuda.synchronize()
+        if W > 1:
+            dist.barrier()
+        comm.fused_allreduce_add_rmsnorm_(view, res, w, 1e-5, max_ctas=16)
+        torch.cuda.synchronize()
+        ok = torch.allclose(view.float(), expect.float(), atol=4e-2, rtol=4e-2)
+        if W > 1:
+            flag = torch.tensor([int(ok)], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = bool(flag.item())
+
+        row = {"tokens": T, "hidden": H, "world": W, "transport": "multimem" if comm.use_mc else ("peer" if comm.in_kernel else "local"),
+               "correct": ok}
+        kw = dict(warmup=args.warmup, iters=args.iters, before=refill, sync_ranks=True)
+        row["norm_full"] = time_us(lambda: ops.add_rmsnorm_(scratch, res, w, 1e-5), warmup=args.warmup, iters=args.iters)
+        row["norm_shard"] = time_us(lambda: ops.add_rmsnorm_(scratch[:rpr], res[:rpr], w, 1e-5), warmup=args.warmup, iters=args.iters)
+        if W > 1:
+            row["nccl_ar"] = time_us(lambda: dist.all_reduce(view), **kw)
+
+            def nccl_norm():
+                dist.all_reduce(view)
+                ops.add_rmsnorm_(view, res, w, 1e-5)
+            row["nccl_ar_norm"] = time_us(nccl_norm, **kw)
+            best = {}
+            for name, fn in (("mm_ar", comm.all_reduce_), ("mm_rs", comm.reduce_scatter_), ("mm_ag", comm.all_gather_)):
+                best[name] = min(time_us(lambda: fn(view, c), **kw) for c in args.ctas)
+            row.update(best)
+            row["simple_fusion"] = min(time_us(lambda: comm.fused_allreduce_add_rmsnorm_(view, res, w, 1e-5, c, mode=2), **kw)
+                                       for c in args.ctas)
+        fused = {}
+        for c in args.ctas:
+            fused[c] = time_us(lambda: comm.fused_allreduce_add_rmsnorm_(view, res, w, 1e-5, c), **kw)
+            row[f"fused_{c}"] = fused[c]
+        row["fused_best"] = min(fused.values())
+        row["best_ctas"] = min(fused, key=fused.get)
+        roof = T * H * 2 / (NVLINK_GBS_MEASURED * 1e9) * 1e6 if W > 1 else 0.0
+        row["roofline_us"] = roof
+        row["roofline_frac"] = (roof / row["fused_best"]) if W > 1 else None
+        rows.append(row)
+        if rank == 0:
+            print({k: (round(v, 1) if isinstance(v, float) else v) for k, v in row.items()}, flush=True)
+    ops.check_status()
+    if rank == 0:
+        write_rows(args.out, f"fused_microbench_w{W}", rows)
+    finish_ranks()
+
+
+if __name__ == "__main__":
+    main()
