@@ -1,0 +1,126 @@
+#!/usr/bin/env python
+"""Runs ONE kernel on a small, fixed case a few times: the command to put under ``ncu`` (single GPU).
+
+    python artifact/kernel_cases.py gemm --m 4096 --n 8192 --k 4096
+    ncu --set full --clock-control none -k regex:gemm_bf16 -s 2 -c 2 -o gpurun_out/gemm python artifact/kernel_cases.py gemm
+
+Inputs are larger than the 126 MB L2 where the kernel's real workloads are, but stay within a few GB.
+Prints the CUDA-event time of the last launch and the achieved rate against the measured peaks."""
+from __future__ import annotations
+
+import argparse
+import math
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from common import measured_peaks  # noqa: E402
+
+import torch  # noqa: E402
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm", "gemm_swiglu", "attn_prefill", "attn_decode", "add_rmsnorm", "rope_kv",
+                                     "moe_router", "fused_local"])
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=8)
+    ap.add_argument("--kv-heads", type=int, default=1)
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--hidden", type=int, default=8192)
+    ap.add_argument("--launches", type=int, default=4)
+    args = ap.parse_args()
+    from tokenweave_b200 import ops
+    torch.cuda.set_device(0)
+    dev, BF = "cuda", torch.bfloat16
+    peaks = measured_peaks()
+    flops = bytes_moved = 0
+
+    if args.case in ("gemm", "gemm_swiglu"):
+        M, N, K = args.m, args.n, args.k
+        a = torch.randn(M, K, device=dev).to(BF)
+        sw = args.case == "gemm_swiglu"
+        w = (torch.randn(2 * N if sw else N, K, device=dev) / math.sqrt(K)).to(BF)
+        out = torch.empty(M, N, device=dev, dtype=BF)
+        fn = lambda: ops.gemm(a, w, out=out, swiglu=sw)
+        flops = 2 * M * (2 * N if sw else N) * K
+    elif args.case == "attn_prefill":
+        T, hq, hkv, D, page = args.tokens, args.heads, args.kv_heads, 128, 128
+        nb = T // page + 1
+        kc, vc = torch.randn(nb, page, hkv, D, device=dev).to(BF), torch.randn(nb, page, hkv, D, device=dev).to(BF)
+        q = torch.randn(T, hq * D, device=dev).to(BF)
+        out = torch.empty_like(q)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        tiles = list(range(0, T, 128))[::-1]
+        meta = (i32([0, T]), i32([T]), torch.arange(nb, dtype=torch.int32, device=dev).view(1, -1), i32([0] * len(tiles)), i32(tiles))
+        fn = lambda: ops.attn_prefill(q, kc, vc, out, meta[0], meta[1], meta[2], meta[3], meta[4], len(tiles), hq, hkv, D, D ** -0.5)
+        flops = 4 * T * T * hq * D // 2
+    elif args.case == "attn_decode":
+        B, kv, hq, hkv, D, page = 256, 2048, args.heads, args.kv_heads, 128, 128
+        nb = B * (kv // page) + 1
+        kc, vc = torch.randn(nb, page, hkv, D, device=dev).to(BF), torch.randn(nb, page, hkv, D, device=dev).to(BF)
+        q = torch.randn(B, hq * D, device=dev).to(BF)
+        out = torch.empty_like(q)
+        bt = (torch.arange(B * (kv // page), dtype=torch.int32, device=dev) + 1).view(B, -1)
+        ar = torch.arange(B, dtype=torch.int32, device=dev)
+        kvl = torch.full((B,), kv, dtype=torch.int32, device=dev)
+        fn = lambda: ops.attn_decode(q, kc, vc, out, ar, ar, kvl, B, bt, hq, hkv, D, D ** -0.5, kv)
+        bytes_moved = 2 * B * kv * hkv * D * 2
+    elif args.case == "add_rmsnorm":
+        T, H = args.tokens, args.hidden
+        x, r = torch.randn(T, H, device=dev).to(BF), torch.randn(T, H, device=dev).to(BF)
+        w = torch.ones(H, device=dev, dtype=BF)
+        fn = lambda: ops.add_rmsnorm_(x, r, w, 1e-5)
+        bytes_moved = 4 * T * H * 2
+    elif args.case == "rope_kv":
+        from tokenweave_b200.ops import reference as ref
+        T, hq, hkv, D, page = args.tokens, args.heads, args.kv_heads, 128, 128
+        qkv = torch.randn(T, (hq + 2 * hkv) * D, device=dev).to(BF)
+        kc = torch.zeros(T // page + 1, page, hkv, D, device=dev, dtype=BF)
+        vc = torch.zeros_like(kc)
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        cs = ref.build_cos_sin_cache(D, T, 500000.0, device=dev)
+        fn = lambda: ops.rope_kv_write_(qkv, pos, pos, cs, kc, vc, hq, hkv, D)
+        bytes_moved = T * (2 * hq + 4 * hkv) * D * 2
+    elif args.case == "moe_router":
+        T, H = args.tokens, 6144
+        x = torch.randn(T, H, device=dev).to(BF)
+        g = (torch.randn(8, H, device=dev) / math.sqrt(H)).to(BF)
+        fn = lambda: ops.moe_router(x, g, 2)
+        bytes_moved = T * H * 2
+    else:   # fused_local: the fused collective kernel on one GPU acting as a world of one (peer transport)
+        from tokenweave_b200.ops import _native
+        T, H = args.tokens, args.hidden
+        x, r = torch.randn(T, H, device=dev).to(BF), torch.randn(T, H, device=dev).to(BF)
+        w = torch.ones(H, device=dev, dtype=BF)
+        pads = torch.zeros(4096, dtype=torch.int32, device=dev)
+        bases = torch.tensor([x.data_ptr()], dtype=torch.int64, device=dev)
+        padp = torch.tensor([pads.data_ptr()], dtype=torch.int64, device=dev)
+        fn = lambda: _native.call("tw_fused_rs_norm_ag", None, bases.data_ptr(), padp.data_ptr(), 0, 1, 0, 10 ** 9,
+                                  ops.status_word().data_ptr(), 0, r.data_ptr(), r.stride(0), w.data_ptr(), T, H,
+                                  1e-5, 16, 0, 0, torch.cuda.current_stream().cuda_stream)
+        bytes_moved = 4 * T * H * 2
+
+    ms = 0.0
+    for _ in range(args.launches):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e)
+    ops.check_status()
+    line = f"{args.case}: {ms * 1e3:.1f} us"
+    if flops:
+        tf = flops / ms / 1e9
+        line += f", {tf:.0f} TFLOP/s = {tf / peaks['bf16_tflops']:.2f} of {peaks['source']} cuBLAS burst peak"
+    if bytes_moved:
+        gbs = bytes_moved / ms / 1e6
+        line += f", {gbs:.0f} GB/s = {gbs / peaks['hbm_gbs']:.2f} of {peaks['source']} copy bandwidth"
+    print(line)
+
+
+if __name__ == "__main__":
+    main()

@@ -27,6 +27,10 @@ def _comm_worker(rank, world, transport):
 
     if transport == "p2p":
         os.environ["TW_DISABLE_NVLS"] = "1"
+    if transport.startswith("native"):
+        os.environ["TW_SYMM_PROVIDER"] = "native"
+        if transport == "native-p2p":
+            os.environ["TW_DISABLE_NVLS"] = "1"
     tp = pstate.init_distributed(rank, world, rank, "cuda")
     errors = []
     try:
@@ -34,7 +38,7 @@ def _comm_worker(rank, world, transport):
         buf = create_symmetric_buffer(rows, H, torch.bfloat16, tp)
         comm = TPCommunicator(buf, tp, wait_budget_ms=3000, transport="auto")
         assert comm.in_kernel
-        if transport == "multimem" and not comm.use_mc:
+        if transport in ("multimem", "native") and not comm.use_mc:
             errors.append("no multicast mapping on this machine")
         g = torch.Generator(device="cuda").manual_seed(100 + rank)
         w = (1 + 0.1 * torch.randn(H, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))).to(torch.bfloat16)
@@ -117,11 +121,16 @@ def _comm_worker(rank, world, transport):
         errors.append(traceback.format_exc())
     torch.cuda.synchronize()
     dist.barrier(group=tp.group)
+    try:
+        buf.close()
+    except Exception:
+        import traceback
+        errors.append(traceback.format_exc())
     pstate.destroy_distributed()
     assert not errors, "\n".join(errors)
 
 
-@pytest.mark.parametrize("transport", ["multimem", "p2p"])
+@pytest.mark.parametrize("transport", ["multimem", "p2p", "native", "native-p2p"])
 def test_fused_and_collectives_two_gpus(transport):
     _need_gpus(2)
     run_ranks(_comm_worker, 2, transport, timeout=300)

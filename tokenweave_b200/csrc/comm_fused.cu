@@ -85,9 +85,9 @@ fused_rs_norm_ag_kernel(const CommCtx c, long long off_bytes, __nv_bfloat16* __r
   const long long shard_off = off_bytes + static_cast<long long>(c.rank) * rows_per_rank * row_bytes;
   uint8_t* local_base = c.peer_bases[c.rank];
 
-  for (int g = blockIdx.x * ROWS; g < rows_per_rank; g += gridDim.x * ROWS) {
-    uint4 x[ROWS];
-    float ss[ROWS];
+  // Software pipeline: the reduce-scatter loads of row group i+1 are in flight while group i goes
+  // through the residual add, the block reduction and the broadcast stores.
+  auto load_group = [&](int g, uint4 (&x)[ROWS]) {
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
       x[r] = make_uint4(0, 0, 0, 0);
@@ -96,6 +96,16 @@ fused_rs_norm_ag_kernel(const CommCtx c, long long off_bytes, __nv_bfloat16* __r
         x[r] = MC ? multimem_ld_reduce_bf16x8(c.mc_base + off) : peer_reduce_bf16x8(c, off);
       }
     }
+  };
+  const int step = gridDim.x * ROWS;
+  uint4 x[ROWS];
+  int g = blockIdx.x * ROWS;
+  if (g < rows_per_rank) load_group(g, x);
+  for (; g < rows_per_rank; g += step) {
+    uint4 xn[ROWS];
+    const bool more = g + step < rows_per_rank;
+    if (more) load_group(g + step, xn);
+    float ss[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
       ss[r] = 0.f;
@@ -138,6 +148,10 @@ fused_rs_norm_ag_kernel(const CommCtx c, long long off_bytes, __nv_bfloat16* __r
           peer_broadcast_16(c, off, o);
         }
       }
+    }
+    if (more) {
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) x[r] = xn[r];
     }
   }
   if (!barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns)) {

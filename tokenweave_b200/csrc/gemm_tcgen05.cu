@@ -11,8 +11,11 @@
 //               memory descriptors, accumulators in TMEM (two buffers, so the epilogue of
 //               tile i overlaps the main loop of tile i+1)
 //   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns -> registers -> bf16 -> global
-// Epilogues: plain, +bias[n], *row_scale[m], and SwiGLU (the B tile holds 128 "gate" rows and
-// 128 "up" rows; the stored value is silu(gate)*up, N/2 output columns per tile).
+// The tile width BN is a run-time value (a multiple of 32 up to 256; the instruction descriptor and
+// the pipeline depth are computed from it), chosen per problem by a wave-quantisation cost model:
+// skinny tensor-parallel shapes such as N = 1280 waste a third of the machine with 256-wide tiles.
+// Epilogues: plain, +bias[n], *row_scale[m], and SwiGLU (the B tile holds BN/2 "gate" rows and
+// BN/2 "up" rows; the stored value is silu(gate)*up, BN/2 output columns per tile).
 // Grouped mode: each 128-row tile of A belongs to one expert (tile_expert[m_tile]); the B rows
 // are offset by expert * n_per_expert; the number of valid tiles is read from device memory.
 //
@@ -28,6 +31,10 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_GROUP_M = 16;
+constexpr int GEMM_MAX_STAGES = 8;
+constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;
+constexpr int GEMM_SMEM_BUDGET = 200 * 1024;   // pipeline stages; barriers and slack come on top
+constexpr int GEMM_TMEM_COLS = 512;
 
 struct GemmParams {
   __nv_bfloat16* C;
@@ -40,18 +47,12 @@ struct GemmParams {
   const int* num_m_tiles_dev;
   int n_per_expert;
   int up_row_offset;
+  int bn;        // accumulator columns per tile
+  int stages;    // pipeline depth
   uint32_t* status;
 };
 
-template <int BN>
-struct GemmSmem {
-  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
-  static constexpr int B_BYTES = BN * GEMM_BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int BAR_BYTES = 256;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
-};
+__host__ __device__ inline int gemm_stage_bytes(int bn) { return GEMM_A_BYTES + bn * GEMM_BK * 2; }
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_tile, int& n_tile) {
   const int group_span = GEMM_GROUP_M * num_n;
@@ -63,21 +64,22 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   n_tile = in_group / rows;
 }
 
-template <int BN, bool SWIGLU>
+template <bool SWIGLU>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
-  using S = GemmSmem<BN>;
-  constexpr int STAGES = S::STAGES;
-  constexpr int OUT_COLS = SWIGLU ? BN / 2 : BN;
-  constexpr uint32_t IDESC = make_idesc_bf16(GEMM_BM, BN, 0, 0);
+  const int BN = p.bn;
+  const int STAGES = p.stages;
+  const int stage_bytes = gemm_stage_bytes(BN);
+  const int OUT_COLS = SWIGLU ? BN / 2 : BN;
+  const uint32_t IDESC = make_idesc_bf16(GEMM_BM, BN, 0, 0);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
-  uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * stage_bytes);
+  uint64_t* empty_bar = full_bar + GEMM_MAX_STAGES;
+  uint64_t* acc_full = empty_bar + GEMM_MAX_STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -98,7 +100,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_alloc(tmem_slot, GEMM_TMEM_COLS);
     tmem_relinquish();
   }
   if (warp == 0 && lane == 0) {
@@ -133,19 +135,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             *abort_flag = 1;
             break;
           }
-          uint8_t* sa = smem + stage * S::STAGE_BYTES;
-          uint8_t* sb = sa + S::A_BYTES;
-          mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+          uint8_t* sa = smem + stage * stage_bytes;
+          uint8_t* sb = sa + GEMM_A_BYTES;
+          mbar_expect_tx(&full_bar[stage], stage_bytes);
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * GEMM_BK, m0);
           if (SWIGLU) {
             tma_load_2d(sb, &tmB, &full_bar[stage], kb * GEMM_BK, b_row0);
             tma_load_2d(sb + (BN / 2) * GEMM_BK * 2, &tmB, &full_bar[stage], kb * GEMM_BK,
                         b_row0 + p.up_row_offset);
           } else {
-#pragma unroll
-            for (int h = 0; h < BN / 128; ++h)
-              tma_load_2d(sb + h * 128 * GEMM_BK * 2, &tmB, &full_bar[stage], kb * GEMM_BK,
-                          b_row0 + h * 128);
+            tma_load_2d(sb, &tmB, &full_bar[stage], kb * GEMM_BK, b_row0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -165,13 +164,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * 256;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
-          const uint32_t sb = sa + S::A_BYTES;
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+          const uint32_t sb = sa + GEMM_A_BYTES;
           const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
           const uint64_t b_desc = make_smem_desc_sw128(sb, 16, 1024);
 #pragma unroll
@@ -208,7 +207,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after_sync();
       const int row = m_tile * GEMM_BM + q * 32 + lane;
       const int n0 = n_tile * OUT_COLS;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * 256;
       const float rs = (p.row_scale != nullptr && row < p.M) ? p.row_scale[row] : 1.f;
       __nv_bfloat16* crow = p.C + static_cast<long long>(row) * p.ldc + n0;
 #pragma unroll 1
@@ -277,27 +276,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 2 * BN);
+    tmem_dealloc(tmem_base, GEMM_TMEM_COLS);
   }
 }
 
-template <int BN, bool SWIGLU>
+template <bool SWIGLU>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
                        cudaStream_t stream) {
-  using S = GemmSmem<BN>;
-  auto kern = gemm_bf16_kernel<BN, SWIGLU>;
+  const int smem = p.stages * gemm_stage_bytes(p.bn) + 256 + 1024;
+  auto kern = gemm_bf16_kernel<SWIGLU>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) {
-      set_last_error("cudaFuncSetAttribute(smem=%d) failed: %s", S::TOTAL, cudaGetErrorString(e));
+      set_last_error("cudaFuncSetAttribute(smem) failed: %s", cudaGetErrorString(e));
       return 1;
     }
     configured_dev = dev;
   }
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error("gemm launch failed: %s", cudaGetErrorString(e));
@@ -306,33 +305,114 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   return 0;
 }
 
+// Kernel and tile-width choice. Cost of a candidate = waves * per-tile time. Per-k-block tile times
+// (arbitrary units, fitted to sweeps on B200 at K = 8192): a single-CTA tile costs 136 up to BN = 128
+// and grows linearly to 208 at BN = 256 (below 128 columns the main loop is bound by the fixed
+// issue/barrier cost per k-block, not by the tensor pipe); a CTA-pair tile (256 rows) costs 155 up to
+// BN = 128 and 198 at BN = 256. A fixed number of k-block equivalents per tile covers prologue,
+// pipeline refill and the non-overlapped part of the epilogue.
+static int g_bn_override = 0;
+static int g_kernel_override = 0;   // 0 auto, 1 single-CTA tiles, 2 CTA pairs
+
+struct GemmPlan {
+  bool pair;
+  int bn;
+};
+
+static double tile_cost_single(int bn) { return bn <= 128 ? 136.0 : 136.0 + (bn - 128) * 0.5625; }
+static double tile_cost_pair(int bn) { return bn <= 128 ? 155.0 : 155.0 + (bn - 128) * 0.336; }
+
+static GemmPlan choose_plan(int M, int N, int K, int sms, bool swiglu, bool grouped) {
+  const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  const double kb_eff = num_kb + 6.0;
+  GemmPlan best{false, 256};
+  double best_cost = 1e30;
+  const int step1 = swiglu ? 64 : 32;
+  if (g_kernel_override != 2 || grouped) {
+    const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
+    for (int bn = 256; bn >= 64; bn -= step1) {
+      if (g_bn_override > 0 && bn != g_bn_override) continue;
+      const int out_cols = swiglu ? bn / 2 : bn;
+      const long long tiles = static_cast<long long>(num_m) * ((N + out_cols - 1) / out_cols);
+      const long long waves = (tiles + sms - 1) / sms;
+      const double cost = waves * tile_cost_single(bn) * kb_eff;
+      if (cost < best_cost * 0.999) {
+        best_cost = cost;
+        best = GemmPlan{false, bn};
+      }
+    }
+  }
+  const int pairs = sms / 2;
+  if (!grouped && g_kernel_override != 1 && pairs >= 1 && (M >= 2048 || g_kernel_override == 2)) {
+    const int num_m2 = (M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
+    for (int bn = 256; bn >= 64; bn -= 64) {
+      if (g_bn_override > 0 && bn != g_bn_override) continue;
+      const int out_cols = swiglu ? bn / 2 : bn;
+      const long long tiles = static_cast<long long>(num_m2) * ((N + out_cols - 1) / out_cols);
+      const long long waves = (tiles + pairs - 1) / pairs;
+      const double cost = waves * tile_cost_pair(bn) * kb_eff * 1.02;   // ties go to the simpler kernel
+      if (cost < best_cost * 0.999) {
+        best_cost = cost;
+        best = GemmPlan{true, bn};
+      }
+    }
+  }
+  return best;
+}
+
 }  // namespace tw
 
 using namespace tw;
 
-// C launcher. `mode` bit 0: SwiGLU epilogue. A is [M,K] with row stride lda, B is
-// [rows_b, K] with row stride ldb (rows_b = N, 2*N for SwiGLU, or experts * n_per_expert).
+// Forces the tile width (0 restores the cost model). For tuning runs and tests.
+extern "C" int tw_gemm_set_tile_override(int bn) {
+  g_bn_override = bn;
+  return 0;
+}
+// Forces the kernel: 0 cost model, 1 single-CTA tiles, 2 CTA pairs.
+extern "C" int tw_gemm_set_kernel_override(int kind) {
+  g_kernel_override = kind;
+  return 0;
+}
+
+extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
+                                 void* C, long long ldc, const void* bias, const float* row_scale, int M, int N,
+                                 int K, int swiglu, int up_row_offset, int bn, int max_ctas, uint32_t* status,
+                                 cudaStream_t stream);
+
+// C launcher. A is [M,K] with row stride lda, B is [rows_b, K] with row stride ldb
+// (rows_b = N, 2*N for SwiGLU, or experts * n_per_expert).
 extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
                             void* C, long long ldc, const void* bias, const float* row_scale, int M,
                             int N, int K, int swiglu, int up_row_offset, const int* tile_expert,
-                            const int* num_m_tiles_dev, int n_per_expert, int max_ctas,
+                            const int* num_m_tiles_dev, int n_per_expert, int max_ctas, int plan_hint,
                             uint32_t* status, cudaStream_t stream) {
+  // plan_hint: 0 = cost model; otherwise kernel * 1000 + tile width (kernel 1 = single-CTA tiles,
+  // 2 = CTA pairs), as produced by the tuning table.
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldc % 8) != 0) {
     set_last_error("tw_gemm_bf16: K, lda, ldb, ldc must be multiples of 8 (got %d, %lld, %lld, %lld)", K,
                    lda, ldb, ldc);
     return 1;
   }
-  // Tile width: 256 accumulator columns unless that leaves most SMs idle.
   int sms = device_sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
-  const int out_cols_256 = swiglu ? 128 : 256;
-  const int tiles_256 = num_m * ((N + out_cols_256 - 1) / out_cols_256);
-  const bool use_256 = tiles_256 >= sms;
-  const int BN = use_256 ? 256 : 128;
+  GemmPlan plan = choose_plan(M, N, K, sms, swiglu != 0, tile_expert != nullptr);
+  if (plan_hint > 0) {
+    const int kind = plan_hint / 1000, bn = plan_hint % 1000;
+    const bool pair_ok = kind == 2 && tile_expert == nullptr && sms >= 2 && bn % 64 == 0;
+    const bool single_ok = kind == 1 && bn % (swiglu ? 64 : 32) == 0;
+    if (bn >= 64 && bn <= 256 && (pair_ok || single_ok)) plan = GemmPlan{pair_ok, bn};
+  }
+  if (plan.pair)
+    return tw_gemm_bf16_pair(A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, M, N, K, swiglu, up_row_offset, plan.bn,
+                             sms, status, stream);
+  const int BN = plan.bn;
   const int out_cols = swiglu ? BN / 2 : BN;
   const int num_n = (N + out_cols - 1) / out_cols;
+  int stages = GEMM_SMEM_BUDGET / gemm_stage_bytes(BN);
+  if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
 
   CUtensorMap tmA, tmB;
   {
@@ -344,7 +424,7 @@ extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long lo
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows_b};
     uint64_t strides[1] = {(uint64_t)ldb * 2};
-    uint32_t box[2] = {GEMM_BK, (uint32_t)(swiglu ? BN / 2 : 128)};
+    uint32_t box[2] = {GEMM_BK, (uint32_t)(swiglu ? BN / 2 : BN)};
     if (!make_tensor_map_bf16(&tmB, B, 2, dims, strides, box)) return 1;
   }
   GemmParams p;
@@ -361,13 +441,10 @@ extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long lo
   p.num_m_tiles_dev = num_m_tiles_dev;
   p.n_per_expert = n_per_expert;
   p.up_row_offset = up_row_offset;
+  p.bn = BN;
+  p.stages = stages;
   p.status = status;
   int grid = num_m * num_n;
   if (grid > sms) grid = sms;
-  if (use_256) {
-    return swiglu ? launch_gemm<256, true>(tmA, tmB, p, grid, stream)
-                  : launch_gemm<256, false>(tmA, tmB, p, grid, stream);
-  }
-  return swiglu ? launch_gemm<128, true>(tmA, tmB, p, grid, stream)
-                : launch_gemm<128, false>(tmA, tmB, p, grid, stream);
+  return swiglu ? launch_gemm<true>(tmA, tmB, p, grid, stream) : launch_gemm<false>(tmA, tmB, p, grid, stream);
 }

@@ -1,0 +1,426 @@
+// bf16 GEMM on CTA pairs (tcgen05 cta_group::2): C[M,N] = A[M,K] * B[N,K]^T, one 256 x BN output tile
+// per pair of SMs.
+//
+// Why pairs: with one CTA per tile every SM pulls a 128x64 slice of A and a BNx64 slice of B from L2
+// per k-block (48 KB at BN = 256). As a pair, each CTA loads its own 128 rows of A and only HALF of
+// the B slice (32 KB per SM per k-block); the MMA unit of the leader CTA reads both halves. That cuts
+// the L2 -> SM traffic per FLOP by a third and makes room for a deeper TMA pipeline (6 stages).
+// No cluster-multicast copy is involved: every CTA issues ordinary tiled TMA loads into its own shared
+// memory; only the completion signal goes to the leader's mbarrier (cta_group::2 form of the copy).
+//
+// Roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only; both CTAs'
+// warp 1 take part in the paired TMEM allocation), warps 2..5 epilogue of the CTA's own 128 rows.
+// Barriers: full[s] lives in the leader and counts the bytes of both CTAs; empty[s] and acc_full[a]
+// exist in both CTAs and are signalled by the leader's tcgen05.commit (one commit per CTA);
+// acc_empty[a] lives in the leader and collects one arrival per epilogue warp of both CTAs.
+// Every wait is bounded (TW_ERR_MBAR_TIMEOUT); the pair leaves together through a cluster barrier.
+#include <string.h>
+
+#include "tw_common.cuh"
+#include "tw_host.h"
+#include "tw_kernels.h"
+
+namespace tw {
+
+constexpr int G2_BM = 128;          // rows per CTA (256 per pair)
+constexpr int G2_BK = 64;
+constexpr int G2_THREADS = 192;
+constexpr int G2_GROUP_M = 8;       // pair-tiles per rasterisation group
+constexpr int G2_MAX_STAGES = 8;
+constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;
+constexpr int G2_SMEM_BUDGET = 200 * 1024;
+constexpr int G2_TMEM_COLS = 512;
+
+struct Gemm2Params {
+  __nv_bfloat16* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  const float* row_scale;
+  int M, N, K;
+  int num_m_tiles, num_n_tiles;   // in 256-row pair tiles
+  int up_row_offset;
+  int bn, stages;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Tiled TMA load into this CTA's shared memory whose completion bytes are credited to an mbarrier
+// given by its cluster address (the leader's barrier).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               ::"r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+__device__ __forceinline__ void pair_tile_coords(int t, int num_m, int num_n, int& m_tile, int& n_tile) {
+  const int group_span = G2_GROUP_M * num_n;
+  const int group = t / group_span;
+  const int first_m = group * G2_GROUP_M;
+  const int rows = min(num_m - first_m, G2_GROUP_M);
+  const int in_group = t - group * group_span;
+  m_tile = first_m + in_group % rows;
+  n_tile = in_group / rows;
+}
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(G2_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const Gemm2Params p) {
+  const int BN = p.bn;
+  const int HALF_N = BN / 2;                       // B rows held by each CTA
+  const int STAGES = p.stages;
+  const int stage_bytes = G2_A_BYTES + HALF_N * G2_BK * 2;
+  const int OUT_COLS = SWIGLU ? BN / 2 : BN;
+  const uint32_t IDESC = make_idesc_bf16(2 * G2_BM, BN, 0, 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * stage_bytes);
+  uint64_t* empty_bar = full_bar + G2_MAX_STAGES;
+  uint64_t* acc_full = empty_bar + G2_MAX_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);   // 4 epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, G2_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                 // both CTAs' barriers exist before anyone signals across
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_m = p.num_m_tiles, num_n = p.num_n_tiles;
+  const int total_tiles = num_m * num_n;
+  const int num_kb = (p.K + G2_BK - 1) / G2_BK;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = pair; t < total_tiles && !*abort_flag; t += num_pairs) {
+        int m_tile, n_tile;
+        pair_tile_coords(t, num_m, num_n, m_tile, n_tile);
+        const int m0 = m_tile * 2 * G2_BM + rank * G2_BM;
+        int b_row0;
+        if (SWIGLU) b_row0 = n_tile * OUT_COLS + (rank ? p.up_row_offset : 0);   // leader: gate rows, peer: up rows
+        else b_row0 = n_tile * BN + rank * HALF_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+            *abort_flag = 1;
+            break;
+          }
+          uint8_t* sa = smem + stage * stage_bytes;
+          uint8_t* sb = sa + G2_A_BYTES;
+          const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * stage_bytes);
+          tma_load_2d_pair(sa, &tmA, leader_full, kb * G2_BK, m0);
+          tma_load_2d_pair(sb, &tmB, leader_full, kb * G2_BK, b_row0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = pair; t < total_tiles && !*abort_flag; t += num_pairs) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+          report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+          const uint32_t sb = sa + G2_A_BYTES;
+          const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t b_desc = make_smem_desc_sw128(sb, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < G2_BK / 16; ++k)
+            umma_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+          // the stage is free in BOTH CTAs once these MMAs have read it
+          const uint32_t e_local = smem_u32(&empty_bar[stage]);
+          umma_commit_pair(map_to_cta(e_local, 0));
+          umma_commit_pair(map_to_cta(e_local, 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) {
+          report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+          *abort_flag = 1;
+          break;
+        }
+        const uint32_t f_local = smem_u32(&acc_full[acc]);
+        umma_commit_pair(map_to_cta(f_local, 0));
+        umma_commit_pair(map_to_cta(f_local, 1));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair; t < total_tiles && !*abort_flag; t += num_pairs) {
+      int m_tile, n_tile;
+      pair_tile_coords(t, num_m, num_n, m_tile, n_tile);
+      if (!mbar_wait(&acc_full[acc], acc_phase)) {
+        report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = m_tile * 2 * G2_BM + rank * G2_BM + q * 32 + lane;
+      const int n0 = n_tile * OUT_COLS;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * 256;
+      const float rs = (p.row_scale != nullptr && row < p.M) ? p.row_scale[row] : 1.f;
+      __nv_bfloat16* crow = p.C + static_cast<long long>(row) * p.ldc + n0;
+#pragma unroll 1
+      for (int c = 0; c < OUT_COLS / 32; ++c) {
+        uint32_t v[32];
+        uint32_t packed[16];
+        tmem_ld_32x32(taddr + c * 32, v);
+        if (SWIGLU) {
+          uint32_t u[32];
+          tmem_ld_32x32(taddr + BN / 2 + c * 32, u);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float g0 = __uint_as_float(v[2 * j]), g1 = __uint_as_float(v[2 * j + 1]);
+            float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            packed[j] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0 * rs, g1 / (1.f + __expf(-g1)) * u1 * rs);
+          }
+        } else {
+          tmem_wait_ld();
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int n = n0 + c * 32 + j;
+              const float b = (n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+              v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            packed[j] = pack_bf16x2(__uint_as_float(v[2 * j]) * rs, __uint_as_float(v[2 * j + 1]) * rs);
+        }
+        if (row < p.M) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = n0 + c * 32 + j * 8;
+            if (n + 8 <= p.N) {
+              *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) =
+                  make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+            } else if (n < p.N) {
+              uint16_t* c16 = reinterpret_cast<uint16_t*>(crow + c * 32 + j * 8);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const uint32_t w = packed[4 * j + (e >> 1)];
+                if (n + e < p.N) c16[e] = (e & 1) ? static_cast<uint16_t>(w >> 16) : static_cast<uint16_t>(w & 0xffffu);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  // ---------------- tear-down ----------------
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                 // nobody signals a barrier of, or reads TMEM paired with, an exited CTA
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, G2_TMEM_COLS);
+  }
+}
+
+template <bool SWIGLU>
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p, int pairs,
+                       cudaStream_t stream) {
+  const int stage_bytes = G2_A_BYTES + (p.bn / 2) * G2_BK * 2;
+  const int smem = p.stages * stage_bytes + 256 + 1024;
+  auto kern = gemm_bf16_pair_kernel<SWIGLU>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) {
+      set_last_error("gemm pair: cudaFuncSetAttribute(smem) failed: %s", cudaGetErrorString(e));
+      return 1;
+    }
+    configured_dev = dev;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(G2_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+  if (e != cudaSuccess) {
+    set_last_error("gemm pair launch failed: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
+
+}  // namespace tw
+
+using namespace tw;
+
+// Same contract as tw_gemm_bf16 without the grouped mode. `bn` is the tile width (multiple of 64,
+// <= 256), `max_ctas` bounds the SMs used (rounded down to an even number).
+extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
+                                 void* C, long long ldc, const void* bias, const float* row_scale, int M, int N,
+                                 int K, int swiglu, int up_row_offset, int bn, int max_ctas, uint32_t* status,
+                                 cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldc % 8) != 0 || bn % 64 != 0 || bn < 64 || bn > 256) {
+    set_last_error("tw_gemm_bf16_pair: bad strides or tile width (K=%d, bn=%d)", K, bn);
+    return 1;
+  }
+  int sms = device_sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  int pairs_avail = sms / 2;
+  if (pairs_avail < 1) {
+    set_last_error("tw_gemm_bf16_pair: needs at least 2 SMs");
+    return 1;
+  }
+  const int num_m = (M + 2 * G2_BM - 1) / (2 * G2_BM);
+  const int out_cols = swiglu ? bn / 2 : bn;
+  const int num_n = (N + out_cols - 1) / out_cols;
+  const int stage_bytes = G2_A_BYTES + (bn / 2) * G2_BK * 2;
+  int stages = G2_SMEM_BUDGET / stage_bytes;
+  if (stages > G2_MAX_STAGES) stages = G2_MAX_STAGES;
+
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t strides[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {G2_BK, G2_BM};
+    if (!make_tensor_map_bf16(&tmA, A, 2, dims, strides, box)) return 1;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows_b};
+    uint64_t strides[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {G2_BK, (uint32_t)(bn / 2)};
+    if (!make_tensor_map_bf16(&tmB, B, 2, dims, strides, box)) return 1;
+  }
+  Gemm2Params p;
+  p.C = reinterpret_cast<__nv_bfloat16*>(C);
+  p.ldc = ldc;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.row_scale = row_scale;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.num_m_tiles = num_m;
+  p.num_n_tiles = num_n;
+  p.up_row_offset = up_row_offset;
+  p.bn = bn;
+  p.stages = stages;
+  p.status = status;
+  int pairs = num_m * num_n;
+  if (pairs > pairs_avail) pairs = pairs_avail;
+  return swiglu ? launch_pair<true>(tmA, tmB, p, pairs, stream) : launch_pair<false>(tmA, tmB, p, pairs, stream);
+}

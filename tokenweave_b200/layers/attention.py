@@ -70,7 +70,8 @@ def plan_attention(q_lens: Sequence[int], kv_lens: Sequence[int]):
 
 def build_attention_metadata(q_lens: Sequence[int], kv_lens: Sequence[int], positions: np.ndarray,
                              slot_mapping: np.ndarray, block_table: np.ndarray, device: torch.device,
-                             pinned: Optional[torch.Tensor] = None) -> AttentionMetadata:
+                             pinned: Optional[torch.Tensor] = None,
+                             device_buffer: Optional[torch.Tensor] = None) -> AttentionMetadata:
     """Pack every int32 array into one staging buffer, copy it to the device once, slice views."""
     q_lens = [int(x) for x in q_lens]
     kv_lens = [int(x) for x in kv_lens]
@@ -100,7 +101,15 @@ def build_attention_metadata(q_lens: Sequence[int], kv_lens: Sequence[int], posi
         hv[off:off + src.size] = src
         offsets[k] = (off, src.size)
         off += s
-    dev = host.to(device, non_blocking=True) if device.type == "cuda" else host
+    if device.type != "cuda":
+        dev = host
+    elif device_buffer is not None and device_buffer.numel() >= total:
+        # persistent device memory: the views keep their addresses from step to step, which is what a
+        # captured CUDA graph needs (the layout depends only on the array sizes)
+        dev = device_buffer[:total]
+        dev.copy_(host, non_blocking=True)
+    else:
+        dev = host.to(device, non_blocking=True)
     view = {k: dev[o:o + n] for k, (o, n) in offsets.items()}
     return AttentionMetadata(
         num_actual_tokens=int(cu[-1]), num_seqs=B, positions=view["positions"], slot_mapping=view["slot_mapping"],

@@ -12,7 +12,7 @@ from typing import Optional
 
 import torch
 
-from . import _native, reference
+from . import _native, gemm_table, reference
 
 __all__ = [
     "gemm", "rmsnorm", "rmsnorm_copy_", "add_rmsnorm_", "rope_kv_write_", "swiglu", "embedding", "argmax",
@@ -102,7 +102,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
     _native.call("tw_gemm_bf16", a.data_ptr(), _row_stride(a), w.data_ptr(), _row_stride(w), rows_b,
                  out.data_ptr(), _row_stride(out), _p(bias), _p(row_scale), M, N, K, int(swiglu),
                  per_expert // 2 if swiglu else 0, _p(tile_expert), _p(num_m_tiles), per_expert, max_ctas,
-                 status_word(a.device).data_ptr(), _stream())
+                 0 if tile_expert is not None else gemm_table.lookup(M, N, K, swiglu, max_ctas),
+                 status_word(a.device).data_ptr(), _stream(),
+                 tag=f"[{M}x{N}x{K}{'+swiglu' if swiglu else ''}]" if _native._timing is not None else "")
     return out
 
 
@@ -223,6 +225,14 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
 _decode_ws: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
+def decode_splits(n_tok: int, hkv: int, max_kv_len: int, sm_count: int = 148) -> int:
+    """How many ways the keys are split so that a small decode batch still fills the machine."""
+    ctas = n_tok * hkv
+    if ctas == 0 or ctas >= 2 * sm_count or max_kv_len <= 512:
+        return 1
+    return max(1, min(32, (2 * sm_count) // ctas, (max_kv_len + 255) // 256))
+
+
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                 tok_row: torch.Tensor, tok_seq: torch.Tensor, tok_kvlen: torch.Tensor, n_tok: int,
                 block_table: torch.Tensor, hq: int, hkv: int, head_dim: int, scale: float, max_kv_len: int,
@@ -232,10 +242,7 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o
         return
     _check_bf16(q, k_cache, v_cache, out)
     page = k_cache.shape[1]
-    ctas = n_tok * hkv
-    splits = 1
-    if ctas < 2 * sm_count and max_kv_len > 512:
-        splits = min(32, max(1, (2 * sm_count) // ctas), (max_kv_len + 255) // 256)
+    splits = decode_splits(n_tok, hkv, max_kv_len, sm_count)
     part_o = part_ml = None
     if splits > 1:
         key = (q.device.index, n_tok * hq * splits * head_dim)

@@ -17,7 +17,7 @@ _lock = threading.Lock()
 vp, ll, i32, f32, u64 = C.c_void_p, C.c_longlong, C.c_int, C.c_float, C.c_ulonglong
 
 _SIGNATURES = {
-    "tw_gemm_bf16": [vp, ll, vp, ll, ll, vp, ll, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp],
+    "tw_gemm_bf16": [vp, ll, vp, ll, ll, vp, ll, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp, vp],
     "tw_rmsnorm": [vp, vp, vp, i32, i32, ll, ll, f32, i32, vp],
     "tw_rmsnorm_copy": [vp, vp, vp, i32, i32, ll, ll, f32, i32, vp],
     "tw_add_rmsnorm": [vp, vp, vp, i32, i32, ll, ll, f32, i32, vp],
@@ -88,6 +88,7 @@ class OptionalSymbols:
 
 
 _launches = 0
+_timing = None      # name -> list of (start event, end event) while op timing is on
 
 
 def launch_count() -> int:
@@ -95,11 +96,38 @@ def launch_count() -> int:
     return _launches
 
 
-def call(name: str, *args) -> None:
+def enable_op_timing(on: bool = True) -> None:
+    """Bracket every launcher call with CUDA events (the layer-wise profile of ``utils/profiler.py``)."""
+    global _timing
+    _timing = {} if on else None
+
+
+def op_timing_summary(reset: bool = True) -> dict:
+    """{op name: (calls, total milliseconds)} of the launches recorded since timing was enabled."""
+    import torch
+    global _timing
+    if _timing is None:
+        return {}
+    torch.cuda.synchronize()
+    out = {k: (len(v), sum(a.elapsed_time(b) for a, b in v)) for k, v in _timing.items()}
+    if reset:
+        _timing = {}
+    return out
+
+
+def call(name: str, *args, tag: str = "") -> None:
     global _launches
     lib = load()
     _launches += 1
-    rc = getattr(lib, name)(*args)
+    if _timing is not None:
+        import torch
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        rc = getattr(lib, name)(*args)
+        b.record()
+        _timing.setdefault(name + tag, []).append((a, b))
+    else:
+        rc = getattr(lib, name)(*args)
     if rc != 0:
         msg = lib.tw_last_error()
         raise NativeLibraryError(f"{name} failed: {msg.decode() if msg else 'unknown error'}")

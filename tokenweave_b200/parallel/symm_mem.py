@@ -51,6 +51,12 @@ class SymmetricBuffer:
     def has_multicast(self) -> bool:
         return self.multicast_ptr != 0
 
+    def close(self) -> None:
+        """Collective tear-down (native provider: unbind / unmap behind a barrier)."""
+        if self.provider == "native" and self.handle is not None:
+            self.handle.close()
+        self.handle = None
+
     def reset_signal_pads(self) -> None:
         """Zero this rank's signal pad (after a kernel reported a peer timeout)."""
         if self.provider == "torch" and self.handle is not None:

@@ -93,6 +93,16 @@ class ModelRunner:
         self.capture_logits = False          # tests: keep the fp32 logits of every step
         self.captured_logits: list = []
         self._h2d_done = torch.cuda.Event() if pin else None   # guards reuse of the pinned staging buffers
+        # CUDA graphs: a step whose shape signature has been seen before is replayed from a captured graph
+        self.use_graphs = bool(tw.use_cuda_graphs) and pin
+        self._meta_dev = [torch.zeros(1 << 20, dtype=torch.int32, device=device) if self.use_graphs else None
+                          for _ in range(2)]
+        self._rows_dev = torch.zeros(max(config.scheduler.max_num_seqs, 1), dtype=torch.long, device=device)
+        self._rows_host = torch.zeros(max(config.scheduler.max_num_seqs, 1), dtype=torch.long, pin_memory=pin)
+        self._graphs: dict = {}
+        self._graph_seen: dict = {}
+        self._graph_pool = None
+        self.graph_replays = 0
 
     # ---- set-up -----------------------------------------------------------------------------
     def load_model(self, embedding_parallel: bool = False) -> None:
@@ -128,12 +138,54 @@ class ModelRunner:
         kv_lens = [e[2] for e in entries]
         n = sum(q_lens)
         max_blocks = max((len(tables[e[0]]) for e in entries), default=1)
+        if self.use_graphs:
+            max_blocks = (max_blocks + 15) // 16 * 16      # fewer distinct graph signatures
         bt = np.zeros((len(entries), max(1, max_blocks)), dtype=np.int32)
         for i, e in enumerate(entries):
             t = tables[e[0]]
             bt[i, : len(t)] = t
         return build_attention_metadata(q_lens, kv_lens, positions[tokens_base:tokens_base + n],
-                                        slots[tokens_base:tokens_base + n], bt, self.device, self._meta_host[which])
+                                        slots[tokens_base:tokens_base + n], bt, self.device, self._meta_host[which],
+                                        self._meta_dev[which])
+
+    def _signature(self, step_in: StepInput, n_logits: int, greedy: bool):
+        parts = [step_in.plan, n_logits, greedy]
+        for m in (step_in.meta, step_in.meta0, step_in.meta1):
+            if m is None:
+                parts.append(None)
+                continue
+            hkv = self.model.layers[0].attn.hkv
+            splits = ops.decode_splits(m.num_single, hkv, m.max_kv_len, self.model.rt.sm_count)
+            parts.append((m.num_actual_tokens, m.num_seqs, m.num_tiles, m.num_single, m.block_table.shape[1], splits))
+        return tuple(parts)
+
+    def _forward_and_logits(self, step_in: StepInput, n_logits: int, greedy: bool):
+        hidden = self.model(step_in)
+        if n_logits == 0:
+            return None, None
+        logits = self.model.compute_logits(hidden.index_select(0, self._rows_dev[:n_logits]))
+        return logits, (ops.argmax(logits) if greedy else None)
+
+    def _run_graphed(self, sig, step_in: StepInput, n_logits: int, greedy: bool):
+        """Eager on the first sight of a signature (which also warms every kernel up), capture on the
+        second, replay from then on."""
+        entry = self._graphs.get(sig)
+        if entry is None:
+            seen = self._graph_seen.get(sig, 0)
+            self._graph_seen[sig] = seen + 1
+            if seen == 0 or len(self._graphs) >= 64:
+                return self._forward_and_logits(step_in, n_logits, greedy)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                out = self._forward_and_logits(step_in, n_logits, greedy)
+            entry = (graph, out)
+            self._graphs[sig] = entry
+        entry[0].replay()
+        self.graph_replays += 1
+        return entry[1]
 
     @torch.inference_mode()
     def execute_model(self, step: StepData) -> StepResult:
@@ -189,19 +241,30 @@ class ModelRunner:
         if self.timing_events is not None:
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             ev[0].record()
-        hidden = self.model(step_in)
+        n_logits = len(logits_rows)
+        reqs = [self.requests[r] for r in sample_reqs]
+        greedy = bool(reqs) and all(r.sampling_params.greedy and not r.sampling_params.needs_penalties
+                                    and r.sampling_params.logprobs is None for r in reqs)
+        if n_logits:
+            self._rows_host[:n_logits] = torch.as_tensor(logits_rows, dtype=torch.long)
+            self._rows_dev[:n_logits].copy_(self._rows_host[:n_logits], non_blocking=True)
+        if self.use_graphs and not self.capture_logits:
+            logits, greedy_ids = self._run_graphed(self._signature(step_in, n_logits, greedy), step_in, n_logits, greedy)
+        else:
+            logits, greedy_ids = self._forward_and_logits(step_in, n_logits, greedy)
         sampled: dict[str, int] = {}
         lp = None
         d2h = 0
         if logits_rows:
-            idx = torch.as_tensor(logits_rows, dtype=torch.long, device=self.device)
-            logits = self.model.compute_logits(hidden.index_select(0, idx))
             if self.capture_logits:
                 self.captured_logits.append((list(sample_reqs), logits.detach().float().cpu().clone()))
-            reqs = [self.requests[r] for r in sample_reqs]
-            out = self.sampler(logits, [r.sampling_params for r in reqs], [r.generator for r in reqs],
-                               [r.token_ids[: r.num_prompt_tokens] for r in reqs],
-                               [r.token_ids[r.num_prompt_tokens:] for r in reqs])
+            if greedy_ids is not None:
+                from ..layers.sampler import SamplerOutput
+                out = SamplerOutput(greedy_ids)
+            else:
+                out = self.sampler(logits, [r.sampling_params for r in reqs], [r.generator for r in reqs],
+                                   [r.token_ids[: r.num_prompt_tokens] for r in reqs],
+                                   [r.token_ids[r.num_prompt_tokens:] for r in reqs])
             if ev is not None:
                 ev[1].record()
             toks = out.token_ids.tolist()            # the device -> host synchronisation point of the step

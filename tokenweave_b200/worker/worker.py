@@ -99,7 +99,12 @@ class Worker:
             self.profiler = None
 
     def shutdown(self) -> None:
-        self.runner = None
         if self.device.type == "cuda":
             torch.cuda.synchronize()
+        if self.runner is not None and self.runner.model is not None and self.runner.model.rt is not None:
+            try:
+                self.runner.model.rt.staging.close()
+            except Exception as e:       # tear-down must not mask the caller's error
+                logger.warning("symmetric buffer tear-down failed: %s", e)
+        self.runner = None
         pstate.destroy_distributed()
