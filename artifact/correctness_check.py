@@ -58,7 +58,7 @@ def main() -> None:
         if rank == 0:
             print(f"{mode} vs {base}: {same}/{args.num_prompts} identical continuations, {first_same}/{args.num_prompts} "
                   f"identical first tokens, max |dlogit| {diff:.4f} (max |logit| {scale:.2f})", flush=True)
-        if mode != "no_ar" and diff > 0.1 * max(1.0, scale):
+        if not mode.startswith("no_") and diff > 0.1 * max(1.0, scale):
             ok = False
     if rank == 0:
         print("CORRECTNESS", "PASS" if ok else "FAIL")

@@ -1,0 +1,74 @@
+"""Offline API extras on CPU: chat, sleep / wake-up, sharded state, request tracing, metrics, CLI flags."""
+import argparse
+import json
+
+import torch
+
+from tokenweave_b200 import LLM, SamplingParams
+from tokenweave_b200.config import EngineArgs
+
+
+def _llm(**kw):
+    args = dict(dtype="float32", device="cpu", tokenizer="byte", block_size=16, max_num_batched_tokens=256)
+    args.update(kw)
+    return LLM("tiny-llama", **args)
+
+
+def test_chat_uses_transcript_template():
+    llm = _llm()
+    out = llm.chat([{"role": "user", "content": "hi"}], SamplingParams(temperature=0, max_tokens=4))[0]
+    assert out.prompt == "user: hi\nassistant: " and len(out.outputs[0].token_ids) == 4
+
+
+def test_sleep_wake_up_and_sharded_state(tmp_path):
+    llm = _llm()
+    sp = SamplingParams(temperature=0, max_tokens=6)
+    before = llm.generate("abc", sp)[0].outputs[0].token_ids
+    worker = llm.llm_engine.core.executor.worker
+    llm.sleep(level=1)
+    assert all(p.numel() == 0 for p in worker.runner.model.parameters())
+    assert worker.runner.model.layers[0].attn.k_cache is None
+    llm.wake_up()
+    assert llm.generate("abc", sp)[0].outputs[0].token_ids == before
+    llm.save_sharded_state(str(tmp_path))
+    for p in worker.runner.model.parameters():
+        p.data.zero_()
+    worker.load_sharded_state(str(tmp_path))
+    assert llm.generate("abc", sp)[0].outputs[0].token_ids == before
+
+
+def test_request_tracer_jsonl(tmp_path):
+    from tokenweave_b200.utils.tracing import SPAN_ATTRS, RequestTracer
+    llm = _llm()
+    out = llm.generate("hello", SamplingParams(temperature=0, max_tokens=3))[0]
+    path = tmp_path / "spans.jsonl"
+    tracer = RequestTracer(jsonl_path=str(path))
+    tracer.record(out)
+    tracer.close()
+    span = json.loads(path.read_text().splitlines()[0])
+    assert set(span["attributes"]) == set(SPAN_ATTRS)
+    assert span["attributes"]["gen_ai.usage.completion_tokens"] == 3
+    assert span["attributes"]["gen_ai.latency.e2e"] >= span["attributes"]["gen_ai.latency.time_to_first_token"] >= 0
+
+
+def test_stat_loggers():
+    from tokenweave_b200.utils.metrics import LoggingStatLogger, PrometheusStatLogger, StepStats
+    lg = LoggingStatLogger(interval_s=0.0)
+    lg.record(StepStats(num_tokens=100, num_running=2, num_waiting=1, kv_usage=0.5, num_generated=2))
+    pm = PrometheusStatLogger("tiny")
+    pm.record(StepStats(num_tokens=64, num_running=1, num_waiting=0, kv_usage=0.25, num_generated=1))
+    pm.record_finished(0.1, 0.5)
+    import prometheus_client
+    text = prometheus_client.generate_latest(pm.registry).decode()
+    assert "tokenweave:prompt_tokens_total" in text and "tokenweave:kv_cache_usage" in text
+
+
+def test_engine_args_cli_round_trip():
+    parser = EngineArgs.add_cli_args(argparse.ArgumentParser())
+    ns = parser.parse_args(["--model", "tiny-qwen2", "--tensor-parallel-size", "2", "--max-num-batched-tokens", "4096",
+                            "--tokenweave-mode", "fuse_only", "--no-enable-chunked-prefill"])
+    args = EngineArgs.from_cli_args(ns)
+    cfg = args.create_engine_config()
+    assert cfg.model.architecture == "qwen2" and cfg.model.qkv_bias
+    assert cfg.parallel.tensor_parallel_size == 2 and cfg.scheduler.max_num_batched_tokens == 4096
+    assert cfg.tokenweave.mode == "fuse_only" and cfg.scheduler.enable_chunked_prefill is False

@@ -183,7 +183,8 @@ class TokenWeaveConfig:
       "fuse_only"         fused kernel, no split
       "baseline_multimem" in-kernel all-reduce, separate add+RMSNorm kernel
       "baseline_nccl"     NCCL all-reduce, separate add+RMSNorm kernel
-      "no_ar"             communication deleted (numerically wrong upper bound)
+      "no_ar"             communication deleted (numerically wrong upper bound); also the cost-attribution
+                          variants "no_ar1", "no_ar2", "no_ln1", "no_ln2", "no_ar_no_ln"
     """
     mode: str = "overlap"
     config_path: Optional[str] = None     # JSON: tokens -> {attention_ctas, mlp_ctas, split_offset}

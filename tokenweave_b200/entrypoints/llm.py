@@ -89,6 +89,40 @@ class LLM:
     def stop_profile(self) -> None:
         self.llm_engine.core.executor.profile(False)
 
+    def chat(self, messages, sampling_params: Optional[SamplingParams] = None, add_generation_prompt: bool = True,
+             use_tqdm: bool = False) -> list[RequestOutput]:
+        """Chat completion: ``messages`` is one conversation (a list of ``{"role", "content"}`` dicts) or a
+        list of conversations. Uses the tokenizer's chat template when it has one, else a plain
+        ``role: content`` transcript (vllm/entrypoints/llm.py ``LLM.chat``)."""
+        tok = self.get_tokenizer()
+        if tok is None:
+            raise ValueError("chat() needs a tokenizer")
+        convs = [messages] if messages and isinstance(messages[0], dict) else list(messages)
+        prompts = []
+        for conv in convs:
+            if hasattr(tok, "apply_chat_template") and getattr(tok, "chat_template", None):
+                prompts.append(tok.apply_chat_template(conv, tokenize=False, add_generation_prompt=add_generation_prompt))
+            else:
+                text = "".join(f"{m['role']}: {m['content']}\n" for m in conv)
+                prompts.append(text + ("assistant: " if add_generation_prompt else ""))
+        return self.generate(prompts, sampling_params, use_tqdm=use_tqdm)
+
+    def sleep(self, level: int = 1) -> None:
+        """Release GPU memory between uses: the KV cache is dropped, and at level 1 the weights move to
+        pinned host memory (level 2 discards them). Counterpart of ``LLM.sleep`` / the cumem allocator of
+        the reference (vllm/device_allocator/cumem.py); here tensors are moved, not unmapped."""
+        if self.llm_engine.has_unfinished_requests():
+            raise RuntimeError("cannot sleep with requests in flight")
+        self.collective_rpc("sleep", level)
+
+    def wake_up(self) -> None:
+        self.collective_rpc("wake_up")
+
+    def save_sharded_state(self, path: str) -> None:
+        """Write every rank's already-sharded parameters to ``path/rank_<r>.safetensors`` so that a later
+        start can skip resharding (vllm/v1/worker/gpu_worker.py:273-285)."""
+        self.collective_rpc("save_sharded_state", path)
+
     def shutdown(self) -> None:
         self.llm_engine.shutdown()
 

@@ -158,7 +158,7 @@ class DecoderModel(nn.Module):
         if Tp > T:
             hidden[T:Tp].zero_()
         self.embed_tokens(step.input_ids, out=hidden[:T])
-        pending = self.embed_tokens.parallel and self.tw_mode != "no_ar"
+        pending = self.embed_tokens.parallel and self.tw_mode not in ("no_ar", "no_ar_no_ln")
         if pending:
             residual[:Tp].zero_()
         else:

@@ -57,21 +57,32 @@ def run_baseline(layers: Sequence, final_norm_w: torch.Tensor, hidden: torch.Ten
     T, Tp = plan.num_tokens, plan.padded_tokens
     h, r = hidden[:Tp], residual[:Tp]
 
-    def reduce_norm(w):
-        if mode == "baseline_nccl":
-            comm.nccl_all_reduce_(hidden[:T])
-        elif mode == "baseline_multimem":
-            comm.all_reduce_(h, plan.attention_ctas)
-        ops.add_rmsnorm_(h, r, w, eps)
+    # Cost-attribution variants of the artifact (numerically wrong on purpose): "no_ar" drops every
+    # all-reduce, "no_ar1" / "no_ar2" only the one after attention / after the MLP, "no_ln1" / "no_ln2"
+    # the add+RMSNorm after attention / after the MLP, "no_ar_no_ln" everything between the blocks.
+    base = "baseline_nccl" if mode in ("baseline_nccl", "no_ar1", "no_ar2") else mode
+    skip_ar = {"no_ar": (1, 2), "no_ar1": (1,), "no_ar2": (2,), "no_ar_no_ln": (1, 2)}.get(mode, ())
+    skip_ln = {"no_ln1": (1,), "no_ln2": (2,), "no_ar_no_ln": (1, 2)}.get(mode, ())
+    if mode in ("no_ln1", "no_ln2"):
+        base = "baseline_multimem"
+
+    def reduce_norm(w, which):
+        if which not in skip_ar:
+            if base == "baseline_nccl":
+                comm.nccl_all_reduce_(hidden[:T])
+            elif base == "baseline_multimem":
+                comm.all_reduce_(h, plan.attention_ctas)
+        if which not in skip_ln:
+            ops.add_rmsnorm_(h, r, w, eps)
 
     if first_pending:
-        reduce_norm(layers[0].input_norm_w)
+        reduce_norm(layers[0].input_norm_w, 0)
     for i, layer in enumerate(layers):
         next_w = layers[i + 1].input_norm_w if i + 1 < len(layers) else final_norm_w
         layer.attn_block(h, T, meta, rt, 0)
-        reduce_norm(layer.post_norm_w)
+        reduce_norm(layer.post_norm_w, 1)
         layer.mlp_block(h, T, rt, 0)
-        reduce_norm(next_w)
+        reduce_norm(next_w, 2)
 
 
 def run_overlap(layers: Sequence, final_norm_w: torch.Tensor, hidden: torch.Tensor, residual: torch.Tensor,

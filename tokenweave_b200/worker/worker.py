@@ -98,6 +98,58 @@ class Worker:
             self.profiler.stop()
             self.profiler = None
 
+    # ---- sleep / wake (weights to host memory, KV cache dropped) ----
+    def sleep(self, level: int = 1) -> None:
+        model = self.runner.model
+        self._sleeping = {}
+        self._param_shapes = {n: tuple(p.shape) for n, p in model.named_parameters()}
+        for name, p in model.named_parameters():
+            if level == 1:
+                host = torch.empty(p.shape, dtype=p.dtype, pin_memory=(self.device.type == "cuda"))
+                host.copy_(p.data)
+                self._sleeping[name] = host
+            p.data = torch.empty(0, dtype=p.dtype, device=self.device)
+        self._kv_shape = None
+        for layer in model.layers:
+            if layer.attn.k_cache is not None:
+                self._kv_shape = tuple(layer.attn.k_cache.shape)
+            layer.attn.bind_kv_cache(None, None)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+
+    def wake_up(self) -> None:
+        model = self.runner.model
+        saved = getattr(self, "_sleeping", None)
+        if saved is None:
+            return
+        if saved:
+            for name, p in model.named_parameters():
+                p.data = saved[name].to(self.device, non_blocking=True)
+        else:
+            # level 2 discarded the weights: bring them back from the checkpoint (or re-draw them)
+            from ..models.loader import load_model_weights
+            for name, p in model.named_parameters():
+                p.data = torch.empty(self._param_shapes[name], dtype=p.dtype, device=self.device)
+            load_model_weights(model, self.config)
+        if self._kv_shape is not None:
+            self.runner.init_kv_cache(self._kv_shape[0])
+        self._sleeping = None
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+
+    def save_sharded_state(self, path: str) -> None:
+        from safetensors.torch import save_file
+        os.makedirs(path, exist_ok=True)
+        state = {n: p.detach().cpu().contiguous() for n, p in self.runner.model.named_parameters()}
+        save_file(state, os.path.join(path, f"rank_{self.rank}.safetensors"))
+
+    def load_sharded_state(self, path: str) -> None:
+        from safetensors.torch import load_file
+        state = load_file(os.path.join(path, f"rank_{self.rank}.safetensors"))
+        for n, p in self.runner.model.named_parameters():
+            p.data.copy_(state[n])
+
     def shutdown(self) -> None:
         if self.device.type == "cuda":
             torch.cuda.synchronize()
