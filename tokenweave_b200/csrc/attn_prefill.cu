@@ -47,7 +47,8 @@ struct AttnSmem {
   static constexpr int HALVES = D / 64;
   static constexpr int Q_BYTES = HALVES * ATT_HALF_BYTES;
   static constexpr int KV_BYTES = HALVES * ATT_HALF_BYTES;  // one K or V tile
-  static constexpr int P_BYTES = 2 * ATT_HALF_BYTES;
+  static constexpr int P_ONE = 2 * ATT_HALF_BYTES;          // one P tile (128 rows x 128 keys, bf16)
+  static constexpr int P_BYTES = 2 * P_ONE;                 // double-buffered
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
@@ -78,9 +79,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* v_full = bars + 5;   // [2]
   uint64_t* v_empty = bars + 7;  // [2]
   uint64_t* s_full = bars + 9;   // [2]
-  uint64_t* p_ready = bars + 11;
-  uint64_t* o_done = bars + 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* p_ready = bars + 11; // [2] one per P buffer
+  uint64_t* o_done = bars + 13;  // [2] P_j V_j complete, indexed by j & 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -109,8 +110,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
     }
-    mbar_init(p_ready, 128);
-    mbar_init(o_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&p_ready[i], 128);
+      mbar_init(&o_done[i], 1);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -189,19 +192,20 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (!ok) break;
         }
         const int st = j & 1;
-        if (!mbar_wait(p_ready, j & 1)) { ok = false; break; }
+        if (!mbar_wait(&p_ready[st], (j >> 1) & 1)) { ok = false; break; }
         if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(smem + S::OFF_V + st * S::KV_BYTES);
+        const uint32_t pj_addr = p_addr + st * S::P_ONE;
 #pragma unroll
         for (int k = 0; k < ATT_BN / 16; ++k) {
           const uint32_t a_off = (k >> 2) * ATT_HALF_BYTES + (k & 3) * 32;
-          umma_ss(tmem_base + COL_O, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
+          umma_ss(tmem_base + COL_O, make_smem_desc_sw128(pj_addr + a_off, 16, 1024),
                   make_smem_desc_sw128(v_addr + k * 16 * 128, ATT_HALF_BYTES, 1024), IDESC_PV,
                   (j | k) != 0 ? 1u : 0u);
         }
         umma_commit(&v_empty[st]);
-        umma_commit(o_done);
+        umma_commit(&o_done[st]);
       }
       if (!ok) {
         report_error(p.status, TW_ERR_MBAR_TIMEOUT);
@@ -252,11 +256,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         m_ref = mx;
         rescale = true;
       }
+      // P is double-buffered: buffer j&1 was last read by P_{j-2} V_{j-2}. O may only be touched once
+      // P_{j-1} V_{j-1} has completed, which the (rare) rescale waits for on its own.
+      if (j > 1) {
+        if (!mbar_wait(&o_done[sb], ((j - 2) >> 1) & 1)) { ok = false; break; }
+      }
       if (j > 0) {
-        // P buffer and O are free once P_{j-1} V_{j-1} has completed.
-        if (!mbar_wait(o_done, (j - 1) & 1)) { ok = false; break; }
-        tc_fence_after_sync();
         if (__any_sync(0xffffffffu, rescale)) {
+          if (!mbar_wait(&o_done[sb ^ 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
+          tc_fence_after_sync();
           l_sum *= alpha;
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
@@ -289,7 +297,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           pk[i] = pack_bf16x2(a, b);
         }
         // columns c*32 .. c*32+31 of the row: key half (c >> 1), 16-byte chunks (c & 1)*4 .. +3
-        uint8_t* dst = p_row + (c >> 1) * ATT_HALF_BYTES;
+        uint8_t* dst = p_row + sb * S::P_ONE + (c >> 1) * ATT_HALF_BYTES;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
@@ -299,9 +307,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       tc_fence_before_sync();
       fence_proxy_async_smem();
-      mbar_arrive(p_ready);
+      mbar_arrive(&p_ready[sb]);
     }
-    if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1);
+    if (ok) ok = mbar_wait(&o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
     if (ok) {
       tc_fence_after_sync();
       const float inv = 1.f / l_sum;

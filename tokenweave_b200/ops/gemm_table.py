@@ -26,6 +26,10 @@ def _load() -> dict:
     global _table
     if _table is None:
         _table = {}
+        forced = os.environ.get("TW_GEMM_KERNEL")       # "1": single-CTA tiles only, "2": CTA pairs only
+        if forced in ("1", "2"):
+            from . import _native
+            _native.load().tw_gemm_set_kernel_override(int(forced))
         path = CONFIG_DIR / "NVIDIA_B200.json"
         if path.exists() and not _disabled:
             with open(path) as f:
