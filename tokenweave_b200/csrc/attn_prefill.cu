@@ -2,7 +2,7 @@
 // prefill). Replaces the FlashAttention-2 varlen call the reference falls back to on Blackwell
 // (vllm/v1/attention/backends/flash_attn.py:713-733, vllm/attention/utils/fa_utils.py:29-34).
 //
-// One CTA per (128-query tile, query head), 192 threads:
+// One CTA per (128-query tile, query head), 320 threads:
 //   warp 0      TMA producer: the Q tile once, then K and V tiles of 128 keys, one
 //               cp.async.bulk.tensor.4d per cache page and 64-column half, straight from the
 //               paged cache [blocks, page, kv_heads, D] through the request's block table
@@ -10,11 +10,12 @@
 //                 S[j&1] = Q K_j^T     (M=128, N=128, K=D, both operands K-major)
 //                 O     += P_j V_j      (M=128, N=D,   K=128, V is an MN-major operand)
 //               S is double-buffered, so Q K_{j+1}^T runs while the softmax of tile j does.
-//   warps 2..5  softmax: thread r owns query row r. Pass 1 reads S from TMEM for the row
-//               maximum, pass 2 re-reads it, exponentiates (exp2, scale folded in), writes bf16
-//               P into shared memory in the swizzled K-major operand layout. O stays in TMEM
-//               across tiles and is rescaled only when the running maximum grows by more than
-//               2^8 (the stale maximum is a valid softmax reference; P stays below 256).
+//   warps 2..9  softmax: TWO threads per query row, each owning 64 of the tile's 128 keys. A thread
+//               reads its half row of S from TMEM once (64 registers), the two halves exchange their
+//               maxima through shared memory, then exponentiate (exp2, scale folded in) and write
+//               bf16 P into shared memory in the swizzled K-major operand layout. O stays in TMEM
+//               across tiles and is rescaled only when the running maximum grows by more than 2^8
+//               (the stale maximum is a valid softmax reference; P stays below 256).
 // Every wait is bounded; a timeout reports TW_ERR_MBAR_TIMEOUT and leaves by the tear-down.
 #include "tw_common.cuh"
 #include "tw_host.h"
@@ -24,7 +25,8 @@ namespace tw {
 
 constexpr int ATT_BM = 128;      // query rows per CTA
 constexpr int ATT_BN = 128;      // keys per tile
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_SOFTMAX_THREADS = 256;
+constexpr int ATT_THREADS = 64 + ATT_SOFTMAX_THREADS;
 constexpr int ATT_HALF_BYTES = 128 * 128;  // a [128 rows x 64 bf16] swizzled half tile
 
 struct AttnParams {
@@ -47,15 +49,19 @@ struct AttnSmem {
   static constexpr int HALVES = D / 64;
   static constexpr int Q_BYTES = HALVES * ATT_HALF_BYTES;
   static constexpr int KV_BYTES = HALVES * ATT_HALF_BYTES;  // one K or V tile
-  static constexpr int P_ONE = 2 * ATT_HALF_BYTES;          // one P tile (128 rows x 128 keys, bf16)
-  static constexpr int P_BYTES = 2 * P_ONE;                 // double-buffered
+  static constexpr int P_BYTES = 2 * ATT_HALF_BYTES;        // 128 rows x 128 keys, bf16
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
   static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
   static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_XCHG = OFF_BAR + 256;            // float [2 parities][2 halves][128 rows]
+  static constexpr int TOTAL = OFF_XCHG + 2 * 2 * 128 * 4 + 1024;
 };
+
+__device__ __forceinline__ void softmax_group_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(ATT_SOFTMAX_THREADS) : "memory");
+}
 
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -63,6 +69,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   using S = AttnSmem<D>;
   constexpr int HALVES = S::HALVES;
+  constexpr int OCOLS = D / 2;     // O columns per softmax thread
   constexpr uint32_t IDESC_QK = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);
   constexpr uint32_t IDESC_PV = make_idesc_bf16(ATT_BM, D, 0, 1);
   constexpr uint32_t TMEM_COLS = 512;
@@ -79,10 +86,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* v_full = bars + 5;   // [2]
   uint64_t* v_empty = bars + 7;  // [2]
   uint64_t* s_full = bars + 9;   // [2]
-  uint64_t* p_ready = bars + 11; // [2] one per P buffer
-  uint64_t* o_done = bars + 13;  // [2] P_j V_j complete, indexed by j & 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* p_ready = bars + 11;
+  uint64_t* o_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xchg = reinterpret_cast<float*>(smem + S::OFF_XCHG);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -110,10 +118,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&p_ready[i], 128);
-      mbar_init(&o_done[i], 1);
-    }
+    mbar_init(p_ready, ATT_SOFTMAX_THREADS);
+    mbar_init(o_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -192,20 +198,19 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (!ok) break;
         }
         const int st = j & 1;
-        if (!mbar_wait(&p_ready[st], (j >> 1) & 1)) { ok = false; break; }
+        if (!mbar_wait(p_ready, j & 1)) { ok = false; break; }
         if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(smem + S::OFF_V + st * S::KV_BYTES);
-        const uint32_t pj_addr = p_addr + st * S::P_ONE;
 #pragma unroll
         for (int k = 0; k < ATT_BN / 16; ++k) {
           const uint32_t a_off = (k >> 2) * ATT_HALF_BYTES + (k & 3) * 32;
-          umma_ss(tmem_base + COL_O, make_smem_desc_sw128(pj_addr + a_off, 16, 1024),
+          umma_ss(tmem_base + COL_O, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
                   make_smem_desc_sw128(v_addr + k * 16 * 128, ATT_HALF_BYTES, 1024), IDESC_PV,
                   (j | k) != 0 ? 1u : 0u);
         }
         umma_commit(&v_empty[st]);
-        umma_commit(&o_done[st]);
+        umma_commit(o_done);
       }
       if (!ok) {
         report_error(p.status, TW_ERR_MBAR_TIMEOUT);
@@ -213,40 +218,45 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
     }
   } else if (n_tiles > 0) {
-    // ---------------- softmax + epilogue (warps 2..5) ----------------
-    const int qr = warp & 3;
+    // ---------------- softmax + epilogue (warps 2..9, two threads per row) ----------------
+    const int qr = warp & 3;                        // TMEM lane quarter of this warp
+    const int kh = (warp - 2) >> 2;                 // which 64-key half of the tile this thread owns
     const int r = qr * 32 + lane;                   // row within the tile
     const int pos = pos0 + min(r, rows_valid - 1);  // padding rows copy the last valid row's mask
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(qr * 32) << 16);
-    uint8_t* p_row = smem + S::OFF_P + r * 128;
+    uint8_t* p_half = smem + S::OFF_P + kh * ATT_HALF_BYTES + r * 128;
     float m_ref = -INFINITY;  // softmax reference (a stale running maximum), log2 domain
-    float l_sum = 0.f;
+    float l_sum = 0.f;        // this thread's half of the row sum
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
+      // The trip count is the same for all 256 threads whatever happens (the named barrier below is
+      // unbounded): after a failed wait the remaining waits are skipped, not the iterations.
       const int sb = j & 1;
-      if (!mbar_wait(&s_full[sb], (j >> 1) & 1)) { ok = false; break; }
+      if (ok) ok = mbar_wait(&s_full[sb], (j >> 1) & 1);
       tc_fence_after_sync();
-      const uint32_t t_s = t_lane + COL_S + sb * ATT_BN;
-      const int k_base = j * ATT_BN;
+      const uint32_t t_s = t_lane + COL_S + sb * ATT_BN + kh * 64;
+      const int k_base = j * ATT_BN + kh * 64;      // first key of this thread's half
+      uint32_t s0[32], s1[32];
+      tmem_ld_32x32(t_s, s0);
+      tmem_ld_32x32(t_s + 32, s1);
+      tmem_wait_ld();
       // warp-uniform: lane 0 holds the smallest position of the warp
-      const bool need_mask = (k_base + ATT_BN - 1) > __shfl_sync(0xffffffffu, pos, 0);
-      // pass 1: row maximum
+      const bool need_mask = (k_base + 63) > __shfl_sync(0xffffffffu, pos, 0);
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + c * 32, v);
-        tmem_wait_ld();
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k_base + c * 32 + i <= pos) mx = fmaxf(mx, __uint_as_float(v[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        for (int i = 0; i < 32; ++i) {
+          if (k_base + i > pos) s0[i] = __float_as_uint(-INFINITY);
+          if (k_base + 32 + i > pos) s1[i] = __float_as_uint(-INFINITY);
         }
       }
-      mx *= p.scale_log2;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+      // the two halves of a row agree on the tile's maximum
+      float* xm = xchg + (j & 1) * 256;
+      xm[kh * 128 + r] = mx;
+      softmax_group_sync();
+      mx = fmaxf(mx, xm[(kh ^ 1) * 128 + r]) * p.scale_log2;
       float alpha = 1.f;
       bool rescale = false;
       if (j == 0) {
@@ -256,68 +266,62 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         m_ref = mx;
         rescale = true;
       }
-      // P is double-buffered: buffer j&1 was last read by P_{j-2} V_{j-2}. O may only be touched once
-      // P_{j-1} V_{j-1} has completed, which the (rare) rescale waits for on its own.
-      if (j > 1) {
-        if (!mbar_wait(&o_done[sb], ((j - 2) >> 1) & 1)) { ok = false; break; }
+      // probabilities of this half row, packed to bf16 in registers
+      uint32_t pk[32];
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a = exp2f(__uint_as_float(s0[2 * i]) * p.scale_log2 - m_ref);
+        const float b = exp2f(__uint_as_float(s0[2 * i + 1]) * p.scale_log2 - m_ref);
+        const float c = exp2f(__uint_as_float(s1[2 * i]) * p.scale_log2 - m_ref);
+        const float d = exp2f(__uint_as_float(s1[2 * i + 1]) * p.scale_log2 - m_ref);
+        part += (a + b) + (c + d);
+        pk[i] = pack_bf16x2(a, b);
+        pk[16 + i] = pack_bf16x2(c, d);
       }
+      l_sum = l_sum * alpha + part;
       if (j > 0) {
+        // the P buffer and O are free once P_{j-1} V_{j-1} has completed
+        if (ok) ok = mbar_wait(o_done, (j - 1) & 1);
+        tc_fence_after_sync();
         if (__any_sync(0xffffffffu, rescale)) {
-          if (!mbar_wait(&o_done[sb ^ 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
-          tc_fence_after_sync();
-          l_sum *= alpha;
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
+          for (int c = 0; c < OCOLS / 32; ++c) {
             uint32_t v[32];
-            tmem_ld_32x32(t_lane + COL_O + c * 32, v);
+            tmem_ld_32x32(t_lane + COL_O + kh * OCOLS + c * 32, v);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32(t_lane + COL_O + c * 32, v);
+            tmem_st_32x32(t_lane + COL_O + kh * OCOLS + c * 32, v);
           }
           tmem_wait_st();
         }
       }
-      // pass 2: probabilities -> shared memory (bf16, swizzled K-major operand layout)
-#pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + c * 32, v);
-        tmem_wait_ld();
-        uint32_t pk[16];
+      // 64 keys = eight 16-byte chunks of this row in the swizzled K-major operand layout
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float a = exp2f(__uint_as_float(v[2 * i]) * p.scale_log2 - m_ref);
-          float b = exp2f(__uint_as_float(v[2 * i + 1]) * p.scale_log2 - m_ref);
-          if (need_mask) {
-            if (k_base + c * 32 + 2 * i > pos) a = 0.f;
-            if (k_base + c * 32 + 2 * i + 1 > pos) b = 0.f;
-          }
-          l_sum += a + b;
-          pk[i] = pack_bf16x2(a, b);
-        }
-        // columns c*32 .. c*32+31 of the row: key half (c >> 1), 16-byte chunks (c & 1)*4 .. +3
-        uint8_t* dst = p_row + sb * S::P_ONE + (c >> 1) * ATT_HALF_BYTES;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
-          *reinterpret_cast<uint4*>(dst + chunk * 16) =
-              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-        }
+      for (int q8 = 0; q8 < 8; ++q8) {
+        const int chunk = q8 ^ (r & 7);
+        *reinterpret_cast<uint4*>(p_half + chunk * 16) =
+            make_uint4(pk[4 * q8], pk[4 * q8 + 1], pk[4 * q8 + 2], pk[4 * q8 + 3]);
       }
       tc_fence_before_sync();
       fence_proxy_async_smem();
-      mbar_arrive(&p_ready[sb]);
+      mbar_arrive(p_ready);     // arrive even after a failed wait so the issuer is not left hanging
     }
-    if (ok) ok = mbar_wait(&o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
+    if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1);
+    // row sum = the two halves' partial sums
+    float* xs = xchg + (n_tiles & 1) * 256;
+    xs[kh * 128 + r] = l_sum;
+    softmax_group_sync();
+    const float l_row = l_sum + xs[(kh ^ 1) * 128 + r];
     if (ok) {
       tc_fence_after_sync();
-      const float inv = 1.f / l_sum;
-      __nv_bfloat16* orow = p.out + static_cast<long long>(q_begin + q0 + r) * p.ldo + head * D;
+      const float inv = 1.f / l_row;
+      __nv_bfloat16* orow = p.out + static_cast<long long>(q_begin + q0 + r) * p.ldo + head * D + kh * OCOLS;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < OCOLS / 32; ++c) {
         uint32_t v[32];
-        tmem_ld_32x32(t_lane + COL_O + c * 32, v);
+        tmem_ld_32x32(t_lane + COL_O + kh * OCOLS + c * 32, v);
         tmem_wait_ld();
         if (r < rows_valid) {
 #pragma unroll
