@@ -55,7 +55,8 @@ def _spmd_rank(rank, world, path, prompts, mode, expect_toks, expect_logits_path
 
 @pytest.mark.parametrize("arch,mode,emb_parallel", [
     ("tiny-llama", "overlap", False), ("tiny-llama", "fuse_only", True), ("tiny-llama", "baseline_nccl", False),
-    ("tiny-qwen2", "overlap", True), ("tiny-mixtral", "overlap", False)])
+    ("tiny-qwen2", "overlap", True), ("tiny-mixtral", "overlap", False), ("tiny-llama", "fused_gemm", False),
+    ("tiny-mixtral", "fused_gemm", False)])
 def test_spmd_tp2_matches_single_process(tmp_path, arch, mode, emb_parallel):
     cfg = _ckpt(tmp_path, arch)
     prompts = _prompts(cfg.vocab_size, [150, 40, 90, 9])      # 289 tokens: overlap schedule with a straddling request

@@ -70,7 +70,10 @@ def _rank(rank, world, path, prompts, mode, expect_path, transport):
                                                  ("tiny-llama-d128", "baseline_nccl", "multimem"),
                                                  ("tiny-llama-d128", "baseline_multimem", "multimem"),
                                                  ("tiny-qwen2", "overlap", "p2p"),
-                                                 ("tiny-mixtral", "overlap", "multimem")])
+                                                 ("tiny-mixtral", "overlap", "multimem"),
+                                                 ("tiny-llama-d128", "fused_gemm", "multimem"),
+                                                 ("tiny-qwen2", "fused_gemm", "p2p"),
+                                                 ("tiny-mixtral", "fused_gemm", "multimem")])
 def test_tp2_matches_single_gpu(tmp_path, arch, mode, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")

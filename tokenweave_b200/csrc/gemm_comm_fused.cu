@@ -284,6 +284,21 @@ __device__ void ag_role(const FusedGemmParams& p, uint32_t epoch) {
   }
 }
 
+// Every CTA of tw_ag_gemm read the call counter when it started; the counter moves on only after the
+// last CTA of the grid is done (p.epoch[1] counts finished CTAs), so a CTA that starts late still sees
+// the value its peers saw.
+__device__ __forceinline__ void finish_epoch(const FusedGemmParams& p, uint32_t epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.epoch + 1, 1u) + 1u == gridDim.x) {
+      p.epoch[1] = 0;
+      __threadfence();
+      p.epoch[0] = epoch;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // MODE 0: tw_gemm_rs_norm (GEMM tiles signal their owners), MODE 1: tw_ag_gemm (tiles wait for shards).
 template <int MODE, bool SWIGLU>
@@ -310,6 +325,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // ---------------- communication CTAs ----------------
     if (MODE == 0) rs_norm_role(p, scratch, &s_ok);
     else ag_role(p, epoch);
+    if (MODE == 1) finish_epoch(p, epoch);
     return;
   }
 
@@ -536,7 +552,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, FG_TMEM_COLS);
   }
-  if (MODE == 1 && blockIdx.x == p.comm_ctas && threadIdx.x == 0) *p.epoch = epoch;   // next call's base
+  if (MODE == 1) finish_epoch(p, epoch);
 }
 
 static int pick_bn(int M, int N, int gemm_ctas, bool swiglu) {

@@ -23,7 +23,7 @@ constexpr int MOE_MAX_TOPK = 8;
 
 // One warp per token, persistent CTAs. The gate weight [E, H] lives in shared memory.
 template <int E>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 moe_router_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                   const __nv_bfloat16* __restrict__ wg, float* __restrict__ topk_w,
                   int* __restrict__ topk_ids, float* __restrict__ logits_out, int T, int H, int topk,
@@ -230,7 +230,7 @@ extern "C" int tw_moe_router(const void* x, long long ldx, const void* wg, float
     set_last_error("moe_router: gate weight (%zu bytes) does not fit in shared memory", smem);
     return 1;
   }
-  int grid = (T + 7) / 8;
+  int grid = (T + 31) / 32;
   const int cap = device_sm_count();
   if (grid > cap) grid = cap;
   auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -239,7 +239,7 @@ extern "C" int tw_moe_router(const void* x, long long ldx, const void* wg, float
   case NE: {                                                                                        \
     auto kern = moe_router_kernel<NE>;                                                              \
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-    kern<<<grid, 256, smem, stream>>>(xb, ldx, wb, topk_w, topk_ids, logits_out, T, H, topk,        \
+    kern<<<grid, 1024, smem, stream>>>(xb, ldx, wb, topk_w, topk_ids, logits_out, T, H, topk,        \
                                       renormalize);                                                 \
     break;                                                                                          \
   }

@@ -67,6 +67,11 @@ class Runtime:
         inter = cfg.intermediate_size // tp.world_size
         self.act = None if cfg.is_moe else torch.zeros(rows, inter, dtype=dt, device=device)
         self.comm = TPCommunicator(self.staging, tp, tw_cfg.wait_budget_ms, tw_cfg.transport)
+        self.flag_buf = None
+        if self.comm.in_kernel:
+            # tile counters and shard epochs of the GEMM kernels that are fused with their collectives
+            self.flag_buf = create_symmetric_buffer(1, 8192, dt, tp, provider, allow_multicast=False)
+            self.comm.attach_flag_buffer(self.flag_buf)
         if device.type == "cuda":
             self.comm_stream = torch.cuda.Stream(device=device, priority=-1)
             self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
@@ -102,6 +107,21 @@ class DecoderLayer(nn.Module):
         qkv = self.qkv_proj(rows[:n], out=rt.qkv[:n], max_ctas=max_ctas)
         attn_out = self.attn(qkv, rt.cos_sin, meta, rt.attn_out[:n])
         self.o_proj(attn_out, out=rows[:n], max_ctas=max_ctas)
+
+    # ---- the same blocks with every GEMM fused with its neighbouring collective ----
+    def attn_block_fused(self, rows: torch.Tensor, n: int, meta: AttentionMetadata, rt: Runtime, comm, residual,
+                         eps: float, comm_ctas: int, gathered: bool) -> None:
+        """rows: [T_pad, H]; on entry this rank's shard holds the normalised input (all rows if ``gathered``);
+        on exit this rank's shard holds the post-attention-norm output and its residual shard is updated."""
+        qkv = comm.ag_gemm(rows, self.qkv_proj.weight, rt.qkv, n, bias=self.qkv_proj.bias, comm_ctas=comm_ctas,
+                           gathered=gathered)
+        attn_out = self.attn(qkv, rt.cos_sin, meta, rt.attn_out[:n])
+        comm.gemm_rs_norm_(attn_out, self.o_proj.weight, rows, n, residual, self.post_norm_w, eps, comm_ctas)
+
+    def mlp_block_fused(self, rows: torch.Tensor, n: int, rt: Runtime, comm, residual, next_norm_w, eps: float,
+                        comm_ctas: int) -> None:
+        act = comm.ag_gemm(rows, self.gate_up_proj.weight, rt.act, n, swiglu=True, comm_ctas=comm_ctas)
+        comm.gemm_rs_norm_(act, self.down_proj.weight, rows, n, residual, next_norm_w, eps, comm_ctas)
 
     def mlp_block(self, rows: torch.Tensor, n: int, rt: Runtime, max_ctas: int) -> None:
         if n == 0:
@@ -168,6 +188,9 @@ class DecoderModel(nn.Module):
         if plan.overlap:
             schedule.run_overlap(self.layers, self.norm_w, hidden, residual, step.meta0, step.meta1, plan, rt.comm,
                                  rt, eps, pending)
+        elif self.tw_mode == "fused_gemm":
+            schedule.run_fused_gemm(self.layers, self.norm_w, hidden, residual, step.meta, plan, rt.comm, rt, eps,
+                                    pending)
         elif self.tw_mode in ("overlap", "fuse_only"):
             schedule.run_fuse_only(self.layers, self.norm_w, hidden, residual, step.meta, plan, rt.comm, rt, eps,
                                    pending)

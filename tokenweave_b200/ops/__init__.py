@@ -228,9 +228,10 @@ _decode_ws: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 def decode_splits(n_tok: int, hkv: int, max_kv_len: int, sm_count: int = 148) -> int:
     """How many ways the keys are split so that a small decode batch still fills the machine."""
     ctas = n_tok * hkv
-    if ctas == 0 or ctas >= 2 * sm_count or max_kv_len <= 512:
+    want = 8 * sm_count          # 4-warp CTAs: eight per SM hide the cache-line latency of the key walk
+    if ctas == 0 or ctas >= want or max_kv_len <= 512:
         return 1
-    return max(1, min(32, (2 * sm_count) // ctas, (max_kv_len + 255) // 256))
+    return max(1, min(32, (want + ctas - 1) // ctas, (max_kv_len + 255) // 256))
 
 
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,

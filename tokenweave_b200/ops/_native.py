@@ -38,6 +38,10 @@ _SIGNATURES = {
     "tw_collective": [vp, vp, vp, i32, i32, i32, u64, vp, ll, ll, i32, i32, vp],
     "tw_oneshot_allreduce": [vp, vp, i32, i32, i32, u64, vp, ll, ll, vp, i32, vp],
     "tw_wait_probe": [vp, u64, vp, vp],
+    "tw_gemm_rs_norm": [vp, ll, vp, ll, i32, i32, i32, vp, vp, vp, vp, vp, i32, i32, u64, vp, ll, i32, vp, ll, vp, f32,
+                        i32, i32, vp],
+    "tw_ag_gemm": [vp, vp, ll, ll, vp, ll, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, i32, u64, vp, ll, i32, i32,
+                   i32, vp],
 }
 
 

@@ -129,3 +129,77 @@ class TPCommunicator:
     def nccl_all_reduce_(self, x: torch.Tensor) -> None:
         if self.world > 1:
             dist.all_reduce(x, group=self.tp.group)
+
+    # ---- GEMM fused with its collective (one kernel each) ----------------------------------
+    FLAG_WORDS_PER_REGION = 256      # 128 tile counters (+128 "done" counters share the range), then epochs
+
+    def attach_flag_buffer(self, flags: "SymmetricBuffer") -> None:
+        """A small zero-initialised symmetric buffer for the tile counters and shard epochs of the fused
+        GEMM kernels (two regions: token subset 0 / unsplit, and subset 1)."""
+        self.flags = flags
+        self._flag_tables = {}
+        self._epochs = torch.zeros(4, dtype=torch.int32, device=flags.tensor.device)
+
+    def _flag_table(self, region: int, which: str) -> int:
+        key = (region, which)
+        t = self._flag_tables.get(key)
+        if t is None:
+            word = region * 512 + (0 if which == "tile" else 256)
+            t = self.flags.pointer_table(word * 4)
+            self._flag_tables[key] = t
+        return t.data_ptr()
+
+    def fused_gemm_available(self, rows_view: torch.Tensor) -> bool:
+        T, H = rows_view.shape
+        return (self.in_kernel and getattr(self, "flags", None) is not None and H <= 8192 and T % self.world == 0
+                and T // self.world <= 128 * 128)
+
+    def gemm_rs_norm_(self, a: torch.Tensor, w: torch.Tensor, out_rows: torch.Tensor, M: int, residual: torch.Tensor,
+                      norm_w: torch.Tensor, eps: float, comm_ctas: int = 8, bias: Optional[torch.Tensor] = None,
+                      region: int = 0, max_ctas: int = 0) -> None:
+        """``out_rows`` ([T, H] rows of the symmetric buffer) receives this rank's partial sums
+        ``a[:M] @ w.T``; when the kernel returns, this rank's shard of ``out_rows`` holds
+        ``rmsnorm(sum over ranks + residual) * norm_w`` and its shard of ``residual`` is updated. Other rows
+        of ``out_rows`` are stale until an all-gather (``ag_gemm`` or ``all_gather_``)."""
+        T, H = out_rows.shape
+        if self.world == 1:
+            ops.gemm(a[:M], w, out=out_rows[:M], bias=bias)
+            ops.add_rmsnorm_(out_rows, residual, norm_w, eps)
+            return
+        if not self.fused_gemm_available(out_rows):
+            ops.gemm(a[:M], w, out=out_rows[:M], bias=bias if self.tp.rank == 0 else None)
+            if self.in_kernel:
+                self.fused_allreduce_add_rmsnorm_(out_rows, residual, norm_w, eps, max_ctas=max(comm_ctas, 8), mode=1)
+            else:
+                dist.all_reduce(out_rows, group=self.tp.group)
+                ops.add_rmsnorm_(out_rows, residual, norm_w, eps)
+            return
+        rpr = T // self.world
+        shard_res = residual[self.tp.rank * rpr:(self.tp.rank + 1) * rpr]
+        _native.call("tw_gemm_rs_norm", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), M, H, a.shape[1],
+                     None if (bias is None or self.tp.rank != 0) else bias.data_ptr(), out_rows.data_ptr(), self._mc(),
+                     self.buf.peer_ptrs_dev, self._flag_table(region, "tile"), self.tp.rank, self.world,
+                     self.budget_ns, ops.status_word(a.device).data_ptr(), self.buf.byte_offset(out_rows), T,
+                     shard_res.data_ptr(), shard_res.stride(0), norm_w.data_ptr(), eps, comm_ctas, max_ctas,
+                     torch.cuda.current_stream().cuda_stream)
+
+    def ag_gemm(self, in_rows: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, swiglu: bool = False,
+                bias: Optional[torch.Tensor] = None, comm_ctas: int = 8, region: int = 0, max_ctas: int = 0,
+                gathered: bool = False) -> torch.Tensor:
+        """All-gather of ``in_rows`` (each rank holds its own shard of the [T, H] rows) fused with
+        ``out[:M] = in_rows[:M] @ w.T`` (optionally SwiGLU / bias). With ``gathered=True`` the rows are
+        already complete on every rank and only the GEMM runs."""
+        T, H = in_rows.shape
+        if gathered or self.world == 1 or not self.in_kernel:
+            return ops.gemm(in_rows[:M], w, out=out[:M], bias=bias, swiglu=swiglu, max_ctas=max_ctas)
+        if not self.fused_gemm_available(in_rows):
+            self.all_gather_(in_rows, max_ctas=max(comm_ctas, 8))
+            return ops.gemm(in_rows[:M], w, out=out[:M], bias=bias, swiglu=swiglu, max_ctas=max_ctas)
+        rows_b = w.shape[0]
+        N = rows_b // 2 if swiglu else rows_b
+        _native.call("tw_ag_gemm", in_rows.data_ptr(), w.data_ptr(), w.stride(0), rows_b, out.data_ptr(), out.stride(0),
+                     None if bias is None else bias.data_ptr(), M, N, H, int(swiglu), N if swiglu else 0, self._mc(),
+                     self.buf.peer_ptrs_dev, self._flag_table(region, "shard"), self._epochs[2 * region:].data_ptr(),
+                     self.tp.rank, self.world, self.budget_ns, ops.status_word(in_rows.device).data_ptr(),
+                     self.buf.byte_offset(in_rows), T, comm_ctas, max_ctas, torch.cuda.current_stream().cuda_stream)
+        return out[:M]

@@ -35,6 +35,11 @@ class SymmetricBuffer:
     provider: str = "local"
     handle: object = None                  # keeps the provider's allocation alive
     signal_pad_words: int = 0
+    peer_ptrs_host: tuple = ()             # the same `world` buffer addresses, on the host
+
+    def pointer_table(self, byte_offset: int) -> torch.Tensor:
+        """Device array of `world` pointers: every rank's copy of the buffer plus ``byte_offset``."""
+        return torch.tensor([p + byte_offset for p in self.peer_ptrs_host], dtype=torch.int64, device=self.tensor.device)
 
     @property
     def base_ptr(self) -> int:
@@ -91,7 +96,7 @@ def _create_torch_buffer(rows: int, cols: int, dtype: torch.dtype, tp: TPState, 
     t.zero_()
     mc = int(hdl.multicast_ptr) if allow_multicast and hdl.multicast_ptr else 0
     buf = SymmetricBuffer(t, tp.rank, tp.world_size, mc, int(hdl.buffer_ptrs_dev), int(hdl.signal_pad_ptrs_dev),
-                          "torch", hdl, int(hdl.signal_pad_size) // 4)
+                          "torch", hdl, int(hdl.signal_pad_size) // 4, tuple(int(x) for x in hdl.buffer_ptrs))
     torch.cuda.synchronize()
     hdl.barrier(channel=0)
     return buf

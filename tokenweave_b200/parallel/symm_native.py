@@ -211,4 +211,4 @@ def create_native_buffer(rows: int, cols: int, dtype: torch.dtype, tp: TPState, 
     torch.cuda.synchronize()
     dist.barrier(group=tp.cpu_group)
     return SymmetricBuffer(data, tp.rank, tp.world_size, mc_va, peer_ptrs.data_ptr(), pad_ptrs.data_ptr(), "native", h,
-                           SIGNAL_PAD_WORDS_NEEDED)
+                           SIGNAL_PAD_WORDS_NEEDED, tuple(bases))

@@ -51,6 +51,37 @@ def run_fuse_only(layers: Sequence, final_norm_w: torch.Tensor, hidden: torch.Te
         comm.fused_allreduce_add_rmsnorm_(h, r, next_w, eps, ctas)
 
 
+def run_fused_gemm(layers: Sequence, final_norm_w: torch.Tensor, hidden: torch.Tensor, residual: torch.Tensor,
+                   meta, plan: SplitPlan, comm: TPCommunicator, rt, eps: float, first_pending: bool = False) -> None:
+    """Every GEMM next to a collective runs fused with it, one kernel each, no kernel-wide barriers:
+
+        qkv_proj      = all-gather  -> GEMM            (tw_ag_gemm; plain GEMM for layer 0, whose input is replicated)
+        o_proj        = GEMM -> reduce-scatter -> residual add -> RMSNorm            (tw_gemm_rs_norm)
+        gate_up_proj  = all-gather  -> GEMM + SwiGLU   (tw_ag_gemm)
+        down_proj     = GEMM -> reduce-scatter -> residual add -> RMSNorm            (tw_gemm_rs_norm)
+
+    Between a tw_gemm_rs_norm and the next tw_ag_gemm only this rank's shard of the rows holds normalised
+    activations. MoE layers (no single GEMM to fuse with) gather, run the expert block and use the stand-alone
+    fused collective without its all-gather. The final norm output is gathered once at the end."""
+    T, Tp = plan.num_tokens, plan.padded_tokens
+    h, r = hidden[:Tp], residual[:Tp]
+    ctas = max(2, min(plan.attention_ctas, 16))
+    gathered = True
+    if first_pending:
+        comm.fused_allreduce_add_rmsnorm_(h, r, layers[0].input_norm_w, eps, plan.attention_ctas)
+    for i, layer in enumerate(layers):
+        next_w = layers[i + 1].input_norm_w if i + 1 < len(layers) else final_norm_w
+        layer.attn_block_fused(h, T, meta, rt, comm, r, eps, ctas, gathered)
+        if layer.moe is not None:
+            comm.all_gather_(h, plan.attention_ctas)
+            layer.moe(h[:T], out=h[:T])
+            comm.fused_allreduce_add_rmsnorm_(h, r, next_w, eps, plan.attention_ctas, mode=1)
+        else:
+            layer.mlp_block_fused(h, T, rt, comm, r, next_w, eps, ctas)
+        gathered = False
+    comm.all_gather_(h, plan.attention_ctas)
+
+
 def run_baseline(layers: Sequence, final_norm_w: torch.Tensor, hidden: torch.Tensor, residual: torch.Tensor,
                  meta, plan: SplitPlan, comm: TPCommunicator, rt, eps: float, mode: str,
                  first_pending: bool = False) -> None:
