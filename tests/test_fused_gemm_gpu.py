@@ -35,7 +35,7 @@ def _worker(rank, world, transport):
         g = torch.Generator(device="cuda").manual_seed(100 + rank)
         # (T_pad, M, K of the row-parallel GEMM, N of the column-parallel GEMM, swiglu)
         cases = [(256, 256, 512, 1024, False), (1024, 1000, 1024, 1536, True), (64, 50, 256, 512, False),
-                 (2048, 2048, 512, 2048, True)]
+                 (2048, 2048, 512, 2048, True), (1374, 1373, 512, 1024, False)]   # last: shards not aligned to tiles
         for rep in range(2):
             for (T, M, K, N2, swiglu) in cases:
                 a = torch.randn(T, K, device="cuda", generator=g).to(torch.bfloat16)

@@ -531,9 +531,13 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           __threadfence_system();
           const int first_row = m_tile * FG_BM;
           const int last_row = min(first_row + FG_BM, p.M) - 1;
+          // every 128-row block of every owner that this tile overlaps gets one count (shards need not
+          // be aligned to tiles, so a tile can feed two blocks of one owner and blocks of two owners)
           for (int o = first_row / p.rows_per_rank; o <= last_row / p.rows_per_rank; ++o) {
-            const int local_first = max(first_row, o * p.rows_per_rank) - o * p.rows_per_rank;
-            red_release_sys_add(p.tile_flags[o] + local_first / FG_BM, 1u);
+            const int base = o * p.rows_per_rank;
+            const int lo = max(first_row, base) - base;
+            const int hi = min(last_row, base + p.rows_per_rank - 1) - base;
+            for (int b = lo / FG_BM; b <= hi / FG_BM; ++b) red_release_sys_add(p.tile_flags[o] + b, 1u);
           }
         }
       }
@@ -611,7 +615,9 @@ static int launch_fused(const void* A, long long lda, const void* B, long long l
   const int smem = p.stages * (FG_A_BYTES + p.bn * FG_BK * 2) + 256 + 1024;
   void (*kern)(CUtensorMap, CUtensorMap, FusedGemmParams) =
       swiglu ? fused_gemm_kernel<MODE, true> : fused_gemm_kernel<MODE, false>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  // the kernel also has a few hundred bytes of static shared memory, so the dynamic part cannot take
+  // the whole 227 KB
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FG_SMEM_BUDGET + 4096);
   if (e != cudaSuccess) {
     set_last_error("fused gemm: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return 1;

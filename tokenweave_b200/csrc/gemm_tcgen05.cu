@@ -49,6 +49,7 @@ struct GemmParams {
   int up_row_offset;
   int bn;        // accumulator columns per tile
   int stages;    // pipeline depth
+  int kb_per_stage;  // 64-wide k-blocks per stage: 2 halves the barrier round trips per FLOP
   uint32_t* status;
 };
 
@@ -70,7 +71,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                  const GemmParams p) {
   const int BN = p.bn;
   const int STAGES = p.stages;
-  const int stage_bytes = gemm_stage_bytes(BN);
+  const int KBPS = p.kb_per_stage;                  // 64-wide k-blocks per pipeline stage (1 or 2)
+  const int b_bytes = BN * GEMM_BK * 2;
+  const int stage_bytes = KBPS * gemm_stage_bytes(BN);
   const int OUT_COLS = SWIGLU ? BN / 2 : BN;
   const uint32_t IDESC = make_idesc_bf16(GEMM_BM, BN, 0, 0);
 
@@ -116,7 +119,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (p.num_m_tiles_dev != nullptr) num_m = min(num_m, *p.num_m_tiles_dev);
   const int num_n = p.num_n_tiles;
   const int total_tiles = num_m * num_n;
-  const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int num_kb = ((p.K + GEMM_BK - 1) / GEMM_BK + KBPS - 1) / KBPS;   // pipeline iterations per tile
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -136,15 +139,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             break;
           }
           uint8_t* sa = smem + stage * stage_bytes;
-          uint8_t* sb = sa + GEMM_A_BYTES;
+          uint8_t* sb = sa + KBPS * GEMM_A_BYTES;
           mbar_expect_tx(&full_bar[stage], stage_bytes);
-          tma_load_2d(sa, &tmA, &full_bar[stage], kb * GEMM_BK, m0);
-          if (SWIGLU) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], kb * GEMM_BK, b_row0);
-            tma_load_2d(sb + (BN / 2) * GEMM_BK * 2, &tmB, &full_bar[stage], kb * GEMM_BK,
-                        b_row0 + p.up_row_offset);
-          } else {
-            tma_load_2d(sb, &tmB, &full_bar[stage], kb * GEMM_BK, b_row0);
+          for (int s = 0; s < KBPS; ++s) {
+            // a k-block past the end of K reads zeros (out-of-bounds fill) and adds nothing
+            const int kx = (kb * KBPS + s) * GEMM_BK;
+            tma_load_2d(sa + s * GEMM_A_BYTES, &tmA, &full_bar[stage], kx, m0);
+            if (SWIGLU) {
+              tma_load_2d(sb + s * b_bytes, &tmB, &full_bar[stage], kx, b_row0);
+              tma_load_2d(sb + s * b_bytes + (BN / 2) * GEMM_BK * 2, &tmB, &full_bar[stage], kx,
+                          b_row0 + p.up_row_offset);
+            } else {
+              tma_load_2d(sb + s * b_bytes, &tmB, &full_bar[stage], kx, b_row0);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -170,13 +177,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * stage_bytes);
-          const uint32_t sb = sa + GEMM_A_BYTES;
-          const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t b_desc = make_smem_desc_sw128(sb, 16, 1024);
+          const uint32_t sb = sa + KBPS * GEMM_A_BYTES;
+          for (int s = 0; s < KBPS; ++s) {
+            const uint64_t a_desc = make_smem_desc_sw128(sa + s * GEMM_A_BYTES, 16, 1024);
+            const uint64_t b_desc = make_smem_desc_sw128(sb + s * b_bytes, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < GEMM_BK / 16; ++k) {
-            // 16 bf16 = 32 bytes further along K: +2 in the descriptor's 16-byte address units
-            umma_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < GEMM_BK / 16; ++k) {
+              // 16 bf16 = 32 bytes further along K: +2 in the descriptor's 16-byte address units
+              umma_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -283,7 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 template <bool SWIGLU>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
                        cudaStream_t stream) {
-  const int smem = p.stages * gemm_stage_bytes(p.bn) + 256 + 1024;
+  const int smem = p.stages * p.kb_per_stage * gemm_stage_bytes(p.bn) + 256 + 1024;
   auto kern = gemm_bf16_kernel<SWIGLU>;
   static thread_local int configured_dev = -1;
   int dev = 0;
@@ -411,7 +420,13 @@ extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long lo
   const int BN = plan.bn;
   const int out_cols = swiglu ? BN / 2 : BN;
   const int num_n = (N + out_cols - 1) / out_cols;
+  // Two k-blocks per stage when at least three such stages fit (216 KB of pipeline at most), else one.
+  int kbps = 1;
   int stages = GEMM_SMEM_BUDGET / gemm_stage_bytes(BN);
+  if (K >= 256 && (216 * 1024) / (2 * gemm_stage_bytes(BN)) >= 3) {
+    kbps = 2;
+    stages = (216 * 1024) / (2 * gemm_stage_bytes(BN));
+  }
   if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
 
   CUtensorMap tmA, tmB;
@@ -443,6 +458,7 @@ extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long lo
   p.up_row_offset = up_row_offset;
   p.bn = BN;
   p.stages = stages;
+  p.kb_per_stage = kbps;
   p.status = status;
   int grid = num_m * num_n;
   if (grid > sms) grid = sms;

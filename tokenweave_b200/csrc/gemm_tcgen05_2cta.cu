@@ -40,8 +40,11 @@ struct Gemm2Params {
   int num_m_tiles, num_n_tiles;   // in 256-row pair tiles
   int up_row_offset;
   int bn, stages;
+  int kb_per_stage;
   uint32_t* status;
 };
+
+static int g_pair_kbps = 2;   // 64-wide k-blocks per pipeline stage: 2 halves the barrier round trips per FLOP
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -115,7 +118,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int BN = p.bn;
   const int HALF_N = BN / 2;                       // B rows held by each CTA
   const int STAGES = p.stages;
-  const int stage_bytes = G2_A_BYTES + HALF_N * G2_BK * 2;
+  const int KBPS = p.kb_per_stage;                 // 64-wide k-blocks per pipeline stage (1 or 2)
+  const int b_half_bytes = HALF_N * G2_BK * 2;
+  const int stage_bytes = KBPS * (G2_A_BYTES + b_half_bytes);
   const int OUT_COLS = SWIGLU ? BN / 2 : BN;
   const uint32_t IDESC = make_idesc_bf16(2 * G2_BM, BN, 0, 0);
 
@@ -162,7 +167,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   const int num_m = p.num_m_tiles, num_n = p.num_n_tiles;
   const int total_tiles = num_m * num_n;
-  const int num_kb = (p.K + G2_BK - 1) / G2_BK;
+  const int num_kb = ((p.K + G2_BK - 1) / G2_BK + KBPS - 1) / KBPS;   // pipeline iterations per tile
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
@@ -185,11 +190,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             break;
           }
           uint8_t* sa = smem + stage * stage_bytes;
-          uint8_t* sb = sa + G2_A_BYTES;
+          uint8_t* sb = sa + KBPS * G2_A_BYTES;
           const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * stage_bytes);
-          tma_load_2d_pair(sa, &tmA, leader_full, kb * G2_BK, m0);
-          tma_load_2d_pair(sb, &tmB, leader_full, kb * G2_BK, b_row0);
+          for (int s = 0; s < KBPS; ++s) {
+            // a k-block past the end of K reads zeros (out-of-bounds fill) and adds nothing
+            const int kx = (kb * KBPS + s) * G2_BK;
+            tma_load_2d_pair(sa + s * G2_A_BYTES, &tmA, leader_full, kx, m0);
+            tma_load_2d_pair(sb + s * b_half_bytes, &tmB, leader_full, kx, b_row0);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -214,12 +223,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * stage_bytes);
-          const uint32_t sb = sa + G2_A_BYTES;
-          const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t b_desc = make_smem_desc_sw128(sb, 16, 1024);
+          const uint32_t sb = sa + KBPS * G2_A_BYTES;
+          for (int s = 0; s < KBPS; ++s) {
+            const uint64_t a_desc = make_smem_desc_sw128(sa + s * G2_A_BYTES, 16, 1024);
+            const uint64_t b_desc = make_smem_desc_sw128(sb + s * b_half_bytes, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < G2_BK / 16; ++k)
-            umma_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < G2_BK / 16; ++k)
+              umma_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+          }
           // the stage is free in BOTH CTAs once these MMAs have read it
           const uint32_t e_local = smem_u32(&empty_bar[stage]);
           umma_commit_pair(map_to_cta(e_local, 0));
@@ -329,7 +340,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 template <bool SWIGLU>
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p, int pairs,
                        cudaStream_t stream) {
-  const int stage_bytes = G2_A_BYTES + (p.bn / 2) * G2_BK * 2;
+  const int stage_bytes = p.kb_per_stage * (G2_A_BYTES + (p.bn / 2) * G2_BK * 2);
   const int smem = p.stages * stage_bytes + 256 + 1024;
   auto kern = gemm_bf16_pair_kernel<SWIGLU>;
   static thread_local int configured_dev = -1;
@@ -368,6 +379,12 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
 
 using namespace tw;
 
+// 1 or 2 k-blocks (of 64) per pipeline stage of the CTA-pair kernel; for tuning runs.
+extern "C" int tw_gemm_set_pair_kbps(int kbps) {
+  g_pair_kbps = (kbps == 1) ? 1 : 2;
+  return 0;
+}
+
 // Same contract as tw_gemm_bf16 without the grouped mode. `bn` is the tile width (multiple of 64,
 // <= 256), `max_ctas` bounds the SMs used (rounded down to an even number).
 extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
@@ -389,7 +406,8 @@ extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, lo
   const int num_m = (M + 2 * G2_BM - 1) / (2 * G2_BM);
   const int out_cols = swiglu ? bn / 2 : bn;
   const int num_n = (N + out_cols - 1) / out_cols;
-  const int stage_bytes = G2_A_BYTES + (bn / 2) * G2_BK * 2;
+  const int kbps = (g_pair_kbps == 2 && K >= 256) ? 2 : 1;
+  const int stage_bytes = kbps * (G2_A_BYTES + (bn / 2) * G2_BK * 2);
   int stages = G2_SMEM_BUDGET / stage_bytes;
   if (stages > G2_MAX_STAGES) stages = G2_MAX_STAGES;
 
@@ -419,6 +437,7 @@ extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, lo
   p.up_row_offset = up_row_offset;
   p.bn = bn;
   p.stages = stages;
+  p.kb_per_stage = kbps;
   p.status = status;
   int pairs = num_m * num_n;
   if (pairs > pairs_avail) pairs = pairs_avail;
