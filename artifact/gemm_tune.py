@@ -44,8 +44,9 @@ def main() -> None:
     from tokenweave_b200 import ops
     from tokenweave_b200.config import resolve_model_config
     from tokenweave_b200.ops import _native
+    from tokenweave_b200.ops import gemm_table
     lib = _native.load()
-    os.environ["TW_GEMM_TABLE"] = "0"
+    gemm_table.set_enabled(False)       # candidates must run as forced, not as an older table says
     torch.cuda.set_device(0)
     todo = []
     for m in args.models:
@@ -70,13 +71,14 @@ def main() -> None:
             out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
             for sms in args.sm_budgets:
                 best = None
-                for kernel in (1, 2):
-                    widths = range(64, 257, 64) if (kernel == 2 or sw) else range(64, 257, 32)
+                for kernel in (2, 1):
+                    widths = range(256, 63, -64) if (kernel == 2 or sw) else range(256, 63, -32)
                     for bn in widths:
                         lib.tw_gemm_set_kernel_override(kernel)
                         lib.tw_gemm_set_tile_override(bn)
                         us = time_us(lambda: ops.gemm(a, w, out=out, swiglu=bool(sw), max_ctas=sms), warmup=2, iters=args.iters)
-                        if best is None or us < best[2]:
+                        # candidates run widest first; a narrower tile must win by 2 % to replace it
+                        if best is None or us < best[2] * 0.98:
                             best = (kernel, bn, us)
                 lib.tw_gemm_set_kernel_override(0)
                 lib.tw_gemm_set_tile_override(0)

@@ -51,6 +51,7 @@ struct FusedGemmParams {
   int num_m_tiles, num_n_tiles;
   int up_row_offset;
   int bn, stages;
+  int kb_per_stage;
   // collective
   uint8_t* mc_base;
   uint8_t* const* peer_bases;
@@ -307,7 +308,9 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                   const FusedGemmParams p) {
   const int BN = p.bn;
   const int STAGES = p.stages;
-  const int stage_bytes = FG_A_BYTES + BN * FG_BK * 2;
+  const int KBPS = p.kb_per_stage;                  // 64-wide k-blocks per pipeline stage (1 or 2)
+  const int b_bytes = BN * FG_BK * 2;
+  const int stage_bytes = KBPS * (FG_A_BYTES + b_bytes);
   const int OUT_COLS = SWIGLU ? BN / 2 : BN;
   const uint32_t IDESC = make_idesc_bf16(FG_BM, BN, 0, 0);
 
@@ -366,7 +369,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   const int num_m = p.num_m_tiles, num_n = p.num_n_tiles;
   const int total_tiles = num_m * num_n;
-  const int num_kb = (p.K + FG_BK - 1) / FG_BK;
+  const int num_kb = ((p.K + FG_BK - 1) / FG_BK + KBPS - 1) / KBPS;   // pipeline iterations per tile
   // Row tiles in the order their inputs become available: MODE 1 starts with this rank's own shard and
   // walks the ring; MODE 0 keeps the natural order (all ranks finish row block 0 first, so rank 0's
   // communication CTAs start first, rank world-1's last).
@@ -407,14 +410,17 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             break;
           }
           uint8_t* sa = smem + stage * stage_bytes;
-          uint8_t* sb = sa + FG_A_BYTES;
+          uint8_t* sb = sa + KBPS * FG_A_BYTES;
           mbar_expect_tx(&full_bar[stage], stage_bytes);
-          tma_load_2d(sa, &tmA, &full_bar[stage], kb * FG_BK, m0);
-          if (SWIGLU) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], kb * FG_BK, b_row0);
-            tma_load_2d(sb + (BN / 2) * FG_BK * 2, &tmB, &full_bar[stage], kb * FG_BK, b_row0 + p.up_row_offset);
-          } else {
-            tma_load_2d(sb, &tmB, &full_bar[stage], kb * FG_BK, b_row0);
+          for (int s = 0; s < KBPS; ++s) {
+            const int kx = (kb * KBPS + s) * FG_BK;   // past the end of K: zero fill
+            tma_load_2d(sa + s * FG_A_BYTES, &tmA, &full_bar[stage], kx, m0);
+            if (SWIGLU) {
+              tma_load_2d(sb + s * b_bytes, &tmB, &full_bar[stage], kx, b_row0);
+              tma_load_2d(sb + s * b_bytes + (BN / 2) * FG_BK * 2, &tmB, &full_bar[stage], kx, b_row0 + p.up_row_offset);
+            } else {
+              tma_load_2d(sb + s * b_bytes, &tmB, &full_bar[stage], kx, b_row0);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -439,12 +445,14 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * stage_bytes);
-          const uint32_t sb = sa + FG_A_BYTES;
-          const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t b_desc = make_smem_desc_sw128(sb, 16, 1024);
+          const uint32_t sb = sa + KBPS * FG_A_BYTES;
+          for (int s = 0; s < KBPS; ++s) {
+            const uint64_t a_desc = make_smem_desc_sw128(sa + s * FG_A_BYTES, 16, 1024);
+            const uint64_t b_desc = make_smem_desc_sw128(sb + s * b_bytes, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < FG_BK / 16; ++k)
-            umma_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < FG_BK / 16; ++k)
+              umma_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+          }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -595,7 +603,9 @@ static int launch_fused(const void* A, long long lda, const void* B, long long l
   const int out_cols = swiglu ? p.bn / 2 : p.bn;
   p.num_m_tiles = (p.M + FG_BM - 1) / FG_BM;
   p.num_n_tiles = (p.N + out_cols - 1) / out_cols;
-  p.stages = FG_SMEM_BUDGET / (FG_A_BYTES + p.bn * FG_BK * 2);
+  const int one_kb = FG_A_BYTES + p.bn * FG_BK * 2;
+  p.kb_per_stage = (p.K >= 256 && FG_SMEM_BUDGET / (2 * one_kb) >= 3) ? 2 : 1;
+  p.stages = FG_SMEM_BUDGET / (p.kb_per_stage * one_kb);
   if (p.stages > FG_MAX_STAGES) p.stages = FG_MAX_STAGES;
   int gemm_ctas = p.num_m_tiles * p.num_n_tiles;
   if (gemm_ctas > gemm_ctas_max) gemm_ctas = gemm_ctas_max;
@@ -612,7 +622,7 @@ static int launch_fused(const void* A, long long lda, const void* B, long long l
     uint32_t box[2] = {FG_BK, (uint32_t)(swiglu ? p.bn / 2 : p.bn)};
     if (!make_tensor_map_bf16(&tmB, B, 2, dims, strides, box)) return 1;
   }
-  const int smem = p.stages * (FG_A_BYTES + p.bn * FG_BK * 2) + 256 + 1024;
+  const int smem = p.stages * p.kb_per_stage * one_kb + 256 + 1024;
   void (*kern)(CUtensorMap, CUtensorMap, FusedGemmParams) =
       swiglu ? fused_gemm_kernel<MODE, true> : fused_gemm_kernel<MODE, false>;
   // the kernel also has a few hundred bytes of static shared memory, so the dynamic part cannot take

@@ -46,6 +46,13 @@ def reload() -> None:
     lookup.cache_clear()
 
 
+def set_enabled(on: bool) -> None:
+    """Turn the table off (every lookup answers 0 = cost model) or back on; tuning runs turn it off."""
+    global _disabled
+    _disabled = not on
+    reload()
+
+
 @lru_cache(maxsize=4096)
 def lookup(M: int, N: int, K: int, swiglu: bool, max_ctas: int = 0) -> int:
     """Plan hint for the launcher: ``kernel * 1000 + bn`` or 0 (let the cost model decide)."""
