@@ -97,9 +97,11 @@ def write_rows(out_dir: str, name: str, rows: list[dict]) -> None:
     os.makedirs(out_dir, exist_ok=True)
     if not rows:
         return
-    keys = list(rows[0].keys())
+    keys = []
+    for r in rows:
+        keys += [k for k in r if k not in keys]
     with open(os.path.join(out_dir, name + ".csv"), "w", newline="") as f:
-        w = csv.DictWriter(f, fieldnames=keys)
+        w = csv.DictWriter(f, fieldnames=keys, restval="")
         w.writeheader()
         w.writerows(rows)
     with open(os.path.join(out_dir, name + ".json"), "w") as f:

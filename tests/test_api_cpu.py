@@ -72,3 +72,40 @@ def test_engine_args_cli_round_trip():
     assert cfg.model.architecture == "qwen2" and cfg.model.qkv_bias
     assert cfg.parallel.tensor_parallel_size == 2 and cfg.scheduler.max_num_batched_tokens == 4096
     assert cfg.tokenweave.mode == "fuse_only" and cfg.scheduler.enable_chunked_prefill is False
+
+
+def test_beam_search_finds_the_most_likely_continuation():
+    """Width-1 beam search is greedy decoding; a wider beam never scores below it, and the returned
+    cumulative log-probabilities equal the sum of the model's per-step log-probabilities."""
+    from tokenweave_b200 import BeamSearchParams, LLM, SamplingParams
+    llm = LLM("tiny-llama", dtype="float32", device="cpu", skip_tokenizer_init=True, block_size=16,
+              max_num_batched_tokens=256, enable_prefix_caching=True, seed=5)
+    prompt = list(range(3, 20))
+    greedy = llm.generate([prompt], SamplingParams(temperature=0, max_tokens=5, ignore_eos=True, logprobs=1))[0].outputs[0]
+    b1 = llm.beam_search([prompt], BeamSearchParams(beam_width=1, max_tokens=5, ignore_eos=True))[0].sequences
+    assert len(b1) == 1 and b1[0].tokens == prompt + greedy.token_ids
+    assert abs(b1[0].cum_logprob - greedy.cumulative_logprob) < 1e-4
+    b4 = llm.beam_search([prompt], BeamSearchParams(beam_width=4, max_tokens=5, ignore_eos=True))[0].sequences
+    assert len(b4) == 4 and len({tuple(s.tokens) for s in b4}) == 4
+    assert b4[0].cum_logprob >= b1[0].cum_logprob - 1e-5
+    assert all(b4[i].cum_logprob >= b4[i + 1].cum_logprob for i in range(3))
+    llm.shutdown()
+
+
+def test_encode_embed_score():
+    from tokenweave_b200 import LLM
+    llm = LLM("tiny-llama", dtype="float32", device="cpu", skip_tokenizer_init=True, block_size=16,
+              max_num_batched_tokens=64, seed=5)
+    a, b = list(range(5, 45)), list(range(50, 150))      # b is prefilled in chunks
+    enc = llm.encode([a, b])
+    H = llm.llm_engine.config.model.hidden_size
+    assert [tuple(e.data.shape) for e in enc] == [(H,), (H,)]
+    emb = llm.embed([a, b])
+    for e, raw in zip(emb, enc):
+        assert abs(float(e.data.norm()) - 1.0) < 1e-5
+        assert torch.allclose(e.data, raw.data / raw.data.norm(), atol=1e-6)
+    s = llm.score(a, [a, b])
+    assert abs(s[0] - 1.0) < 1e-5 and s[1] < 0.9999
+    # a later generate() is unaffected by the capture switch
+    assert not llm.llm_engine.core.executor.worker.runner.capture_hidden
+    llm.shutdown()

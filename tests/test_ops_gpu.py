@@ -219,3 +219,113 @@ def test_moe_pipeline(T, H, I, E):
     out = torch.empty(T, H, device=DEV, dtype=BF)
     ops.moe_combine(y, sorted_pos, out, topk)
     close(out, expect, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("kind", sorted(ref.ACTIVATION_KINDS))
+def test_activations(kind):
+    gated = ref.ACTIVATION_KINDS[kind] <= 4
+    x = rnd(333, 2 * 1096 if gated else 1096, scale=2.0)
+    out = ops.activation(x, kind, param=0.25)
+    close(out, ref.activation(x, kind, 0.25))
+    # strided input: a column slice of a wider buffer
+    wide = rnd(64, 4096, scale=2.0)
+    view = wide[:, 512:512 + (1024 if gated else 512)]
+    close(ops.activation(view, kind, param=0.25), ref.activation(view, kind, 0.25))
+
+
+def test_copy_and_swap_pages():
+    cache = rnd(24, 16, 2, 128)
+    want = cache.clone()
+    pairs = torch.tensor([[0, 5], [1, 6], [7, 23], [3, 2]], dtype=torch.int64, device=DEV)
+    for s, d in pairs.tolist():
+        want[d] = cache[s]
+    ops.copy_pages(cache, pairs)
+    assert torch.equal(cache, want)
+    host = torch.zeros(10, 16, 2, 128, dtype=BF).pin_memory()
+    out_pairs = [(4, 0), (5, 1), (6, 2), (20, 7)]
+    ops.swap_pages(cache, host, out_pairs)
+    torch.cuda.synchronize()
+    for s, d in out_pairs:
+        assert torch.equal(host[d], cache[s].cpu())
+    back = torch.zeros_like(cache)
+    ops.swap_pages(host, back, [(0, 9), (1, 10), (7, 3)])
+    torch.cuda.synchronize()
+    assert torch.equal(back[9], cache[4]) and torch.equal(back[10], cache[5]) and torch.equal(back[3], cache[20])
+
+
+@pytest.mark.parametrize("T,H,D", [(1, 4, 128), (77, 8, 128), (300, 3, 64)])
+def test_merge_attn_states(T, H, D):
+    a, b = rnd(T, H, D), rnd(T, H, D)
+    la = torch.randn(H, T, device=DEV) * 3
+    lb = torch.randn(H, T, device=DEV) * 3
+    lb[0, 0] = -math.inf                 # an empty partial result takes weight zero
+    if T > 2:
+        la[1, 2] = math.inf
+    out, lse = ops.merge_attn_states(a, la, b, lb, want_lse=True)
+    want, want_lse = ref.merge_attn_states(a, la, b, lb)
+    close(out, want)
+    assert torch.allclose(lse, want_lse, atol=1e-4, rtol=1e-4)
+    # against attention itself: softmax over the union of two key sets
+    q = torch.randn(H, D, device=DEV)
+    k = torch.randn(H, 40, D, device=DEV)
+    v = torch.randn(H, 40, D, device=DEV)
+    s = torch.einsum("hd,hkd->hk", q, k)
+    full = torch.einsum("hk,hkd->hd", torch.softmax(s, -1), v)
+    o1 = torch.einsum("hk,hkd->hd", torch.softmax(s[:, :15], -1), v[:, :15]).to(BF).unsqueeze(0).contiguous()
+    o2 = torch.einsum("hk,hkd->hd", torch.softmax(s[:, 15:], -1), v[:, 15:]).to(BF).unsqueeze(0).contiguous()
+    l1 = torch.logsumexp(s[:, :15], -1).unsqueeze(1).contiguous()
+    l2 = torch.logsumexp(s[:, 15:], -1).unsqueeze(1).contiguous()
+    close(ops.merge_attn_states(o1, l1, o2, l2)[0], full, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("T,H", [(1, 128), (77, 1024), (300, 8192), (9, 12288)])
+def test_quant_fp8(T, H):
+    x = rnd(T, H, scale=3.0)
+    q, s = ops.quant_fp8(x)
+    q_ref, s_ref = ref.quant_fp8(x)
+    assert torch.allclose(s, s_ref, rtol=1e-6, atol=0)
+    # identical up to one e4m3 step where x / scale lands on a rounding boundary
+    dq, dq_ref = q.float() * s[:, None], q_ref.float() * s_ref[:, None]
+    assert (dq - dq_ref).abs().max() <= 0.07 * x.float().abs().max()
+    assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 1e-3
+    static = torch.tensor([0.05], device=DEV)
+    q2, _ = ops.quant_fp8(x, scale=static)
+    assert (q2.view(torch.uint8) != ref.quant_fp8(x, static)[0].view(torch.uint8)).float().mean() < 1e-3
+    # fused with RMSNorm, with and without the residual add
+    w = rnd(H, scale=0.5)
+    qn, sn = ops.rmsnorm_quant_fp8(x, w, 1e-5)
+    y = ref.rmsnorm(x, w, 1e-5)
+    close(qn.float() * sn[:, None], y, atol=0.05 * y.float().abs().max().item(), rtol=0.07)
+    res = rnd(T, H)
+    res_want = (x + res)
+    res_in = res.clone()
+    qa, sa = ops.rmsnorm_quant_fp8(x, w, 1e-5, residual=res_in)
+    assert torch.equal(res_in, res_want)
+    y2 = ref.rmsnorm(res_want, w, 1e-5)
+    close(qa.float() * sa[:, None], y2, atol=0.05 * y2.float().abs().max().item(), rtol=0.07)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 1280, 1024), (1000, 1000, 208), (4096, 7168, 1024),
+                                   (77, 8, 512), (2048, 8192, 3584)])
+def test_gemm_fp8(M, N, K):
+    a, w = rnd(M, K), rnd(N, K, scale=1 / math.sqrt(K))
+    aq, a_s = ops.quant_fp8(a)
+    wq, w_s = ops.quant_fp8(w)
+    bias = rnd(N)
+    out = ops.gemm_fp8(aq, wq, a_s, w_s, bias=bias)
+    # exact products of the same quantised operands: only accumulation order and the final rounding differ
+    close(out, ref.gemm_fp8(aq, wq, a_s, w_s, bias))
+    # and the quantised result approximates the bf16 product
+    full = ref.gemm(a, w).float() + bias.float()
+    assert (out.float() - full).abs().mean() < 0.05 * full.abs().mean() + 0.02
+    close(ops.gemm_fp8(aq, wq, None, None), ref.gemm_fp8(aq, wq, None, None), atol=2e-2 * 16, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,I,K", [(256, 512, 256), (1000, 3584, 1024), (4096, 3584, 8192)])
+def test_gemm_fp8_swiglu(M, I, K):
+    a, w = rnd(M, K), rnd(2 * I, K, scale=1 / math.sqrt(K))
+    aq, a_s = ops.quant_fp8(a)
+    wq, w_s = ops.quant_fp8(w)
+    out = ops.gemm_fp8(aq, wq, a_s, w_s, swiglu=True)
+    assert out.shape == (M, I)
+    close(out, ref.gemm_fp8(aq, wq, a_s, w_s, swiglu=True))

@@ -3,8 +3,9 @@ token-split compute/communication overlap and fused all-reduce + RMSNorm."""
 
 __version__ = "0.1.0"
 
-from .sampling_params import SamplingParams  # noqa: E402,F401
-from .outputs import CompletionOutput, RequestOutput  # noqa: E402,F401
+from .sampling_params import BeamSearchParams, SamplingParams  # noqa: E402,F401
+from .outputs import (BeamSearchOutput, BeamSearchSequence, CompletionOutput, PoolingOutput,  # noqa: E402,F401
+                      RequestOutput)
 
 
 def __getattr__(name):

@@ -207,6 +207,7 @@ class EngineConfig:
     scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
     tokenweave: TokenWeaveConfig = field(default_factory=TokenWeaveConfig)
     load_format: str = "auto"             # "auto" | "dummy" | "safetensors"
+    quantization: Optional[str] = None    # None | "fp8" (e4m3 weights per channel, dynamic per-token activations)
     seed: int = 0
     device: str = "auto"                  # "auto" | "cuda" | "cpu"
     enforce_eager: bool = True
@@ -241,6 +242,7 @@ class EngineArgs:
     enforce_eager: bool = True
     disable_custom_all_reduce: bool = True
     load_format: str = "auto"
+    quantization: Optional[str] = None
     device: str = "auto"
     num_hidden_layers_override: Optional[int] = None
     disable_log_stats: bool = True
@@ -261,6 +263,11 @@ class EngineArgs:
                                      self.max_model_len, self.num_hidden_layers_override)
         max_len = model.max_model_len
         budget = self.max_num_batched_tokens or (8192 if self.enable_chunked_prefill else max(max_len, 8192))
+        if self.quantization not in (None, "fp8"):
+            raise ValueError(f"unknown quantization {self.quantization!r} (supported: fp8)")
+        if self.quantization and self.tokenweave_mode == "fused_gemm":
+            raise ValueError("the fused GEMM+collective kernels take bf16 weights: use tokenweave_mode "
+                             "overlap or fuse_only with quantization")
         load_format = self.load_format
         if load_format == "auto":
             load_format = "safetensors" if model.path else "dummy"
@@ -280,7 +287,7 @@ class EngineArgs:
                                         split_offset=self.tokenweave_split_offset,
                                         attention_ctas=self.tokenweave_attention_ctas,
                                         mlp_ctas=self.tokenweave_mlp_ctas),
-            load_format=load_format, seed=self.seed, device=self.device, enforce_eager=self.enforce_eager,
+            load_format=load_format, quantization=self.quantization, seed=self.seed, device=self.device, enforce_eager=self.enforce_eager,
             tokenizer=self.tokenizer, skip_tokenizer_init=self.skip_tokenizer_init,
             disable_log_stats=self.disable_log_stats)
 

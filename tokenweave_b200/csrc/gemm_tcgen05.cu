@@ -41,6 +41,7 @@ struct GemmParams {
   long long ldc;
   const __nv_bfloat16* bias;
   const float* row_scale;
+  const float* col_scale;   // fp8 only: per-output-channel weight scale (may be null)
   int M, N, K;
   int num_m_tiles, num_n_tiles;
   const int* tile_expert;
@@ -65,7 +66,9 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   n_tile = in_group / rows;
 }
 
-template <bool SWIGLU>
+// FP8: operands are e4m3 bytes, a k-block is 128 elements (the same 128 bytes per row), the MMA is
+// kind::f8f6f4 (K = 32 per instruction) and the epilogue applies acc * row_scale[m] * col_scale[n] + bias[n].
+template <bool SWIGLU, bool FP8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
@@ -75,7 +78,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int b_bytes = BN * GEMM_BK * 2;
   const int stage_bytes = KBPS * gemm_stage_bytes(BN);
   const int OUT_COLS = SWIGLU ? BN / 2 : BN;
-  const uint32_t IDESC = make_idesc_bf16(GEMM_BM, BN, 0, 0);
+  constexpr int BK_ELEMS = FP8 ? 2 * GEMM_BK : GEMM_BK;
+  const uint32_t IDESC = FP8 ? make_idesc_e4m3(GEMM_BM, BN) : make_idesc_bf16(GEMM_BM, BN, 0, 0);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -119,7 +123,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (p.num_m_tiles_dev != nullptr) num_m = min(num_m, *p.num_m_tiles_dev);
   const int num_n = p.num_n_tiles;
   const int total_tiles = num_m * num_n;
-  const int num_kb = ((p.K + GEMM_BK - 1) / GEMM_BK + KBPS - 1) / KBPS;   // pipeline iterations per tile
+  const int num_kb = ((p.K + BK_ELEMS - 1) / BK_ELEMS + KBPS - 1) / KBPS;   // pipeline iterations per tile
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -143,7 +147,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(&full_bar[stage], stage_bytes);
           for (int s = 0; s < KBPS; ++s) {
             // a k-block past the end of K reads zeros (out-of-bounds fill) and adds nothing
-            const int kx = (kb * KBPS + s) * GEMM_BK;
+            const int kx = (kb * KBPS + s) * BK_ELEMS;
             tma_load_2d(sa + s * GEMM_A_BYTES, &tmA, &full_bar[stage], kx, m0);
             if (SWIGLU) {
               tma_load_2d(sb + s * b_bytes, &tmB, &full_bar[stage], kx, b_row0);
@@ -184,7 +188,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int k = 0; k < GEMM_BK / 16; ++k) {
               // 16 bf16 = 32 bytes further along K: +2 in the descriptor's 16-byte address units
-              umma_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+              if (FP8)
+                umma_ss_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+              else
+                umma_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
             }
           }
           umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
@@ -232,13 +239,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int j = 0; j < 16; ++j) {
             float g0 = __uint_as_float(v[2 * j]), g1 = __uint_as_float(v[2 * j + 1]);
             float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            if (FP8) {
+              // gate and up rows of the weight carry their own channel scales; the token scale (rs)
+              // de-quantises both, so it goes in before the non-linearity
+              const int n = min(n0 + c * 32 + 2 * j, p.N - 2);
+              g0 *= rs;
+              g1 *= rs;
+              if (p.col_scale != nullptr) {
+                g0 *= p.col_scale[n];
+                g1 *= p.col_scale[n + 1];
+                u0 *= p.col_scale[p.up_row_offset + n];
+                u1 *= p.col_scale[p.up_row_offset + n + 1];
+              }
+              packed[j] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0 * rs, g1 / (1.f + __expf(-g1)) * u1 * rs);
+              continue;
+            }
             float s0 = g0 / (1.f + __expf(-g0)) * u0;
             float s1 = g1 / (1.f + __expf(-g1)) * u1;
             packed[j] = pack_bf16x2(s0 * rs, s1 * rs);
           }
         } else {
           tmem_wait_ld();
-          if (p.bias != nullptr) {
+          if (FP8) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int n = n0 + c * 32 + j;
+              const float cs = (p.col_scale != nullptr && n < p.N) ? p.col_scale[n] : 1.f;
+              const float b = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+              v[j] = __float_as_uint(__uint_as_float(v[j]) * rs * cs + b);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              packed[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+          } else if (p.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int n = n0 + c * 32 + j;
@@ -246,9 +279,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
             }
           }
+          if (!FP8) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            packed[j] = pack_bf16x2(__uint_as_float(v[2 * j]) * rs, __uint_as_float(v[2 * j + 1]) * rs);
+            for (int j = 0; j < 16; ++j)
+              packed[j] = pack_bf16x2(__uint_as_float(v[2 * j]) * rs, __uint_as_float(v[2 * j + 1]) * rs);
+          }
         }
         if (row < p.M) {
 #pragma unroll
@@ -289,11 +324,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-template <bool SWIGLU>
+template <bool SWIGLU, bool FP8>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
                        cudaStream_t stream) {
   const int smem = p.stages * p.kb_per_stage * gemm_stage_bytes(p.bn) + 256 + 1024;
-  auto kern = gemm_bf16_kernel<SWIGLU>;
+  auto kern = gemm_bf16_kernel<SWIGLU, FP8>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -389,28 +424,32 @@ extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, lo
                                  int K, int swiglu, int up_row_offset, int bn, int max_ctas, uint32_t* status,
                                  cudaStream_t stream);
 
-// C launcher. A is [M,K] with row stride lda, B is [rows_b, K] with row stride ldb
-// (rows_b = N, 2*N for SwiGLU, or experts * n_per_expert).
-extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
-                            void* C, long long ldc, const void* bias, const float* row_scale, int M,
-                            int N, int K, int swiglu, int up_row_offset, const int* tile_expert,
-                            const int* num_m_tiles_dev, int n_per_expert, int max_ctas, int plan_hint,
-                            uint32_t* status, cudaStream_t stream) {
+// Shared launcher body. A is [M,K] with row stride lda, B is [rows_b, K] with row stride ldb
+// (rows_b = N, 2*N for SwiGLU, or experts * n_per_expert); strides count elements (2 bytes, or 1 for fp8).
+static int gemm_dispatch(bool fp8, const void* A, long long lda, const void* B, long long ldb, long long rows_b,
+                         void* C, long long ldc, const void* bias, const float* row_scale, const float* col_scale,
+                         int M, int N, int K, int swiglu, int up_row_offset, const int* tile_expert,
+                         const int* num_m_tiles_dev, int n_per_expert, int max_ctas, int plan_hint,
+                         uint32_t* status, cudaStream_t stream) {
   // plan_hint: 0 = cost model; otherwise kernel * 1000 + tile width (kernel 1 = single-CTA tiles,
   // 2 = CTA pairs), as produced by the tuning table.
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldc % 8) != 0) {
-    set_last_error("tw_gemm_bf16: K, lda, ldb, ldc must be multiples of 8 (got %d, %lld, %lld, %lld)", K,
-                   lda, ldb, ldc);
+  const int in_align = fp8 ? 16 : 8;   // 16 bytes of operand elements
+  if ((K % in_align) != 0 || (lda % in_align) != 0 || (ldb % in_align) != 0 || (ldc % 8) != 0) {
+    set_last_error("tw_gemm: K, lda, ldb must be multiples of %d and ldc of 8 (got %d, %lld, %lld, %lld)", in_align,
+                   K, lda, ldb, ldc);
     return 1;
   }
+  const int esz = fp8 ? 1 : 2;
+  const int bk_elems = fp8 ? 2 * GEMM_BK : GEMM_BK;
   int sms = device_sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
-  GemmPlan plan = choose_plan(M, N, K, sms, swiglu != 0, tile_expert != nullptr);
+  // the cost model sees k-blocks: an fp8 problem has K / 128 of them; CTA pairs are bf16-only
+  GemmPlan plan = choose_plan(M, N, fp8 ? K / 2 : K, sms, swiglu != 0, tile_expert != nullptr || fp8);
   if (plan_hint > 0) {
     const int kind = plan_hint / 1000, bn = plan_hint % 1000;
-    const bool pair_ok = kind == 2 && tile_expert == nullptr && sms >= 2 && bn % 64 == 0;
+    const bool pair_ok = !fp8 && kind == 2 && tile_expert == nullptr && sms >= 2 && bn % 64 == 0;
     const bool single_ok = kind == 1 && bn % (swiglu ? 64 : 32) == 0;
     if (bn >= 64 && bn <= 256 && (pair_ok || single_ok)) plan = GemmPlan{pair_ok, bn};
   }
@@ -423,7 +462,7 @@ extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long lo
   // Two k-blocks per stage when at least three such stages fit (216 KB of pipeline at most), else one.
   int kbps = 1;
   int stages = GEMM_SMEM_BUDGET / gemm_stage_bytes(BN);
-  if (K >= 256 && (216 * 1024) / (2 * gemm_stage_bytes(BN)) >= 3) {
+  if (K >= 4 * bk_elems && (216 * 1024) / (2 * gemm_stage_bytes(BN)) >= 3) {
     kbps = 2;
     stages = (216 * 1024) / (2 * gemm_stage_bytes(BN));
   }
@@ -432,21 +471,24 @@ extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long lo
   CUtensorMap tmA, tmB;
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
-    uint64_t strides[1] = {(uint64_t)lda * 2};
-    uint32_t box[2] = {GEMM_BK, GEMM_BM};
-    if (!make_tensor_map_bf16(&tmA, A, 2, dims, strides, box)) return 1;
+    uint64_t strides[1] = {(uint64_t)lda * esz};
+    uint32_t box[2] = {(uint32_t)bk_elems, GEMM_BM};
+    if (!(fp8 ? make_tensor_map_u8(&tmA, A, 2, dims, strides, box) : make_tensor_map_bf16(&tmA, A, 2, dims, strides, box)))
+      return 1;
   }
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows_b};
-    uint64_t strides[1] = {(uint64_t)ldb * 2};
-    uint32_t box[2] = {GEMM_BK, (uint32_t)(swiglu ? BN / 2 : BN)};
-    if (!make_tensor_map_bf16(&tmB, B, 2, dims, strides, box)) return 1;
+    uint64_t strides[1] = {(uint64_t)ldb * esz};
+    uint32_t box[2] = {(uint32_t)bk_elems, (uint32_t)(swiglu ? BN / 2 : BN)};
+    if (!(fp8 ? make_tensor_map_u8(&tmB, B, 2, dims, strides, box) : make_tensor_map_bf16(&tmB, B, 2, dims, strides, box)))
+      return 1;
   }
   GemmParams p;
   p.C = reinterpret_cast<__nv_bfloat16*>(C);
   p.ldc = ldc;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.row_scale = row_scale;
+  p.col_scale = col_scale;
   p.M = M;
   p.N = N;
   p.K = K;
@@ -462,5 +504,32 @@ extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long lo
   p.status = status;
   int grid = num_m * num_n;
   if (grid > sms) grid = sms;
-  return swiglu ? launch_gemm<true>(tmA, tmB, p, grid, stream) : launch_gemm<false>(tmA, tmB, p, grid, stream);
+  if (fp8)
+    return swiglu ? launch_gemm<true, true>(tmA, tmB, p, grid, stream)
+                  : launch_gemm<false, true>(tmA, tmB, p, grid, stream);
+  return swiglu ? launch_gemm<true, false>(tmA, tmB, p, grid, stream)
+                : launch_gemm<false, false>(tmA, tmB, p, grid, stream);
+}
+
+extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
+                            void* C, long long ldc, const void* bias, const float* row_scale, int M,
+                            int N, int K, int swiglu, int up_row_offset, const int* tile_expert,
+                            const int* num_m_tiles_dev, int n_per_expert, int max_ctas, int plan_hint,
+                            uint32_t* status, cudaStream_t stream) {
+  return gemm_dispatch(false, A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, nullptr, M, N, K, swiglu,
+                       up_row_offset, tile_expert, num_m_tiles_dev, n_per_expert, max_ctas, plan_hint, status,
+                       stream);
+}
+
+// e4m3 x e4m3 -> bf16: C = (A * B^T) * row_scale[m] * col_scale[n] + bias[n] (scales fp32, either may be
+// null). The counterpart of the reference's CUTLASS sm100 fp8 scaled-mm
+// (csrc/quantization/cutlass_w8a8/c3x/scaled_mm_sm100_fp8.cu) with per-token / per-channel scales.
+extern "C" int tw_gemm_fp8(const void* A, long long lda, const void* B, long long ldb, long long rows_b, void* C,
+                           long long ldc, const void* bias, const float* row_scale, const float* col_scale, int M,
+                           int N, int K, int swiglu, int up_row_offset, const int* tile_expert,
+                           const int* num_m_tiles_dev, int n_per_expert, int max_ctas, int plan_hint,
+                           uint32_t* status, cudaStream_t stream) {
+  return gemm_dispatch(true, A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, col_scale, M, N, K, swiglu,
+                       up_row_offset, tile_expert, num_m_tiles_dev, n_per_expert, max_ctas, plan_hint, status,
+                       stream);
 }

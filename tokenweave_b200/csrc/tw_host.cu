@@ -34,8 +34,8 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                          const uint64_t* strides_bytes, const uint32_t* box) {
+static bool make_tensor_map_typed(CUtensorMap* out, CUtensorMapDataType dtype, const void* base, int rank,
+                                  const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) {
     set_last_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -62,7 +62,7 @@ bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const ui
       }
     }
   }
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base),
+  CUresult r = fn(out, dtype, (cuuint32_t)rank, const_cast<void*>(base),
                   gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -73,6 +73,16 @@ bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const ui
     return false;
   }
   return true;
+}
+
+bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box) {
+  return make_tensor_map_typed(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, rank, dims, strides_bytes, box);
+}
+
+bool make_tensor_map_u8(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                        const uint64_t* strides_bytes, const uint32_t* box) {
+  return make_tensor_map_typed(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, base, rank, dims, strides_bytes, box);
 }
 
 int device_sm_count() {

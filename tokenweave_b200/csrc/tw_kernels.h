@@ -37,6 +37,28 @@ int tw_embedding(const int* ids, const void* table, void* out, long long ldo, in
                  int vocab_end, cudaStream_t stream);
 int tw_argmax(const float* logits, long long ld, int* out, int rows, int V, cudaStream_t stream);
 
+// ---- fp8 (e4m3) path (gemm_tcgen05.cu, quant_fp8.cu) ----
+int tw_gemm_fp8(const void* A, long long lda, const void* B, long long ldb, long long rows_b, void* C,
+                long long ldc, const void* bias, const float* row_scale, const float* col_scale, int M, int N,
+                int K, int swiglu, int up_row_offset, const int* tile_expert, const int* num_m_tiles_dev,
+                int n_per_expert, int max_ctas, int plan_hint, uint32_t* status, cudaStream_t stream);
+int tw_quant_fp8(const void* x, long long ldx, void* out, long long ldo, float* scales, int T, int H, int dynamic,
+                 int max_ctas, cudaStream_t stream);
+int tw_rmsnorm_quant_fp8(const void* x, void* residual, const void* w, void* out, long long ldo, float* scales,
+                         int T, int H, long long ldx, long long ldr, float eps, int dynamic, int max_ctas,
+                         cudaStream_t stream);
+
+// ---- activations, KV page copy / swap, partial-attention merge (misc_ops.cu) ----
+// kind: 0 silu*mul, 1 gelu*mul, 2 gelu_tanh*mul, 3 mul*silu, 4 fatrelu*mul (param = threshold),
+//       5 gelu_new, 6 gelu_fast, 7 gelu_quick, 8 gelu, 9 silu (kinds >= 5 are unary: x is [T, d])
+int tw_activation(const void* x, long long ldx, void* out, long long ldo, int T, int d, int kind, float param,
+                  cudaStream_t stream);
+int tw_copy_pages(void* cache, long long page_bytes, const long long* pairs_dev, int n_pairs, cudaStream_t stream);
+int tw_swap_pages(const void* src, void* dst, long long page_bytes, const long long* pairs_host, int n_pairs,
+                  cudaStream_t stream);
+int tw_merge_attn_states(void* out, float* out_lse, const void* a_out, const float* a_lse, const void* b_out,
+                         const float* b_lse, int T, int H, int D, cudaStream_t stream);
+
 // ---- attention (attn_prefill.cu, attn_decode.cu) ----
 int tw_attn_prefill(const void* q, long long ldq, int T, const void* k_cache, const void* v_cache,
                     int num_blocks, int page, void* out, long long ldo, const int* cu_q, const int* kv_lens,

@@ -88,6 +88,13 @@ class LLMEngine:
             self.core.add_request(child)
         self.parents[request_id] = parent
 
+    def tokenize_prompt(self, prompt: Union[str, list[int], dict]) -> list[int]:
+        """Token ids of a prompt given as text, ids, or a ``{"prompt" / "prompt_token_ids"}`` dict."""
+        if isinstance(prompt, dict):
+            ids = prompt.get("prompt_token_ids")
+            return list(ids) if ids is not None else self._encode(prompt.get("prompt"))
+        return self._encode(prompt) if isinstance(prompt, str) else list(prompt)
+
     def _encode(self, text: str) -> list[int]:
         if self.tokenizer is None:
             raise ValueError("text prompts need a tokenizer (skip_tokenizer_init is set)")

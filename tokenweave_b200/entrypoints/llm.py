@@ -13,8 +13,8 @@ from typing import Any, Optional, Sequence, Union
 
 from ..config import EngineArgs, ModelConfig
 from ..engine.llm_engine import LLMEngine
-from ..outputs import RequestOutput
-from ..sampling_params import SamplingParams
+from ..outputs import BeamSearchOutput, BeamSearchSequence, PoolingOutput, RequestOutput
+from ..sampling_params import BeamSearchParams, SamplingParams
 from ..utils.logging import init_logger
 
 logger = init_logger(__name__)
@@ -78,6 +78,91 @@ class LLM:
         if bar is not None:
             bar.close()
         return [final[r] for r in request_ids if r in final]
+
+    # ---- beam search ------------------------------------------------------------------------
+    def beam_search(self, prompts: Sequence[PromptType], params: "BeamSearchParams") -> list["BeamSearchOutput"]:
+        """Beam search driven from the host, one engine step per generated position: every live beam
+        asks for one token with the ``2 * beam_width`` best log-probabilities, the expansions are
+        ranked by cumulative log-probability, beams that emit EOS retire to the finished set
+        (vllm/entrypoints/llm.py ``LLM.beam_search``). With ``enable_prefix_caching`` the shared
+        prefixes of the beams are not recomputed."""
+        tok = self.get_tokenizer()
+        eos = getattr(tok, "eos_token_id", None) if tok is not None else None
+        if eos is None:
+            eos = self.llm_engine.eos_token_id
+        width = params.beam_width
+        step_sp = SamplingParams(temperature=0.0, max_tokens=1, logprobs=2 * width, ignore_eos=True, detokenize=False)
+        results = []
+        for prompt in prompts:
+            ids = self.llm_engine.tokenize_prompt(prompt)
+            live = [BeamSearchSequence(tokens=list(ids), cum_logprob=0.0)]
+            done: list[BeamSearchSequence] = []
+            for _ in range(params.max_tokens):
+                if not live:
+                    break
+                outs = self.generate(prompt_token_ids=[b.tokens for b in live], sampling_params=step_sp)
+                cand = []
+                for beam, out in zip(live, outs):
+                    lps = out.outputs[0].logprobs[0]
+                    for t, lp in lps.items():
+                        seq = BeamSearchSequence(tokens=beam.tokens + [int(t)], cum_logprob=beam.cum_logprob + float(lp))
+                        if int(t) == eos and not params.ignore_eos:
+                            done.append(seq)
+                        else:
+                            cand.append(seq)
+                cand.sort(key=lambda s: s.cum_logprob, reverse=True)
+                live = cand[:width]
+            done.extend(live)
+
+            def score(s: BeamSearchSequence) -> float:
+                n = len(s.tokens) - len(ids)
+                if s.tokens[-1] == eos:
+                    n -= 1
+                return s.cum_logprob / (max(n, 1) ** params.length_penalty)
+
+            best = sorted(done, key=score, reverse=True)[:width]
+            for s in best:
+                s.text = tok.decode(s.tokens[len(ids):]) if tok is not None else None
+            results.append(BeamSearchOutput(sequences=best))
+        return results
+
+    # ---- pooling ------------------------------------------------------------------------------
+    def encode(self, prompts: Union[PromptType, Sequence[PromptType]], normalize: bool = False) -> list["PoolingOutput"]:
+        """Last-token pooling of the final-norm hidden state (the default pooler of decoder-only models in
+        the reference, vllm/model_executor/layers/pooler.py ``PoolingType.LAST``): one vector per prompt."""
+        if isinstance(prompts, (str, dict)) or (isinstance(prompts, list) and prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        prompts = list(prompts)
+        self.collective_rpc("set_capture_hidden", True)
+        try:
+            outs = self.generate(prompts, SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, detokenize=False))
+            captured = self.collective_rpc("take_captured_hidden")[0]
+        finally:
+            self.collective_rpc("set_capture_hidden", False)
+        res = []
+        for o in outs:
+            vec = captured[o.request_id]
+            if normalize:
+                vec = vec / vec.norm().clamp_min(1e-12)
+            res.append(PoolingOutput(request_id=o.request_id, prompt_token_ids=o.prompt_token_ids, data=vec))
+        return res
+
+    def embed(self, prompts: Union[PromptType, Sequence[PromptType]]) -> list["PoolingOutput"]:
+        """L2-normalised :meth:`encode` (``LLM.embed`` of the reference)."""
+        return self.encode(prompts, normalize=True)
+
+    def score(self, text_1: Union[PromptType, Sequence[PromptType]], text_2: Union[PromptType, Sequence[PromptType]]) -> list[float]:
+        """Cosine similarity of the embeddings of ``text_1`` and ``text_2`` (one-to-many or pairwise), the
+        embedding-model branch of the reference's ``LLM.score``."""
+        one = lambda x: isinstance(x, (str, dict)) or (isinstance(x, list) and x and isinstance(x[0], int))  # noqa: E731
+        a = [text_1] if one(text_1) else list(text_1)
+        b = [text_2] if one(text_2) else list(text_2)
+        if len(a) == 1 and len(b) > 1:
+            a = a * len(b)
+        if len(a) != len(b):
+            raise ValueError("score() takes one-to-many or equally long lists")
+        ea, eb = self.embed(a), self.embed(b)
+        return [float((x.data * y.data).sum()) for x, y in zip(ea, eb)]
 
     # ---- utilities ------------------------------------------------------------------------------
     def collective_rpc(self, method: str, *args, **kwargs) -> list[Any]:

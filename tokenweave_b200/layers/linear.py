@@ -21,7 +21,37 @@ def _param(*shape, dtype, device) -> nn.Parameter:
     return nn.Parameter(torch.empty(*shape, dtype=dtype, device=device), requires_grad=False)
 
 
-class ReplicatedLinear(nn.Module):
+class _QuantizableLinear(nn.Module):
+    """Shared GEMM dispatch of the linear layers. After :meth:`quantize_fp8_` the bf16 weight is replaced
+    by an e4m3 weight with one fp32 scale per output channel and every call quantises its input per
+    token on the fly (dynamic activation scales) before the fp8 tcgen05 GEMM — the scheme of the
+    reference's ``Fp8LinearMethod`` with dynamic activation quantisation
+    (vllm/model_executor/layers/quantization/fp8.py) on its sm100 scaled-mm."""
+
+    weight_scale: Optional[torch.Tensor] = None
+
+    def quantize_fp8_(self) -> None:
+        if self.weight_scale is not None:
+            return
+        q, scale = ops.quant_fp8(self.weight.data)
+        self.weight = nn.Parameter(q, requires_grad=False)
+        self.weight_scale = scale
+
+    def _gemm(self, x: torch.Tensor, out: Optional[torch.Tensor], *, bias=None, row_scale=None, swiglu=False,
+              max_ctas: int = 0) -> torch.Tensor:
+        if self.weight_scale is None:
+            return ops.gemm(x, self.weight, out=out, bias=bias, row_scale=row_scale, swiglu=swiglu, max_ctas=max_ctas)
+        if out is None:
+            n = self.weight.shape[0] // 2 if swiglu else self.weight.shape[0]
+            out = torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
+        xq, x_scale = ops.quant_fp8(x, max_ctas=max_ctas)
+        if row_scale is not None:
+            x_scale = x_scale * row_scale
+        return ops.gemm_fp8(xq, self.weight, x_scale, self.weight_scale, out=out, bias=bias, swiglu=swiglu,
+                            max_ctas=max_ctas)
+
+
+class ReplicatedLinear(_QuantizableLinear):
     def __init__(self, in_features: int, out_features: int, bias: bool = False, *, dtype, device):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
@@ -29,13 +59,13 @@ class ReplicatedLinear(nn.Module):
         self.bias = _param(out_features, dtype=dtype, device=device) if bias else None
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
-        return ops.gemm(x, self.weight, out=out, bias=self.bias, max_ctas=max_ctas)
+        return self._gemm(x, out, bias=self.bias, max_ctas=max_ctas)
 
     def weight_loader(self, param: nn.Parameter, loaded: torch.Tensor, shard_id=None) -> None:
         param.data.copy_(loaded)
 
 
-class ColumnParallelLinear(nn.Module):
+class ColumnParallelLinear(_QuantizableLinear):
     """Output features sharded over the TP ranks; the input is replicated."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = False, *, dtype, device):
@@ -49,7 +79,7 @@ class ColumnParallelLinear(nn.Module):
         self.bias = _param(self.out_per_rank, dtype=dtype, device=device) if bias else None
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
-        return ops.gemm(x, self.weight, out=out, bias=self.bias, max_ctas=max_ctas)
+        return self._gemm(x, out, bias=self.bias, max_ctas=max_ctas)
 
     def weight_loader(self, param: nn.Parameter, loaded: torch.Tensor, shard_id=None) -> None:
         r = get_tp().rank
@@ -67,7 +97,7 @@ class MergedColumnParallelLinear(ColumnParallelLinear):
 
     def forward_swiglu(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
         """silu(x @ gate.T) * (x @ up.T), fused into the GEMM epilogue."""
-        return ops.gemm(x, self.weight, out=out, swiglu=True, max_ctas=max_ctas)
+        return self._gemm(x, out, swiglu=True, max_ctas=max_ctas)
 
     def weight_loader(self, param: nn.Parameter, loaded: torch.Tensor, shard_id=None) -> None:
         tp = get_tp()
@@ -82,7 +112,7 @@ class MergedColumnParallelLinear(ColumnParallelLinear):
         param.data.narrow(0, dst_off, size).copy_(loaded.narrow(0, tp.rank * size, size))
 
 
-class QKVParallelLinear(nn.Module):
+class QKVParallelLinear(_QuantizableLinear):
     """Packed [q | k | v] projection; KV heads are replicated when tp > num_kv_heads
     (vllm/model_executor/layers/linear.py:856-897)."""
 
@@ -104,7 +134,7 @@ class QKVParallelLinear(nn.Module):
         self.bias = _param(self.out_per_rank, dtype=dtype, device=device) if bias else None
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
-        return ops.gemm(x, self.weight, out=out, bias=self.bias, max_ctas=max_ctas)
+        return self._gemm(x, out, bias=self.bias, max_ctas=max_ctas)
 
     def weight_loader(self, param: nn.Parameter, loaded: torch.Tensor, shard_id=None) -> None:
         tp = get_tp()
@@ -118,7 +148,7 @@ class QKVParallelLinear(nn.Module):
         param.data.narrow(0, dst, size).copy_(loaded.narrow(0, src, size))
 
 
-class RowParallelLinear(nn.Module):
+class RowParallelLinear(_QuantizableLinear):
     """Input features sharded; the output holds this rank's partial sums (no all-reduce here)."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = False, *, dtype, device):
@@ -133,7 +163,7 @@ class RowParallelLinear(nn.Module):
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, max_ctas: int = 0,
                 row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
         bias = self.bias if get_tp().rank == 0 else None   # added once across the reduction
-        return ops.gemm(x, self.weight, out=out, bias=bias, row_scale=row_scale, max_ctas=max_ctas)
+        return self._gemm(x, out, bias=bias, row_scale=row_scale, max_ctas=max_ctas)
 
     def weight_loader(self, param: nn.Parameter, loaded: torch.Tensor, shard_id=None) -> None:
         r = get_tp().rank

@@ -16,7 +16,7 @@ from . import _native, gemm_table, reference
 
 __all__ = [
     "gemm", "rmsnorm", "rmsnorm_copy_", "add_rmsnorm_", "rope_kv_write_", "swiglu", "embedding", "argmax",
-    "attn_prefill", "attn_decode", "moe_router", "moe_align", "moe_scatter", "moe_combine", "status_word",
+    "quant_fp8", "rmsnorm_quant_fp8", "gemm_fp8", "activation", "copy_pages", "swap_pages", "merge_attn_states", "attn_prefill", "attn_decode", "moe_router", "moe_align", "moe_scatter", "moe_combine", "status_word",
     "check_status", "reset_status", "STATUS_CODES", "KernelStatusError",
 ]
 
@@ -108,6 +108,79 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
     return out
 
 
+FP8 = torch.float8_e4m3fn
+
+
+def quant_fp8(x: torch.Tensor, scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+              max_ctas: int = 0):
+    """bf16 ``[T, H]`` -> (e4m3 ``[T, H]``, fp32 scales). ``scale`` None: dynamic per-token scales
+    ``max|row| / 448`` (``[T]``); else the given one-element tensor is used for every row (static)."""
+    T, H = x.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=FP8, device=x.device)
+    if not x.is_cuda:
+        q, s = reference.quant_fp8(x, scale)
+        out.copy_(q)
+        return out, s
+    _check_bf16(x)
+    scales = torch.empty(T, dtype=torch.float32, device=x.device) if scale is None else scale
+    _native.call("tw_quant_fp8", x.data_ptr(), _row_stride(x), out.data_ptr(), _row_stride(out), scales.data_ptr(),
+                 T, H, int(scale is None), max_ctas, _stream())
+    return out, scales
+
+
+def rmsnorm_quant_fp8(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None,
+                      scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, max_ctas: int = 0):
+    """``q = e4m3(rmsnorm(x [+ residual]) * weight / scale)``; with ``residual`` the sum is written back to
+    ``residual`` first. Returns ``(q, scales)`` like :func:`quant_fp8`."""
+    T, H = x.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=FP8, device=x.device)
+    if not x.is_cuda:
+        if residual is not None:
+            residual.copy_((x + residual))
+            y = reference.rmsnorm(residual, weight, eps)
+        else:
+            y = reference.rmsnorm(x, weight, eps)
+        q, s = reference.quant_fp8(y, scale)
+        out.copy_(q)
+        return out, s
+    _check_bf16(x, weight, residual)
+    scales = torch.empty(T, dtype=torch.float32, device=x.device) if scale is None else scale
+    _native.call("tw_rmsnorm_quant_fp8", x.data_ptr(), _p(residual), weight.data_ptr(), out.data_ptr(),
+                 _row_stride(out), scales.data_ptr(), T, H, _row_stride(x),
+                 _row_stride(residual) if residual is not None else 0, float(eps), int(scale is None), max_ctas,
+                 _stream())
+    return out, scales
+
+
+def gemm_fp8(a: torch.Tensor, w: torch.Tensor, a_scale: Optional[torch.Tensor], w_scale: Optional[torch.Tensor],
+             out: Optional[torch.Tensor] = None, *, bias: Optional[torch.Tensor] = None, swiglu: bool = False,
+             max_ctas: int = 0) -> torch.Tensor:
+    """``out[m, n] = (a @ w.T)[m, n] * a_scale[m] * w_scale[n] + bias[n]`` in bf16, ``a`` ``[M, K]`` and ``w``
+    ``[N, K]`` being e4m3 (per-token and per-output-channel scales, fp32, either may be None). With
+    ``swiglu`` the weight is ``[gate; up]`` and the result ``silu(gate part) * (up part)``."""
+    M, K = a.shape
+    rows_b = w.shape[0]
+    N = rows_b // 2 if swiglu else rows_b
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    if not a.is_cuda:
+        out.copy_(reference.gemm_fp8(a, w, a_scale, w_scale, bias, swiglu))
+        return out
+    if a.dtype != FP8 or w.dtype != FP8:
+        raise TypeError("gemm_fp8 takes float8_e4m3fn operands")
+    _check_bf16(out, bias)
+    for s, n in ((a_scale, M), (w_scale, rows_b)):
+        if s is not None and (s.dtype != torch.float32 or s.numel() != n or not s.is_contiguous()):
+            raise ValueError("scales must be contiguous fp32 vectors of one value per row / output channel")
+    _native.call("tw_gemm_fp8", a.data_ptr(), _row_stride(a), w.data_ptr(), _row_stride(w), rows_b, out.data_ptr(),
+                 _row_stride(out), _p(bias), _p(a_scale), _p(w_scale), M, N, K, int(swiglu), N if swiglu else 0,
+                 None, None, rows_b, max_ctas, 0, status_word(a.device).data_ptr(), _stream(),
+                 tag=f"[fp8 {M}x{N}x{K}{'+swiglu' if swiglu else ''}]" if _native._timing is not None else "")
+    return out
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None,
             max_ctas: int = 0) -> torch.Tensor:
     if out is None:
@@ -176,6 +249,76 @@ def swiglu(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _check_bf16(x, out)
     _native.call("tw_swiglu", x.data_ptr(), _row_stride(x), out.data_ptr(), _row_stride(out), T, d, _stream())
     return out
+
+
+def activation(x: torch.Tensor, kind: str, out: Optional[torch.Tensor] = None, param: float = 0.0) -> torch.Tensor:
+    """Gated (``*_and_mul``: ``x`` is ``[T, 2d]``) or unary (``x`` is ``[T, d]``) activation; the kinds
+    are the keys of ``reference.ACTIVATION_KINDS`` (vllm/model_executor/layers/activation.py)."""
+    code = reference.ACTIVATION_KINDS[kind]
+    T = x.shape[0]
+    d = x.shape[1] // 2 if code <= 4 else x.shape[1]
+    if out is None:
+        out = torch.empty(T, d, dtype=x.dtype, device=x.device)
+    if not x.is_cuda:
+        out.copy_(reference.activation(x, kind, param))
+        return out
+    _check_bf16(x, out)
+    _native.call("tw_activation", x.data_ptr(), _row_stride(x), out.data_ptr(), _row_stride(out), T, d, code,
+                 float(param), _stream())
+    return out
+
+
+def copy_pages(cache: torch.Tensor, pairs: torch.Tensor) -> None:
+    """Copies page ``pairs[i, 0]`` onto page ``pairs[i, 1]`` of one paged cache tensor ``[pages, ...]``
+    (the copy-on-write step of csrc/cache_kernels.cu:69-130). ``pairs``: int64 ``[n, 2]``."""
+    if pairs.numel() == 0:
+        return
+    if not cache.is_cuda:
+        cache[pairs[:, 1].long()] = cache[pairs[:, 0].long()]
+        return
+    assert cache.is_contiguous() and pairs.dtype == torch.int64 and pairs.is_contiguous()
+    pairs = pairs.to(cache.device)
+    page_bytes = cache.stride(0) * cache.element_size()
+    _native.call("tw_copy_pages", cache.data_ptr(), page_bytes, pairs.data_ptr(), pairs.shape[0], _stream())
+
+
+def swap_pages(src: torch.Tensor, dst: torch.Tensor, pairs) -> None:
+    """Copies page ``s`` of ``src`` to page ``d`` of ``dst`` for every ``(s, d)`` in ``pairs`` (host list);
+    either tensor may live in pinned host memory (csrc/cache_kernels.cu:24-66). Consecutive pages
+    travel as one asynchronous copy on the current stream."""
+    pairs = [(int(s), int(d)) for s, d in pairs]
+    if not pairs:
+        return
+    if not (src.is_cuda or dst.is_cuda):
+        for s, d in pairs:
+            dst[d].copy_(src[s])
+        return
+    assert src.is_contiguous() and dst.is_contiguous() and src.shape[1:] == dst.shape[1:] and src.dtype == dst.dtype
+    import ctypes
+    flat = (ctypes.c_longlong * (2 * len(pairs)))(*[v for p in pairs for v in p])
+    page_bytes = src.stride(0) * src.element_size()
+    _native.call("tw_swap_pages", src.data_ptr(), dst.data_ptr(), page_bytes, ctypes.addressof(flat), len(pairs),
+                 _stream())
+
+
+def merge_attn_states(a_out: torch.Tensor, a_lse: torch.Tensor, b_out: torch.Tensor, b_lse: torch.Tensor,
+                      out: Optional[torch.Tensor] = None, want_lse: bool = False):
+    """Merges two partial attention results over disjoint key sets (csrc/attention/merge_attn_states.cu).
+    Outputs ``[T, H, D]`` bf16, log-sum-exps ``[H, T]`` fp32. Returns ``out`` or ``(out, lse)``."""
+    T, H, D = a_out.shape
+    if out is None:
+        out = torch.empty_like(a_out)
+    if not a_out.is_cuda:
+        o, lse = reference.merge_attn_states(a_out, a_lse, b_out, b_lse)
+        out.copy_(o)
+        return (out, lse) if want_lse else out
+    _check_bf16(a_out, b_out, out)
+    assert a_out.is_contiguous() and b_out.is_contiguous() and out.is_contiguous()
+    assert a_lse.dtype == torch.float32 and b_lse.dtype == torch.float32 and a_lse.is_contiguous() and b_lse.is_contiguous()
+    lse = torch.empty(H, T, dtype=torch.float32, device=a_out.device) if want_lse else None
+    _native.call("tw_merge_attn_states", out.data_ptr(), _p(lse), a_out.data_ptr(), a_lse.data_ptr(),
+                 b_out.data_ptr(), b_lse.data_ptr(), T, H, D, _stream())
+    return (out, lse) if want_lse else out
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, vocab_start: int = 0,

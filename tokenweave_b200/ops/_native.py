@@ -25,6 +25,13 @@ _SIGNATURES = {
     "tw_swiglu": [vp, ll, vp, ll, i32, i32, vp],
     "tw_embedding": [vp, vp, vp, ll, i32, i32, i32, i32, vp],
     "tw_argmax": [vp, ll, vp, i32, i32, vp],
+    "tw_gemm_fp8": [vp, ll, vp, ll, ll, vp, ll, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp, vp],
+    "tw_quant_fp8": [vp, ll, vp, ll, vp, i32, i32, i32, i32, vp],
+    "tw_rmsnorm_quant_fp8": [vp, vp, vp, vp, ll, vp, i32, i32, ll, ll, f32, i32, i32, vp],
+    "tw_activation": [vp, ll, vp, ll, i32, i32, i32, f32, vp],
+    "tw_copy_pages": [vp, ll, vp, i32, vp],
+    "tw_swap_pages": [vp, vp, ll, vp, i32, vp],
+    "tw_merge_attn_states": [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
     "tw_attn_prefill": [vp, ll, i32, vp, vp, i32, i32, vp, ll, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32,
                         f32, vp, vp],
     "tw_attn_decode": [vp, ll, vp, vp, i32, vp, ll, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp, vp,

@@ -56,6 +56,85 @@ def swiglu(x: torch.Tensor) -> torch.Tensor:
     return (F.silu(xf[..., :d]) * xf[..., d:]).to(x.dtype)
 
 
+FP8_MAX = 448.0
+
+
+def quant_fp8(x: torch.Tensor, scale: Optional[torch.Tensor] = None):
+    """(e4m3 tensor, scales): per-token ``max|row| / 448`` when ``scale`` is None, else the given scalar."""
+    xf = x.float()
+    if scale is None:
+        s = (xf.abs().amax(dim=-1) / FP8_MAX).clamp_min(1e-10)
+        q = (xf / s.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+        return q, s
+    q = (xf / scale.float().reshape(())).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q, scale
+
+
+def gemm_fp8(a: torch.Tensor, w: torch.Tensor, a_scale: Optional[torch.Tensor], w_scale: Optional[torch.Tensor],
+             bias: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
+    """fp32 product of the dequantised operands, scaled per row and per output channel, rounded once."""
+    acc = a.float() @ w.float().t()
+    if a_scale is not None:
+        acc = acc * a_scale.float().unsqueeze(-1)
+    if w_scale is not None:
+        acc = acc * w_scale.float().unsqueeze(0)
+    if swiglu:
+        n = acc.shape[1] // 2
+        return (F.silu(acc[:, :n]) * acc[:, n:]).to(torch.bfloat16)
+    if bias is not None:
+        acc = acc + bias.float()
+    return acc.to(torch.bfloat16)
+
+
+ACTIVATION_KINDS = {"silu_and_mul": 0, "gelu_and_mul": 1, "gelu_tanh_and_mul": 2, "mul_and_silu": 3,
+                    "fatrelu_and_mul": 4, "gelu_new": 5, "gelu_fast": 6, "quick_gelu": 7, "gelu": 8, "silu": 9}
+
+
+def activation(x: torch.Tensor, kind: str, param: float = 0.0) -> torch.Tensor:
+    """The activation functions of vllm/model_executor/layers/activation.py in fp32, rounded once."""
+    xf = x.float()
+    if ACTIVATION_KINDS[kind] <= 4:
+        d = x.shape[-1] // 2
+        a, b = xf[..., :d], xf[..., d:]
+        if kind == "silu_and_mul":
+            y = F.silu(a) * b
+        elif kind == "gelu_and_mul":
+            y = F.gelu(a) * b
+        elif kind == "gelu_tanh_and_mul":
+            y = F.gelu(a, approximate="tanh") * b
+        elif kind == "mul_and_silu":
+            y = a * F.silu(b)
+        else:
+            y = torch.where(a > param, a, torch.zeros_like(a)) * b
+    elif kind == "gelu_new":
+        y = F.gelu(xf, approximate="tanh")
+    elif kind == "gelu_fast":
+        y = 0.5 * xf * (1.0 + torch.tanh(xf * 0.7978845608 * (1.0 + 0.044715 * xf * xf)))
+    elif kind == "quick_gelu":
+        y = xf * torch.sigmoid(1.702 * xf)
+    elif kind == "gelu":
+        y = F.gelu(xf)
+    else:
+        y = F.silu(xf)
+    return y.to(x.dtype)
+
+
+def merge_attn_states(a_out: torch.Tensor, a_lse: torch.Tensor, b_out: torch.Tensor, b_lse: torch.Tensor):
+    """Merge two partial attention results over disjoint key sets. Outputs ``[T, H, D]``, log-sum-exps
+    ``[H, T]`` (natural log). Returns (merged output, merged lse)."""
+    la = torch.where(torch.isinf(a_lse), torch.full_like(a_lse, -math.inf), a_lse).float()
+    lb = torch.where(torch.isinf(b_lse), torch.full_like(b_lse, -math.inf), b_lse).float()
+    m = torch.maximum(la, lb)
+    safe = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    ea, eb = torch.exp(la - safe), torch.exp(lb - safe)
+    tot = ea + eb
+    wa = torch.where(tot > 0, ea / tot, torch.zeros_like(tot)).t().unsqueeze(-1)
+    wb = torch.where(tot > 0, eb / tot, torch.zeros_like(tot)).t().unsqueeze(-1)
+    out = (a_out.float() * wa + b_out.float() * wb).to(a_out.dtype)
+    lse = torch.where(tot > 0, safe + torch.log(tot), torch.full_like(tot, -math.inf))
+    return out, lse
+
+
 def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``silu(a @ Wg.T) * (a @ Wu.T)`` where ``w_gate_up = [Wg; Wu]``, rounded once at the end."""
     inter = w_gate_up.shape[0] // 2

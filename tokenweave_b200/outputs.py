@@ -36,3 +36,24 @@ class RequestOutput:
     outputs: list[CompletionOutput]
     finished: bool
     metrics: RequestMetrics = field(default_factory=RequestMetrics)
+
+
+@dataclass
+class BeamSearchSequence:
+    """One hypothesis of ``LLM.beam_search``: prompt + generated token ids and their summed log-probability."""
+    tokens: list[int]
+    cum_logprob: float = 0.0
+    text: Optional[str] = None
+
+
+@dataclass
+class BeamSearchOutput:
+    sequences: list[BeamSearchSequence]
+
+
+@dataclass
+class PoolingOutput:
+    """Result of ``LLM.encode`` / ``LLM.embed``: ``data`` is the pooled hidden state (fp32, on the host)."""
+    request_id: str
+    prompt_token_ids: list[int]
+    data: "object"

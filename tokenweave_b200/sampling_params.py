@@ -52,3 +52,17 @@ class SamplingParams:
     def clone(self) -> "SamplingParams":
         import copy
         return copy.deepcopy(self)
+
+
+@dataclass
+class BeamSearchParams:
+    """Parameters of ``LLM.beam_search`` (vllm/sampling_params.py ``BeamSearchParams``)."""
+    beam_width: int
+    max_tokens: int
+    ignore_eos: bool = False
+    temperature: float = 0.0
+    length_penalty: float = 1.0
+
+    def __post_init__(self):
+        if self.beam_width < 1 or self.max_tokens < 1:
+            raise ValueError("beam_width and max_tokens must be at least 1")

@@ -92,6 +92,8 @@ class ModelRunner:
         self.timing_events = None
         self.capture_logits = False          # tests: keep the fp32 logits of every step
         self.captured_logits: list = []
+        self.capture_hidden = False          # pooling requests: keep the final-norm hidden row of every sampled position
+        self.captured_hidden: dict = {}
         self._h2d_done = torch.cuda.Event() if pin else None   # guards reuse of the pinned staging buffers
         # CUDA graphs: a step whose shape signature has been seen before is replayed from a captured graph
         self.use_graphs = bool(tw.use_cuda_graphs) and pin
@@ -163,7 +165,10 @@ class ModelRunner:
         hidden = self.model(step_in)
         if n_logits == 0:
             return None, None
-        logits = self.model.compute_logits(hidden.index_select(0, self._rows_dev[:n_logits]))
+        rows = hidden.index_select(0, self._rows_dev[:n_logits])
+        if self.capture_hidden:
+            self._last_hidden_rows = rows
+        logits = self.model.compute_logits(rows)
         return logits, (ops.argmax(logits) if greedy else None)
 
     def _run_graphed(self, sig, step_in: StepInput, n_logits: int, greedy: bool):
@@ -248,7 +253,7 @@ class ModelRunner:
         if n_logits:
             self._rows_host[:n_logits] = torch.as_tensor(logits_rows, dtype=torch.long)
             self._rows_dev[:n_logits].copy_(self._rows_host[:n_logits], non_blocking=True)
-        if self.use_graphs and not self.capture_logits:
+        if self.use_graphs and not self.capture_logits and not self.capture_hidden:
             logits, greedy_ids = self._run_graphed(self._signature(step_in, n_logits, greedy), step_in, n_logits, greedy)
         else:
             logits, greedy_ids = self._forward_and_logits(step_in, n_logits, greedy)
@@ -256,6 +261,10 @@ class ModelRunner:
         lp = None
         d2h = 0
         if logits_rows:
+            if self.capture_hidden:
+                rows = self._last_hidden_rows.detach().float().cpu()
+                for rid, row in zip(sample_reqs, rows):
+                    self.captured_hidden.setdefault(rid, row.clone())
             if self.capture_logits:
                 self.captured_logits.append((list(sample_reqs), logits.detach().float().cpu().clone()))
             if greedy_ids is not None:

@@ -138,6 +138,15 @@ class Worker:
         if self.device.type == "cuda":
             torch.cuda.synchronize()
 
+    def set_capture_hidden(self, on: bool) -> None:
+        """Pooling support: keep the final-norm hidden state at every request's first sampled position."""
+        self.runner.capture_hidden = bool(on)
+        self.runner.captured_hidden = {}
+
+    def take_captured_hidden(self) -> dict:
+        out, self.runner.captured_hidden = self.runner.captured_hidden, {}
+        return out
+
     def save_sharded_state(self, path: str) -> None:
         from safetensors.torch import save_file
         os.makedirs(path, exist_ok=True)
