@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--mode", default="overlap",
                     choices=["overlap", "fuse_only", "fused_gemm", "baseline_nccl", "baseline_multimem", "no_ar"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the result invalid)")
+    ap.add_argument("--cuda-graphs", action="store_true",
+                    help="replay the step from a CUDA graph (captured during warm-up; needs --warmup >= 3)")
     return ap.parse_args()
 
 
@@ -147,7 +149,8 @@ def main() -> None:
               distributed_executor_backend="external_launcher" if n > 1 else "uni",
               max_num_batched_tokens=T, max_model_len=T + 64, block_size=128, enable_chunked_prefill=True,
               enable_prefix_caching=False, load_format="dummy", tokenweave_mode=args.mode,
-              num_gpu_blocks_override=(T + 64) // 128 + 8, num_hidden_layers_override=args.layers, seed=0)
+              num_gpu_blocks_override=(T + 64) // 128 + 8, num_hidden_layers_override=args.layers, seed=0,
+              tokenweave_cuda_graphs=args.cuda_graphs)
     cfg = llm.llm_engine.config.model
     runner = llm.llm_engine.core.executor.worker.runner
     g = torch.Generator().manual_seed(1234)
@@ -161,8 +164,12 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    warm_launches = 0
     for i in range(args.warmup):
+        l0 = _native.launch_count()
         llm.generate(prompt_token_ids=[pinned_prompts[i].tolist()], sampling_params=sp)
+        if i == 0:
+            warm_launches = _native.launch_count() - l0
     barrier()
     ops.check_status()
 
@@ -185,6 +192,9 @@ def main() -> None:
         d2h += runner.d2h_bytes_last_step
     barrier()
     launches = _native.launch_count() - launches0
+    if args.cuda_graphs:
+        # replayed steps launch the kernels recorded at capture time: count those (the eager warm-up step's)
+        launches = warm_launches * args.steps
     dev_ms = sum(a.elapsed_time(b) for a, b in runner.timing_events)
     assert len(runner.timing_events) == args.steps, "one engine step per generate call expected"
     runner.timing_events = None
@@ -209,7 +219,7 @@ def main() -> None:
         "data": "synthetic random token ids, random-init weights (no checkpoint)",
         "config": {"model": args.model, "global_batch": 1, "seq_len": T, "parallelism": f"tp{n}",
                    "layers": cfg.num_layers, "tokenweave_mode": args.mode if n > 1 else "single-gpu",
-                   "transport": transport,
+                   "transport": transport, "cuda_graphs": bool(args.cuda_graphs),
                    "l2": "per-rank weights (>= 17 GB) exceed the 126 MB L2; a 256 MB buffer is zeroed between steps",
                    "baseline": "TokenWeave on 8xH100, same prompt length (artifact/csvs/figure_11a.csv)"},
         "clocks": clocks,

@@ -120,3 +120,30 @@ def test_message_queue_large_payload_and_timeout():
         r0.dequeue(timeout=0.05)
     for q in (r0, r1, w):
         q.close()
+
+
+def test_engines_built_one_after_another_under_torchrun(tmp_path):
+    """Several engines in one torchrun job (what the benchmark scripts do, one per schedule): every
+    re-initialisation of the process group must use fresh rendezvous keys in the launcher's store."""
+    import subprocess
+    import sys
+    from tw_testing import free_port
+    script = tmp_path / "reinit.py"
+    script.write_text(
+        "import os\n"
+        "from tokenweave_b200 import LLM, SamplingParams\n"
+        "for i in range(3):\n"
+        "    llm = LLM('tiny-llama', dtype='float32', device='cpu', tensor_parallel_size=2, skip_tokenizer_init=True,\n"
+        "              distributed_executor_backend='external_launcher', block_size=16, max_num_batched_tokens=128)\n"
+        "    out = llm.generate(prompt_token_ids=[[1, 2, 3, 4, 5]], sampling_params=SamplingParams(temperature=0, max_tokens=3))\n"
+        "    if os.environ['RANK'] == '0':\n"
+        "        print('RESULT', i, out[0].outputs[0].token_ids, flush=True)\n"
+        "    llm.shutdown()\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(free_port()), str(script)],
+                         env=env, capture_output=True, text=True, timeout=280)
+    assert res.returncode == 0, res.stderr[-3000:]
+    lines = [ln.split(" ", 2)[2] for ln in res.stdout.splitlines() if ln.startswith("RESULT")]
+    assert len(lines) == 3 and len(set(lines)) == 1

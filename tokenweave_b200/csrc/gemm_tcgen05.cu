@@ -261,12 +261,46 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         } else {
           tmem_wait_ld();
           if (FP8) {
+            const int nc = n0 + c * 32;
+            if (nc + 32 <= p.N && (p.N & 7) == 0) {
+              // whole chunk in range: channel scales and bias come in as 16-byte vectors (the same
+              // addresses for every thread of the warp, one transaction each)
+              if (p.col_scale != nullptr) {
+                const float4* cs4 = reinterpret_cast<const float4*>(p.col_scale + nc);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int n = n0 + c * 32 + j;
-              const float cs = (p.col_scale != nullptr && n < p.N) ? p.col_scale[n] : 1.f;
-              const float b = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
-              v[j] = __float_as_uint(__uint_as_float(v[j]) * rs * cs + b);
+                for (int j = 0; j < 8; ++j) {
+                  const float4 s = __ldg(cs4 + j);
+                  v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) * (rs * s.x));
+                  v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) * (rs * s.y));
+                  v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) * (rs * s.z));
+                  v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) * (rs * s.w));
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * rs);
+              }
+              if (p.bias != nullptr) {
+                const uint4* b4 = reinterpret_cast<const uint4*>(p.bias + nc);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint4 b = __ldg(b4 + j);
+                  const uint32_t* bu = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = unpack_bf16x2(bu[e]);
+                    v[8 * j + 2 * e] = __float_as_uint(__uint_as_float(v[8 * j + 2 * e]) + f.x);
+                    v[8 * j + 2 * e + 1] = __float_as_uint(__uint_as_float(v[8 * j + 2 * e + 1]) + f.y);
+                  }
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int n = nc + j;
+                const float cs = (p.col_scale != nullptr && n < p.N) ? p.col_scale[n] : 1.f;
+                const float b = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+                v[j] = __float_as_uint(__uint_as_float(v[j]) * rs * cs + b);
+              }
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j)

@@ -1,0 +1,280 @@
+"""OpenAI-compatible HTTP server on top of :class:`AsyncLLMEngine`.
+
+    python -m tokenweave_b200.entrypoints.api_server --model <dir or preset> --tensor-parallel-size 1 --port 8000
+
+Endpoints: ``GET /health``, ``GET /v1/models``, ``POST /v1/completions``, ``POST /v1/chat/completions``
+(both with ``"stream": true`` server-sent events), ``POST /tokenize``, ``POST /detokenize``,
+``GET /metrics`` (Prometheus text). A lean counterpart of vllm/entrypoints/openai/api_server.py and
+serving_completion.py / serving_chat.py: the request fields that map onto ``SamplingParams`` are
+honoured, the rest of the OpenAI schema (tools, response formats, multimodal parts) is not served.
+Tensor-parallel serving uses the multiprocess executor (one worker process per GPU).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import time
+import uuid
+from typing import Any, AsyncIterator, Optional
+
+from ..config import EngineArgs
+from ..engine.async_engine import AsyncLLMEngine, EngineDeadError
+from ..outputs import RequestOutput
+from ..sampling_params import SamplingParams
+from ..utils.logging import init_logger
+
+logger = init_logger(__name__)
+
+_SAMPLING_FIELDS = ("n", "temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty",
+                    "repetition_penalty", "seed", "stop", "stop_token_ids", "max_tokens", "min_tokens", "ignore_eos",
+                    "skip_special_tokens")
+
+
+def sampling_params_from_request(body: dict, default_max_tokens: int = 16) -> SamplingParams:
+    kw = {k: body[k] for k in _SAMPLING_FIELDS if body.get(k) is not None}
+    if "max_completion_tokens" in body and body["max_completion_tokens"] is not None:
+        kw["max_tokens"] = body["max_completion_tokens"]
+    kw.setdefault("max_tokens", default_max_tokens)
+    lp = body.get("logprobs")
+    if isinstance(lp, bool):            # chat schema: logprobs: true + top_logprobs: k
+        lp = (body.get("top_logprobs") or 0) if lp else None
+    if lp is not None:
+        kw["logprobs"] = int(lp)
+    return SamplingParams(**kw)
+
+
+def _usage(out: RequestOutput) -> dict:
+    gen = sum(len(c.token_ids) for c in out.outputs)
+    return {"prompt_tokens": len(out.prompt_token_ids), "completion_tokens": gen,
+            "total_tokens": len(out.prompt_token_ids) + gen}
+
+
+def _logprobs_block(comp, tokenizer) -> Optional[dict]:
+    if comp.logprobs is None:
+        return None
+    dec = (lambda t: tokenizer.decode([t])) if tokenizer is not None else (lambda t: str(t))
+    toks = [dec(t) for t in comp.token_ids]
+    chosen = [float(lp.get(t, 0.0)) for lp, t in zip(comp.logprobs, comp.token_ids)]
+    top = [{dec(t): float(v) for t, v in lp.items()} for lp in comp.logprobs]
+    return {"tokens": toks, "token_logprobs": chosen, "top_logprobs": top}
+
+
+def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None):
+    from fastapi import FastAPI, Request
+    from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+    app = FastAPI(title="tokenweave_b200")
+    model_cfg = engine.engine.config.model
+    name = served_model_name or model_cfg.name
+    tokenizer = engine.engine.tokenizer
+    prom = None
+    try:
+        from ..utils.metrics import PrometheusStatLogger
+        prom = PrometheusStatLogger(name)
+        engine.engine.stat_logger = prom
+    except Exception:       # prometheus_client missing: /metrics answers 501
+        prom = None
+
+    def error(status: int, msg: str, typ: str = "invalid_request_error"):
+        return JSONResponse({"error": {"message": msg, "type": typ, "code": status}}, status_code=status)
+
+    def finished_metrics(out: RequestOutput) -> None:
+        if prom is not None and out.finished:
+            m = out.metrics
+            prom.record_finished((m.first_token_time - m.arrival_time) if m.first_token_time else None,
+                                 (m.finished_time - m.arrival_time) if m.finished_time else None)
+
+    @app.get("/health")
+    async def health():
+        return JSONResponse({"status": "ok"}) if engine.is_running else error(503, "engine is not running", "server_error")
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": name, "object": "model", "created": int(time.time()),
+                                            "owned_by": "tokenweave_b200", "max_model_len": model_cfg.max_model_len}]}
+
+    @app.get("/metrics")
+    async def metrics():
+        if prom is None:
+            return error(501, "prometheus_client is not installed", "server_error")
+        import prometheus_client as pc
+        return PlainTextResponse(pc.generate_latest(prom.registry).decode(), media_type="text/plain; version=0.0.4")
+
+    @app.post("/tokenize")
+    async def tokenize(req: Request):
+        body = await req.json()
+        if tokenizer is None:
+            return error(400, "the server runs without a tokenizer")
+        ids = list(tokenizer.encode(body.get("prompt", "")))
+        return {"tokens": ids, "count": len(ids), "max_model_len": model_cfg.max_model_len}
+
+    @app.post("/detokenize")
+    async def detokenize(req: Request):
+        body = await req.json()
+        if tokenizer is None:
+            return error(400, "the server runs without a tokenizer")
+        return {"prompt": tokenizer.decode(body.get("tokens", []))}
+
+    async def run_all(prompts: list, sp: SamplingParams, base_id: str) -> list[RequestOutput]:
+        import asyncio
+
+        async def one(i, p):
+            last = None
+            async for out in engine.generate(p, sp, f"{base_id}-{i}"):
+                last = out
+            finished_metrics(last)
+            return last
+        return await asyncio.gather(*[one(i, p) for i, p in enumerate(prompts)])
+
+    def normalise_prompts(prompt: Any) -> list:
+        if isinstance(prompt, str):
+            return [prompt]
+        if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
+            return [prompt]
+        if isinstance(prompt, list) and prompt:
+            return list(prompt)
+        raise ValueError("prompt must be a string, a list of strings, a list of token ids or a list of those")
+
+    # ---- /v1/completions ----------------------------------------------------------------------
+    @app.post("/v1/completions")
+    async def completions(req: Request):
+        body = await req.json()
+        try:
+            prompts = normalise_prompts(body.get("prompt"))
+            sp = sampling_params_from_request(body)
+            if tokenizer is None:
+                sp.detokenize = False
+                if any(isinstance(p, str) for p in prompts):
+                    return error(400, "text prompts need a tokenizer; send token ids")
+        except (ValueError, TypeError) as e:
+            return error(400, str(e))
+        rid = "cmpl-" + uuid.uuid4().hex
+        created = int(time.time())
+        echo = bool(body.get("echo"))
+
+        def choice(out: RequestOutput, p_idx: int, comp, text: str, finish) -> dict:
+            return {"index": p_idx * sp.n + comp.index, "text": text, "token_ids": list(comp.token_ids) if tokenizer is None else None,
+                    "logprobs": _logprobs_block(comp, tokenizer), "finish_reason": finish, "stop_reason": comp.stop_reason}
+
+        if body.get("stream"):
+            if len(prompts) != 1:
+                return error(400, "streaming takes a single prompt")
+
+            async def sse() -> AsyncIterator[str]:
+                sent = {}
+                try:
+                    async for out in engine.generate(prompts[0], sp, rid + "-0"):
+                        for comp in out.outputs:
+                            prev = sent.get(comp.index, 0)
+                            delta = comp.text[prev:]
+                            sent[comp.index] = len(comp.text)
+                            if delta or comp.finish_reason:
+                                chunk = {"id": rid, "object": "text_completion", "created": created, "model": name,
+                                         "choices": [{"index": comp.index, "text": delta, "logprobs": None,
+                                                      "finish_reason": comp.finish_reason}]}
+                                yield f"data: {json.dumps(chunk)}\n\n"
+                        if out.finished:
+                            finished_metrics(out)
+                            yield f"data: {json.dumps({'id': rid, 'object': 'text_completion', 'created': created, 'model': name, 'choices': [], 'usage': _usage(out)})}\n\n"
+                except (EngineDeadError, ValueError) as e:
+                    yield f"data: {json.dumps({'error': {'message': str(e)}})}\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(sse(), media_type="text/event-stream")
+
+        try:
+            outs = await run_all(prompts, sp, rid)
+        except ValueError as e:
+            return error(400, str(e))
+        except EngineDeadError as e:
+            return error(500, str(e), "server_error")
+        choices, usage = [], {"prompt_tokens": 0, "completion_tokens": 0, "total_tokens": 0}
+        for i, out in enumerate(outs):
+            for comp in out.outputs:
+                text = comp.text
+                if echo and out.prompt is not None:
+                    text = out.prompt + text
+                choices.append(choice(out, i, comp, text, comp.finish_reason))
+            for k, v in _usage(out).items():
+                usage[k] += v
+        return {"id": rid, "object": "text_completion", "created": created, "model": name, "choices": choices, "usage": usage}
+
+    # ---- /v1/chat/completions -----------------------------------------------------------------
+    def chat_prompt(messages: list, add_generation_prompt: bool = True) -> str:
+        if hasattr(tokenizer, "apply_chat_template") and getattr(tokenizer, "chat_template", None):
+            return tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt)
+        text = "".join(f"{m['role']}: {m['content']}\n" for m in messages)
+        return text + ("assistant: " if add_generation_prompt else "")
+
+    @app.post("/v1/chat/completions")
+    async def chat(req: Request):
+        body = await req.json()
+        if tokenizer is None:
+            return error(400, "chat completions need a tokenizer")
+        msgs = body.get("messages")
+        if not isinstance(msgs, list) or not msgs:
+            return error(400, "messages must be a non-empty list")
+        try:
+            sp = sampling_params_from_request(body, default_max_tokens=256)
+            prompt = chat_prompt(msgs, body.get("add_generation_prompt", True))
+        except (ValueError, TypeError, KeyError) as e:
+            return error(400, str(e))
+        rid = "chatcmpl-" + uuid.uuid4().hex
+        created = int(time.time())
+        if body.get("stream"):
+            async def sse() -> AsyncIterator[str]:
+                sent = {}
+                first = True
+                try:
+                    async for out in engine.generate(prompt, sp, rid):
+                        for comp in out.outputs:
+                            prev = sent.get(comp.index, 0)
+                            delta = comp.text[prev:]
+                            sent[comp.index] = len(comp.text)
+                            d = {"content": delta}
+                            if first:
+                                d["role"] = "assistant"
+                                first = False
+                            if delta or comp.finish_reason:
+                                chunk = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": name,
+                                         "choices": [{"index": comp.index, "delta": d, "finish_reason": comp.finish_reason}]}
+                                yield f"data: {json.dumps(chunk)}\n\n"
+                        if out.finished:
+                            finished_metrics(out)
+                except (EngineDeadError, ValueError) as e:
+                    yield f"data: {json.dumps({'error': {'message': str(e)}})}\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(sse(), media_type="text/event-stream")
+        try:
+            out = (await run_all([prompt], sp, rid))[0]
+        except ValueError as e:
+            return error(400, str(e))
+        except EngineDeadError as e:
+            return error(500, str(e), "server_error")
+        choices = [{"index": c.index, "message": {"role": "assistant", "content": c.text},
+                    "logprobs": _logprobs_block(c, tokenizer), "finish_reason": c.finish_reason} for c in out.outputs]
+        return {"id": rid, "object": "chat.completion", "created": created, "model": name, "choices": choices,
+                "usage": _usage(out)}
+
+    return app
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--served-model-name", default=None)
+    EngineArgs.add_cli_args(ap)
+    ns = ap.parse_args()
+    args = EngineArgs.from_cli_args(ns)
+    if args.tensor_parallel_size > 1 and args.distributed_executor_backend == "auto":
+        args.distributed_executor_backend = "mp"
+    engine = AsyncLLMEngine.from_engine_args(args)
+    import uvicorn
+    try:
+        uvicorn.run(build_app(engine, ns.served_model_name), host=ns.host, port=ns.port, log_level="info")
+    finally:
+        engine.shutdown()
+
+
+if __name__ == "__main__":
+    main()

@@ -42,6 +42,29 @@ def tp_world_size() -> int:
     return _STATE.world_size
 
 
+_init_generation = 0
+
+
+def _generation_store(init_method: str, rank: int, world_size: int, timeout_s: float):
+    """Rendezvous store for ``tcp://host:port`` with a per-initialisation key prefix.
+
+    A process that builds several engines one after another re-initialises the process group against
+    the same TCP store (under ``torch.distributed.run`` the launcher's store outlives every group),
+    and torch restarts its group counter on destroy, so the second group would find the first one's
+    keys — a stale NCCL unique id among them, which a rank that runs ahead of rank 0 then reads.
+    Prefixing every generation's keys keeps them apart."""
+    global _init_generation
+    if not init_method.startswith("tcp://"):
+        return None
+    host, _, port = init_method[len("tcp://"):].partition(":")
+    gen = _init_generation
+    _init_generation += 1
+    agent_store = os.environ.get("TORCHELASTIC_USE_AGENT_STORE", "") == "True"
+    base = dist.TCPStore(host, int(port), world_size, is_master=(rank == 0 and not agent_store),
+                         timeout=datetime.timedelta(seconds=timeout_s), wait_for_workers=False)
+    return dist.PrefixStore(f"tw_init_{gen}", base)
+
+
 def init_distributed(rank: int, world_size: int, local_rank: Optional[int] = None, device: str = "auto",
                      init_method: Optional[str] = None, timeout_s: float = 600.0) -> TPState:
     """Join (or create) the job's process group and bind this process to its GPU."""
@@ -61,10 +84,15 @@ def init_distributed(rank: int, world_size: int, local_rank: Optional[int] = Non
                 addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
                 port = os.environ.get("MASTER_PORT", "29611")
                 init_method = f"tcp://{addr}:{port}"
-            kwargs = dict(backend="nccl" if use_cuda else "gloo", init_method=init_method, rank=rank,
-                          world_size=world_size, timeout=datetime.timedelta(seconds=timeout_s))
+            kwargs = dict(backend="nccl" if use_cuda else "gloo", rank=rank, world_size=world_size,
+                          timeout=datetime.timedelta(seconds=timeout_s))
             if use_cuda:
                 kwargs["device_id"] = dev
+            store = _generation_store(init_method, rank, world_size, timeout_s)
+            if store is not None:
+                kwargs["store"] = store
+            else:
+                kwargs["init_method"] = init_method
             dist.init_process_group(**kwargs)
             owns = True
         group = dist.group.WORLD
