@@ -1,0 +1,120 @@
+"""OpenAI-compatible server and the asynchronous engine front on CPU (tiny random-weight model, byte
+tokenizer): completions, chat, streaming, token-id prompts, aborts, metrics."""
+import asyncio
+import json
+
+import pytest
+
+from tokenweave_b200 import SamplingParams
+from tokenweave_b200.config import EngineArgs
+from tokenweave_b200.engine.async_engine import AsyncLLMEngine
+
+fastapi = pytest.importorskip("fastapi")
+pytest.importorskip("httpx")
+
+
+@pytest.fixture(scope="module")
+def engine():
+    eng = AsyncLLMEngine.from_engine_args(EngineArgs(model="tiny-llama", dtype="float32", device="cpu", block_size=16,
+                                                     max_num_batched_tokens=128, seed=1))
+    yield eng
+    eng.shutdown()
+
+
+@pytest.fixture(scope="module")
+def client(engine):
+    from starlette.testclient import TestClient
+    from tokenweave_b200.entrypoints.api_server import build_app
+    with TestClient(build_app(engine, "tiny")) as c:
+        yield c
+
+
+def test_health_models_tokenize(client):
+    assert client.get("/health").json() == {"status": "ok"}
+    models = client.get("/v1/models").json()
+    assert models["data"][0]["id"] == "tiny"
+    tok = client.post("/tokenize", json={"prompt": "hi"}).json()
+    assert tok["tokens"] == [256, 104, 105] and tok["count"] == 3
+    assert client.post("/detokenize", json={"tokens": [104, 105]}).json()["prompt"] == "hi"
+
+
+def test_completion_matches_offline_engine(client, engine):
+    body = {"model": "tiny", "prompt": "hello world", "max_tokens": 6, "temperature": 0, "ignore_eos": True, "logprobs": 2}
+    r = client.post("/v1/completions", json=body)
+    assert r.status_code == 200, r.text
+    data = r.json()
+    assert data["object"] == "text_completion" and len(data["choices"]) == 1
+    ch = data["choices"][0]
+    assert ch["finish_reason"] == "length"
+    assert data["usage"] == {"prompt_tokens": 12, "completion_tokens": 6, "total_tokens": 18}
+    assert len(ch["logprobs"]["token_logprobs"]) == 6 and all(len(t) >= 1 for t in ch["logprobs"]["top_logprobs"])
+    # the same request again is deterministic, and a batch of prompts keeps its order
+    again = client.post("/v1/completions", json=body).json()["choices"][0]["text"]
+    assert again == ch["text"]
+    both = client.post("/v1/completions", json={**body, "prompt": ["hello world", "abc"], "logprobs": None}).json()
+    assert [c["index"] for c in both["choices"]] == [0, 1] and both["choices"][0]["text"] == ch["text"]
+    # token-id prompt
+    ids = client.post("/v1/completions", json={"prompt": [256, 104, 105], "max_tokens": 3, "temperature": 0}).json()
+    assert ids["usage"]["prompt_tokens"] == 3
+
+
+def test_streaming_completion_concatenates_to_the_full_text(client):
+    body = {"prompt": "stream me", "max_tokens": 8, "temperature": 0, "ignore_eos": True}
+    full = client.post("/v1/completions", json=body).json()["choices"][0]["text"]
+    text, done, usage = "", False, None
+    with client.stream("POST", "/v1/completions", json={**body, "stream": True}) as r:
+        assert r.status_code == 200
+        for line in r.iter_lines():
+            if not line.startswith("data: "):
+                continue
+            payload = line[len("data: "):]
+            if payload == "[DONE]":
+                done = True
+                break
+            chunk = json.loads(payload)
+            for c in chunk["choices"]:
+                text += c["text"]
+            usage = chunk.get("usage", usage)
+    assert done and text == full and usage["completion_tokens"] == 8
+
+
+def test_chat_completion_and_stream(client):
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+    r = client.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 5, "temperature": 0, "ignore_eos": True})
+    assert r.status_code == 200, r.text
+    data = r.json()
+    assert data["object"] == "chat.completion" and data["choices"][0]["message"]["role"] == "assistant"
+    assert data["usage"]["completion_tokens"] == 5
+    pieces = []
+    with client.stream("POST", "/v1/chat/completions", json={"messages": msgs, "max_tokens": 5, "temperature": 0,
+                                                             "ignore_eos": True, "stream": True}) as s:
+        for line in s.iter_lines():
+            if line.startswith("data: ") and line != "data: [DONE]":
+                pieces.append(json.loads(line[6:])["choices"][0]["delta"].get("content", ""))
+    assert "".join(pieces) == data["choices"][0]["message"]["content"]
+
+
+def test_bad_requests_are_rejected_and_the_server_keeps_serving(client):
+    assert client.post("/v1/completions", json={"prompt": "x", "temperature": -1}).status_code == 400
+    assert client.post("/v1/completions", json={"prompt": [999999], "max_tokens": 2}).status_code == 400
+    assert client.post("/v1/chat/completions", json={"messages": []}).status_code == 400
+    assert client.post("/v1/completions", json={"prompt": "still alive", "max_tokens": 2}).status_code == 200
+    m = client.get("/metrics")
+    assert m.status_code == 200 and "tokenweave:generation_tokens_total" in m.text
+
+
+def test_async_engine_abort_frees_the_request(engine):
+    async def run():
+        agen = engine.generate([1, 2, 3, 4], SamplingParams(temperature=0, max_tokens=10_000, ignore_eos=True), "abort-me")
+        n = 0
+        async for out in agen:
+            n += 1
+            if n == 3:
+                break
+        await agen.aclose()                 # the consumer walks away: the request must be aborted
+        for _ in range(200):
+            if not engine.engine.has_unfinished_requests():
+                return True
+            await asyncio.sleep(0.01)
+        return False
+    assert asyncio.run(run())

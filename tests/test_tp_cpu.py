@@ -147,3 +147,22 @@ def test_engines_built_one_after_another_under_torchrun(tmp_path):
     assert res.returncode == 0, res.stderr[-3000:]
     lines = [ln.split(" ", 2)[2] for ln in res.stdout.splitlines() if ln.startswith("RESULT")]
     assert len(lines) == 3 and len(set(lines)) == 1
+
+
+def _ep_rank(rank, world, path, prompts, expect_toks, expect_logits_path):
+    toks, logits = _generate(path, prompts, tensor_parallel_size=world, distributed_executor_backend="external_launcher",
+                             tokenweave_mode="overlap", tokenweave_threshold=128, enable_expert_parallel=True)
+    assert toks == expect_toks, f"rank {rank}: {toks} != {expect_toks}"
+    torch.testing.assert_close(logits, torch.load(expect_logits_path), atol=2e-4, rtol=2e-4)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_mixtral_matches_single_process(tmp_path, world):
+    """enable_expert_parallel: every rank holds whole experts (8 / world each) and the partial sums meet in
+    the same fused reduce-scatter as tensor-sharded experts; results equal the single-process model."""
+    cfg = _ckpt(tmp_path, "tiny-mixtral")
+    prompts = _prompts(cfg.vocab_size, [150, 40, 90, 9])
+    toks, logits = _generate(str(tmp_path), prompts)
+    lp = str(tmp_path / "expect_logits.pt")
+    torch.save(logits, lp)
+    run_ranks(_ep_rank, world, str(tmp_path), prompts, toks, lp)

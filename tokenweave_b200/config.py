@@ -43,6 +43,7 @@ class ModelConfig:
     tie_word_embeddings: bool = False
     dtype: torch.dtype = torch.bfloat16
     eos_token_id: Optional[int] = None
+    expert_parallel: bool = False       # MoE: whole experts per rank instead of tensor-sharded experts
     init_std: float = 0.02
     path: Optional[str] = None           # checkpoint directory (None: random init)
 
@@ -240,6 +241,7 @@ class EngineArgs:
     max_num_seqs: int = 256
     enable_chunked_prefill: bool = True
     enforce_eager: bool = True
+    enable_expert_parallel: bool = False
     disable_custom_all_reduce: bool = True
     load_format: str = "auto"
     quantization: Optional[str] = None
@@ -261,6 +263,10 @@ class EngineArgs:
     def create_engine_config(self) -> EngineConfig:
         model = resolve_model_config(self.model, None if self.dtype == "auto" else self.dtype,
                                      self.max_model_len, self.num_hidden_layers_override)
+        if self.enable_expert_parallel and model.is_moe:
+            if model.num_experts % self.tensor_parallel_size:
+                raise ValueError("enable_expert_parallel needs num_experts divisible by tensor_parallel_size")
+            model.expert_parallel = True
         max_len = model.max_model_len
         budget = self.max_num_batched_tokens or (8192 if self.enable_chunked_prefill else max(max_len, 8192))
         if self.quantization not in (None, "fp8"):

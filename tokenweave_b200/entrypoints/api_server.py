@@ -9,8 +9,6 @@ serving_completion.py / serving_chat.py: the request fields that map onto ``Samp
 honoured, the rest of the OpenAI schema (tools, response formats, multimodal parts) is not served.
 Tensor-parallel serving uses the multiprocess executor (one worker process per GPU).
 """
-from __future__ import annotations
-
 import argparse
 import json
 import time

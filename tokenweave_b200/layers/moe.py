@@ -25,17 +25,28 @@ TILE_ROWS = 128
 
 class FusedMoE(nn.Module):
     def __init__(self, num_experts: int, top_k: int, hidden: int, intermediate: int, *, dtype, device,
-                 renormalize: bool = True):
+                 renormalize: bool = True, expert_parallel: bool = False):
         super().__init__()
         tp = get_tp()
-        assert intermediate % tp.world_size == 0
-        self.E, self.top_k, self.hidden = num_experts, top_k, hidden
-        self.inter_per_rank = intermediate // tp.world_size
+        self.num_experts_global, self.top_k, self.hidden = num_experts, top_k, hidden
+        self.expert_parallel = expert_parallel and tp.world_size > 1
+        if self.expert_parallel:
+            # whole experts per rank (vllm/model_executor/layers/fused_moe/layer.py:332-374 ``determine_expert_map``):
+            # every rank routes all tokens, runs the pairs that hit its experts and contributes a partial
+            # sum, so the collective that follows is the same reduce-scatter as with tensor-sharded experts
+            assert num_experts % tp.world_size == 0
+            self.E = num_experts // tp.world_size
+            self.expert_base = tp.rank * self.E
+            self.inter_per_rank = intermediate
+        else:
+            assert intermediate % tp.world_size == 0
+            self.E, self.expert_base = num_experts, 0
+            self.inter_per_rank = intermediate // tp.world_size
         self.renormalize = renormalize
         I = self.inter_per_rank
         self.gate = nn.Parameter(torch.empty(num_experts, hidden, dtype=dtype, device=device), requires_grad=False)
-        self.w13 = nn.Parameter(torch.empty(num_experts, 2 * I, hidden, dtype=dtype, device=device), requires_grad=False)
-        self.w2 = nn.Parameter(torch.empty(num_experts, hidden, I, dtype=dtype, device=device), requires_grad=False)
+        self.w13 = nn.Parameter(torch.empty(self.E, 2 * I, hidden, dtype=dtype, device=device), requires_grad=False)
+        self.w2 = nn.Parameter(torch.empty(self.E, hidden, I, dtype=dtype, device=device), requires_grad=False)
         self._ws_tokens = 0
         self._ws = None
 
@@ -43,6 +54,15 @@ class FusedMoE(nn.Module):
     def load_expert_weight(self, expert: int, which: str, loaded: torch.Tensor) -> None:
         tp = get_tp()
         I = self.inter_per_rank
+        if self.expert_parallel:
+            expert -= self.expert_base
+            if not 0 <= expert < self.E:
+                return                                  # another rank's expert
+            dst = {"w1": self.w13.data[expert, :I], "w3": self.w13.data[expert, I:], "w2": self.w2.data[expert]}
+            if which not in dst:
+                raise KeyError(which)
+            dst[which].copy_(loaded)
+            return
         if which == "w1":
             self.w13.data[expert, :I].copy_(loaded.narrow(0, tp.rank * I, I))
         elif which == "w3":
@@ -76,6 +96,10 @@ class FusedMoE(nn.Module):
         if T == 0:
             return out
         topk_w, topk_ids, _ = ops.moe_router(x, self.gate, self.top_k, self.renormalize)
+        if self.expert_parallel:
+            # local expert index, or -1 for pairs that belong to another rank (align / scatter / combine skip them)
+            local = topk_ids - self.expert_base
+            topk_ids = torch.where((local >= 0) & (local < self.E), local, torch.full_like(local, -1))
         if not x.is_cuda:
             out.copy_(reference.moe_experts(x, self.w13, self.w2, topk_w, topk_ids))
             return out

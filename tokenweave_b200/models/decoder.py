@@ -93,7 +93,8 @@ class DecoderLayer(nn.Module):
         self.input_norm_w = nn.Parameter(torch.ones(H, dtype=dt, device=device), requires_grad=False)
         self.post_norm_w = nn.Parameter(torch.ones(H, dtype=dt, device=device), requires_grad=False)
         if cfg.is_moe:
-            self.moe = FusedMoE(cfg.num_experts, cfg.num_experts_per_tok, H, cfg.intermediate_size, dtype=dt, device=device)
+            self.moe = FusedMoE(cfg.num_experts, cfg.num_experts_per_tok, H, cfg.intermediate_size, dtype=dt, device=device,
+                                expert_parallel=cfg.expert_parallel)
             self.gate_up_proj = self.down_proj = None
         else:
             self.moe = None
