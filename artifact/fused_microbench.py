@@ -29,6 +29,29 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 
+def burst_us(fn, n: int, reps: int = 9) -> float:
+    """Per-launch device time of ``n`` back-to-back launches (median over ``reps``, max over ranks)."""
+    import statistics
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e) * 1e3 / n)
+    med = statistics.median(times)
+    if dist.is_initialized():
+        t = torch.tensor([med], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        med = float(t.item())
+    return med
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, nargs="+", default=[64, 256, 1024, 4096, 8192, 16384])
@@ -38,6 +61,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--transport", default="auto", choices=["auto", "multimem", "p2p"])
     ap.add_argument("--sync-ranks", action="store_true", help="host barrier before every timed iteration")
+    ap.add_argument("--burst", type=int, default=20,
+                    help="also time this many back-to-back launches per event pair (steady-state latency per launch, "
+                         "warm L2, no host in between: how the kernels run inside a model step); 0 disables")
     ap.add_argument("--out", default=os.path.join("gpurun_out", "fused_microbench"))
     args = ap.parse_args()
     if args.transport == "p2p":
@@ -114,6 +140,11 @@ def main() -> None:
             fused[c] = time_us(lambda: comm.fused_allreduce_add_rmsnorm_(view, res, w, 1e-5, c), **kw)
             row[f"fused_{c}"] = fused[c]
         row["fused_best"] = min(fused.values())
+        if args.burst > 0:
+            cb = min(fused, key=fused.get)
+            row["fused_burst"] = burst_us(lambda: comm.fused_allreduce_add_rmsnorm_(view, res, w, 1e-5, cb), args.burst)
+            if W > 1:
+                row["nccl_ar_norm_burst"] = burst_us(nccl_norm, args.burst)
         row["best_ctas"] = min(fused, key=fused.get)
         roof = T * H * 2 / (NVLINK_GBS_MEASURED * 1e9) * 1e6 if W > 1 else 0.0
         row["roofline_us"] = roof

@@ -21,7 +21,7 @@ import torch  # noqa: E402
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_swiglu", "attn_prefill", "attn_decode", "add_rmsnorm", "rope_kv",
+    ap.add_argument("case", choices=["gemm", "gemm_swiglu", "gemm_fp8", "rmsnorm_quant_fp8", "attn_prefill", "attn_decode", "add_rmsnorm", "rope_kv",
                                      "moe_router", "fused_local"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=8192)
@@ -46,6 +46,20 @@ def main() -> None:
         out = torch.empty(M, N, device=dev, dtype=BF)
         fn = lambda: ops.gemm(a, w, out=out, swiglu=sw)
         flops = 2 * M * (2 * N if sw else N) * K
+    elif args.case == "gemm_fp8":
+        M, N, K = args.m, args.n, args.k
+        aq, a_s = ops.quant_fp8(torch.randn(M, K, device=dev).to(BF))
+        wq, w_s = ops.quant_fp8((torch.randn(N, K, device=dev) / math.sqrt(K)).to(BF))
+        out = torch.empty(M, N, device=dev, dtype=BF)
+        fn = lambda: ops.gemm_fp8(aq, wq, a_s, w_s, out=out)
+        flops = 2 * M * N * K
+    elif args.case == "rmsnorm_quant_fp8":
+        T, H = args.tokens, args.hidden
+        x, r = torch.randn(T, H, device=dev).to(BF), torch.randn(T, H, device=dev).to(BF)
+        w = torch.ones(H, device=dev, dtype=BF)
+        q = torch.empty(T, H, device=dev, dtype=torch.float8_e4m3fn)
+        fn = lambda: ops.rmsnorm_quant_fp8(x, w, 1e-5, residual=r, out=q)
+        bytes_moved = T * H * (2 + 2 + 2 + 1)
     elif args.case == "attn_prefill":
         T, hq, hkv, D, page = args.tokens, args.heads, args.kv_heads, 128, 128
         nb = T // page + 1

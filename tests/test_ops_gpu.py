@@ -282,15 +282,14 @@ def test_merge_attn_states(T, H, D):
 def test_quant_fp8(T, H):
     x = rnd(T, H, scale=3.0)
     q, s = ops.quant_fp8(x)
-    q_ref, s_ref = ref.quant_fp8(x)
-    assert torch.allclose(s, s_ref, rtol=1e-6, atol=0)
-    # identical up to one e4m3 step where x / scale lands on a rounding boundary
-    dq, dq_ref = q.float() * s[:, None], q_ref.float() * s_ref[:, None]
-    assert (dq - dq_ref).abs().max() <= 0.07 * x.float().abs().max()
-    assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 1e-3
+    # The oracle runs on the CPU: torch's CUDA division by the Python scalar 448 multiplies by a reciprocal,
+    # which moves the scale by an ulp and with it the 0.6 % of bf16 inputs that sit on e4m3 rounding ties.
+    q_ref, s_ref = ref.quant_fp8(x.cpu())
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
     static = torch.tensor([0.05], device=DEV)
     q2, _ = ops.quant_fp8(x, scale=static)
-    assert (q2.view(torch.uint8) != ref.quant_fp8(x, static)[0].view(torch.uint8)).float().mean() < 1e-3
+    assert torch.equal(q2.cpu().view(torch.uint8), ref.quant_fp8(x.cpu(), static.cpu())[0].view(torch.uint8))
     # fused with RMSNorm, with and without the residual add
     w = rnd(H, scale=0.5)
     qn, sn = ops.rmsnorm_quant_fp8(x, w, 1e-5)

@@ -119,18 +119,20 @@ quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict_
       scale = fmaxf(amax / FP8_E4M3_MAX, 1e-10f);
       if (threadIdx.x == 0) scales[t] = scale;
     }
-    // true division (not a reciprocal multiply): bf16 inputs land on e4m3 rounding ties often enough
-    // that a one-ulp difference in the quotient would change the result against x / scale
+    // one IEEE reciprocal per row, then a multiply per element (the reference's is_scale_inverted form,
+    // csrc/quantization/fp8/common.cuh); the PyTorch oracle computes x * (1 / scale) the same way, which
+    // matters because 0.6 % of bf16 inputs sit exactly on e4m3 rounding ties
+    const float rscale = __frcp_rn(scale);
     uint2* orow = reinterpret_cast<uint2*>(out + t * ldo);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
         uint2 o;
-        o.x = to_e4m3x2(__fdiv_rn(y[i][0], scale), __fdiv_rn(y[i][1], scale)) |
-              (static_cast<uint32_t>(to_e4m3x2(__fdiv_rn(y[i][2], scale), __fdiv_rn(y[i][3], scale))) << 16);
-        o.y = to_e4m3x2(__fdiv_rn(y[i][4], scale), __fdiv_rn(y[i][5], scale)) |
-              (static_cast<uint32_t>(to_e4m3x2(__fdiv_rn(y[i][6], scale), __fdiv_rn(y[i][7], scale))) << 16);
+        o.x = to_e4m3x2(y[i][0] * rscale, y[i][1] * rscale) |
+              (static_cast<uint32_t>(to_e4m3x2(y[i][2] * rscale, y[i][3] * rscale)) << 16);
+        o.y = to_e4m3x2(y[i][4] * rscale, y[i][5] * rscale) |
+              (static_cast<uint32_t>(to_e4m3x2(y[i][6] * rscale, y[i][7] * rscale)) << 16);
         orow[v] = o;
       }
     }

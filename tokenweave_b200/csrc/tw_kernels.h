@@ -37,6 +37,11 @@ int tw_embedding(const int* ids, const void* table, void* out, long long ldo, in
                  int vocab_end, cudaStream_t stream);
 int tw_argmax(const float* logits, long long ld, int* out, int rows, int V, cudaStream_t stream);
 
+// ---- sampling (sampling.cu) ----
+// params: `rows` records of 32 bytes {float temperature (<= 0: greedy), int top_k (<= 0: off), float top_p,
+// float min_p, uint64 seed, uint64 pad}; out: sampled token id per row.
+int tw_sample(const float* logits, long long ld, int rows, int V, const void* params, int* out, cudaStream_t stream);
+
 // ---- fp8 (e4m3) path (gemm_tcgen05.cu, quant_fp8.cu) ----
 int tw_gemm_fp8(const void* A, long long lda, const void* B, long long ldb, long long rows_b, void* C,
                 long long ldc, const void* bias, const float* row_scale, const float* col_scale, int M, int N,

@@ -61,7 +61,35 @@ def _filter_top_k_top_p(logits: torch.Tensor, top_k: torch.Tensor, top_p: torch.
     return logits
 
 
+_MASK64 = (1 << 64) - 1
+
+
 class Sampler:
+    """On a GPU a batch that is not all-greedy is sampled by one launch of the fused kernel
+    (``ops.sample``: temperature, top-k / top-p / min-p and the draw, no sort); on the CPU, and as the
+    oracle of that kernel, the sort-based PyTorch path below is used."""
+
+    def __init__(self, seed: int = 0, use_fused_kernel: bool = True):
+        import random
+        self._rng = random.Random(seed)      # row seeds of unseeded requests; identical on every TP rank
+        self.use_fused_kernel = use_fused_kernel
+
+    def _row_seeds(self, params: Sequence[SamplingParams], output_tokens) -> list[int]:
+        seeds = []
+        for i, sp in enumerate(params):
+            if sp.seed is None:
+                seeds.append(self._rng.getrandbits(64))
+            else:       # a seeded request repeats: the draw depends on (seed, position) only
+                n = len(output_tokens[i]) if output_tokens is not None else 0
+                seeds.append(((sp.seed + 1) * 0x9E3779B97F4A7C15 + (n + 1) * 0xD1B54A32D192ED03) & _MASK64)
+        return seeds
+
+    def _sample_fused(self, logits: torch.Tensor, params: Sequence[SamplingParams], output_tokens) -> torch.Tensor:
+        packed = ops.pack_sample_params(
+            [0.0 if sp.greedy else sp.temperature for sp in params], [sp.top_k for sp in params],
+            [sp.top_p for sp in params], [sp.min_p for sp in params], self._row_seeds(params, output_tokens))
+        return ops.sample(logits, packed.pin_memory().to(logits.device, non_blocking=True))
+
     def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                  generators: Sequence[Optional[torch.Generator]], prompt_tokens=None, output_tokens=None) -> SamplerOutput:
         B, V = logits.shape
@@ -71,6 +99,8 @@ class Sampler:
         raw_logprobs = torch.log_softmax(logits, dim=-1) if want_logprobs else None
         if all(sp.greedy for sp in params):
             ids = ops.argmax(logits)
+        elif logits.is_cuda and self.use_fused_kernel:
+            ids = self._sample_fused(logits, params, output_tokens)
         else:
             dev = logits.device
             temp = torch.tensor([1.0 if sp.greedy else sp.temperature for sp in params], dtype=torch.float32, device=dev)

@@ -349,6 +349,29 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def pack_sample_params(temperature, top_k, top_p, min_p, seeds) -> torch.Tensor:
+    """Host-side record array for :func:`sample`: one 32-byte record per row
+    ``{f32 temperature, i32 top_k, f32 top_p, f32 min_p, u64 seed, u64 pad}`` as an int32 ``[B, 8]`` tensor."""
+    import numpy as np
+    B = len(temperature)
+    rec = np.zeros(B, dtype=np.dtype([("t", "<f4"), ("k", "<i4"), ("p", "<f4"), ("m", "<f4"), ("s", "<u8"), ("z", "<u8")]))
+    rec["t"], rec["k"], rec["p"], rec["m"] = temperature, top_k, top_p, min_p
+    rec["s"] = np.asarray([int(s) & 0xFFFFFFFFFFFFFFFF for s in seeds], dtype=np.uint64)
+    return torch.from_numpy(rec.view(np.int32).reshape(B, 8))
+
+
+def sample(logits: torch.Tensor, packed_params: torch.Tensor) -> torch.Tensor:
+    """One token per row of fp32 ``logits`` under per-row temperature / top-k / top-p / min-p and seed
+    (``packed_params`` from :func:`pack_sample_params`, on the logits' device). CUDA only."""
+    assert logits.is_cuda and logits.dtype == torch.float32 and packed_params.is_cuda
+    rows, V = logits.shape
+    assert packed_params.shape == (rows, 8) and packed_params.dtype == torch.int32 and packed_params.is_contiguous()
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _native.call("tw_sample", logits.data_ptr(), _row_stride(logits), rows, V, packed_params.data_ptr(), out.data_ptr(),
+                 _stream())
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                  cu_q: torch.Tensor, kv_lens: torch.Tensor, block_table: torch.Tensor, tile_seq: torch.Tensor,

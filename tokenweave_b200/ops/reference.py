@@ -62,11 +62,13 @@ FP8_MAX = 448.0
 def quant_fp8(x: torch.Tensor, scale: Optional[torch.Tensor] = None):
     """(e4m3 tensor, scales): per-token ``max|row| / 448`` when ``scale`` is None, else the given scalar."""
     xf = x.float()
+    # x * (1 / scale): one reciprocal per row and a multiply per element, the arithmetic of the kernels
+    # (bf16 inputs sit on e4m3 rounding ties often enough for the last ulp of the quotient to matter)
     if scale is None:
-        s = (xf.abs().amax(dim=-1) / FP8_MAX).clamp_min(1e-10)
-        q = (xf / s.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+        s = (xf.abs().amax(dim=-1) / torch.tensor(FP8_MAX, dtype=torch.float32, device=x.device)).clamp_min(1e-10)
+        q = (xf * s.reciprocal().unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
         return q, s
-    q = (xf / scale.float().reshape(())).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    q = (xf * scale.float().reshape(()).reciprocal()).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q, scale
 
 

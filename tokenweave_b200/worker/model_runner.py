@@ -75,7 +75,7 @@ class ModelRunner:
         self.tp = get_tp()
         self.model: Optional[DecoderModel] = None
         self.requests: dict[str, _CachedRequest] = {}
-        self.sampler = Sampler()
+        self.sampler = Sampler(seed=config.seed)
         self.block_size = config.cache.block_size
         self.max_tokens = config.scheduler.max_num_batched_tokens
         tw = config.tokenweave
