@@ -215,6 +215,7 @@ class EngineConfig:
     tokenizer: Optional[str] = None
     skip_tokenizer_init: bool = False
     disable_log_stats: bool = True
+    enable_sleep_mode: bool = False       # weights and KV cache on the VMM allocator: LLM.sleep() frees their memory
 
     def resolved_device(self) -> str:
         if self.device != "auto":
@@ -248,6 +249,7 @@ class EngineArgs:
     device: str = "auto"
     num_hidden_layers_override: Optional[int] = None
     disable_log_stats: bool = True
+    enable_sleep_mode: bool = False       # weights and KV cache on the VMM allocator: LLM.sleep() frees their memory
     # TokenWeave
     tokenweave_mode: str = "overlap"
     tokenweave_config: Optional[str] = None
@@ -295,7 +297,7 @@ class EngineArgs:
                                         mlp_ctas=self.tokenweave_mlp_ctas),
             load_format=load_format, quantization=self.quantization, seed=self.seed, device=self.device, enforce_eager=self.enforce_eager,
             tokenizer=self.tokenizer, skip_tokenizer_init=self.skip_tokenizer_init,
-            disable_log_stats=self.disable_log_stats)
+            disable_log_stats=self.disable_log_stats, enable_sleep_mode=self.enable_sleep_mode)
 
     @staticmethod
     def add_cli_args(parser: argparse.ArgumentParser) -> argparse.ArgumentParser:

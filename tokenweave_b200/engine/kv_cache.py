@@ -67,6 +67,15 @@ class BlockPool:
     def lookup(self, h: bytes) -> Optional[int]:
         return self.block_of.get(h) if self.enable_caching else None
 
+    def reset_prefix_cache(self) -> bool:
+        """Forget every cached prefix (the KV contents are gone, e.g. after sleep). Only legal while no
+        request holds blocks; returns False otherwise (vllm/v1/core/block_pool.py ``reset_prefix_cache``)."""
+        if any(r > 0 for r in self.ref[1:]):
+            return False
+        self.hash_of.clear()
+        self.block_of.clear()
+        return True
+
 
 def block_hashes(token_ids: list[int], block_size: int) -> list[bytes]:
     """Chained hash of every full block of a token sequence."""

@@ -198,7 +198,11 @@ class LLM:
         the reference (vllm/device_allocator/cumem.py); here tensors are moved, not unmapped."""
         if self.llm_engine.has_unfinished_requests():
             raise RuntimeError("cannot sleep with requests in flight")
+        self.reset_prefix_cache()           # the KV contents do not survive
         self.collective_rpc("sleep", level)
+
+    def reset_prefix_cache(self) -> bool:
+        return self.llm_engine.core.scheduler.kv.pool.reset_prefix_cache()
 
     def wake_up(self) -> None:
         self.collective_rpc("wake_up")

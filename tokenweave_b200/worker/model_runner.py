@@ -107,10 +107,14 @@ class ModelRunner:
         self.graph_replays = 0
 
     # ---- set-up -----------------------------------------------------------------------------
-    def load_model(self, embedding_parallel: bool = False) -> None:
+    def load_model(self, embedding_parallel: bool = False, weights_pool=None) -> None:
+        """``weights_pool``: optional allocation context for the parameters only (sleep mode); activation
+        buffers, the rotary table and the symmetric staging buffer stay in ordinary memory."""
+        import contextlib
         from ..models.registry import build_model
         t0 = time.monotonic()
-        self.model = build_model(self.config, self.device, embedding_parallel)
+        with (weights_pool if weights_pool is not None else contextlib.nullcontext()):
+            self.model = build_model(self.config, self.device, embedding_parallel)
         self.model.setup_runtime(self.max_tokens, self.config.tokenweave)
         logger.info("model %s ready on %s in %.1fs (%.2f GB of weights on this rank)", self.config.model.name,
                     self.device, time.monotonic() - t0,

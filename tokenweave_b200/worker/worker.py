@@ -45,8 +45,19 @@ class Worker:
         torch.manual_seed(self.config.seed)
         self.runner = ModelRunner(self.config, self.device)
 
+    def _sleep_pool(self, tag: int):
+        """Allocation context of sleep mode: the VMM pool of ``tag`` on a GPU with ``enable_sleep_mode``,
+        else nothing."""
+        import contextlib
+        if self.config.enable_sleep_mode and self.device.type == "cuda":
+            from ..utils.sleep_allocator import SleepAllocator
+            return SleepAllocator.get().use_pool(tag)
+        return contextlib.nullcontext()
+
     def load_model(self) -> None:
-        self.runner.load_model(embedding_parallel=bool(int(os.getenv("TW_EMBEDDING_PARALLEL", "0"))))
+        from ..utils.sleep_allocator import TAG_WEIGHTS
+        self.runner.load_model(embedding_parallel=bool(int(os.getenv("TW_EMBEDDING_PARALLEL", "0"))),
+                               weights_pool=self._sleep_pool(TAG_WEIGHTS))
 
     def determine_num_blocks(self) -> int:
         """KV blocks that fit in what is left of ``gpu_memory_utilization`` after weights and workspaces."""
@@ -70,7 +81,9 @@ class Worker:
         return min(n, max_useful)
 
     def init_kv_cache(self, num_blocks: int) -> None:
-        self.runner.init_kv_cache(num_blocks)
+        from ..utils.sleep_allocator import TAG_KV_CACHE
+        with self._sleep_pool(TAG_KV_CACHE):
+            self.runner.init_kv_cache(num_blocks)
         logger.info("KV cache: %d blocks of %d tokens", num_blocks, self.config.cache.block_size)
 
     def execute_model(self, step: StepData) -> StepResult:
@@ -100,6 +113,17 @@ class Worker:
 
     # ---- sleep / wake (weights to host memory, KV cache dropped) ----
     def sleep(self, level: int = 1) -> None:
+        if self.config.enable_sleep_mode and self.device.type == "cuda":
+            # VMM path: physical memory of weights and KV cache is released, addresses stay valid.
+            # Level 1 keeps the weights in pinned host memory; level 2 discards them too.
+            from ..utils.sleep_allocator import TAG_WEIGHTS, SleepAllocator
+            alloc = SleepAllocator.get()
+            before = torch.cuda.mem_get_info(self.device)[0]
+            alloc.sleep(offload_tags=(TAG_WEIGHTS,) if level == 1 else ())
+            self._vmm_sleep_level = level
+            logger.info("sleep level %d freed %.2f GB of device memory (%.2f GB held on the host)", level,
+                        (torch.cuda.mem_get_info(self.device)[0] - before) / 1e9, alloc.host_bytes() / 1e9)
+            return
         model = self.runner.model
         self._sleeping = {}
         self._param_shapes = {n: tuple(p.shape) for n, p in model.named_parameters()}
@@ -120,6 +144,22 @@ class Worker:
 
     def wake_up(self) -> None:
         model = self.runner.model
+        level = getattr(self, "_vmm_sleep_level", None)
+        if level is not None:
+            from ..utils.sleep_allocator import SleepAllocator
+            SleepAllocator.get().wake_up()
+            if level >= 2:        # the weights were discarded: reload (or re-draw) them into the same tensors
+                from ..models.loader import load_model_weights
+                if self.config.quantization:
+                    raise RuntimeError("sleep level 2 with online quantisation needs a fresh engine")
+                load_model_weights(model, self.config)
+            for layer in model.layers:      # the KV cache came back uninitialised
+                if layer.attn.k_cache is not None:
+                    layer.attn.k_cache.zero_()
+                    layer.attn.v_cache.zero_()
+            torch.cuda.synchronize()
+            self._vmm_sleep_level = None
+            return
         saved = getattr(self, "_sleeping", None)
         if saved is None:
             return
