@@ -89,6 +89,8 @@ def main() -> None:
                 best_base = (ms, c)
         table[str(n)] = {"attention_ctas": best[2], "mlp_ctas": best[3], "split_offset": best[1],
                          "baseline_ctas": best_base[1]}
+        if best_base[0] < best[0]:
+            table[str(n)]["overlap"] = 0        # the unsplit fused schedule wins at this size
         if rank == 0:
             print(f"tokens {n}: overlap best {best[0]:.2f} ms (offset {best[1]}, attn {best[2]}, mlp {best[3]}); "
                   f"fuse-only best {best_base[0]:.2f} ms ({best_base[1]} CTAs)", flush=True)

@@ -39,8 +39,11 @@ def test_nearest_key_and_split_formula(tmp_path):
 
 def test_split_divisible_by_world_and_env_override(monkeypatch):
     pl = TokenWeavePlanner("llama", 8, "overlap")
+    # the tuned B200 file marks the 1024-token entry "overlap": 0 (the unsplit fused schedule measured faster)
+    assert pl.plan(1024).overlap is False and pl.plan(1535).overlap is False and pl.plan(1537).overlap is True
+    forced = TokenWeavePlanner("llama", 8, "overlap", force_overlap=True)
     for t in (1024, 1025, 3000, 8192, 12345):
-        p = pl.plan(t)
+        p = forced.plan(t)
         assert p.overlap and p.split % 8 == 0 and (p.padded_tokens - p.split) % 8 == 0
         assert p.tokens_0 + p.tokens_1 == t
     monkeypatch.setenv("TW_SPLIT_OFFSET", "128")

@@ -1,8 +1,9 @@
 """Per-model TokenWeave configuration files and the split planner.
 
 File schema (same as vllm/tokenweave_configs/*.json of the reference):
-``{"<tokens>": {"attention_ctas": n, "mlp_ctas": n, "split_offset": n [, "baseline_ctas": n]}}``,
-file names ``{llama,qwen2,mixtral}_config_{tp}.json``. The entry with the key nearest to the step's
+``{"<tokens>": {"attention_ctas": n, "mlp_ctas": n, "split_offset": n [, "baseline_ctas": n] [, "overlap": 0|1]}}``,
+(``"overlap": 0``, written by the config generator where the unsplit fused schedule measured faster, sends
+token counts nearest to that key down the fuse-only path even above the model's threshold), file names ``{llama,qwen2,mixtral}_config_{tp}.json``. The entry with the key nearest to the step's
 token count is used (vllm/model_executor/models/llama.py:516-520); the cut is
 ``round_up(T, 256) // 2 + split_offset`` (llama.py:521). The planner is the single source of truth for
 the cut: the model runner builds the per-split attention metadata from the same ``SplitPlan`` the
@@ -93,10 +94,12 @@ class TokenWeavePlanner:
         if can_overlap and num_tokens >= self.threshold:
             e = self.entry(num_tokens)
             padded = (num_tokens + PAD_GRANULARITY - 1) // PAD_GRANULARITY * PAD_GRANULARITY
+            if e.get("overlap", 1) == 0 and not self.force_overlap:
+                padded = 0          # tuned: the unsplit schedule is faster at this size
             split = padded // 2 + e["split_offset"]
             split = max(w, min(split, padded - w))
             split -= split % w
-            if 0 < split < num_tokens and (padded - split) % w == 0:
+            if padded and 0 < split < num_tokens and (padded - split) % w == 0:
                 return SplitPlan(num_tokens, padded, True, split, e["attention_ctas"], e["mlp_ctas"],
                                  16 if num_tokens < 16384 else 32)
         padded = (num_tokens + w - 1) // w * w
