@@ -31,8 +31,11 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--attn-variant", type=int, default=0, help="attn_prefill: 0 auto, 1 one head per CTA, 2 head pairs")
     args = ap.parse_args()
     from tokenweave_b200 import ops
+    from tokenweave_b200.ops import _native
+    _native.load().tw_attn_set_variant(args.attn_variant)
     torch.cuda.set_device(0)
     dev, BF = "cuda", torch.bfloat16
     peaks = measured_peaks()

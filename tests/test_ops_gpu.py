@@ -143,8 +143,13 @@ def _make_paged(seqs, hkv, D, page, extra_blocks=3):
     (8, 2, 128, 16, [(200, 1000), (1, 77), (128, 640), (5, 5)]),
     (4, 4, 64, 32, [(333, 333), (64, 500)]),
     (16, 2, 128, 64, [(1024, 1024), (700, 2048)]),
+    (4, 2, 64, 32, [(333, 333), (64, 500), (1, 130)]),
+    (6, 1, 128, 128, [(513, 1300)]),
 ])
-def test_attn_prefill(hq, hkv, D, page, seqs):
+@pytest.mark.parametrize("variant", [1, 2])      # one head per CTA / two heads of a KV group per CTA
+def test_attn_prefill(hq, hkv, D, page, seqs, variant):
+    from tokenweave_b200.ops import _native
+    _native.load().tw_attn_set_variant(variant)
     kc, vc, bt, cu, kv_lens = _make_paged(seqs, hkv, D, page)
     T = cu[-1]
     q = rnd(T, hq * D)
@@ -160,6 +165,7 @@ def test_attn_prefill(hq, hkv, D, page, seqs):
     ops.attn_prefill(q, kc, vc, out, i32(cu), i32(kv_lens), bt, i32(tile_seq), i32(tile_q0), len(tile_seq), hq,
                      hkv, D, scale)
     torch.cuda.synchronize()
+    _native.load().tw_attn_set_variant(0)
     close(out, expect, atol=2e-2, rtol=3e-2)
 
 

@@ -59,8 +59,11 @@ struct AttnSmem {
   static constexpr int TOTAL = OFF_XCHG + 2 * 2 * 128 * 4 + 1024;
 };
 
-__device__ __forceinline__ void softmax_group_sync() {
-  asm volatile("bar.sync 1, %0;" ::"n"(ATT_SOFTMAX_THREADS) : "memory");
+// The two threads of a query row sit in warps w and w + 4 (same TMEM lane quarter). Each such warp pair
+// meets on its own named barrier (ids 1..4, 64 threads), so the four pairs drift apart in time and their
+// load / max / exp2 / store phases overlap on the SM instead of marching in lockstep.
+__device__ __forceinline__ void softmax_pair_sync(int quarter) {
+  asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory");
 }
 
 template <int D>
@@ -229,7 +232,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     float l_sum = 0.f;        // this thread's half of the row sum
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      // The trip count is the same for all 256 threads whatever happens (the named barrier below is
+      // The trip count is the same for all 256 threads whatever happens (the named barriers below are
       // unbounded): after a failed wait the remaining waits are skipped, not the iterations.
       const int sb = j & 1;
       if (ok) ok = mbar_wait(&s_full[sb], (j >> 1) & 1);
@@ -255,7 +258,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // the two halves of a row agree on the tile's maximum
       float* xm = xchg + (j & 1) * 256;
       xm[kh * 128 + r] = mx;
-      softmax_group_sync();
+      softmax_pair_sync(qr);
       mx = fmaxf(mx, xm[(kh ^ 1) * 128 + r]) * p.scale_log2;
       float alpha = 1.f;
       bool rescale = false;
@@ -312,7 +315,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // row sum = the two halves' partial sums
     float* xs = xchg + (n_tiles & 1) * 256;
     xs[kh * 128 + r] = l_sum;
-    softmax_group_sync();
+    softmax_pair_sync(qr);
     const float l_row = l_sum + xs[(kh ^ 1) * 128 + r];
     if (ok) {
       tc_fence_after_sync();
@@ -351,6 +354,375 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Head-pair variant: one CTA serves the SAME 128-query tile of TWO query heads that share a KV head
+// (grouped-query attention), so every K and V tile is fetched once for both, and the two heads' softmax
+// groups run out of phase: while group A exponentiates tile j, the tensor core works on Q_B K_j^T and
+// P_B V_{j-1}. That keeps the MUFU and tensor pipes busy across the phases that a single softmax group
+// spends waiting (TMEM load latency, the barrier hand-offs), which is what bounds the single-head kernel.
+//   warp 0      TMA: Q_A and Q_B once; K_0 V_0 K_1 V_1 ... through a ring of three tile slots
+//   warp 1      MMA: S_A, S_B (one TMEM buffer each), O_A, O_B (TMEM, 4 x 128 columns in all)
+//   warps 2..5  softmax of head A, one thread per query row (the row's 128 scores are read from TMEM
+//               twice, 64 at a time, so 64 registers hold them); warps 6..9 the same for head B
+template <int D>
+struct AttnPairSmem {
+  static constexpr int HALVES = D / 64;
+  static constexpr int Q_BYTES = HALVES * ATT_HALF_BYTES;     // one head's Q tile
+  static constexpr int KV_BYTES = HALVES * ATT_HALF_BYTES;    // one K or V tile
+  static constexpr int P_BYTES = 2 * ATT_HALF_BYTES;          // one head's P tile: 128 rows x 128 keys
+  static constexpr int RING = 3;
+  static constexpr int OFF_Q = 0;                              // [2 heads]
+  static constexpr int OFF_P = OFF_Q + 2 * Q_BYTES;            // [2 heads]
+  static constexpr int OFF_RING = OFF_P + 2 * P_BYTES;         // [RING]
+  static constexpr int OFF_BAR = OFF_RING + RING * KV_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  using S = AttnPairSmem<D>;
+  constexpr int HALVES = S::HALVES;
+  constexpr int RING = S::RING;
+  constexpr uint32_t IDESC_QK = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);
+  constexpr uint32_t IDESC_PV = make_idesc_bf16(ATT_BM, D, 0, 1);
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t COL_S = 0;     // S_A at 0, S_B at 128
+  constexpr uint32_t COL_O = 256;   // O_A at 256, O_B at 384
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  uint64_t* q_full = bars + 0;
+  uint64_t* ring_full = bars + 1;    // [3]
+  uint64_t* ring_empty = bars + 4;   // [3]
+  uint64_t* s_full = bars + 7;       // [2 heads]
+  uint64_t* p_ready = bars + 9;      // [2 heads]
+  uint64_t* o_done = bars + 11;      // [2 heads]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head0 = blockIdx.x * 2;          // heads head0 and head0 + 1 share a KV head
+  const int tile = blockIdx.y;
+  const int kvh = head0 / (p.hq / p.hkv);
+
+  const int seq = p.tile_seq[tile];
+  const int q0 = p.tile_q0[tile];
+  const int q_begin = p.cu_q[seq];
+  const int q_len = p.cu_q[seq + 1] - q_begin;
+  const int kv_len = p.kv_lens[seq];
+  const int rows_valid = min(ATT_BM, q_len - q0);
+  const int pos0 = kv_len - q_len + q0;
+  const int kv_end = min(kv_len, pos0 + rows_valid);
+  const int n_tiles = (kv_end + ATT_BN - 1) / ATT_BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < RING; ++i) {
+      mbar_init(&ring_full[i], 1);
+      mbar_init(&ring_empty[i], 1);
+    }
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&s_full[g], 1);
+      mbar_init(&p_ready[g], 128);
+      mbar_init(&o_done[g], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0 && n_tiles > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, 2 * S::Q_BYTES);
+#pragma unroll
+      for (int g = 0; g < 2; ++g)
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h)
+          tma_load_2d(smem + S::OFF_Q + g * S::Q_BYTES + h * ATT_HALF_BYTES, &tmQ, q_full,
+                      (head0 + g) * D + h * 64, q_begin + q0);
+      const int pages_per_tile = ATT_BN / p.page;
+      const int last_page = (kv_len - 1) / p.page;
+      const int* table = p.block_table + static_cast<long long>(seq) * p.max_blocks;
+      // stream of tiles K_0 V_0 K_1 V_1 ...: element i lives in ring slot i % 3
+      for (int i = 0; i < 2 * n_tiles; ++i) {
+        const int j = i >> 1;
+        const int slot = i % RING;
+        const uint32_t ph = (i / RING) & 1;
+        if (!mbar_wait(&ring_empty[slot], ph ^ 1)) { report_error(p.status, TW_ERR_MBAR_TIMEOUT); *abort_flag = 1; break; }
+        mbar_expect_tx(&ring_full[slot], S::KV_BYTES);
+        const CUtensorMap* tm = (i & 1) ? &tmV : &tmK;
+        for (int pg = 0; pg < pages_per_tile; ++pg) {
+          const int block = table[min(j * pages_per_tile + pg, last_page)];
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h)
+            tma_load_4d(smem + S::OFF_RING + slot * S::KV_BYTES + h * ATT_HALF_BYTES + pg * p.page * 128, tm,
+                        &ring_full[slot], h * 64, kvh, 0, block);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && n_tiles > 0) {
+      bool ok = mbar_wait(q_full, 0);
+      // S_g = Q_g K_j^T; K_j is stream element 2j. `last` releases the slot (both heads have read it).
+      auto issue_qk = [&](int g, int j, bool last) {
+        const int i = 2 * j, slot = i % RING;
+        if (!mbar_wait(&ring_full[slot], (i / RING) & 1)) return false;
+        tc_fence_after_sync();
+        const uint32_t q_addr = smem_u32(smem + S::OFF_Q + g * S::Q_BYTES);
+        const uint32_t k_addr = smem_u32(smem + S::OFF_RING + slot * S::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * ATT_HALF_BYTES + (k & 3) * 32;
+          umma_ss(tmem_base + COL_S + g * ATT_BN, make_smem_desc_sw128(q_addr + off, 16, 1024),
+                  make_smem_desc_sw128(k_addr + off, 16, 1024), IDESC_QK, k != 0 ? 1u : 0u);
+        }
+        if (last) umma_commit(&ring_empty[slot]);
+        umma_commit(&s_full[g]);
+        return true;
+      };
+      // O_g += P_g V_j; V_j is stream element 2j + 1.
+      auto issue_pv = [&](int g, int j, bool last) {
+        const int i = 2 * j + 1, slot = i % RING;
+        if (!mbar_wait(&p_ready[g], j & 1)) return false;
+        if (!mbar_wait(&ring_full[slot], (i / RING) & 1)) return false;
+        tc_fence_after_sync();
+        const uint32_t p_addr = smem_u32(smem + S::OFF_P + g * S::P_BYTES);
+        const uint32_t v_addr = smem_u32(smem + S::OFF_RING + slot * S::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < ATT_BN / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * ATT_HALF_BYTES + (k & 3) * 32;
+          umma_ss(tmem_base + COL_O + g * 128, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
+                  make_smem_desc_sw128(v_addr + k * 16 * 128, ATT_HALF_BYTES, 1024), IDESC_PV,
+                  (j | k) != 0 ? 1u : 0u);
+        }
+        if (last) umma_commit(&ring_empty[slot]);
+        umma_commit(&o_done[g]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0, 0, false);
+      if (ok) ok = issue_qk(1, 0, true);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        ok = issue_pv(0, j, false);
+        if (ok && j + 1 < n_tiles) ok = issue_qk(0, j + 1, false);
+        if (ok) ok = issue_pv(1, j, true);
+        if (ok && j + 1 < n_tiles) ok = issue_qk(1, j + 1, true);
+      }
+      if (!ok) {
+        report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+        *abort_flag = 1;
+      }
+    }
+  } else if (n_tiles > 0) {
+    // ---------------- softmax + epilogue: warps 2..5 head A, warps 6..9 head B ----------------
+    const int g = (warp - 2) >> 2;
+    const int qr = warp & 3;                        // TMEM lane quarter of this warp
+    const int r = qr * 32 + lane;                   // row within the tile
+    const int pos = pos0 + min(r, rows_valid - 1);  // padding rows copy the last valid row's mask
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(qr * 32) << 16);
+    const uint32_t t_s = t_lane + COL_S + g * ATT_BN;
+    const uint32_t t_o = t_lane + COL_O + g * 128;
+    uint8_t* p_row = smem + S::OFF_P + g * S::P_BYTES + r * 128;
+    float m_ref = -INFINITY;
+    float l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      if (ok) ok = mbar_wait(&s_full[g], j & 1);
+      tc_fence_after_sync();
+      const int k_base = j * ATT_BN;
+      const bool need_mask = (k_base + ATT_BN - 1) > __shfl_sync(0xffffffffu, pos, 0);
+      // pass 1: row maximum over both 64-key halves; the second half stays in registers
+      uint32_t s0[32], s1[32];
+      float mx = -INFINITY;
+      tmem_ld_32x32(t_s, s0);
+      tmem_ld_32x32(t_s + 32, s1);
+      tmem_wait_ld();
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (k_base + i > pos) s0[i] = __float_as_uint(-INFINITY);
+          if (k_base + 32 + i > pos) s1[i] = __float_as_uint(-INFINITY);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+      tmem_ld_32x32(t_s + 64, s0);
+      tmem_ld_32x32(t_s + 96, s1);
+      tmem_wait_ld();
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (k_base + 64 + i > pos) s0[i] = __float_as_uint(-INFINITY);
+          if (k_base + 96 + i > pos) s1[i] = __float_as_uint(-INFINITY);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+      mx *= p.scale_log2;
+      float alpha = 1.f;
+      bool rescale = false;
+      if (j == 0) {
+        m_ref = mx;
+      } else if (mx > m_ref + 8.f) {
+        alpha = exp2f(m_ref - mx);
+        m_ref = mx;
+        rescale = true;
+      }
+      // pass 2a: the second half (keys 64..127 of the tile) is still in registers
+      uint32_t pk[32];
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a = exp2f(__uint_as_float(s0[2 * i]) * p.scale_log2 - m_ref);
+        const float b = exp2f(__uint_as_float(s0[2 * i + 1]) * p.scale_log2 - m_ref);
+        const float c = exp2f(__uint_as_float(s1[2 * i]) * p.scale_log2 - m_ref);
+        const float d = exp2f(__uint_as_float(s1[2 * i + 1]) * p.scale_log2 - m_ref);
+        part += (a + b) + (c + d);
+        pk[i] = pack_bf16x2(a, b);
+        pk[16 + i] = pack_bf16x2(c, d);
+      }
+      // the first half is read again while the second half's exponentials retire
+      tmem_ld_32x32(t_s, s0);
+      tmem_ld_32x32(t_s + 32, s1);
+      if (j > 0) {
+        // P_g and O_g are free once P_g V_{j-1} has completed
+        if (ok) ok = mbar_wait(&o_done[g], (j - 1) & 1);
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, rescale)) {
+          tmem_wait_ld();
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(t_o + c * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(t_o + c * 32, v);
+          }
+          tmem_wait_st();
+        }
+      }
+#pragma unroll
+      for (int q8 = 0; q8 < 8; ++q8) {
+        const int chunk = q8 ^ (r & 7);
+        *reinterpret_cast<uint4*>(p_row + ATT_HALF_BYTES + chunk * 16) =
+            make_uint4(pk[4 * q8], pk[4 * q8 + 1], pk[4 * q8 + 2], pk[4 * q8 + 3]);
+      }
+      // pass 2b: the first half
+      tmem_wait_ld();
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (k_base + i > pos) s0[i] = __float_as_uint(-INFINITY);
+          if (k_base + 32 + i > pos) s1[i] = __float_as_uint(-INFINITY);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a = exp2f(__uint_as_float(s0[2 * i]) * p.scale_log2 - m_ref);
+        const float b = exp2f(__uint_as_float(s0[2 * i + 1]) * p.scale_log2 - m_ref);
+        const float c = exp2f(__uint_as_float(s1[2 * i]) * p.scale_log2 - m_ref);
+        const float d = exp2f(__uint_as_float(s1[2 * i + 1]) * p.scale_log2 - m_ref);
+        part += (a + b) + (c + d);
+        pk[i] = pack_bf16x2(a, b);
+        pk[16 + i] = pack_bf16x2(c, d);
+      }
+      l_sum = l_sum * alpha + part;
+#pragma unroll
+      for (int q8 = 0; q8 < 8; ++q8) {
+        const int chunk = q8 ^ (r & 7);
+        *reinterpret_cast<uint4*>(p_row + chunk * 16) =
+            make_uint4(pk[4 * q8], pk[4 * q8 + 1], pk[4 * q8 + 2], pk[4 * q8 + 3]);
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      mbar_arrive(&p_ready[g]);   // arrive even after a failed wait so the issuer is not left waiting
+    }
+    if (ok) ok = mbar_wait(&o_done[g], (n_tiles - 1) & 1);
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv = 1.f / l_sum;
+      __nv_bfloat16* orow = p.out + static_cast<long long>(q_begin + q0 + r) * p.ldo + (head0 + g) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_o + c * 32, v);
+        tmem_wait_ld();
+        if (r < rows_valid) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[8 * q4 + 0]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = o;
+          }
+        }
+      }
+    } else {
+      report_error(p.status, TW_ERR_MBAR_TIMEOUT);
+      *abort_flag = 1;
+    }
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+static int g_attn_variant = 0;   // 0 auto, 1 one head per CTA, 2 head pairs
+
+template <int D>
+static int launch_prefill_pair(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                               const AttnParams& p, int num_tiles, cudaStream_t stream) {
+  using S = AttnPairSmem<D>;
+  auto kern = attn_prefill_pair_kernel<D>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) {
+      set_last_error("attn_prefill (head pairs): cudaFuncSetAttribute(smem=%d) failed: %s", S::TOTAL,
+                     cudaGetErrorString(e));
+      return 1;
+    }
+    configured_dev = dev;
+  }
+  dim3 grid(p.hq / 2, num_tiles);
+  kern<<<grid, ATT_THREADS, S::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error("attn_prefill (head pairs) launch failed: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
 }
 
 template <int D>
@@ -432,6 +804,17 @@ extern "C" int tw_attn_prefill(const void* q, long long ldq, int T, const void* 
   p.hkv = hkv;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  // Query heads that share a KV head go two to a CTA when the group size is even.
+  const bool pair = ((hq / hkv) % 2 == 0) && g_attn_variant != 1;
+  if (pair)
+    return D == 128 ? launch_prefill_pair<128>(tmQ, tmK, tmV, p, num_tiles, stream)
+                    : launch_prefill_pair<64>(tmQ, tmK, tmV, p, num_tiles, stream);
   return D == 128 ? launch_prefill<128>(tmQ, tmK, tmV, p, num_tiles, stream)
                   : launch_prefill<64>(tmQ, tmK, tmV, p, num_tiles, stream);
+}
+
+// Kernel choice for tuning runs and tests: 0 automatic, 1 one head per CTA, 2 head pairs where legal.
+extern "C" int tw_attn_set_variant(int variant) {
+  g_attn_variant = variant;
+  return 0;
 }
