@@ -696,7 +696,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   }
 }
 
-static int g_attn_variant = 0;   // 0 auto, 1 one head per CTA, 2 head pairs
+static int g_attn_variant = 1;   // 0 auto, 1 one head per CTA, 2 head pairs
 
 template <int D>
 static int launch_prefill_pair(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
