@@ -31,7 +31,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--launches", type=int, default=4)
-    ap.add_argument("--attn-variant", type=int, default=0, help="attn_prefill: 0 auto, 1 one head per CTA, 2 head pairs")
+    ap.add_argument("--attn-variant", type=int, default=-1,
+                    help="attn_prefill: -1 library default, 0 auto, 1 one head per CTA, 2 head pairs")
     args = ap.parse_args()
     from tokenweave_b200 import ops
     from tokenweave_b200.ops import _native

@@ -696,7 +696,8 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   }
 }
 
-static int g_attn_variant = 1;   // 0 auto, 1 one head per CTA, 2 head pairs
+constexpr int ATTN_DEFAULT_VARIANT = 1;
+static int g_attn_variant = ATTN_DEFAULT_VARIANT;   // 0 auto, 1 one head per CTA, 2 head pairs
 
 template <int D>
 static int launch_prefill_pair(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
@@ -813,8 +814,9 @@ extern "C" int tw_attn_prefill(const void* q, long long ldq, int T, const void* 
                   : launch_prefill<64>(tmQ, tmK, tmV, p, num_tiles, stream);
 }
 
-// Kernel choice for tuning runs and tests: 0 automatic, 1 one head per CTA, 2 head pairs where legal.
+// Kernel choice for tuning runs and tests: 0 automatic, 1 one head per CTA, 2 head pairs where legal,
+// negative: back to the library default.
 extern "C" int tw_attn_set_variant(int variant) {
-  g_attn_variant = variant;
+  g_attn_variant = variant < 0 ? ATTN_DEFAULT_VARIANT : variant;
   return 0;
 }
