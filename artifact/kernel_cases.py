@@ -33,10 +33,13 @@ def main() -> None:
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--attn-variant", type=int, default=-1,
                     help="attn_prefill: -1 library default, 0 auto, 1 one head per CTA, 2 head pairs")
+    ap.add_argument("--attn-ring", type=int, default=0, help="attn_prefill head pairs: K/V tile slots (0 = all that fit)")
+    ap.add_argument("--head-dim", type=int, default=128)
     args = ap.parse_args()
     from tokenweave_b200 import ops
     from tokenweave_b200.ops import _native
     _native.load().tw_attn_set_variant(args.attn_variant)
+    _native.load().tw_attn_set_ring(args.attn_ring)
     torch.cuda.set_device(0)
     dev, BF = "cuda", torch.bfloat16
     peaks = measured_peaks()
@@ -65,7 +68,7 @@ def main() -> None:
         fn = lambda: ops.rmsnorm_quant_fp8(x, w, 1e-5, residual=r, out=q)
         bytes_moved = T * H * (2 + 2 + 2 + 1)
     elif args.case == "attn_prefill":
-        T, hq, hkv, D, page = args.tokens, args.heads, args.kv_heads, 128, 128
+        T, hq, hkv, D, page = args.tokens, args.heads, args.kv_heads, args.head_dim, 128
         nb = T // page + 1
         kc, vc = torch.randn(nb, page, hkv, D, device=dev).to(BF), torch.randn(nb, page, hkv, D, device=dev).to(BF)
         q = torch.randn(T, hq * D, device=dev).to(BF)
