@@ -29,6 +29,7 @@ def main() -> None:
     ap.add_argument("--max-num-seqs", type=int, default=256)
     ap.add_argument("--modes", nargs="+", default=["overlap", "baseline_multimem", "no_ar"])
     ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--cuda-graphs", action="store_true", help="replay repeated step shapes (decode) from CUDA graphs")
     ap.add_argument("--out", default=os.path.join("gpurun_out", "throughput"))
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -41,7 +42,8 @@ def main() -> None:
                   distributed_executor_backend="external_launcher" if world > 1 else "uni",
                   max_num_batched_tokens=args.max_num_batched_tokens, max_num_seqs=args.max_num_seqs,
                   max_model_len=args.input_len + args.output_len + 64, block_size=128, load_format="dummy",
-                  tokenweave_mode=mode, num_hidden_layers_override=args.layers, enable_prefix_caching=False)
+                  tokenweave_mode=mode, num_hidden_layers_override=args.layers, enable_prefix_caching=False,
+                  tokenweave_cuda_graphs=args.cuda_graphs)
         vocab = llm.llm_engine.config.model.vocab_size
         g = torch.Generator().manual_seed(0)
         prompts = [torch.randint(0, vocab, (args.input_len,), generator=g).tolist() for _ in range(args.num_prompts)]
@@ -62,6 +64,7 @@ def main() -> None:
         n_in = sum(len(o.prompt_token_ids) for o in outs)
         row = {"model": args.model, "tp": world, "mode": mode, "input_len": args.input_len,
                "output_len": args.output_len, "num_prompts": len(outs), "chunk_budget": args.max_num_batched_tokens,
+               "cuda_graphs": bool(args.cuda_graphs),
                "requests_per_s": len(outs) / dt, "total_tokens_per_s": (n_in + n_out) / dt,
                "output_tokens_per_s": n_out / dt, "elapsed_s": dt}
         rows.append(row)

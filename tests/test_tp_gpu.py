@@ -96,3 +96,50 @@ def test_tp2_matches_single_gpu(tmp_path, arch, mode, transport):
     ep = str(tmp_path / "expect.pt")
     torch.save(expect, ep)
     run_ranks(_rank, 2, str(tmp_path), prompts, mode, ep, transport, timeout=300)
+
+
+def _graph_rank(rank, world, path, prompts, mode):
+    import torch.distributed as dist
+    from tokenweave_b200 import LLM, SamplingParams, ops
+    err = None
+    try:
+        results = []
+        for graphs in (False, True):
+            llm = LLM(path, device="cuda", skip_tokenizer_init=True, block_size=128, max_num_batched_tokens=2048,
+                      num_gpu_blocks_override=64, tensor_parallel_size=world,
+                      distributed_executor_backend="external_launcher", tokenweave_mode=mode,
+                      tokenweave_threshold=1024, tokenweave_cuda_graphs=graphs)
+            runs = []
+            for _ in range(3):      # same shapes three times: eager, capture, replay
+                outs = llm.generate(prompts, SamplingParams(temperature=0, max_tokens=5))
+                runs.append([o.outputs[0].token_ids for o in outs])
+            torch.cuda.synchronize()
+            ops.check_status()
+            replays = llm.llm_engine.core.executor.worker.runner.graph_replays
+            results.append((runs, replays))
+            dist.barrier()
+            llm.shutdown()
+        (eager_runs, r0), (graph_runs, r1) = results
+        if r0 != 0 or r1 < 4:
+            err = f"rank {rank}: expected graph replays only with the option on, got {r0} / {r1}"
+        elif any(run != eager_runs[0] for run in eager_runs + graph_runs):
+            err = f"rank {rank}: tokens differ between eager and graph replay: {eager_runs[0]} vs {graph_runs}"
+    except Exception:
+        import traceback
+        err = traceback.format_exc()
+    assert err is None, err
+
+
+@pytest.mark.parametrize("mode", ["overlap", "fuse_only"])
+def test_tp2_cuda_graph_replay_matches_eager(tmp_path, mode):
+    """Both streams of the overlap schedule and the in-kernel collectives under CUDA-graph capture and replay."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    arch = "tiny-llama-d128"
+    cfg = ModelConfig(name=arch, **MODEL_PRESETS[arch])
+    st = make_hf_state(cfg, seed=5, dtype=torch.bfloat16)
+    hf = hf_config_dict(cfg)
+    hf["torch_dtype"] = "bfloat16"
+    save_hf_checkpoint(st, hf, str(tmp_path))
+    prompts = _prompts(cfg.vocab_size, [700, 300, 333, 40])
+    run_ranks(_graph_rank, 2, str(tmp_path), prompts, mode, timeout=300)

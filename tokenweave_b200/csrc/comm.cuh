@@ -82,21 +82,50 @@ __device__ __forceinline__ bool wait_signal(uint32_t* addr, uint64_t budget_ns) 
   }
 }
 
-// Barrier between CTA `blockIdx.x` of every rank. Thread t < world raises rank t's flag
-// [channel_base + blockIdx.x * world + rank] and consumes its own flag [.. + t]; the pads return
-// to all-zero, so the protocol needs no epoch and can be replayed from a CUDA graph.
+// Barrier between CTA `blockIdx.x` of every rank, one-way signals only. Thread t < world stores 1
+// into rank t's flag [set][blockIdx.x * world + rank] (a plain system-scope store: nothing comes
+// back over NVLink), then polls its own flag [set][.. + t] in local memory until it reads 1 and
+// clears it. `seq` counts the barriers of the kernel: consecutive barriers alternate between two
+// flag sets, which is what makes the plain store safe — a peer can run at most one barrier ahead
+// (it cannot pass barrier k + 1 without this rank's signal for it, sent only after barrier k was
+// consumed and cleared here), so its next signal lands in the other set, and the set of barrier k
+// is written again only at barrier k + 2. Every kernel runs an even number of barriers, so each
+// starts on set 0 and the pads are all-zero between kernels: no epoch, replayable from a CUDA
+// graph. (The reference's compare-and-swap protocol, csrc/tokenweave_multimem_utils.cuh:157-207,
+// pays a remote atomic round trip per signal; measured here that was about 8 us per barrier.)
 // Returns false (for the whole CTA) if any wait ran out of budget.
+constexpr int BARRIER_SET_WORDS = 128 * 8;   // flags of one set: up to 128 CTAs x 8 ranks
+
 template <MemOrder O>
 __device__ __forceinline__ bool barrier_all_ranks(uint32_t* const* signal_pads, int channel_base, int rank,
-                                                  int world, uint64_t budget_ns) {
+                                                  int world, uint64_t budget_ns, int seq) {
   int failed = 0;
   if (O == MemOrder::AcqRel) __syncthreads();  // every thread's stores precede the release
   if (threadIdx.x < world) {
     const int peer = threadIdx.x;
-    uint32_t* remote = signal_pads[peer] + channel_base + blockIdx.x * world + rank;
-    uint32_t* local = signal_pads[rank] + channel_base + blockIdx.x * world + peer;
-    if (!put_signal<O>(remote, budget_ns)) failed = 1;
-    if (!failed && !wait_signal<O>(local, budget_ns)) failed = 1;
+    const int base = channel_base + (seq & 1) * BARRIER_SET_WORDS + blockIdx.x * world;
+    uint32_t* remote = signal_pads[peer] + base + rank;
+    uint32_t* local = signal_pads[rank] + base + peer;
+    if (O == MemOrder::AcqRel)
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(1u) : "memory");
+    else
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(1u) : "memory");
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+      uint32_t v = 0;
+      for (int i = 0; i < 64 && v == 0; ++i) {
+        if (O == MemOrder::AcqRel)
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
+        else
+          asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
+      }
+      if (v != 0) break;
+      if (globaltimer_ns() - t0 > budget_ns) {
+        failed = 1;
+        break;
+      }
+    }
+    if (!failed) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(local), "r"(0u) : "memory");
   }
   return __syncthreads_or(failed) == 0;
 }

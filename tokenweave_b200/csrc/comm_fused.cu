@@ -76,7 +76,7 @@ fused_rs_norm_ag_kernel(const CommCtx c, long long off_bytes, __nv_bfloat16* __r
   const int nvec = H >> 3;
   const int v = threadIdx.x;
   const bool active = v < nvec;
-  if (!barrier_all_ranks<MemOrder::Relaxed>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns)) {
+  if (!barrier_all_ranks<MemOrder::Relaxed>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns, 0)) {
     if (threadIdx.x == 0) report_error(c.status, TW_ERR_PEER_TIMEOUT);
     return;
   }
@@ -154,7 +154,7 @@ fused_rs_norm_ag_kernel(const CommCtx c, long long off_bytes, __nv_bfloat16* __r
       for (int r = 0; r < ROWS; ++r) x[r] = xn[r];
     }
   }
-  if (!barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns)) {
+  if (!barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns, 1)) {
     if (threadIdx.x == 0) report_error(c.status, TW_ERR_PEER_TIMEOUT);
   }
 }
@@ -172,7 +172,7 @@ simple_fusion_kernel(const CommCtx c, long long off_bytes, __nv_bfloat16* __rest
   const long long row_bytes = static_cast<long long>(H) * 2;
   const long long shard_off = off_bytes + static_cast<long long>(c.rank) * rows_per_rank * row_bytes;
   uint8_t* local_base = c.peer_bases[c.rank];
-  bool ok = barrier_all_ranks<MemOrder::Relaxed>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns);
+  bool ok = barrier_all_ranks<MemOrder::Relaxed>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns, 0);
   if (ok) {
     // phase 1: reduce-scatter into the local copy
     for (int g = blockIdx.x; g < rows_per_rank; g += gridDim.x) {
@@ -182,7 +182,7 @@ simple_fusion_kernel(const CommCtx c, long long off_bytes, __nv_bfloat16* __rest
         *reinterpret_cast<uint4*>(local_base + off) = x;
       }
     }
-    ok = barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns);
+    ok = barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns, 1);
   }
   if (ok) {
     // phase 2: residual add + RMSNorm on the local shard
@@ -222,7 +222,7 @@ simple_fusion_kernel(const CommCtx c, long long off_bytes, __nv_bfloat16* __rest
         *reinterpret_cast<uint4*>(local_base + off) = o;
       }
     }
-    ok = barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns);
+    ok = barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns, 2);
   }
   if (ok) {
     // phase 3: all-gather
@@ -234,7 +234,7 @@ simple_fusion_kernel(const CommCtx c, long long off_bytes, __nv_bfloat16* __rest
         else peer_broadcast_16(c, off, o);
       }
     }
-    ok = barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns);
+    ok = barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns, 3);
   }
   if (!ok && threadIdx.x == 0) report_error(c.status, TW_ERR_PEER_TIMEOUT);
 }
@@ -246,7 +246,7 @@ simple_fusion_kernel(const CommCtx c, long long off_bytes, __nv_bfloat16* __rest
 template <bool MC>
 __global__ void __launch_bounds__(1024)
 collective_kernel(const CommCtx c, long long off_bytes, long long n_vec, int op) {
-  if (!barrier_all_ranks<MemOrder::Relaxed>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns)) {
+  if (!barrier_all_ranks<MemOrder::Relaxed>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns, 0)) {
     if (threadIdx.x == 0) report_error(c.status, TW_ERR_PEER_TIMEOUT);
     return;
   }
@@ -278,7 +278,7 @@ collective_kernel(const CommCtx c, long long off_bytes, long long n_vec, int op)
       }
     }
   }
-  if (!barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns)) {
+  if (!barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns, 1)) {
     if (threadIdx.x == 0) report_error(c.status, TW_ERR_PEER_TIMEOUT);
   }
 }
@@ -287,7 +287,7 @@ collective_kernel(const CommCtx c, long long off_bytes, long long n_vec, int op)
 // to a private output (the small-message path of a classic custom all-reduce).
 __global__ void __launch_bounds__(512)
 oneshot_allreduce_kernel(const CommCtx c, long long off_bytes, long long n_vec, uint4* __restrict__ out) {
-  if (!barrier_all_ranks<MemOrder::Relaxed>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns)) {
+  if (!barrier_all_ranks<MemOrder::Relaxed>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns, 0)) {
     if (threadIdx.x == 0) report_error(c.status, TW_ERR_PEER_TIMEOUT);
     return;
   }
@@ -295,7 +295,7 @@ oneshot_allreduce_kernel(const CommCtx c, long long off_bytes, long long n_vec, 
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n_vec; i += stride)
     out[i] = peer_reduce_bf16x8(c, off_bytes + i * 16);
   // peers may overwrite their buffers only after everyone has finished reading them
-  if (!barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns)) {
+  if (!barrier_all_ranks<MemOrder::AcqRel>(c.signal_pads, c.channel_base, c.rank, c.world, c.budget_ns, 1)) {
     if (threadIdx.x == 0) report_error(c.status, TW_ERR_PEER_TIMEOUT);
   }
 }
@@ -351,6 +351,7 @@ extern "C" int tw_fused_rs_norm_ag(void* mc_base, void* const* peer_bases, uint3
   int grid = max_ctas > 0 ? max_ctas : 16;
   int rows = rows_in_flight;
   if (rows <= 0) rows = rows_per_rank >= grid * 4 ? 4 : (rows_per_rank >= grid * 2 ? 2 : 1);
+  if (grid > 128) grid = 128;     // barrier flags exist for 128 CTAs x 8 ranks
   if (grid * rows > rows_per_rank) grid = (rows_per_rank + rows - 1) / rows;
   if (grid < 1) grid = 1;
   const CommCtx c = make_ctx(mc_base, peer_bases, signal_pads, rank, world, channel_base, budget_ns, status);
@@ -395,6 +396,7 @@ extern "C" int tw_collective(void* mc_base, void* const* peer_bases, uint32_t* c
   int threads = 1024;
   if (per_rank < 1024) threads = static_cast<int>(((per_rank + 31) / 32) * 32);
   const long long need = (per_rank + threads - 1) / threads;
+  if (grid > 128) grid = 128;
   if (grid > need) grid = static_cast<int>(need);
   if (grid < 1) grid = 1;
   const CommCtx c = make_ctx(mc_base, peer_bases, signal_pads, rank, world, channel_base, budget_ns, status);
@@ -414,6 +416,7 @@ extern "C" int tw_oneshot_allreduce(void* const* peer_bases, uint32_t* const* si
   }
   const long long n_vec = n_bytes / 16;
   int grid = max_ctas > 0 ? max_ctas : 36;
+  if (grid > 128) grid = 128;
   const long long need = (n_vec + 511) / 512;
   if (grid > need) grid = static_cast<int>(need);
   const CommCtx c = make_ctx(nullptr, peer_bases, signal_pads, rank, world, channel_base, budget_ns, status);

@@ -21,7 +21,7 @@ import torch
 from .. import envs
 from .state import TPState, get_tp
 
-SIGNAL_PAD_WORDS_NEEDED = 128 * 8 + 64   # barrier slots for up to 128 CTAs x 8 ranks, plus spare flags
+SIGNAL_PAD_WORDS_NEEDED = 2 * 128 * 8 + 64   # two alternating sets of barrier flags (128 CTAs x 8 ranks each), plus spare flags
 
 
 @dataclass

@@ -141,17 +141,23 @@ def run_overlap(layers: Sequence, final_norm_w: torch.Tensor, hidden: torch.Tens
     a_sms = max(1, sms - a_ctas) if on_gpu and comm.world > 1 else 0
     m_sms = max(1, sms - m_ctas) if on_gpu and comm.world > 1 else 0
 
+    pending = [False]     # work enqueued on X since the last join
+
     def comm_async(x, r, w, ctas):
         if on_gpu:
             X.wait_stream(C)
             with torch.cuda.stream(X):
                 comm.fused_allreduce_add_rmsnorm_(x, r, w, eps, ctas)
+            pending[0] = True
         else:
             comm.fused_allreduce_add_rmsnorm_(x, r, w, eps, ctas)
 
     def join():
-        if on_gpu:
+        # Only when X has work of this step: under stream capture a wait on X's earlier, uncaptured work
+        # (layer 0 enqueues nothing before its first join) is an illegal cross-stream dependency.
+        if on_gpu and pending[0]:
             C.wait_stream(X)
+            pending[0] = False
 
     if first_pending:
         comm.fused_allreduce_add_rmsnorm_(s0, r0, layers[0].input_norm_w, eps, a_ctas)
