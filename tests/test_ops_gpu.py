@@ -323,7 +323,9 @@ def test_gemm_fp8(M, N, K):
     # and the quantised result approximates the bf16 product
     full = ref.gemm(a, w).float() + bias.float()
     assert (out.float() - full).abs().mean() < 0.05 * full.abs().mean() + 0.02
-    close(ops.gemm_fp8(aq, wq, None, None), ref.gemm_fp8(aq, wq, None, None), atol=2e-2 * 16, rtol=2e-2)
+    # unscaled: sums of products of up to 448 * 448 that cancel; the absolute slack follows the magnitude
+    raw = ref.gemm_fp8(aq, wq, None, None)
+    close(ops.gemm_fp8(aq, wq, None, None), raw, atol=1e-4 * raw.float().abs().max().item(), rtol=2e-2)
 
 
 @pytest.mark.parametrize("M,I,K", [(256, 512, 256), (1000, 3584, 1024), (4096, 3584, 8192)])

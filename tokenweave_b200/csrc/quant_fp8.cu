@@ -91,12 +91,12 @@ quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict_
       block_sum<1>(ss, scratch);
       inv = rsqrtf(ss[0] / static_cast<float>(H) + eps);
     }
-    // y in fp32 (normalised value rounded to bf16 before the weight, as in the bf16 norms)
-    float y[VPT][8];
+    // y = the value to quantise, kept as packed bf16 in place of x (the normalised value is rounded to
+    // bf16 before the weight and after it, as in the bf16 norms, so nothing is lost by packing)
     float amax = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const uint32_t* u = reinterpret_cast<const uint32_t*>(&xv[i]);
+      uint32_t* u = reinterpret_cast<uint32_t*>(&xv[i]);
       const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv[i]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -105,11 +105,9 @@ quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict_
           const float2 g = unpack_bf16x2(wu[j]);
           f.x = __bfloat162float(__float2bfloat16_rn(f.x * inv)) * g.x;
           f.y = __bfloat162float(__float2bfloat16_rn(f.y * inv)) * g.y;
-          f.x = __bfloat162float(__float2bfloat16_rn(f.x));
-          f.y = __bfloat162float(__float2bfloat16_rn(f.y));
+          u[j] = pack_bf16x2(f.x, f.y);
+          f = unpack_bf16x2(u[j]);
         }
-        y[i][2 * j] = f.x;
-        y[i][2 * j + 1] = f.y;
         amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
       }
     }
@@ -128,11 +126,12 @@ quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict_
     for (int i = 0; i < VPT; ++i) {
       const int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
+        const uint32_t* u = reinterpret_cast<const uint32_t*>(&xv[i]);
+        const float2 a = unpack_bf16x2(u[0]), b = unpack_bf16x2(u[1]);
+        const float2 c = unpack_bf16x2(u[2]), d = unpack_bf16x2(u[3]);
         uint2 o;
-        o.x = to_e4m3x2(y[i][0] * rscale, y[i][1] * rscale) |
-              (static_cast<uint32_t>(to_e4m3x2(y[i][2] * rscale, y[i][3] * rscale)) << 16);
-        o.y = to_e4m3x2(y[i][4] * rscale, y[i][5] * rscale) |
-              (static_cast<uint32_t>(to_e4m3x2(y[i][6] * rscale, y[i][7] * rscale)) << 16);
+        o.x = to_e4m3x2(a.x * rscale, a.y * rscale) | (static_cast<uint32_t>(to_e4m3x2(b.x * rscale, b.y * rscale)) << 16);
+        o.y = to_e4m3x2(c.x * rscale, c.y * rscale) | (static_cast<uint32_t>(to_e4m3x2(d.x * rscale, d.y * rscale)) << 16);
         orow[v] = o;
       }
     }
@@ -154,7 +153,7 @@ static int launch_quant(const void* x, void* res, const void* w, void* out, floa
     return 1;
   }
   int grid = T;
-  int cap = device_sm_count() * 2;
+  int cap = device_sm_count() * 4;
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
   auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
