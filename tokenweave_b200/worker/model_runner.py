@@ -123,6 +123,14 @@ class ModelRunner:
     def init_kv_cache(self, num_blocks: int) -> None:
         self.model.init_kv_cache(num_blocks, self.block_size)
 
+    def release_graphs(self) -> None:
+        """Drop every captured CUDA graph and the pool they allocate from."""
+        if self._graphs:
+            torch.cuda.synchronize()
+        self._graphs.clear()
+        self._graph_seen.clear()
+        self._graph_pool = None
+
     # ---- one step ---------------------------------------------------------------------------
     def _update_states(self, step: StepData) -> None:
         for rid in step.finished_req_ids:

@@ -202,6 +202,10 @@ class Worker:
     def shutdown(self) -> None:
         if self.device.type == "cuda":
             torch.cuda.synchronize()
+        if self.runner is not None:
+            # captured graphs hold NCCL kernels (the logits gather) and pool memory: release them before the
+            # communicator goes away, or its destruction waits on them
+            self.runner.release_graphs()
         if self.runner is not None and self.runner.model is not None and self.runner.model.rt is not None:
             try:
                 self.runner.model.rt.staging.close()
