@@ -12,7 +12,7 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from common import NVLINK_GBS_MEASURED, finish_ranks, init_ranks, time_us, write_rows  # noqa: E402
+from common import NVLINK_GBS_MEASURED, RESULTS_DIR, finish_ranks, init_ranks, time_us, write_rows  # noqa: E402
 
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
@@ -26,7 +26,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--transport", default="auto", choices=["auto", "multimem", "p2p"])
-    ap.add_argument("--out", default=os.path.join("gpurun_out", "collectives_bench"))
+    ap.add_argument("--out", default=os.path.join(RESULTS_DIR, "collectives_bench"))
     args = ap.parse_args()
     if args.transport == "p2p":
         os.environ["TW_DISABLE_NVLS"] = "1"

@@ -21,6 +21,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+RESULTS_DIR = os.environ.get("TW_RESULTS_DIR", "results")     # where the benchmarks write their CSV / JSON / logs
 NVLINK_GBS_MEASURED = 770.0      # peer copy, per direction per GPU, measured on this pool
 _flush = None
 

@@ -17,7 +17,7 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from common import write_rows  # noqa: E402
+from common import RESULTS_DIR, write_rows  # noqa: E402
 
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
@@ -34,7 +34,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--layers", type=int, default=None, help="tune on a truncated stack (per-layer behaviour is identical)")
-    ap.add_argument("--out-dir", default=os.path.join("gpurun_out", "configs"))
+    ap.add_argument("--out-dir", default=os.path.join(RESULTS_DIR, "configs"))
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

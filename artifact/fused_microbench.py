@@ -23,7 +23,7 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from common import NVLINK_GBS_MEASURED, finish_ranks, init_ranks, time_us, write_rows  # noqa: E402
+from common import NVLINK_GBS_MEASURED, RESULTS_DIR, finish_ranks, init_ranks, time_us, write_rows  # noqa: E402
 
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
@@ -64,7 +64,7 @@ def main() -> None:
     ap.add_argument("--burst", type=int, default=20,
                     help="also time this many back-to-back launches per event pair (steady-state latency per launch, "
                          "warm L2, no host in between: how the kernels run inside a model step); 0 disables")
-    ap.add_argument("--out", default=os.path.join("gpurun_out", "fused_microbench"))
+    ap.add_argument("--out", default=os.path.join(RESULTS_DIR, "fused_microbench"))
     args = ap.parse_args()
     if args.transport == "p2p":
         os.environ["TW_DISABLE_NVLS"] = "1"

@@ -2,7 +2,7 @@
 """GEMM kernels on the linear-layer shapes of the served models against the library GEMMs of the box:
 bf16 ``tw_gemm_bf16`` vs ``torch.matmul`` (cuBLAS), the SwiGLU-epilogue GEMM vs cuBLAS + a separate
 activation kernel, and the e4m3 ``tw_gemm_fp8`` vs ``torch._scaled_mm`` (cuBLASLt fp8). Single GPU.
-Prints one line per shape and writes ``gpurun_out/gemm_bench/gemm_bench.csv``. TFLOP/s fractions are
+Prints one line per shape and writes ``results/gemm_bench/gemm_bench.csv`` (``TW_RESULTS_DIR`` overrides the folder). TFLOP/s fractions are
 relative to the measured cuBLAS bf16 burst throughput of ``MEASURED_PEAKS.json`` when present.
 
     python artifact/gemm_bench.py --models llama-3.3-70b --tp 8 --tokens 4096 8192
@@ -14,7 +14,7 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from common import measured_peaks, time_us, write_rows  # noqa: E402
+from common import RESULTS_DIR, measured_peaks, time_us, write_rows  # noqa: E402
 from gemm_tune import shapes_for  # noqa: E402
 
 import torch  # noqa: E402
@@ -28,7 +28,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--fp8", action=argparse.BooleanOptionalAction, default=True)
     ap.add_argument("--square", type=int, nargs="*", default=[8192], help="extra M=N=K problems")
-    ap.add_argument("--out", default=os.path.join("gpurun_out", "gemm_bench"))
+    ap.add_argument("--out", default=os.path.join(RESULTS_DIR, "gemm_bench"))
     args = ap.parse_args()
     from tokenweave_b200 import ops
     from tokenweave_b200.config import resolve_model_config

@@ -2,7 +2,7 @@
 """Runs ONE kernel on a small, fixed case a few times: the command to put under ``ncu`` (single GPU).
 
     python artifact/kernel_cases.py gemm --m 4096 --n 8192 --k 4096
-    ncu --set full --clock-control none -k regex:gemm_bf16 -s 2 -c 2 -o gpurun_out/gemm python artifact/kernel_cases.py gemm
+    ncu --set full --clock-control none -k regex:gemm_bf16 -s 2 -c 2 -o results/gemm python artifact/kernel_cases.py gemm
 
 Inputs are larger than the 126 MB L2 where the kernel's real workloads are, but stay within a few GB.
 Prints the CUDA-event time of the last launch and the achieved rate against the measured peaks."""

@@ -8,7 +8,7 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from common import ROOT  # noqa: E402,F401
+from common import RESULTS_DIR, ROOT  # noqa: E402,F401
 
 import torch  # noqa: E402
 
@@ -20,7 +20,7 @@ def main() -> None:
     ap.add_argument("--mode", default="overlap")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--layers", type=int, default=None)
-    ap.add_argument("--out", default=os.path.join("gpurun_out", "op_profile.txt"))
+    ap.add_argument("--out", default=os.path.join(RESULTS_DIR, "op_profile.txt"))
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

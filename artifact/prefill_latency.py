@@ -14,7 +14,7 @@ import sys
 import time
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from common import write_rows  # noqa: E402
+from common import RESULTS_DIR, write_rows  # noqa: E402
 
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
@@ -78,7 +78,7 @@ def main() -> None:
     ap.add_argument("--attention-ctas", type=int, default=None)
     ap.add_argument("--mlp-ctas", type=int, default=None)
     ap.add_argument("--fuse-only-ctas", type=int, default=16)
-    ap.add_argument("--out", default=os.path.join("gpurun_out", "prefill_latency"))
+    ap.add_argument("--out", default=os.path.join(RESULTS_DIR, "prefill_latency"))
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -10,7 +10,7 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from common import time_us, write_rows  # noqa: E402
+from common import RESULTS_DIR, time_us, write_rows  # noqa: E402
 
 import torch  # noqa: E402
 
@@ -23,7 +23,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--intermediate", type=int, default=28672)
     ap.add_argument("--iters", type=int, default=50)
-    ap.add_argument("--out", default=os.path.join("gpurun_out", "smart_split"))
+    ap.add_argument("--out", default=os.path.join(RESULTS_DIR, "smart_split"))
     args = ap.parse_args()
     from tokenweave_b200 import ops
     torch.cuda.set_device(0)

@@ -13,7 +13,7 @@ import sys
 import time
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from common import write_rows  # noqa: E402
+from common import RESULTS_DIR, write_rows  # noqa: E402
 
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
@@ -30,7 +30,7 @@ def main() -> None:
     ap.add_argument("--modes", nargs="+", default=["overlap", "baseline_multimem", "no_ar"])
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--cuda-graphs", action="store_true", help="replay repeated step shapes (decode) from CUDA graphs")
-    ap.add_argument("--out", default=os.path.join("gpurun_out", "throughput"))
+    ap.add_argument("--out", default=os.path.join(RESULTS_DIR, "throughput"))
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
