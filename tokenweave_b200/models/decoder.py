@@ -20,7 +20,7 @@ import torch
 from torch import nn
 
 from .. import ops
-from ..config import EngineConfig, ModelConfig
+from ..config import ModelConfig
 from ..layers.attention import Attention, AttentionMetadata
 from ..layers.embedding import ParallelLMHead, VocabEmbedding
 from ..layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear

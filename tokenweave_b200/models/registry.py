@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config import EngineConfig, ModelConfig
+from ..config import EngineConfig
 
 
 def get_model_class(architecture: str):

@@ -1,7 +1,7 @@
 """Sampling parameters of a request (subset of vllm/sampling_params.py used by offline inference)."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional, Union
 
 
