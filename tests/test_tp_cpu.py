@@ -166,3 +166,19 @@ def test_expert_parallel_mixtral_matches_single_process(tmp_path, world):
     lp = str(tmp_path / "expect_logits.pt")
     torch.save(logits, lp)
     run_ranks(_ep_rank, world, str(tmp_path), prompts, toks, lp)
+
+
+def _spec_rank(rank, world, path, prompts, expect_toks):
+    toks, _ = _generate(path, prompts, tensor_parallel_size=world, distributed_executor_backend="external_launcher",
+                        tokenweave_mode="overlap", tokenweave_threshold=128, speculative_config=4)
+    assert toks == expect_toks, f"rank {rank}: {toks} != {expect_toks}"
+
+
+def test_speculative_decoding_under_tp2_matches_plain_single_process(tmp_path):
+    """Every SPMD rank drafts and verifies the same tokens (the proposer is a pure function of the history)."""
+    cfg = _ckpt(tmp_path, "tiny-llama")
+    g = torch.Generator().manual_seed(4)
+    base = torch.randint(0, cfg.vocab_size, (20,), generator=g).tolist()
+    prompts = [base * 6, base[:9] * 5, torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()]
+    toks, _ = _generate(str(tmp_path), prompts)
+    run_ranks(_spec_rank, 2, str(tmp_path), prompts, toks)

@@ -216,6 +216,7 @@ class EngineConfig:
     skip_tokenizer_init: bool = False
     disable_log_stats: bool = True
     enable_sleep_mode: bool = False       # weights and KV cache on the VMM allocator: LLM.sleep() frees their memory
+    speculative: Any = None               # engine.spec_decode.SpecDecodeConfig (n-gram drafts for greedy requests)
 
     def resolved_device(self) -> str:
         if self.device != "auto":
@@ -250,6 +251,8 @@ class EngineArgs:
     num_hidden_layers_override: Optional[int] = None
     disable_log_stats: bool = True
     enable_sleep_mode: bool = False       # weights and KV cache on the VMM allocator: LLM.sleep() frees their memory
+    # {"method": "ngram", "num_speculative_tokens": k, "prompt_lookup_max": n, "prompt_lookup_min": m}, or just k
+    speculative_config: Any = None
     # TokenWeave
     tokenweave_mode: str = "overlap"
     tokenweave_config: Optional[str] = None
@@ -297,7 +300,15 @@ class EngineArgs:
                                         mlp_ctas=self.tokenweave_mlp_ctas),
             load_format=load_format, quantization=self.quantization, seed=self.seed, device=self.device, enforce_eager=self.enforce_eager,
             tokenizer=self.tokenizer, skip_tokenizer_init=self.skip_tokenizer_init,
-            disable_log_stats=self.disable_log_stats, enable_sleep_mode=self.enable_sleep_mode)
+            disable_log_stats=self.disable_log_stats, enable_sleep_mode=self.enable_sleep_mode,
+            speculative=self._speculative())
+
+    def _speculative(self):
+        from .engine.spec_decode import SpecDecodeConfig
+        value = self.speculative_config
+        if isinstance(value, str):          # command line: a JSON object or a bare integer
+            value = json.loads(value)
+        return SpecDecodeConfig.from_user(value)
 
     @staticmethod
     def add_cli_args(parser: argparse.ArgumentParser) -> argparse.ArgumentParser:

@@ -35,7 +35,7 @@ class EngineCore:
         self.executor.init_kv_cache(num_blocks)
         self.num_blocks = num_blocks
         self.kv = KVCacheManager(num_blocks, config.cache.block_size, config.cache.enable_prefix_caching)
-        self.scheduler = Scheduler(config.scheduler, self.kv)
+        self.scheduler = Scheduler(config.scheduler, self.kv, config.speculative)
         self._sent_blocks: dict[str, int] = {}     # blocks of each request already known to the workers
         self.last_stats: Optional[StepStats] = None
 
@@ -67,7 +67,8 @@ class EngineCore:
             else:
                 new_blocks = r.block_ids[self._sent_blocks.get(r.request_id, 0):]
             self._sent_blocks[r.request_id] = len(r.block_ids)
-            step.scheduled.append((r.request_id, s.num_computed_tokens, s.num_new_tokens, list(new_blocks)))
+            step.scheduled.append((r.request_id, s.num_computed_tokens, s.num_new_tokens, list(new_blocks),
+                                   list(s.spec_token_ids)))
         return step
 
     def step(self) -> list[Request]:
@@ -90,7 +91,7 @@ class EngineCore:
         self._last_logprobs = dict(zip(result.req_ids, result.logprobs)) if result.logprobs else {}
         self.last_stats = StepStats(num_tokens=sched.total_num_tokens, num_running=len(self.scheduler.running),
                                     num_waiting=len(self.scheduler.waiting), kv_usage=self.kv.usage(),
-                                    num_generated=len(touched))
+                                    num_generated=self.scheduler.last_emitted)
         return touched
 
     def shutdown(self) -> None:

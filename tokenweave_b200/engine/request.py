@@ -39,6 +39,7 @@ class Request:
     output_token_ids: list[int] = field(default_factory=list)
     num_computed_tokens: int = 0       # tokens whose KV is in the cache
     block_ids: list[int] = field(default_factory=list)
+    spec_token_ids: list[int] = field(default_factory=list)   # drafts to verify in the next step
     stop_reason: Optional[object] = None
     first_scheduled_time: Optional[float] = None
     first_token_time: Optional[float] = None

@@ -25,6 +25,7 @@ class ScheduledRequest:
     num_new_tokens: int
     num_computed_tokens: int     # before this step
     is_new: bool                 # first time (or resumed after preemption) on the workers
+    spec_token_ids: list[int] = field(default_factory=list)   # drafts verified in this step (the last tokens)
 
 
 @dataclass
@@ -43,14 +44,20 @@ class SchedulerOutput:
 @dataclass
 class ModelRunnerOutput:
     req_ids: list[str]
-    sampled_token_ids: list[Optional[int]]        # None for requests still prefilling
+    # None for requests still prefilling; an int, or (speculative decoding) the list of tokens the step emitted
+    sampled_token_ids: list
     logprobs: Optional[list] = None
 
 
 class Scheduler:
-    def __init__(self, config: SchedulerConfig, kv: KVCacheManager):
+    def __init__(self, config: SchedulerConfig, kv: KVCacheManager, spec=None):
+        from .spec_decode import SpecDecodeConfig
         self.config = config
         self.kv = kv
+        self.spec = spec if spec is not None else SpecDecodeConfig()
+        self.num_draft_tokens = 0          # statistics of speculative decoding
+        self.num_accepted_tokens = 0
+        self.last_emitted = 0
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self.requests: dict[str, Request] = {}
@@ -98,6 +105,13 @@ class Scheduler:
             if not self.config.enable_chunked_prefill and n < req.num_tokens - req.num_computed_tokens:
                 i += 1
                 continue
+            drafts: list[int] = []
+            if req.spec_token_ids:
+                # a decoding request (one uncomputed token) takes its drafts along as extra query tokens
+                if n == 1 and req.num_tokens - req.num_computed_tokens == 1:
+                    drafts = req.spec_token_ids[:max(0, budget - n)]
+                    n += len(drafts)
+                req.spec_token_ids = []
             while not self.kv.allocate_slots(req, n):
                 victim = self.running.pop()     # most recently admitted
                 self._preempt(victim)
@@ -107,7 +121,7 @@ class Scheduler:
                     break
             if n == 0:
                 break
-            out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, False))
+            out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, False, drafts))
             budget -= n
             i += 1
 
@@ -144,6 +158,7 @@ class Scheduler:
         self.kv.free(req)
         req.status = RequestStatus.PREEMPTED
         req.num_computed_tokens = 0
+        req.spec_token_ids = []
         self.waiting.appendleft(req)
 
     # ---- results ------------------------------------------------------------------------
@@ -151,35 +166,70 @@ class Scheduler:
         """Advance every scheduled request; returns the requests that produced a token or finished."""
         sampled = dict(zip(result.req_ids, result.sampled_token_ids))
         touched: list[Request] = []
+        self.last_emitted = 0              # tokens appended to outputs by this step
         for s in sched.scheduled:
             req = s.request
             if req.status.finished:
                 continue
-            req.num_computed_tokens = s.num_computed_tokens + s.num_new_tokens
-            self.kv.cache_full_blocks(req)
             tok = sampled.get(req.request_id)
-            if req.num_computed_tokens < req.num_tokens or tok is None:
+            toks = [int(t) for t in tok] if isinstance(tok, (list, tuple)) else ([] if tok is None else [int(tok)])
+            # drafts that the model did not confirm leave no valid KV behind: they are not "computed"
+            rejected = 0
+            if s.spec_token_ids:
+                accepted = max(0, len(toks) - 1)
+                rejected = len(s.spec_token_ids) - accepted
+                self.num_draft_tokens += len(s.spec_token_ids)
+                self.num_accepted_tokens += accepted
+            req.num_computed_tokens = s.num_computed_tokens + s.num_new_tokens - rejected
+            if req.num_computed_tokens - (len(toks) - 1 if s.spec_token_ids else 0) < req.num_tokens or not toks:
+                self.kv.cache_full_blocks(req)
                 continue                       # still prefilling: the sampled token (if any) is discarded
-            req.output_token_ids.append(int(tok))
-            if req.first_token_time is None:
-                req.first_token_time = time.monotonic()
+            stop = None
+            for t in toks:
+                req.output_token_ids.append(t)
+                self.last_emitted += 1
+                if req.first_token_time is None:
+                    req.first_token_time = time.monotonic()
+                stop = self._stop_decision(req)
+                if stop is not None:
+                    break                      # tokens the step produced beyond a stop are dropped
+            req.num_computed_tokens = min(req.num_computed_tokens, req.num_tokens)
+            self.kv.cache_full_blocks(req)     # while the request still owns its blocks
+            if stop is not None:
+                self._stop_running(req, *stop)
+            else:
+                self._propose_drafts(req)
             touched.append(req)
-            self._check_stop(req)
         return touched
 
-    def _check_stop(self, req: Request) -> None:
+    def _propose_drafts(self, req: Request) -> None:
+        """n-gram drafts for the next step of a greedy decoding request (empty when nothing matches)."""
+        from .spec_decode import clamp_drafts, ngram_propose, spec_eligible
+        if not self.spec.enabled or not spec_eligible(req.sampling_params):
+            return
+        drafts = ngram_propose(req.all_token_ids, self.spec.num_speculative_tokens, self.spec.prompt_lookup_max,
+                               self.spec.prompt_lookup_min)
+        req.spec_token_ids = clamp_drafts(drafts, req.num_tokens, self.config.max_model_len,
+                                          req.sampling_params.max_tokens, len(req.output_token_ids))
+
+    def _stop_decision(self, req: Request):
+        """(status, stop_reason) if the request's last token ends it, else None. No side effects."""
         sp = req.sampling_params
         last = req.output_token_ids[-1]
         n_out = len(req.output_token_ids)
         if n_out >= sp.min_tokens:
             if not sp.ignore_eos and req.eos_token_id is not None and last == req.eos_token_id:
-                self._stop_running(req, RequestStatus.FINISHED_STOPPED, None)
-                return
+                return RequestStatus.FINISHED_STOPPED, None
             if last in sp.stop_token_ids:
-                self._stop_running(req, RequestStatus.FINISHED_STOPPED, last)
-                return
+                return RequestStatus.FINISHED_STOPPED, last
         if (sp.max_tokens is not None and n_out >= sp.max_tokens) or req.num_tokens >= self.config.max_model_len:
-            self._stop_running(req, RequestStatus.FINISHED_LENGTH, None)
+            return RequestStatus.FINISHED_LENGTH, None
+        return None
+
+    def _check_stop(self, req: Request) -> None:
+        stop = self._stop_decision(req)
+        if stop is not None:
+            self._stop_running(req, *stop)
 
     def finish_request(self, req: Request, status: RequestStatus, stop_reason=None) -> None:
         """Used by the front end for stop strings detected after detokenisation."""

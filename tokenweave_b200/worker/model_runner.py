@@ -99,8 +99,11 @@ class ModelRunner:
         self.use_graphs = bool(tw.use_cuda_graphs) and pin
         self._meta_dev = [torch.zeros(1 << 20, dtype=torch.int32, device=device) if self.use_graphs else None
                           for _ in range(2)]
-        self._rows_dev = torch.zeros(max(config.scheduler.max_num_seqs, 1), dtype=torch.long, device=device)
-        self._rows_host = torch.zeros(max(config.scheduler.max_num_seqs, 1), dtype=torch.long, pin_memory=pin)
+        # logits rows per step: one per sequence, plus one per draft token under speculative decoding
+        k_spec = config.speculative.num_speculative_tokens if config.speculative is not None else 0
+        n_rows = max(config.scheduler.max_num_seqs, 1) * (1 + k_spec)
+        self._rows_dev = torch.zeros(n_rows, dtype=torch.long, device=device)
+        self._rows_host = torch.zeros(n_rows, dtype=torch.long, pin_memory=pin)
         self._graphs: dict = {}
         self._graph_seen: dict = {}
         self._graph_pool = None
@@ -220,10 +223,16 @@ class ModelRunner:
         logits_rows, sample_reqs = [], []
         row = 0
         bs = self.block_size
-        for b, (rid, computed, n_new, new_blocks) in enumerate(step.scheduled):
+        spec: dict[str, list[int]] = {}          # request -> drafts verified in this step
+        for b, (rid, computed, n_new, new_blocks, *rest) in enumerate(step.scheduled):
             req = self.requests[rid]
             req.block_ids.extend(new_blocks)
-            ids[row:row + n_new] = req.token_ids[computed:computed + n_new]
+            drafts = list(rest[0]) if rest and rest[0] else []
+            n_base = n_new - len(drafts)             # tokens of the request itself; the drafts follow them
+            ids[row:row + n_base] = req.token_ids[computed:computed + n_base]
+            if drafts:
+                ids[row + n_base:row + n_new] = drafts
+                spec[rid] = drafts
             pos = np.arange(computed, computed + n_new, dtype=np.int32)
             positions[row:row + n_new] = pos
             blocks = np.asarray(req.block_ids, dtype=np.int32)
@@ -231,9 +240,11 @@ class ModelRunner:
             q_lens.append(n_new)
             kv_lens.append(computed + n_new)
             tables[b] = req.block_ids
-            if computed + n_new >= len(req.token_ids):
-                logits_rows.append(row + n_new - 1)
-                sample_reqs.append(rid)
+            if computed + n_base >= len(req.token_ids):
+                # one logits row at the request's last own token, and one after every draft
+                for k in range(len(drafts) + 1):
+                    logits_rows.append(row + n_base - 1 + k)
+                    sample_reqs.append(rid)
             row += n_new
 
         plan = self.planner.plan(T)
@@ -291,9 +302,22 @@ class ModelRunner:
             toks = out.token_ids.tolist()            # the device -> host synchronisation point of the step
             d2h = len(toks) * 4
             lp = out.logprobs
-            for rid, tok in zip(sample_reqs, toks):
-                sampled[rid] = int(tok)
-                self.requests[rid].token_ids.append(int(tok))
+            i = 0
+            while i < len(toks):
+                rid = sample_reqs[i]
+                drafts = spec.get(rid)
+                if drafts:
+                    # speculative decoding: rows i .. i + len(drafts) are the model's choices after the last
+                    # sampled token and after every draft; keep the confirmed drafts and one more token
+                    from ..engine.spec_decode import accept_greedy
+                    emitted = accept_greedy(drafts, toks[i:i + len(drafts) + 1])
+                    sampled[rid] = emitted
+                    self.requests[rid].token_ids.extend(emitted)
+                    i += len(drafts) + 1
+                else:
+                    sampled[rid] = int(toks[i])
+                    self.requests[rid].token_ids.append(int(toks[i]))
+                    i += 1
         elif ev is not None:
             ev[1].record()
         if ev is not None:
