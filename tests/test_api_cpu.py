@@ -109,3 +109,20 @@ def test_encode_embed_score():
     # a later generate() is unaffected by the capture switch
     assert not llm.llm_engine.core.executor.worker.runner.capture_hidden
     llm.shutdown()
+
+
+def test_min_tokens_masks_eos_and_allowed_token_ids_restrict_generation():
+    from tokenweave_b200 import LLM
+    llm = LLM("tiny-llama", dtype="float32", device="cpu", skip_tokenizer_init=True, block_size=16,
+              max_num_batched_tokens=128, seed=5)
+    prompt = list(range(3, 30))
+    free = llm.generate([prompt], SamplingParams(temperature=0, max_tokens=6, ignore_eos=True))[0].outputs[0].token_ids
+    eos_like = free[1]                       # make the second greedy token a stop token
+    early = llm.generate([prompt], SamplingParams(temperature=0, max_tokens=6, stop_token_ids=[eos_like]))[0].outputs[0]
+    assert early.token_ids == free[:2] and early.finish_reason == "stop"
+    late = llm.generate([prompt], SamplingParams(temperature=0, max_tokens=6, stop_token_ids=[eos_like], min_tokens=4))[0].outputs[0]
+    assert len(late.token_ids) >= 4 and eos_like not in late.token_ids[:3]
+    only = llm.generate([prompt], SamplingParams(temperature=0.9, seed=1, max_tokens=8, ignore_eos=True,
+                                                 allowed_token_ids=[10, 11, 12]))[0].outputs[0].token_ids
+    assert set(only) <= {10, 11, 12}
+    llm.shutdown()

@@ -85,3 +85,26 @@ def test_logprobs_hold_the_sampled_token_and_the_top_n():
     assert set(top) <= set(lp) and int(out.token_ids[0]) in lp
     for t, v in lp.items():
         assert math.isclose(v, float(ref[t]), abs_tol=1e-6)
+
+
+def test_logit_bias_allowed_tokens_bad_words_min_tokens():
+    logits = torch.tensor([[1.0, 5.0, 3.0, 2.0, 0.0, -1.0]])
+    s = Sampler()
+
+    def pick(sp, outputs=()):
+        return int(s(logits.clone(), [sp], [None], [[]], [list(outputs)]).token_ids[0])
+    assert pick(SamplingParams(temperature=0)) == 1
+    assert pick(SamplingParams(temperature=0, logit_bias={1: -100, "3": 10})) == 3      # string keys as in JSON bodies
+    assert pick(SamplingParams(temperature=0, allowed_token_ids=[0, 4, 5])) == 0
+    assert pick(SamplingParams(temperature=0, bad_words_token_ids=[[1]])) == 2           # single-token word: always banned
+    assert pick(SamplingParams(temperature=0, bad_words_token_ids=[[7, 1]])) == 1        # prefix 7 not generated yet
+    assert pick(SamplingParams(temperature=0, bad_words_token_ids=[[7, 1]]), outputs=[3, 7]) == 2
+    # below min_tokens the EOS and stop tokens cannot be sampled
+    sp = SamplingParams(temperature=0, min_tokens=3, stop_token_ids=[2], eos_token_id=1)
+    assert pick(sp, outputs=[0]) == 3 and pick(sp, outputs=[0, 0, 0]) == 1
+    # sampled (non-greedy) rows honour the masks too
+    ids = _draw(logits[0], SamplingParams(allowed_token_ids=[2, 3]), n=500)
+    assert set(ids.tolist()) <= {2, 3}
+    import pytest
+    with pytest.raises(ValueError):
+        SamplingParams(allowed_token_ids=[])

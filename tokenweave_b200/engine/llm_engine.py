@@ -75,6 +75,10 @@ class LLMEngine:
                 sp.n = 1
                 if sp.seed is not None:
                     sp.seed = sp.seed + i
+            if sp.min_tokens > 0 and sp.eos_token_id is None and not sp.ignore_eos:
+                if sp is params:
+                    sp = params.clone()          # the caller's object stays untouched
+                sp.eos_token_id = self.eos_token_id     # the sampler masks it until min_tokens is reached
             cid = request_id if params.n == 1 else f"{i}_{request_id}"
             child = Request(cid, list(ids), sp, eos_token_id=self.eos_token_id, prompt=text)
             parent.children.append(child)

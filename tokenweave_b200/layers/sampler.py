@@ -38,6 +38,30 @@ def apply_penalties(logits: torch.Tensor, params: Sequence[SamplingParams], prom
             counts = torch.bincount(out_ids[out_ids < V], minlength=V).to(logits.dtype)
             logits[i] -= sp.frequency_penalty * counts
             logits[i] -= sp.presence_penalty * (counts > 0).to(logits.dtype)
+        # logit bias, allowed-token and bad-word masks, minimum length
+        # (vllm/v1/sample/sampler.py ``apply_logits_bias`` / ``apply_allowed_token_ids`` / ``apply_bad_words``,
+        # vllm/v1/sample/logits_processor.py ``MinTokensLogitsProcessor``)
+        if sp.logit_bias:
+            ids = torch.as_tensor([t for t in sp.logit_bias if 0 <= t < V], dtype=torch.long, device=logits.device)
+            vals = torch.as_tensor([sp.logit_bias[int(t)] for t in ids.tolist()], dtype=logits.dtype, device=logits.device)
+            logits[i, ids] += vals
+        if sp.allowed_token_ids is not None:
+            keep = torch.as_tensor([t for t in sp.allowed_token_ids if 0 <= t < V], dtype=torch.long, device=logits.device)
+            masked = torch.full_like(logits[i], float("-inf"))
+            masked[keep] = logits[i, keep]
+            logits[i] = masked
+        if sp.bad_words_token_ids:
+            hist = list(output_tokens[i])
+            for word in sp.bad_words_token_ids:
+                prefix, last = word[:-1], word[-1]
+                # the last token of a bad word is banned when the tokens generated so far end with its prefix
+                if 0 <= last < V and (not prefix or (len(hist) >= len(prefix) and hist[-len(prefix):] == list(prefix))):
+                    logits[i, last] = float("-inf")
+        if sp.min_tokens > 0 and len(output_tokens[i]) < sp.min_tokens:
+            stops = [t for t in ([sp.eos_token_id] if sp.eos_token_id is not None else []) + list(sp.stop_token_ids)
+                     if 0 <= t < V]
+            if stops:
+                logits[i, torch.as_tensor(stops, dtype=torch.long, device=logits.device)] = float("-inf")
     return logits
 
 

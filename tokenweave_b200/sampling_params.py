@@ -24,8 +24,18 @@ class SamplingParams:
     logprobs: Optional[int] = None
     detokenize: bool = True
     skip_special_tokens: bool = True
+    logit_bias: Optional[dict] = None                   # token id -> additive bias (clamped to [-100, 100])
+    allowed_token_ids: Optional[list[int]] = None       # every other token is masked out
+    bad_words_token_ids: Optional[list[list[int]]] = None   # token sequences that must not be generated
+    eos_token_id: Optional[int] = None                  # filled in by the engine; masked while below min_tokens
 
     def __post_init__(self):
+        if self.logit_bias is not None:
+            self.logit_bias = {int(k): max(-100.0, min(100.0, float(v))) for k, v in self.logit_bias.items()}
+        if self.allowed_token_ids is not None and not self.allowed_token_ids:
+            raise ValueError("allowed_token_ids must not be empty")
+        if self.bad_words_token_ids is not None and any(len(w) == 0 for w in self.bad_words_token_ids):
+            raise ValueError("bad_words_token_ids must not contain empty sequences")
         if isinstance(self.stop, str):
             self.stop = [self.stop]
         self.stop = list(self.stop or [])
@@ -47,7 +57,10 @@ class SamplingParams:
 
     @property
     def needs_penalties(self) -> bool:
-        return (self.presence_penalty != 0.0 or self.frequency_penalty != 0.0 or self.repetition_penalty != 1.0)
+        """True when the logits must be edited before sampling (penalties, biases, masks)."""
+        return (self.presence_penalty != 0.0 or self.frequency_penalty != 0.0 or self.repetition_penalty != 1.0
+                or bool(self.logit_bias) or self.allowed_token_ids is not None or bool(self.bad_words_token_ids)
+                or self.min_tokens > 0)
 
     def clone(self) -> "SamplingParams":
         import copy
