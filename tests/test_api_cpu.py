@@ -126,3 +126,21 @@ def test_min_tokens_masks_eos_and_allowed_token_ids_restrict_generation():
                                                  allowed_token_ids=[10, 11, 12]))[0].outputs[0].token_ids
     assert set(only) <= {10, 11, 12}
     llm.shutdown()
+
+
+def test_guided_choice_generates_exactly_one_of_the_choices():
+    from tokenweave_b200 import LLM
+    llm = LLM("tiny-llama", dtype="float32", device="cpu", block_size=16, max_num_batched_tokens=128, seed=7)   # byte tokenizer
+    choices = ["yes", "no", "maybe", "yes please"]
+    for temp, seed in ((0.0, None), (1.0, 3), (1.0, 4), (1.5, 5)):
+        out = llm.generate(["Answer:"], SamplingParams(temperature=temp, seed=seed, max_tokens=32, guided_choice=choices))[0]
+        assert out.outputs[0].text in choices, out.outputs[0].text
+        assert out.outputs[0].finish_reason == "stop"
+    # token-id form without a tokenizer
+    raw = LLM("tiny-llama", dtype="float32", device="cpu", skip_tokenizer_init=True, block_size=16,
+              max_num_batched_tokens=128, seed=7)
+    ids = raw.generate([[1, 2, 3]], SamplingParams(temperature=0, max_tokens=8, ignore_eos=True,
+                                                   guided_choice_token_ids=[[5, 6, 7], [9, 9]]))[0].outputs[0].token_ids
+    assert ids in ([5, 6, 7], [9, 9])
+    llm.shutdown()
+    raw.shutdown()

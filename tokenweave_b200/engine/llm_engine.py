@@ -75,6 +75,14 @@ class LLMEngine:
                 sp.n = 1
                 if sp.seed is not None:
                     sp.seed = sp.seed + i
+            if sp.guided_choice and not sp.guided_choice_token_ids:
+                if self.tokenizer is None:
+                    raise ValueError("guided_choice needs a tokenizer (or pass guided_choice_token_ids)")
+                if sp is params:
+                    sp = params.clone()
+                sp.guided_choice_token_ids = [list(self.tokenizer.encode(c, add_special_tokens=False))
+                                              for c in sp.guided_choice]
+                sp.eos_token_id = self.eos_token_id
             if sp.min_tokens > 0 and sp.eos_token_id is None and not sp.ignore_eos:
                 if sp is params:
                     sp = params.clone()          # the caller's object stays untouched

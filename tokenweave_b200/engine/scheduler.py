@@ -222,6 +222,12 @@ class Scheduler:
                 return RequestStatus.FINISHED_STOPPED, None
             if last in sp.stop_token_ids:
                 return RequestStatus.FINISHED_STOPPED, last
+        if sp.guided_choice_token_ids:
+            out = req.output_token_ids
+            done = any(list(c) == out for c in sp.guided_choice_token_ids)
+            longer = any(len(c) > len(out) and list(c[:len(out)]) == out for c in sp.guided_choice_token_ids)
+            if done and not longer:
+                return RequestStatus.FINISHED_STOPPED, None      # the chosen string is complete
         if (sp.max_tokens is not None and n_out >= sp.max_tokens) or req.num_tokens >= self.config.max_model_len:
             return RequestStatus.FINISHED_LENGTH, None
         return None

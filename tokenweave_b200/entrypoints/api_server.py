@@ -25,7 +25,7 @@ logger = init_logger(__name__)
 
 _SAMPLING_FIELDS = ("n", "temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty",
                     "repetition_penalty", "seed", "stop", "stop_token_ids", "max_tokens", "min_tokens", "ignore_eos",
-                    "skip_special_tokens", "logit_bias", "allowed_token_ids", "bad_words_token_ids")
+                    "skip_special_tokens", "logit_bias", "allowed_token_ids", "bad_words_token_ids", "guided_choice")
 
 
 def sampling_params_from_request(body: dict, default_max_tokens: int = 16) -> SamplingParams:

@@ -57,6 +57,20 @@ def apply_penalties(logits: torch.Tensor, params: Sequence[SamplingParams], prom
                 # the last token of a bad word is banned when the tokens generated so far end with its prefix
                 if 0 <= last < V and (not prefix or (len(hist) >= len(prefix) and hist[-len(prefix):] == list(prefix))):
                     logits[i, last] = float("-inf")
+        if sp.guided_choice_token_ids:
+            # constrained to one of several token sequences: only the tokens that continue a still-possible
+            # choice are allowed; a completed choice that is a prefix of a longer one may also end (EOS)
+            hist = list(output_tokens[i])
+            n = len(hist)
+            alive = [c for c in sp.guided_choice_token_ids if len(c) >= n and list(c[:n]) == hist]
+            allowed = {int(c[n]) for c in alive if len(c) > n and 0 <= c[n] < V}
+            if any(len(c) == n for c in alive) and sp.eos_token_id is not None:
+                allowed.add(int(sp.eos_token_id))
+            if allowed:
+                keep = torch.as_tensor(sorted(allowed), dtype=torch.long, device=logits.device)
+                masked = torch.full_like(logits[i], float("-inf"))
+                masked[keep] = logits[i, keep]
+                logits[i] = masked
         if sp.min_tokens > 0 and len(output_tokens[i]) < sp.min_tokens:
             stops = [t for t in ([sp.eos_token_id] if sp.eos_token_id is not None else []) + list(sp.stop_token_ids)
                      if 0 <= t < V]

@@ -28,6 +28,11 @@ class SamplingParams:
     allowed_token_ids: Optional[list[int]] = None       # every other token is masked out
     bad_words_token_ids: Optional[list[list[int]]] = None   # token sequences that must not be generated
     eos_token_id: Optional[int] = None                  # filled in by the engine; masked while below min_tokens
+    # Constrained decoding to one of several strings (the "choice" mode of the reference's guided decoding,
+    # vllm/sampling_params.py ``GuidedDecodingParams.choice``): texts here, tokenised by the engine into
+    # ``guided_choice_token_ids``; generation stops when a choice is complete.
+    guided_choice: Optional[list[str]] = None
+    guided_choice_token_ids: Optional[list[list[int]]] = None
 
     def __post_init__(self):
         if self.logit_bias is not None:
@@ -60,7 +65,7 @@ class SamplingParams:
         """True when the logits must be edited before sampling (penalties, biases, masks)."""
         return (self.presence_penalty != 0.0 or self.frequency_penalty != 0.0 or self.repetition_penalty != 1.0
                 or bool(self.logit_bias) or self.allowed_token_ids is not None or bool(self.bad_words_token_ids)
-                or self.min_tokens > 0)
+                or self.min_tokens > 0 or bool(self.guided_choice_token_ids))
 
     def clone(self) -> "SamplingParams":
         import copy
