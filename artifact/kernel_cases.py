@@ -22,7 +22,7 @@ import torch  # noqa: E402
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["gemm", "gemm_swiglu", "gemm_fp8", "rmsnorm_quant_fp8", "attn_prefill", "attn_decode", "add_rmsnorm", "rope_kv",
-                                     "moe_router", "fused_local"])
+                                     "moe_router", "fused_local", "sample"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=4096)
@@ -45,7 +45,13 @@ def main() -> None:
     peaks = measured_peaks()
     flops = bytes_moved = 0
 
-    if args.case in ("gemm", "gemm_swiglu"):
+    if args.case == "sample":
+        B, V = 256, 128256          # a full decode batch over the Llama-3 vocabulary: 131 MB of fp32 logits
+        logits = torch.randn(B, V, device=dev) * 3
+        packed = ops.pack_sample_params([0.8] * B, [50] * B, [0.9] * B, [0.0] * B, range(B)).to(dev)
+        fn = lambda: ops.sample(logits, packed)
+        bytes_moved = B * V * 4 * 11          # the row is read 11 times (max, 4 + sum + 4 radix passes, draw), mostly from L2
+    elif args.case in ("gemm", "gemm_swiglu"):
         M, N, K = args.m, args.n, args.k
         a = torch.randn(M, K, device=dev).to(BF)
         sw = args.case == "gemm_swiglu"

@@ -77,7 +77,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
     for (int g = 0; g < DEC_GMAX; ++g) s[g] = 0.f;
     if (valid) {
       const uint4* kr = reinterpret_cast<const uint4*>(k_cache + row_off);
-#pragma unroll 4
+#pragma unroll 8
       for (int v = 0; v < D / 8; ++v) {
         const uint4 kv = kr[v];
         const uint32_t* ku = reinterpret_cast<const uint32_t*>(&kv);
@@ -109,19 +109,19 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
 #pragma unroll
       for (int e = 0; e < EPL; ++e) o[g][e] *= alpha;
     }
-    // values
+    // values: eight value rows are requested before the first is used, so that a warp keeps 2 KB of
+    // loads in flight instead of one 256-byte row (one dependent load per key left the kernel at a
+    // seventh of the memory bandwidth)
     const int n_keys = min(32, kv_len - ch * 32);
-    for (int kk = 0; kk < n_keys; ++kk) {
-      const long long off = __shfl_sync(0xffffffffu, row_off, kk);
+    auto accumulate = [&](uint2 vv, int kk) {
       float vf[EPL];
+      const float2 a = unpack_bf16x2(vv.x);
+      vf[0] = a.x;
+      vf[1] = a.y;
       if (EPL == 4) {
-        const uint2 vv = *reinterpret_cast<const uint2*>(v_cache + off + lane * 4);
-        const float2 a = unpack_bf16x2(vv.x), b = unpack_bf16x2(vv.y);
-        vf[0] = a.x; vf[1] = a.y; vf[2] = b.x; vf[3] = b.y;
-      } else {
-        const uint32_t vv = *reinterpret_cast<const uint32_t*>(v_cache + off + lane * 2);
-        const float2 a = unpack_bf16x2(vv);
-        vf[0] = a.x; vf[1] = a.y;
+        const float2 b = unpack_bf16x2(vv.y);
+        vf[2] = b.x;
+        vf[3] = b.y;
       }
 #pragma unroll
       for (int g = 0; g < DEC_GMAX; ++g) {
@@ -129,7 +129,23 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
 #pragma unroll
         for (int e = 0; e < EPL; ++e) o[g][e] += pg * vf[e];
       }
+    };
+    auto load_row = [&](int kk) {
+      const long long off = __shfl_sync(0xffffffffu, row_off, kk);
+      uint2 vv = make_uint2(0u, 0u);
+      if (EPL == 4) vv = *reinterpret_cast<const uint2*>(v_cache + off + lane * 4);
+      else vv.x = *reinterpret_cast<const uint32_t*>(v_cache + off + lane * 2);
+      return vv;
+    };
+    int kk = 0;
+    for (; kk + 8 <= n_keys; kk += 8) {
+      uint2 vv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) vv[u] = load_row(kk + u);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) accumulate(vv[u], kk + u);
     }
+    for (; kk < n_keys; ++kk) accumulate(load_row(kk), kk);
   }
 
   // merge the warps of the CTA
