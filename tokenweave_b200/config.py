@@ -217,6 +217,8 @@ class EngineConfig:
     disable_log_stats: bool = True
     enable_sleep_mode: bool = False       # weights and KV cache on the VMM allocator: LLM.sleep() frees their memory
     speculative: Any = None               # engine.spec_decode.SpecDecodeConfig (n-gram drafts for greedy requests)
+    enable_lora: bool = False             # serve requests through LoRA adapters (tokenweave_b200.lora)
+    max_loras: int = 8                    # adapters resident per worker (least recently used is evicted)
 
     def resolved_device(self) -> str:
         if self.device != "auto":
@@ -253,6 +255,8 @@ class EngineArgs:
     enable_sleep_mode: bool = False       # weights and KV cache on the VMM allocator: LLM.sleep() frees their memory
     # {"method": "ngram", "num_speculative_tokens": k, "prompt_lookup_max": n, "prompt_lookup_min": m}, or just k
     speculative_config: Any = None
+    enable_lora: bool = False
+    max_loras: int = 8
     # TokenWeave
     tokenweave_mode: str = "overlap"
     tokenweave_config: Optional[str] = None
@@ -301,7 +305,14 @@ class EngineArgs:
             load_format=load_format, quantization=self.quantization, seed=self.seed, device=self.device, enforce_eager=self.enforce_eager,
             tokenizer=self.tokenizer, skip_tokenizer_init=self.skip_tokenizer_init,
             disable_log_stats=self.disable_log_stats, enable_sleep_mode=self.enable_sleep_mode,
-            speculative=self._speculative())
+            speculative=self._speculative(), enable_lora=self._lora_checked(model), max_loras=self.max_loras)
+
+    def _lora_checked(self, model) -> bool:
+        if self.enable_lora and self.tokenweave_mode == "fused_gemm":
+            raise ValueError("LoRA deltas are applied after the base GEMMs: use tokenweave_mode overlap or fuse_only")
+        if self.enable_lora and self.quantization:
+            raise ValueError("LoRA on quantised base weights is not supported")
+        return self.enable_lora
 
     def _speculative(self):
         from .engine.spec_decode import SpecDecodeConfig

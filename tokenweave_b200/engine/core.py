@@ -62,7 +62,7 @@ class EngineCore:
             r = s.request
             if s.is_new:
                 step.new_requests.append(NewRequestData(r.request_id, r.all_token_ids, r.num_prompt_tokens,
-                                                        r.sampling_params, list(r.block_ids)))
+                                                        r.sampling_params, list(r.block_ids), r.lora_request))
                 new_blocks: list[int] = []
             else:
                 new_blocks = r.block_ids[self._sent_blocks.get(r.request_id, 0):]

@@ -77,10 +77,11 @@ class BlockPool:
         return True
 
 
-def block_hashes(token_ids: list[int], block_size: int) -> list[bytes]:
-    """Chained hash of every full block of a token sequence."""
+def block_hashes(token_ids: list[int], block_size: int, salt: bytes = b"") -> list[bytes]:
+    """Chained hash of every full block of a token sequence. ``salt`` separates sequences whose KV differs
+    for the same tokens (requests served through different LoRA adapters)."""
     out = []
-    prev = b""
+    prev = salt
     for i in range(0, len(token_ids) - block_size + 1, block_size):
         m = hashlib.sha256(prev)
         m.update(b",".join(str(t).encode() for t in token_ids[i:i + block_size]))
@@ -102,7 +103,7 @@ class KVCacheManager:
         blocks = []
         # never reuse the whole prompt: the last token must be recomputed to produce logits
         usable = (req.num_tokens - 1) // self.block_size
-        for h in block_hashes(req.all_token_ids, self.block_size)[:usable]:
+        for h in block_hashes(req.all_token_ids, self.block_size, req.cache_salt)[:usable]:
             b = self.pool.lookup(h)
             if b is None:
                 break
@@ -129,7 +130,7 @@ class KVCacheManager:
         if not self.enable_caching:
             return
         full = req.num_computed_tokens // self.block_size
-        for i, h in enumerate(block_hashes(req.all_token_ids[:full * self.block_size], self.block_size)):
+        for i, h in enumerate(block_hashes(req.all_token_ids[:full * self.block_size], self.block_size, req.cache_salt)):
             self.pool.cache_block(req.block_ids[i], h)
 
     def free(self, req: Request) -> None:

@@ -53,7 +53,10 @@ class LLMEngine:
         return cls(args.create_engine_config())
 
     # ---- requests ---------------------------------------------------------------------------
-    def add_request(self, request_id: str, prompt: Union[str, list[int], dict], params: SamplingParams) -> None:
+    def add_request(self, request_id: str, prompt: Union[str, list[int], dict], params: SamplingParams,
+                    lora_request=None) -> None:
+        if lora_request is not None and not self.config.enable_lora:
+            raise ValueError("pass enable_lora=True to serve LoRA adapters")
         text: Optional[str] = None
         if isinstance(prompt, dict):
             text = prompt.get("prompt")
@@ -88,7 +91,7 @@ class LLMEngine:
                     sp = params.clone()          # the caller's object stays untouched
                 sp.eos_token_id = self.eos_token_id     # the sampler masks it until min_tokens is reached
             cid = request_id if params.n == 1 else f"{i}_{request_id}"
-            child = Request(cid, list(ids), sp, eos_token_id=self.eos_token_id, prompt=text)
+            child = Request(cid, list(ids), sp, eos_token_id=self.eos_token_id, prompt=text, lora_request=lora_request)
             parent.children.append(child)
             detok = None
             if self.tokenizer is not None and params.detokenize:

@@ -40,6 +40,12 @@ class Request:
     num_computed_tokens: int = 0       # tokens whose KV is in the cache
     block_ids: list[int] = field(default_factory=list)
     spec_token_ids: list[int] = field(default_factory=list)   # drafts to verify in the next step
+    lora_request: Optional[object] = None                     # tokenweave_b200.lora.LoRARequest
+
+    @property
+    def cache_salt(self) -> bytes:
+        """Prefix-cache key component: KV computed under one adapter is not valid under another."""
+        return b"" if self.lora_request is None else f"lora{self.lora_request.lora_int_id}|".encode()
     stop_reason: Optional[object] = None
     first_scheduled_time: Optional[float] = None
     first_token_time: Optional[float] = None

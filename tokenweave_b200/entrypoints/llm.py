@@ -40,9 +40,11 @@ class LLM:
     # ---- generation ---------------------------------------------------------------------------
     def generate(self, prompts: Union[PromptType, Sequence[PromptType], None] = None,
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
-                 prompt_token_ids: Optional[Sequence[list[int]]] = None, use_tqdm: bool = False) -> list[RequestOutput]:
+                 prompt_token_ids: Optional[Sequence[list[int]]] = None, use_tqdm: bool = False,
+                 lora_request=None) -> list[RequestOutput]:
         """Generate completions; results come back in prompt order. A prompt is text, a list of token
-        ids, or ``{"prompt": ..., "prompt_token_ids": [...]}``."""
+        ids, or ``{"prompt": ..., "prompt_token_ids": [...]}``. ``lora_request``: a
+        :class:`tokenweave_b200.lora.LoRARequest` for all prompts, or one (or None) per prompt."""
         if prompts is None:
             if prompt_token_ids is None:
                 raise ValueError("give prompts or prompt_token_ids")
@@ -56,10 +58,13 @@ class LLM:
             sampling_params = [sampling_params] * len(prompts)
         if len(sampling_params) != len(prompts):
             raise ValueError("one SamplingParams per prompt (or a single one for all)")
+        loras = lora_request if isinstance(lora_request, (list, tuple)) else [lora_request] * len(prompts)
+        if len(loras) != len(prompts):
+            raise ValueError("one LoRARequest per prompt (or a single one for all)")
         ids = []
-        for p, sp in zip(prompts, sampling_params):
+        for p, sp, lr in zip(prompts, sampling_params, loras):
             rid = str(next(self._counter))
-            self.llm_engine.add_request(rid, p, sp)
+            self.llm_engine.add_request(rid, p, sp, lora_request=lr)
             ids.append(rid)
         return self._run_engine(ids, use_tqdm)
 

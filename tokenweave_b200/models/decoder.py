@@ -101,12 +101,32 @@ class DecoderLayer(nn.Module):
             self.gate_up_proj = MergedColumnParallelLinear(H, [cfg.intermediate_size] * 2, False, dtype=dt, device=device)
             self.down_proj = RowParallelLinear(cfg.intermediate_size, H, False, dtype=dt, device=device)
 
+    layer_idx = 0        # set by the model; keys the LoRA weights of this layer
+
+    def _lora_segments(self, rows: torch.Tensor, n: int, rt: Runtime) -> list:
+        """Adapters used by the token rows of this block call (``rows`` is a view of the staging buffer, so
+        its offset tells which rows of the step it covers)."""
+        lora = getattr(rt, "lora", None)
+        if lora is None or not lora.active:
+            return []
+        row0 = (rows.data_ptr() - rt.hidden.data_ptr()) // (rt.hidden.stride(0) * rt.hidden.element_size())
+        return lora.segments(int(row0), n, rows.device)
+
     def attn_block(self, rows: torch.Tensor, n: int, meta: AttentionMetadata, rt: Runtime, max_ctas: int) -> None:
         """rows[:n] (normalised activations) -> this rank's partial o_proj output, in place."""
         if n == 0:
             return
+        segs = self._lora_segments(rows, n, rt)
         qkv = self.qkv_proj(rows[:n], out=rt.qkv[:n], max_ctas=max_ctas)
+        if segs:
+            from ..lora import LoRAManager
+            LoRAManager.apply(segs, self.layer_idx, "qkv_proj", rows[:n], qkv)
         attn_out = self.attn(qkv, rt.cos_sin, meta, rt.attn_out[:n])
+        if segs:
+            # the o_proj output overwrites rows[:n], which is also nothing the delta needs: the delta reads attn_out
+            self.o_proj(attn_out, out=rows[:n], max_ctas=max_ctas)
+            LoRAManager.apply(segs, self.layer_idx, "o_proj", attn_out, rows[:n])
+            return
         self.o_proj(attn_out, out=rows[:n], max_ctas=max_ctas)
 
     # ---- the same blocks with every GEMM fused with its neighbouring collective ----
@@ -130,6 +150,16 @@ class DecoderLayer(nn.Module):
         if self.moe is not None:
             self.moe(rows[:n], out=rows[:n], max_ctas=max_ctas)
             return
+        segs = self._lora_segments(rows, n, rt)
+        if segs:
+            # the adapter's gate / up deltas go in before the activation, so the SwiGLU epilogue cannot be used
+            from ..lora import LoRAManager
+            gate_up = self.gate_up_proj(rows[:n], max_ctas=max_ctas)
+            LoRAManager.apply(segs, self.layer_idx, "gate_up_proj", rows[:n], gate_up)
+            act = ops.swiglu(gate_up, out=rt.act[:n])
+            self.down_proj(act, out=rows[:n], max_ctas=max_ctas)
+            LoRAManager.apply(segs, self.layer_idx, "down_proj", act, rows[:n])
+            return
         act = self.gate_up_proj.forward_swiglu(rows[:n], out=rt.act[:n], max_ctas=max_ctas)
         self.down_proj(act, out=rows[:n], max_ctas=max_ctas)
 
@@ -143,6 +173,8 @@ class DecoderModel(nn.Module):
         dt = cfg.dtype
         self.embed_tokens = VocabEmbedding(cfg.vocab_size, cfg.hidden_size, embedding_parallel, dtype=dt, device=device)
         self.layers = nn.ModuleList([DecoderLayer(cfg, device=device) for _ in range(cfg.num_layers)])
+        for i, layer in enumerate(self.layers):
+            layer.layer_idx = i
         self.norm_w = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dt, device=device), requires_grad=False)
         self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, dtype=dt, device=device)
         self.rt: Optional[Runtime] = None

@@ -37,6 +37,7 @@ class NewRequestData:
     num_prompt_tokens: int
     sampling_params: SamplingParams
     block_ids: list[int]
+    lora_request: Optional[object] = None        # tokenweave_b200.lora.LoRARequest
 
 
 @dataclass
@@ -66,6 +67,7 @@ class _CachedRequest:
     sampling_params: SamplingParams
     block_ids: list[int]
     generator: Optional[torch.Generator] = None
+    lora_id: int = 0
 
 
 class ModelRunner:
@@ -92,6 +94,7 @@ class ModelRunner:
         self.timing_events = None
         self.capture_logits = False          # tests: keep the fp32 logits of every step
         self.captured_logits: list = []
+        self.lora = None                     # LoRAManager when the engine was built with enable_lora
         self.capture_hidden = False          # pooling requests: keep the final-norm hidden row of every sampled position
         self.captured_hidden: dict = {}
         self._h2d_done = torch.cuda.Event() if pin else None   # guards reuse of the pinned staging buffers
@@ -119,6 +122,10 @@ class ModelRunner:
         with (weights_pool if weights_pool is not None else contextlib.nullcontext()):
             self.model = build_model(self.config, self.device, embedding_parallel)
         self.model.setup_runtime(self.max_tokens, self.config.tokenweave)
+        if self.config.enable_lora:
+            from ..lora import LoRAManager
+            self.lora = LoRAManager(self.model, self.config.max_loras)
+            self.model.rt.lora = self.lora
         logger.info("model %s ready on %s in %.1fs (%.2f GB of weights on this rank)", self.config.model.name,
                     self.device, time.monotonic() - t0,
                     sum(p.numel() * p.element_size() for p in self.model.parameters()) / 1e9)
@@ -146,7 +153,14 @@ class ModelRunner:
             if sp.seed is not None:
                 gen = torch.Generator(device=self.device)
                 gen.manual_seed(sp.seed)
-            self.requests[nr.req_id] = _CachedRequest(list(nr.token_ids), nr.num_prompt_tokens, sp, list(nr.block_ids), gen)
+            lora_id = 0
+            if nr.lora_request is not None:
+                if self.lora is None:
+                    raise RuntimeError("a request names a LoRA adapter but the engine was built without enable_lora")
+                self.lora.ensure_loaded(nr.lora_request)
+                lora_id = nr.lora_request.lora_int_id
+            self.requests[nr.req_id] = _CachedRequest(list(nr.token_ids), nr.num_prompt_tokens, sp, list(nr.block_ids), gen,
+                                                      lora_id)
 
     def _build_metadata(self, entries, tokens_base: int, positions: np.ndarray, slots: np.ndarray,
                         tables: dict[int, list[int]], which: int) -> AttentionMetadata:
@@ -224,6 +238,7 @@ class ModelRunner:
         row = 0
         bs = self.block_size
         spec: dict[str, list[int]] = {}          # request -> drafts verified in this step
+        row_lora: list[int] = []                 # adapter id of every token row (0 = none)
         for b, (rid, computed, n_new, new_blocks, *rest) in enumerate(step.scheduled):
             req = self.requests[rid]
             req.block_ids.extend(new_blocks)
@@ -245,7 +260,11 @@ class ModelRunner:
                 for k in range(len(drafts) + 1):
                     logits_rows.append(row + n_base - 1 + k)
                     sample_reqs.append(rid)
+            if self.lora is not None:
+                row_lora.extend([req.lora_id] * n_new)
             row += n_new
+        if self.lora is not None:
+            self.lora.set_batch(row_lora)
 
         plan = self.planner.plan(T)
         ids_dev = self._ids_dev[:T]
@@ -276,7 +295,8 @@ class ModelRunner:
         if n_logits:
             self._rows_host[:n_logits] = torch.as_tensor(logits_rows, dtype=torch.long)
             self._rows_dev[:n_logits].copy_(self._rows_host[:n_logits], non_blocking=True)
-        if self.use_graphs and not self.capture_logits and not self.capture_hidden:
+        lora_active = self.lora is not None and self.lora.active      # row gathers of a step are not graph-stable
+        if self.use_graphs and not self.capture_logits and not self.capture_hidden and not lora_active:
             logits, greedy_ids = self._run_graphed(self._signature(step_in, n_logits, greedy), step_in, n_logits, greedy)
         else:
             logits, greedy_ids = self._forward_and_logits(step_in, n_logits, greedy)
