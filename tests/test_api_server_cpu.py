@@ -103,6 +103,30 @@ def test_bad_requests_are_rejected_and_the_server_keeps_serving(client):
     assert m.status_code == 200 and "tokenweave:generation_tokens_total" in m.text
 
 
+def test_adapter_selected_by_model_name(tmp_path):
+    from starlette.testclient import TestClient
+    from tokenweave_b200.config import MODEL_PRESETS, ModelConfig
+    from tokenweave_b200.entrypoints.api_server import build_app
+    from test_lora_cpu import _make_adapter
+    from tw_testing import make_hf_state
+    cfg = ModelConfig(name="tiny-llama", **MODEL_PRESETS["tiny-llama"])
+    _make_adapter(str(tmp_path / "ad"), cfg, make_hf_state(cfg, seed=0), r=4, alpha=64, seed=3)
+    eng = AsyncLLMEngine.from_engine_args(EngineArgs(model="tiny-llama", dtype="float32", device="cpu", block_size=16,
+                                                     max_num_batched_tokens=128, seed=1, enable_lora=True))
+    try:
+        with TestClient(build_app(eng, "tiny", {"tiny-ad": str(tmp_path / "ad")})) as c:
+            assert [m["id"] for m in c.get("/v1/models").json()["data"]] == ["tiny", "tiny-ad"]
+            body = {"prompt": "hello world", "max_tokens": 8, "temperature": 0, "ignore_eos": True, "logprobs": 1}
+            base = c.post("/v1/completions", json={**body, "model": "tiny"}).json()["choices"][0]
+            ad = c.post("/v1/completions", json={**body, "model": "tiny-ad"}).json()["choices"][0]
+            assert ad["logprobs"]["token_logprobs"] != base["logprobs"]["token_logprobs"]
+            again = c.post("/v1/completions", json={**body, "model": "tiny"}).json()["choices"][0]
+            assert again["logprobs"]["token_logprobs"] == base["logprobs"]["token_logprobs"]
+            assert c.post("/v1/completions", json={**body, "model": "nobody"}).status_code == 400
+    finally:
+        eng.shutdown()
+
+
 def test_async_engine_abort_frees_the_request(engine):
     async def run():
         agen = engine.generate([1, 2, 3, 4], SamplingParams(temperature=0, max_tokens=10_000, ignore_eos=True), "abort-me")

@@ -12,6 +12,9 @@ def __getattr__(name):
     if name == "LLM":
         from .entrypoints.llm import LLM
         return LLM
+    if name == "LoRARequest":
+        from .lora import LoRARequest
+        return LoRARequest
     if name == "EngineArgs":
         from .config import EngineArgs
         return EngineArgs

@@ -58,13 +58,13 @@ class AsyncLLMEngine:
                 drained = False
                 while True:
                     try:
-                        kind, rid, prompt, params = self._inbox.get_nowait()
+                        kind, rid, prompt, params, lora = self._inbox.get_nowait()
                     except queue.Empty:
                         break
                     drained = True
                     if kind == "add":
                         try:
-                            self.engine.add_request(rid, prompt, params)
+                            self.engine.add_request(rid, prompt, params, lora_request=lora)
                         except Exception as e:      # bad request: report to its caller, keep serving
                             self._deliver(rid, e)
                     else:
@@ -89,7 +89,7 @@ class AsyncLLMEngine:
         return self._thread.is_alive() and self._dead is None
 
     async def generate(self, prompt: Union[str, list[int], dict], params: SamplingParams,
-                       request_id: str) -> AsyncIterator[RequestOutput]:
+                       request_id: str, lora_request=None) -> AsyncIterator[RequestOutput]:
         """Yields a snapshot of the request after every engine step that touched it; the last one has
         ``finished`` set. Cancelling the consumer aborts the request."""
         if self._dead is not None:
@@ -100,7 +100,7 @@ class AsyncLLMEngine:
             if request_id in self._streams:
                 raise ValueError(f"request id {request_id} is already in flight")
             self._streams[request_id] = (loop, q)
-        self._inbox.put(("add", request_id, prompt, params))
+        self._inbox.put(("add", request_id, prompt, params, lora_request))
         self._wake.set()
         finished = False
         try:
@@ -117,11 +117,11 @@ class AsyncLLMEngine:
             with self._lock:
                 self._streams.pop(request_id, None)
             if not finished:
-                self._inbox.put(("abort", request_id, None, None))
+                self._inbox.put(("abort", request_id, None, None, None))
                 self._wake.set()
 
     async def abort(self, request_id: str) -> None:
-        self._inbox.put(("abort", request_id, None, None))
+        self._inbox.put(("abort", request_id, None, None, None))
         self._wake.set()
 
     def shutdown(self) -> None:

@@ -57,14 +57,30 @@ def _logprobs_block(comp, tokenizer) -> Optional[dict]:
     return {"tokens": toks, "token_logprobs": chosen, "top_logprobs": top}
 
 
-def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None):
+def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
+              lora_modules: Optional[dict] = None):
+    """``lora_modules`` maps a served adapter name to its directory: a request whose ``model`` field is
+    such a name runs through that adapter (``--lora-modules name=path`` of the reference's server,
+    vllm/entrypoints/openai/serving_models.py)."""
     from fastapi import FastAPI, Request
     from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+    from ..lora import LoRARequest
 
     app = FastAPI(title="tokenweave_b200")
     model_cfg = engine.engine.config.model
     name = served_model_name or model_cfg.name
     tokenizer = engine.engine.tokenizer
+    adapters = {n: LoRARequest(n, i + 1, path) for i, (n, path) in enumerate((lora_modules or {}).items())}
+
+    def pick_adapter(body: dict):
+        """The adapter a request names in ``model`` (None for the base model); unknown names are an error."""
+        m = body.get("model")
+        if m in adapters:
+            return adapters[m]
+        if m is None or not adapters or m == name or m == model_cfg.name:
+            return None         # a server without adapters answers every model name with its one model
+        raise ValueError(f"model {m!r} is not served (base model: {name!r}, adapters: {sorted(adapters)})")
     prom = None
     try:
         from ..utils.metrics import PrometheusStatLogger
@@ -88,8 +104,9 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None):
 
     @app.get("/v1/models")
     async def models():
-        return {"object": "list", "data": [{"id": name, "object": "model", "created": int(time.time()),
-                                            "owned_by": "tokenweave_b200", "max_model_len": model_cfg.max_model_len}]}
+        card = lambda i, parent: {"id": i, "object": "model", "created": int(time.time()), "owned_by": "tokenweave_b200",  # noqa: E731
+                                  "parent": parent, "max_model_len": model_cfg.max_model_len}
+        return {"object": "list", "data": [card(name, None)] + [card(a, name) for a in adapters]}
 
     @app.get("/metrics")
     async def metrics():
@@ -113,12 +130,12 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None):
             return error(400, "the server runs without a tokenizer")
         return {"prompt": tokenizer.decode(body.get("tokens", []))}
 
-    async def run_all(prompts: list, sp: SamplingParams, base_id: str) -> list[RequestOutput]:
+    async def run_all(prompts: list, sp: SamplingParams, base_id: str, lora=None) -> list[RequestOutput]:
         import asyncio
 
         async def one(i, p):
             last = None
-            async for out in engine.generate(p, sp, f"{base_id}-{i}"):
+            async for out in engine.generate(p, sp, f"{base_id}-{i}", lora_request=lora):
                 last = out
             finished_metrics(last)
             return last
@@ -140,6 +157,7 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None):
         try:
             prompts = normalise_prompts(body.get("prompt"))
             sp = sampling_params_from_request(body)
+            lora = pick_adapter(body)
             if tokenizer is None:
                 sp.detokenize = False
                 if any(isinstance(p, str) for p in prompts):
@@ -161,7 +179,7 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None):
             async def sse() -> AsyncIterator[str]:
                 sent = {}
                 try:
-                    async for out in engine.generate(prompts[0], sp, rid + "-0"):
+                    async for out in engine.generate(prompts[0], sp, rid + "-0", lora_request=lora):
                         for comp in out.outputs:
                             prev = sent.get(comp.index, 0)
                             delta = comp.text[prev:]
@@ -180,7 +198,7 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None):
             return StreamingResponse(sse(), media_type="text/event-stream")
 
         try:
-            outs = await run_all(prompts, sp, rid)
+            outs = await run_all(prompts, sp, rid, lora)
         except ValueError as e:
             return error(400, str(e))
         except EngineDeadError as e:
@@ -214,6 +232,7 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None):
         try:
             sp = sampling_params_from_request(body, default_max_tokens=256)
             prompt = chat_prompt(msgs, body.get("add_generation_prompt", True))
+            lora = pick_adapter(body)
         except (ValueError, TypeError, KeyError) as e:
             return error(400, str(e))
         rid = "chatcmpl-" + uuid.uuid4().hex
@@ -223,7 +242,7 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None):
                 sent = {}
                 first = True
                 try:
-                    async for out in engine.generate(prompt, sp, rid):
+                    async for out in engine.generate(prompt, sp, rid, lora_request=lora):
                         for comp in out.outputs:
                             prev = sent.get(comp.index, 0)
                             delta = comp.text[prev:]
@@ -243,7 +262,7 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None):
                 yield "data: [DONE]\n\n"
             return StreamingResponse(sse(), media_type="text/event-stream")
         try:
-            out = (await run_all([prompt], sp, rid))[0]
+            out = (await run_all([prompt], sp, rid, lora))[0]
         except ValueError as e:
             return error(400, str(e))
         except EngineDeadError as e:
@@ -261,15 +280,20 @@ def main() -> None:
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--served-model-name", default=None)
+    ap.add_argument("--lora-modules", nargs="*", default=[], metavar="NAME=PATH",
+                    help="adapters to serve; a request selects one by its name in the model field (needs --enable-lora)")
     EngineArgs.add_cli_args(ap)
     ns = ap.parse_args()
     args = EngineArgs.from_cli_args(ns)
+    lora_modules = dict(m.split("=", 1) for m in ns.lora_modules)
+    if lora_modules:
+        args.enable_lora = True
     if args.tensor_parallel_size > 1 and args.distributed_executor_backend == "auto":
         args.distributed_executor_backend = "mp"
     engine = AsyncLLMEngine.from_engine_args(args)
     import uvicorn
     try:
-        uvicorn.run(build_app(engine, ns.served_model_name), host=ns.host, port=ns.port, log_level="info")
+        uvicorn.run(build_app(engine, ns.served_model_name, lora_modules), host=ns.host, port=ns.port, log_level="info")
     finally:
         engine.shutdown()
 
