@@ -27,7 +27,48 @@ def _prompts(vocab, lens, seed=0):
     return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
 
 
-@pytest.mark.parametrize("arch", ["tiny-llama", "tiny-qwen2", "tiny-mixtral"])
+def test_phi3_packed_checkpoint_and_mistral_config(tmp_path):
+    """Phi-3 stores the fused qkv / gate_up tensors; Mistral brings a sliding window and (newer configs) the
+    rope settings under ``rope_parameters``. Both must load into the shared decoder and match the naive model."""
+    preset = dict(MODEL_PRESETS["tiny-llama"], architecture="phi3", rope_theta=10000.0)
+    cfg = ModelConfig(name="tiny-phi3", **preset)
+    st = make_hf_state(cfg, seed=4)
+    packed = {k: v for k, v in st.items() if not any(s in k for s in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj"))}
+    for l in range(cfg.num_layers):
+        p = f"model.layers.{l}."
+        packed[p + "self_attn.qkv_proj.weight"] = torch.cat([st[p + f"self_attn.{n}_proj.weight"] for n in "qkv"], 0)
+        packed[p + "mlp.gate_up_proj.weight"] = torch.cat([st[p + "mlp.gate_proj.weight"], st[p + "mlp.up_proj.weight"]], 0)
+    save_hf_checkpoint(packed, hf_config_dict(cfg), str(tmp_path / "phi3"))
+    prompts = _prompts(cfg.vocab_size, [40, 9])
+    llm = _engine(str(tmp_path / "phi3"))
+    assert llm.llm_engine.config.model.architecture == "phi3"
+    r = _runner(llm)
+    r.capture_logits = True
+    llm.generate(prompts, SamplingParams(temperature=0, max_tokens=1))
+    got = {rid: row for reqs, logits in r.captured_logits for rid, row in zip(reqs, logits)}
+    for i, p in enumerate(prompts):
+        torch.testing.assert_close(got[str(i)], naive_logits(cfg, st, p)[-1], atol=2e-4, rtol=2e-4)
+    llm.shutdown()
+
+    mcfg = ModelConfig(name="tiny-mistral", **dict(MODEL_PRESETS["tiny-llama"], architecture="mistral", rope_theta=1e6))
+    hf = hf_config_dict(mcfg)
+    del hf["rope_theta"]
+    hf.update(rope_parameters={"rope_type": "default", "rope_theta": 1e6}, sliding_window=256, max_position_embeddings=2048)
+    mst = make_hf_state(mcfg, seed=6)
+    save_hf_checkpoint(mst, hf, str(tmp_path / "mistral"))
+    llm = _engine(str(tmp_path / "mistral"))
+    m = llm.llm_engine.config.model
+    assert (m.architecture, m.rope_theta, m.max_model_len) == ("mistral", 1e6, 256)
+    r = _runner(llm)
+    r.capture_logits = True
+    llm.generate(prompts, SamplingParams(temperature=0, max_tokens=1))
+    got = {rid: row for reqs, logits in r.captured_logits for rid, row in zip(reqs, logits)}
+    for i, p in enumerate(prompts):
+        torch.testing.assert_close(got[str(i)], naive_logits(mcfg, mst, p)[-1], atol=2e-4, rtol=2e-4)
+    llm.shutdown()
+
+
+@pytest.mark.parametrize("arch", ["tiny-llama", "tiny-qwen2", "tiny-mixtral", "tiny-qwen3"])
 def test_engine_matches_naive_forward(tmp_path, arch):
     preset = dict(MODEL_PRESETS[arch])
     if arch != "tiny-llama":

@@ -108,6 +108,32 @@ def test_rope_kv_write(hq, hkv, D, page):
     assert torch.equal(vc, vc2)
 
 
+@pytest.mark.parametrize("hq,hkv,D", [(8, 2, 128), (5, 1, 64), (2, 2, 256)])
+def test_rope_kv_write_with_qk_norm(hq, hkv, D):
+    """Per-head RMSNorm of q and k inside the rope + cache-write launch (Qwen3 layout)."""
+    T, blocks, page = 77, 8, 16
+    qkv = rnd(T, (hq + 2 * hkv) * D) * 3
+    pos = torch.randint(0, 4000, (T,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(blocks * page, device=DEV)[:T].to(torch.int32)
+    cs = ref.build_cos_sin_cache(D, 4096, 1e6, device=DEV)
+    qw, kw = (1 + 0.3 * torch.randn(D, device=DEV)).to(BF), (1 + 0.3 * torch.randn(D, device=DEV)).to(BF)
+    kc, vc = torch.zeros(blocks, page, hkv, D, device=DEV, dtype=BF), torch.zeros(blocks, page, hkv, D, device=DEV, dtype=BF)
+    kc2, vc2 = kc.clone(), vc.clone()
+    q1, q2 = qkv.clone(), qkv.clone()
+    ops.rope_kv_write_(q1, pos, slots, cs, kc, vc, hq, hkv, D, write_k_back=True, qk_norm=(qw, kw, 1e-6))
+    ref.rope_kv_write_(q2, pos, slots, cs, kc2, vc2, hq, hkv, D, qk_norm=(qw, kw, 1e-6))
+    close(q1, q2, atol=3e-2)
+    close(kc, kc2, atol=3e-2)
+    assert torch.equal(vc, vc2)
+    # and against the unrounded fp32 definition: normalise, scale, rotate
+    x = qkv[:, : (hq + hkv) * D].float().view(T, hq + hkv, D)
+    w = torch.cat([qw.float().expand(hq, D), kw.float().expand(hkv, D)], 0)
+    x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    c, s = cs[pos.long(), : D // 2].unsqueeze(1), cs[pos.long(), D // 2:].unsqueeze(1)
+    want = torch.cat([x[..., : D // 2] * c - x[..., D // 2:] * s, x[..., D // 2:] * c + x[..., : D // 2] * s], -1)
+    close(q1[:, : (hq + hkv) * D].float().view(T, hq + hkv, D), want, atol=6e-2)
+
+
 def test_swiglu_embedding_argmax():
     x = rnd(300, 2 * 3584)
     close(ops.swiglu(x), ref.swiglu(x))

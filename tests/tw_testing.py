@@ -38,6 +38,9 @@ def make_hf_state(cfg, seed=0, dtype=torch.float32):
             st[p + "self_attn.q_proj.bias"] = r(cfg.num_q_heads * D)
             st[p + "self_attn.k_proj.bias"] = r(cfg.num_kv_heads * D)
             st[p + "self_attn.v_proj.bias"] = r(cfg.num_kv_heads * D)
+        if getattr(cfg, "qk_norm", False):
+            st[p + "self_attn.q_norm.weight"] = (1 + 0.2 * torch.randn(D, generator=g)).to(dtype)
+            st[p + "self_attn.k_norm.weight"] = (1 + 0.2 * torch.randn(D, generator=g)).to(dtype)
         if cfg.num_experts:
             st[p + "block_sparse_moe.gate.weight"] = r(cfg.num_experts, H)
             for e in range(cfg.num_experts):
@@ -52,7 +55,8 @@ def make_hf_state(cfg, seed=0, dtype=torch.float32):
 
 
 def hf_config_dict(cfg):
-    arch = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "mixtral": "MixtralForCausalLM"}[cfg.architecture]
+    arch = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "mixtral": "MixtralForCausalLM",
+            "qwen3": "Qwen3ForCausalLM", "mistral": "MistralForCausalLM", "phi3": "Phi3ForCausalLM"}[cfg.architecture]
     d = dict(architectures=[arch], hidden_size=cfg.hidden_size, num_hidden_layers=cfg.num_layers,
              num_attention_heads=cfg.num_q_heads, num_key_value_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
              intermediate_size=cfg.intermediate_size, vocab_size=cfg.vocab_size, rms_norm_eps=cfg.rms_norm_eps,
@@ -87,8 +91,10 @@ def naive_logits(cfg, st, ids):
         if cfg.qkv_bias:
             q, k, v = (q + st[p + "self_attn.q_proj.bias"].float(), k + st[p + "self_attn.k_proj.bias"].float(),
                        v + st[p + "self_attn.v_proj.bias"].float())
-        q = rope(q.view(T, cfg.num_q_heads, D))
-        k = rope(k.view(T, cfg.num_kv_heads, D))
+        q, k = q.view(T, cfg.num_q_heads, D), k.view(T, cfg.num_kv_heads, D)
+        if getattr(cfg, "qk_norm", False):
+            q, k = norm(q, st[p + "self_attn.q_norm.weight"]), norm(k, st[p + "self_attn.k_norm.weight"])
+        q, k = rope(q), rope(k)
         v = v.view(T, cfg.num_kv_heads, D)
         rep = cfg.num_q_heads // cfg.num_kv_heads
         k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)

@@ -25,7 +25,7 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 class ModelConfig:
     """Architecture of a decoder-only transformer (Llama-3.x, Qwen2.5, Mixtral layouts)."""
     name: str = "tiny-llama"
-    architecture: str = "llama"          # "llama" | "qwen2" | "mixtral"
+    architecture: str = "llama"          # "llama" | "qwen2" | "mixtral" | "qwen3" | "mistral" | "phi3"
     hidden_size: int = 256
     num_layers: int = 2
     num_q_heads: int = 4
@@ -37,6 +37,7 @@ class ModelConfig:
     rope_theta: float = 500000.0
     rope_scaling: Optional[dict] = None
     qkv_bias: bool = False
+    qk_norm: bool = False                # RMSNorm over head_dim on every q and k head before rope (Qwen3)
     num_experts: int = 0                 # 0 = dense MLP
     num_experts_per_tok: int = 2
     max_model_len: int = 8192
@@ -62,23 +63,39 @@ class ModelConfig:
     def from_hf_dict(cfg: dict, name: str = "", path: Optional[str] = None) -> "ModelConfig":
         archs = cfg.get("architectures") or [cfg.get("model_type", "llama")]
         a = archs[0].lower()
-        arch = "mixtral" if "mixtral" in a else "qwen2" if "qwen2" in a else "llama"
+        if any(k in a for k in ("moe", "vl", "omni", "audio")) and "mixtral" not in a:
+            raise ValueError(f"unsupported architecture {archs[0]!r}")
+        arch = ("mixtral" if "mixtral" in a else "qwen3" if "qwen3" in a else "qwen2" if "qwen2" in a
+                else "phi3" if "phi3" in a else "mistral" if "mistral" in a else "llama")
         heads = cfg["num_attention_heads"]
         head_dim = cfg.get("head_dim") or cfg["hidden_size"] // heads
-        dt = _DTYPES.get(str(cfg.get("torch_dtype", "bfloat16")), torch.bfloat16) or torch.bfloat16
+        dt = _DTYPES.get(str(cfg.get("torch_dtype", cfg.get("dtype", "bfloat16"))), torch.bfloat16) or torch.bfloat16
         eos = cfg.get("eos_token_id")
         if isinstance(eos, list):
             eos = eos[0]
+        # newer Hugging Face configs keep theta and the scaling rule together under "rope_parameters"
+        rp = dict(cfg.get("rope_parameters") or {})
+        if rp:
+            cfg = dict(cfg)
+            cfg.setdefault("rope_theta", rp.pop("rope_theta", None) or (1e6 if arch != "llama" else 10000.0))
+            if rp.get("rope_type", "default") != "default":
+                cfg.setdefault("rope_scaling", rp)
+        max_len = cfg.get("max_position_embeddings", 8192)
+        window = cfg.get("sliding_window")
+        if window and cfg.get("use_sliding_window", True) and window < max_len:
+            # no sliding-window attention kernel: serve the span in which full and windowed attention agree
+            max_len = int(window)
         return ModelConfig(
             name=name or cfg.get("_name_or_path", arch), architecture=arch, hidden_size=cfg["hidden_size"],
             num_layers=cfg["num_hidden_layers"], num_q_heads=heads,
             num_kv_heads=cfg.get("num_key_value_heads", heads), head_dim=head_dim,
             intermediate_size=cfg["intermediate_size"], vocab_size=cfg["vocab_size"],
-            rms_norm_eps=cfg.get("rms_norm_eps", 1e-6 if arch == "qwen2" else 1e-5),
-            rope_theta=cfg.get("rope_theta", 1e6 if arch in ("qwen2", "mixtral") else 10000.0),
+            rms_norm_eps=cfg.get("rms_norm_eps", 1e-6 if arch in ("qwen2", "qwen3") else 1e-5),
+            rope_theta=cfg.get("rope_theta") or (1e6 if arch in ("qwen2", "qwen3", "mixtral") else 10000.0),
             rope_scaling=cfg.get("rope_scaling"), qkv_bias=cfg.get("attention_bias", arch == "qwen2"),
+            qk_norm=arch == "qwen3",
             num_experts=cfg.get("num_local_experts", 0), num_experts_per_tok=cfg.get("num_experts_per_tok", 2),
-            max_model_len=cfg.get("max_position_embeddings", 8192),
+            max_model_len=max_len,
             tie_word_embeddings=cfg.get("tie_word_embeddings", False), dtype=dt, eos_token_id=eos, path=path)
 
     @staticmethod
@@ -106,6 +123,18 @@ MODEL_PRESETS: dict[str, dict[str, Any]] = {
     "tiny-mixtral": dict(architecture="mixtral", hidden_size=512, num_layers=2, num_q_heads=4, num_kv_heads=2,
                          head_dim=128, intermediate_size=512, vocab_size=2048, rms_norm_eps=1e-5, rope_theta=1e6,
                          num_experts=8, num_experts_per_tok=2, max_model_len=4096),
+    "tiny-qwen3": dict(architecture="qwen3", hidden_size=512, num_layers=2, num_q_heads=4, num_kv_heads=2,
+                       head_dim=128, intermediate_size=1024, vocab_size=2048, rms_norm_eps=1e-6,
+                       rope_theta=1e6, qk_norm=True, max_model_len=4096),
+    "qwen3-32b": dict(architecture="qwen3", hidden_size=5120, num_layers=64, num_q_heads=64, num_kv_heads=8,
+                      head_dim=128, intermediate_size=25600, vocab_size=151936, rms_norm_eps=1e-6,
+                      rope_theta=1e6, qk_norm=True, max_model_len=40960),
+    "mistral-large-2": dict(architecture="mistral", hidden_size=12288, num_layers=88, num_q_heads=96, num_kv_heads=8,
+                            head_dim=128, intermediate_size=28672, vocab_size=32768, rms_norm_eps=1e-5,
+                            rope_theta=1e6, max_model_len=131072),
+    "phi-3-medium-4k": dict(architecture="phi3", hidden_size=5120, num_layers=40, num_q_heads=40, num_kv_heads=10,
+                            head_dim=128, intermediate_size=17920, vocab_size=32064, rms_norm_eps=1e-5,
+                            rope_theta=10000.0, max_model_len=4096),
     "llama-3.3-70b": dict(architecture="llama", hidden_size=8192, num_layers=80, num_q_heads=64, num_kv_heads=8,
                           head_dim=128, intermediate_size=28672, vocab_size=128256, rms_norm_eps=1e-5,
                           rope_theta=500000.0, max_model_len=131072,

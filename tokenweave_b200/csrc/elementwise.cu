@@ -33,11 +33,18 @@ __device__ __forceinline__ void rotate8(const uint4& x, const uint4& y, const fl
 // qkv: [T, (hq + 2*hkv) * D] (row stride ld). cos_sin: [max_pos, D] fp32, cos in the first
 // D/2 columns, sin in the last D/2. Caches: [num_slots, hkv, D]; slot < 0 skips the write.
 // Rows >= num_actual are left untouched (padding rows of a split).
+// QKNORM: q and k heads are RMS-normalised over D (weights q_norm_w / k_norm_w, [D]) before the rotation,
+// the per-head norm of the Qwen3 layout. The D/16 threads that share a head are neighbouring lanes of one
+// warp (the item index is head-major and D/16 is a power of two that divides the block size), so the sum
+// of squares is a shuffle reduction inside that lane group.
+template <bool QKNORM>
 __global__ void __launch_bounds__(256)
 rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, const int* __restrict__ positions,
                      const int* __restrict__ slots, const float* __restrict__ cos_sin,
                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                     int hq, int hkv, int D, int write_k_back) {
+                     int hq, int hkv, int D, int write_k_back,
+                     const __nv_bfloat16* __restrict__ q_norm_w, const __nv_bfloat16* __restrict__ k_norm_w,
+                     float eps) {
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int slot = (slots != nullptr) ? slots[t] : -1;
@@ -54,6 +61,34 @@ rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, const int* _
       __nv_bfloat16* h = row + head * D;
       uint4 x = *reinterpret_cast<const uint4*>(h + v * 8);
       uint4 y = *reinterpret_cast<const uint4*>(h + half + v * 8);
+      if constexpr (QKNORM) {
+        uint32_t* xu = reinterpret_cast<uint32_t*>(&x);
+        uint32_t* yu = reinterpret_cast<uint32_t*>(&y);
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = unpack_bf16x2(xu[j]);
+          const float2 b = unpack_bf16x2(yu[j]);
+          ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+        }
+        const int lane = threadIdx.x & 31;
+        const uint32_t group = (vec_per_half >= 32) ? 0xffffffffu
+                                                    : (((1u << vec_per_half) - 1u) << (lane & ~(vec_per_half - 1)));
+        for (int o = vec_per_half >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(group, ss, o);
+        const float r = rsqrtf(ss / static_cast<float>(D) + eps);
+        const __nv_bfloat16* w = (head < hq) ? q_norm_w : k_norm_w;
+        const uint4 wx = *reinterpret_cast<const uint4*>(w + v * 8);
+        const uint4 wy = *reinterpret_cast<const uint4*>(w + half + v * 8);
+        const uint32_t* wxu = reinterpret_cast<const uint32_t*>(&wx);
+        const uint32_t* wyu = reinterpret_cast<const uint32_t*>(&wy);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = unpack_bf16x2(xu[j]), wa = unpack_bf16x2(wxu[j]);
+          const float2 b = unpack_bf16x2(yu[j]), wb = unpack_bf16x2(wyu[j]);
+          xu[j] = pack_bf16x2(a.x * r * wa.x, a.y * r * wa.y);
+          yu[j] = pack_bf16x2(b.x * r * wb.x, b.y * r * wb.y);
+        }
+      }
       uint4 xo, yo;
       rotate8(x, y, cs + v * 8, cs + half + v * 8, xo, yo);
       if (head < hq) {
@@ -174,11 +209,29 @@ extern "C" int tw_rope_kv_write(void* qkv, long long ld, const int* positions, c
     set_last_error("rope_kv_write: head_dim must be a multiple of 16 and the row stride of 8");
     return 1;
   }
-  rope_kv_write_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(qkv), ld, positions, slots,
-                                               cos_sin, reinterpret_cast<__nv_bfloat16*>(k_cache),
-                                               reinterpret_cast<__nv_bfloat16*>(v_cache), hq, hkv, D,
-                                               write_k_back);
+  rope_kv_write_kernel<false><<<T, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(qkv), ld, positions, slots,
+                                                      cos_sin, reinterpret_cast<__nv_bfloat16*>(k_cache),
+                                                      reinterpret_cast<__nv_bfloat16*>(v_cache), hq, hkv, D,
+                                                      write_k_back, nullptr, nullptr, 0.f);
   return check_launch("rope_kv_write");
+}
+
+// The same with q and k heads RMS-normalised over head_dim before the rotation (Qwen3).
+extern "C" int tw_rope_kv_write_qknorm(void* qkv, long long ld, const int* positions, const int* slots,
+                                       const float* cos_sin, void* k_cache, void* v_cache, int T, int hq,
+                                       int hkv, int D, int write_k_back, const void* q_norm_w,
+                                       const void* k_norm_w, float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int vph = D >> 4;
+  if (D % 16 != 0 || ld % 8 != 0 || vph < 1 || vph > 32 || (vph & (vph - 1)) != 0 || !q_norm_w || !k_norm_w) {
+    set_last_error("rope_kv_write_qknorm: head_dim must be 16 * a power of two (<= 512), row stride a multiple of 8");
+    return 1;
+  }
+  rope_kv_write_kernel<true><<<T, 256, 0, stream>>>(
+      reinterpret_cast<__nv_bfloat16*>(qkv), ld, positions, slots, cos_sin, reinterpret_cast<__nv_bfloat16*>(k_cache),
+      reinterpret_cast<__nv_bfloat16*>(v_cache), hq, hkv, D, write_k_back,
+      reinterpret_cast<const __nv_bfloat16*>(q_norm_w), reinterpret_cast<const __nv_bfloat16*>(k_norm_w), eps);
+  return check_launch("rope_kv_write_qknorm");
 }
 
 extern "C" int tw_swiglu(const void* x, long long ldx, void* out, long long ldo, int T, int d,

@@ -32,6 +32,9 @@ int tw_add_rmsnorm(void* x, void* residual, const void* w, int T, int H, long lo
 int tw_rope_kv_write(void* qkv, long long ld, const int* positions, const int* slots, const float* cos_sin,
                      void* k_cache, void* v_cache, int T, int hq, int hkv, int D, int write_k_back,
                      cudaStream_t stream);
+int tw_rope_kv_write_qknorm(void* qkv, long long ld, const int* positions, const int* slots, const float* cos_sin,
+                            void* k_cache, void* v_cache, int T, int hq, int hkv, int D, int write_k_back,
+                            const void* q_norm_w, const void* k_norm_w, float eps, cudaStream_t stream);
 int tw_swiglu(const void* x, long long ldx, void* out, long long ldo, int T, int d, cudaStream_t stream);
 int tw_embedding(const int* ids, const void* table, void* out, long long ldo, int T, int H, int vocab_start,
                  int vocab_end, cudaStream_t stream);

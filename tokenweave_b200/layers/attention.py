@@ -128,6 +128,7 @@ class Attention(nn.Module):
         self.scale = scale if scale is not None else head_dim ** -0.5
         self.k_cache: Optional[torch.Tensor] = None   # [blocks, page, hkv, D]
         self.v_cache: Optional[torch.Tensor] = None
+        self.qk_norm: Optional[tuple] = None          # (q weight [D], k weight [D], eps): per-head RMSNorm before rope
 
     def bind_kv_cache(self, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
         self.k_cache, self.v_cache = k_cache, v_cache
@@ -138,7 +139,7 @@ class Attention(nn.Module):
         if n == 0:
             return out
         ops.rope_kv_write_(qkv, meta.positions, meta.slot_mapping, cos_sin, self.k_cache, self.v_cache, self.hq,
-                           self.hkv, self.head_dim)
+                           self.hkv, self.head_dim, qk_norm=self.qk_norm)
         q = qkv[:, : self.hq * self.head_dim]
         if not qkv.is_cuda:
             out[:n] = reference.paged_attention(q[:n], self.k_cache, self.v_cache, meta.cu_q_cpu, meta.kv_lens_cpu,

@@ -90,6 +90,11 @@ class DecoderLayer(nn.Module):
         self.qkv_proj = QKVParallelLinear(H, D, cfg.num_q_heads, cfg.num_kv_heads, cfg.qkv_bias, dtype=dt, device=device)
         self.o_proj = RowParallelLinear(cfg.num_q_heads * D, H, False, dtype=dt, device=device)
         self.attn = Attention(self.qkv_proj.q_heads, self.qkv_proj.kv_heads, D)
+        if cfg.qk_norm:
+            # one weight vector per projection, shared by all heads (and therefore by all ranks)
+            self.q_norm_w = nn.Parameter(torch.ones(D, dtype=dt, device=device), requires_grad=False)
+            self.k_norm_w = nn.Parameter(torch.ones(D, dtype=dt, device=device), requires_grad=False)
+            self.attn.qk_norm = (self.q_norm_w, self.k_norm_w, cfg.rms_norm_eps)
         self.input_norm_w = nn.Parameter(torch.ones(H, dtype=dt, device=device), requires_grad=False)
         self.post_norm_w = nn.Parameter(torch.ones(H, dtype=dt, device=device), requires_grad=False)
         if cfg.is_moe:
@@ -268,6 +273,12 @@ class DecoderModel(nn.Module):
     # HuggingFace name -> (module path, shard id)
     STACKED = [(".q_proj", ".qkv_proj", "q"), (".k_proj", ".qkv_proj", "k"), (".v_proj", ".qkv_proj", "v"),
                (".gate_proj", ".gate_up_proj", 0), (".up_proj", ".gate_up_proj", 1)]
+    # HuggingFace name of an already fused projection -> (module, shard ids, rows of each piece)
+    PACKED = {
+        ".qkv_proj": lambda c: ("qkv_proj", ("q", "k", "v"),
+                                [c.num_q_heads * c.head_dim, c.num_kv_heads * c.head_dim, c.num_kv_heads * c.head_dim]),
+        ".gate_up_proj": lambda c: ("gate_up_proj", (0, 1), [c.intermediate_size, c.intermediate_size]),
+    }
 
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
         """Load HuggingFace-layout tensors (``model.layers.N.self_attn.q_proj.weight`` ...), sharding on
@@ -313,8 +324,19 @@ class DecoderModel(nn.Module):
                 layer.moe.load_expert_weight(int(e), which, t)
             return
         rest = rest.replace("self_attn.", "").replace("mlp.", "")
+        if rest in ("q_norm.weight", "k_norm.weight"):
+            getattr(layer, rest[0] + "_norm_w").data.copy_(t)
+            return
         kind = "bias" if rest.endswith(".bias") else "weight"
         stem = "." + rest[: -len(kind) - 1]
+        if stem in self.PACKED:
+            # checkpoints that store the fused projection (Phi-3): cut it at the full-model boundaries and
+            # hand the pieces to the same shard loaders as separate tensors would get
+            ours, shards, sizes = self.PACKED[stem](self.cfg)
+            mod = getattr(layer, ours)
+            for shard, piece in zip(shards, t.split(sizes, dim=0)):
+                mod.weight_loader(getattr(mod, kind), piece, shard)
+            return
         for hf, ours, shard in self.STACKED:
             if stem == hf:
                 mod = getattr(layer, ours[1:])

@@ -8,9 +8,13 @@ from ..config import EngineConfig
 
 def get_model_class(architecture: str):
     from .llama import LlamaForCausalLM
+    from .mistral import MistralForCausalLM
     from .mixtral import MixtralForCausalLM
+    from .phi3 import Phi3ForCausalLM
     from .qwen2 import Qwen2ForCausalLM
-    table = {"llama": LlamaForCausalLM, "qwen2": Qwen2ForCausalLM, "mixtral": MixtralForCausalLM}
+    from .qwen3 import Qwen3ForCausalLM
+    table = {"llama": LlamaForCausalLM, "qwen2": Qwen2ForCausalLM, "mixtral": MixtralForCausalLM,
+             "qwen3": Qwen3ForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM}
     if architecture not in table:
         raise ValueError(f"unsupported architecture {architecture!r} (supported: {sorted(table)})")
     return table[architecture]

@@ -221,18 +221,29 @@ def add_rmsnorm_(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, 
 
 def rope_kv_write_(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor],
                    cos_sin: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                   hq: int, hkv: int, head_dim: int, write_k_back: bool = False) -> None:
-    """Rotate q (and k) of the first ``len(positions)`` rows of ``qkv`` and write k, v to the cache."""
+                   hq: int, hkv: int, head_dim: int, write_k_back: bool = False,
+                   qk_norm: Optional[tuple] = None) -> None:
+    """Rotate q (and k) of the first ``len(positions)`` rows of ``qkv`` and write k, v to the cache.
+    ``qk_norm = (q_weight, k_weight, eps)`` RMS-normalises every q and k head over ``head_dim`` first
+    (the Qwen3 layout), in the same launch."""
     T = positions.shape[0]
     if T == 0:
         return
     if not qkv.is_cuda:
         reference.rope_kv_write_(qkv[:T], positions, slots, cos_sin, k_cache, v_cache, hq, hkv, head_dim,
-                                 write_k_back=True)
+                                 write_k_back=True, qk_norm=qk_norm)
         return
     _check_bf16(qkv, k_cache, v_cache)
     assert positions.dtype == torch.int32 and (slots is None or slots.dtype == torch.int32)
     assert cos_sin.dtype == torch.float32 and cos_sin.shape[1] == head_dim
+    if qk_norm is not None:
+        qw, kw, eps = qk_norm
+        _check_bf16(qw, kw)
+        assert qw.numel() == head_dim and kw.numel() == head_dim
+        _native.call("tw_rope_kv_write_qknorm", qkv.data_ptr(), _row_stride(qkv), positions.data_ptr(), _p(slots),
+                     cos_sin.data_ptr(), _p(k_cache), _p(v_cache), T, hq, hkv, head_dim, int(write_k_back),
+                     qw.data_ptr(), kw.data_ptr(), float(eps), _stream())
+        return
     _native.call("tw_rope_kv_write", qkv.data_ptr(), _row_stride(qkv), positions.data_ptr(), _p(slots),
                  cos_sin.data_ptr(), _p(k_cache), _p(v_cache), T, hq, hkv, head_dim, int(write_k_back),
                  _stream())

@@ -22,6 +22,7 @@ _SIGNATURES = {
     "tw_rmsnorm_copy": [vp, vp, vp, i32, i32, ll, ll, f32, i32, vp],
     "tw_add_rmsnorm": [vp, vp, vp, i32, i32, ll, ll, f32, i32, vp],
     "tw_rope_kv_write": [vp, ll, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "tw_rope_kv_write_qknorm": [vp, ll, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, f32, vp],
     "tw_swiglu": [vp, ll, vp, ll, i32, i32, vp],
     "tw_embedding": [vp, vp, vp, ll, i32, i32, i32, i32, vp],
     "tw_argmax": [vp, ll, vp, i32, i32, vp],

@@ -154,13 +154,44 @@ def build_cos_sin_cache(head_dim: int, max_pos: int, theta: float,
     """fp32 table ``[max_pos, head_dim]``: cos in the first half of each row, sin in the second.
 
     ``rope_scaling`` supports the Llama-3 frequency rescaling
-    (vllm/model_executor/layers/rotary_embedding.py:808-851) and plain linear scaling.
+    (vllm/model_executor/layers/rotary_embedding.py:808-851), linear position scaling (:184-260),
+    dynamic NTK scaling evaluated at the extended length (:263-343) and YaRN (:346-440: per-frequency
+    blend of interpolated and extrapolated frequencies plus the attention-temperature factor that
+    multiplies cos and sin). All variants only change this table; the rotary kernel is the same.
     """
     half = head_dim // 2
-    inv_freq = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim))
+    exponents = torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim
+    inv_freq = 1.0 / (theta ** exponents)
+    mscale = 1.0
     if rope_scaling:
-        kind = rope_scaling.get("rope_type", rope_scaling.get("type", ""))
-        if kind == "llama3":
+        kind = rope_scaling.get("rope_type", rope_scaling.get("type", "default"))
+        if kind in ("default", "", None):
+            pass
+        elif kind == "dynamic":
+            factor = float(rope_scaling["factor"])
+            orig = float(rope_scaling.get("original_max_position_embeddings", max_pos / factor))
+            base = theta * ((factor * (orig * factor) / orig) - (factor - 1)) ** (head_dim / (head_dim - 2))
+            inv_freq = 1.0 / (base ** exponents)
+        elif kind == "yarn":
+            factor = float(rope_scaling["factor"])
+            orig = float(rope_scaling.get("original_max_position_embeddings", max_pos / factor))
+            beta_fast = float(rope_scaling.get("beta_fast", 32))
+            beta_slow = float(rope_scaling.get("beta_slow", 1))
+
+            def corr_dim(rot):      # the dimension whose wavelength makes `rot` turns over the original length
+                return head_dim * math.log(orig / (rot * 2 * math.pi)) / (2 * math.log(theta))
+            lo = max(math.floor(corr_dim(beta_fast)), 0)
+            hi = min(math.ceil(corr_dim(beta_slow)), head_dim - 1)
+            if rope_scaling.get("truncate", True) is False:
+                lo, hi = max(corr_dim(beta_fast), 0), min(corr_dim(beta_slow), head_dim - 1)
+            if lo == hi:
+                hi += 0.001
+            ramp = ((torch.arange(half, dtype=torch.float64) - lo) / (hi - lo)).clamp(0, 1)
+            extrap = 1.0 - ramp                                   # 1 where the frequency is kept as is
+            inv_freq = inv_freq / factor * (1 - extrap) + inv_freq * extrap
+            att = rope_scaling.get("attention_factor")
+            mscale = float(att) if att is not None else (0.1 * math.log(factor) + 1.0 if factor > 1 else 1.0)
+        elif kind == "llama3":
             factor = float(rope_scaling["factor"])
             low = float(rope_scaling.get("low_freq_factor", 1.0))
             high = float(rope_scaling.get("high_freq_factor", 4.0))
@@ -174,17 +205,21 @@ def build_cos_sin_cache(head_dim: int, max_pos: int, theta: float,
             inv_freq = scaled
         elif kind == "linear":
             inv_freq = inv_freq / float(rope_scaling["factor"])
+        else:
+            raise ValueError(f"unsupported rope_scaling type {kind!r} (default, linear, dynamic, yarn, llama3)")
     t = torch.arange(max_pos, dtype=torch.float64)
     freqs = torch.outer(t, inv_freq)
-    return torch.cat([freqs.cos(), freqs.sin()], dim=-1).float().to(device)
+    return (torch.cat([freqs.cos(), freqs.sin()], dim=-1) * mscale).float().to(device)
 
 
 def rope_kv_write_(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor],
                    cos_sin: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                   hq: int, hkv: int, head_dim: int, write_k_back: bool = True) -> None:
+                   hq: int, hkv: int, head_dim: int, write_k_back: bool = True,
+                   qk_norm: Optional[tuple] = None) -> None:
     """NeoX rotary on the q and k heads of ``qkv`` ([T, (hq+2*hkv)*D]) in place, then scatter the
     rotated k and the v rows into the paged caches ([blocks, page, hkv, D]) at ``slots``
-    (negative slots are skipped)."""
+    (negative slots are skipped). ``qk_norm = (q_weight, k_weight, eps)``: RMSNorm over ``head_dim`` of
+    every q and k head before the rotation (vllm/model_executor/models/qwen3.py ``q_norm`` / ``k_norm``)."""
     T = qkv.shape[0]
     if T == 0:
         return
@@ -194,6 +229,12 @@ def rope_kv_write_(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[t
     cos = cs[:, :half].unsqueeze(1)
     sin = cs[:, half:].unsqueeze(1)
     qk = qkv[:, : (hq + hkv) * D].reshape(T, hq + hkv, D).float()
+    if qk_norm is not None:
+        qw, kw, eps = qk_norm
+        w = torch.cat([qw.float().expand(hq, D), kw.float().expand(hkv, D)], 0)
+        qk = qk * torch.rsqrt(qk.pow(2).mean(-1, keepdim=True) + eps) * w
+        if qkv.dtype != torch.float32:      # the kernel rounds the normalised head to the storage type once
+            qk = qk.to(qkv.dtype).float()
     x, y = qk[..., :half], qk[..., half:]
     rot = torch.cat([x * cos - y * sin, y * cos + x * sin], dim=-1).to(qkv.dtype)
     k_rot = rot[:, hq:]

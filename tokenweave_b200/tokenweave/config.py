@@ -22,6 +22,8 @@ from .. import envs
 CONFIG_DIR = Path(__file__).resolve().parent.parent / "tokenweave_configs"
 PAD_GRANULARITY = 256
 DEFAULT_THRESHOLD = {"llama": 1024, "qwen2": 1024, "mixtral": 2048}
+# architectures without a tuned table of their own use the table of the family with the same layer shape
+CONFIG_FAMILY = {"qwen3": "qwen2", "mistral": "llama", "phi3": "llama"}
 
 
 @lru_cache(maxsize=32)
@@ -33,10 +35,13 @@ def load_config(path: str) -> dict[int, dict[str, int]]:
 
 def default_config_path(architecture: str, tp_size: int) -> Optional[str]:
     """``<arch>_config_<tp>.json``; falls back to the nearest larger TP size that has a file."""
-    for tp in sorted({tp_size, 8, 4, 2}, key=lambda t: (t < tp_size, abs(t - tp_size))):
-        p = CONFIG_DIR / f"{architecture}_config_{tp}.json"
-        if p.exists():
-            return str(p)
+    for arch in (architecture, CONFIG_FAMILY.get(architecture)):
+        if arch is None:
+            continue
+        for tp in sorted({tp_size, 8, 4, 2}, key=lambda t: (t < tp_size, abs(t - tp_size))):
+            p = CONFIG_DIR / f"{arch}_config_{tp}.json"
+            if p.exists():
+                return str(p)
     return None
 
 
