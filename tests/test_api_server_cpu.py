@@ -55,7 +55,10 @@ def test_completion_matches_offline_engine(client, engine):
     assert [c["index"] for c in both["choices"]] == [0, 1] and both["choices"][0]["text"] == ch["text"]
     # token-id prompt
     ids = client.post("/v1/completions", json={"prompt": [256, 104, 105], "max_tokens": 3, "temperature": 0}).json()
-    assert ids["usage"]["prompt_tokens"] == 3
+    assert ids["usage"]["prompt_tokens"] == 3 and ids["choices"][0]["prompt_logprobs"] is None
+    plp = client.post("/v1/completions", json={"prompt": [256, 104, 105], "max_tokens": 1, "temperature": 0,
+                                               "prompt_logprobs": 2}).json()["choices"][0]["prompt_logprobs"]
+    assert plp[0] is None and "104" in plp[1] and "105" in plp[2] and all(v <= 0 for v in plp[1].values())
 
 
 def test_streaming_completion_concatenates_to_the_full_text(client):

@@ -27,6 +27,31 @@ def _prompts(vocab, lens, seed=0):
     return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
 
 
+def test_prompt_logprobs_match_the_naive_model(tmp_path):
+    """Chunked prefill (3 chunks) with the prefix cache on: every prompt position still gets its entry, and a
+    second request with the same prompt (a would-be cache hit) gets the same numbers."""
+    cfg = ModelConfig(name="tiny-llama", **MODEL_PRESETS["tiny-llama"])
+    st = make_hf_state(cfg, seed=2)
+    save_hf_checkpoint(st, hf_config_dict(cfg), str(tmp_path))
+    llm = _engine(str(tmp_path), max_num_batched_tokens=64, enable_prefix_caching=True)
+    prompts = _prompts(cfg.vocab_size, [150, 20])
+    sp = SamplingParams(temperature=0, max_tokens=2, prompt_logprobs=3)
+    outs = llm.generate(prompts + [prompts[0]], [sp, SamplingParams(temperature=0, max_tokens=2), sp])
+    assert outs[1].prompt_logprobs is None
+    want = torch.log_softmax(naive_logits(cfg, st, prompts[0]), -1)
+    for out in (outs[0], outs[2]):
+        plp = out.prompt_logprobs
+        assert len(plp) == 150 and plp[0] is None
+        for p in range(1, 150):
+            tok = prompts[0][p]
+            assert abs(plp[p][tok] - want[p - 1, tok].item()) < 2e-4
+            top = want[p - 1].topk(3)
+            assert set(top.indices.tolist()) <= set(plp[p]) and len(plp[p]) <= 4
+            for t, v in zip(top.indices.tolist(), top.values.tolist()):
+                assert abs(plp[p][t] - v) < 2e-4
+    llm.shutdown()
+
+
 def test_phi3_packed_checkpoint_and_mistral_config(tmp_path):
     """Phi-3 stores the fused qkv / gate_up tensors; Mistral brings a sliding window and (newer configs) the
     rope settings under ``rope_parameters``. Both must load into the shared decoder and match the naive model."""

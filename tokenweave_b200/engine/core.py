@@ -86,6 +86,11 @@ class EngineCore:
         except ExecutorFailure as e:
             self.dead = True
             raise EngineDeadError(str(e)) from e
+        if result.prompt_logprobs:
+            by_id = {s.request.request_id: s.request for s in sched.scheduled}
+            for rid, items in result.prompt_logprobs.items():
+                if rid in by_id:
+                    by_id[rid].prompt_logprobs.update(items)      # keyed by position: a recompute overwrites
         touched = self.scheduler.update_from_output(
             sched, ModelRunnerOutput(result.req_ids, result.sampled_token_ids, result.logprobs))
         self._last_logprobs = dict(zip(result.req_ids, result.logprobs)) if result.logprobs else {}

@@ -169,7 +169,12 @@ class LLMEngine:
         metrics = RequestMetrics(parent.arrival, min((c.first_scheduled_time or parent.arrival) for c in parent.children),
                                  min(first) if first else None,
                                  max((c.finished_time or 0.0) for c in parent.children) if finished else None)
-        return RequestOutput(parent.request_id, parent.prompt, parent.prompt_token_ids, comps, finished, metrics)
+        plp = None
+        if parent.params.prompt_logprobs is not None:
+            got = parent.children[0].prompt_logprobs        # the children share the prompt
+            plp = [None] + [got.get(p) for p in range(1, len(parent.prompt_token_ids))]
+        return RequestOutput(parent.request_id, parent.prompt, parent.prompt_token_ids, comps, finished, metrics,
+                             prompt_logprobs=plp)
 
     def shutdown(self) -> None:
         self.core.shutdown()

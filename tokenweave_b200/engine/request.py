@@ -41,15 +41,16 @@ class Request:
     block_ids: list[int] = field(default_factory=list)
     spec_token_ids: list[int] = field(default_factory=list)   # drafts to verify in the next step
     lora_request: Optional[object] = None                     # tokenweave_b200.lora.LoRARequest
+    prompt_logprobs: dict = field(default_factory=dict)       # prompt position -> {token id: log-probability}
+    stop_reason: Optional[object] = None
+    first_scheduled_time: Optional[float] = None
+    first_token_time: Optional[float] = None
+    finished_time: Optional[float] = None
 
     @property
     def cache_salt(self) -> bytes:
         """Prefix-cache key component: KV computed under one adapter is not valid under another."""
         return b"" if self.lora_request is None else f"lora{self.lora_request.lora_int_id}|".encode()
-    stop_reason: Optional[object] = None
-    first_scheduled_time: Optional[float] = None
-    first_token_time: Optional[float] = None
-    finished_time: Optional[float] = None
 
     @property
     def num_prompt_tokens(self) -> int:

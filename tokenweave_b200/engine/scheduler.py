@@ -130,7 +130,8 @@ class Scheduler:
             while self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
                 req = self.waiting[0]
                 cached, n_cached = ([], 0)
-                if req.num_computed_tokens == 0:
+                if req.num_computed_tokens == 0 and req.sampling_params.prompt_logprobs is None:
+                    # (prompt log-probabilities need the hidden state of every prompt position: no cache hits)
                     cached, n_cached = self.kv.get_computed_blocks(req)
                 remaining = req.num_tokens - req.num_computed_tokens - n_cached
                 n = min(remaining, budget)

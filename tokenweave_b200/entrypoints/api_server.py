@@ -25,7 +25,8 @@ logger = init_logger(__name__)
 
 _SAMPLING_FIELDS = ("n", "temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty",
                     "repetition_penalty", "seed", "stop", "stop_token_ids", "max_tokens", "min_tokens", "ignore_eos",
-                    "skip_special_tokens", "logit_bias", "allowed_token_ids", "bad_words_token_ids", "guided_choice")
+                    "skip_special_tokens", "logit_bias", "allowed_token_ids", "bad_words_token_ids", "guided_choice",
+                    "prompt_logprobs")
 
 
 def sampling_params_from_request(body: dict, default_max_tokens: int = 16) -> SamplingParams:
@@ -169,8 +170,12 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
         echo = bool(body.get("echo"))
 
         def choice(out: RequestOutput, p_idx: int, comp, text: str, finish) -> dict:
+            plp = out.prompt_logprobs
+            if plp is not None:      # JSON object keys are strings
+                plp = [None if d is None else {str(t): v for t, v in d.items()} for d in plp]
             return {"index": p_idx * sp.n + comp.index, "text": text, "token_ids": list(comp.token_ids) if tokenizer is None else None,
-                    "logprobs": _logprobs_block(comp, tokenizer), "finish_reason": finish, "stop_reason": comp.stop_reason}
+                    "logprobs": _logprobs_block(comp, tokenizer), "finish_reason": finish, "stop_reason": comp.stop_reason,
+                    "prompt_logprobs": plp}
 
         if body.get("stream"):
             if len(prompts) != 1:

@@ -36,6 +36,9 @@ class RequestOutput:
     outputs: list[CompletionOutput]
     finished: bool
     metrics: RequestMetrics = field(default_factory=RequestMetrics)
+    # with ``SamplingParams.prompt_logprobs``: one entry per prompt token, None for the first, then
+    # ``{token id: log-probability}`` holding the prompt token itself and the k most likely tokens there
+    prompt_logprobs: Optional[list] = None
 
 
 @dataclass

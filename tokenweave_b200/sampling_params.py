@@ -22,6 +22,9 @@ class SamplingParams:
     min_tokens: int = 0
     ignore_eos: bool = False
     logprobs: Optional[int] = None
+    # log-probability of every prompt token given its prefix, plus the k most likely tokens at each position
+    # (vllm/sampling_params.py ``prompt_logprobs``); such a request does not reuse cached prefixes
+    prompt_logprobs: Optional[int] = None
     detokenize: bool = True
     skip_special_tokens: bool = True
     logit_bias: Optional[dict] = None                   # token id -> additive bias (clamped to [-100, 100])

@@ -58,6 +58,8 @@ class StepResult:
     sampled_token_ids: list[Optional[int]]
     logprobs: Optional[list] = None
     device_time_ms: Optional[float] = None
+    # request id -> [(prompt position, {token id: log-probability})] for the prompt positions of this step
+    prompt_logprobs: Optional[dict] = None
 
 
 @dataclass
@@ -239,6 +241,7 @@ class ModelRunner:
         bs = self.block_size
         spec: dict[str, list[int]] = {}          # request -> drafts verified in this step
         row_lora: list[int] = []                 # adapter id of every token row (0 = none)
+        prompt_lp_jobs: list[tuple[str, int, int, int]] = []     # (request, first row, first position, rows)
         for b, (rid, computed, n_new, new_blocks, *rest) in enumerate(step.scheduled):
             req = self.requests[rid]
             req.block_ids.extend(new_blocks)
@@ -262,6 +265,10 @@ class ModelRunner:
                     sample_reqs.append(rid)
             if self.lora is not None:
                 row_lora.extend([req.lora_id] * n_new)
+            if req.sampling_params.prompt_logprobs is not None and computed < req.num_prompt_tokens - 1:
+                # rows of prompt positions p whose successor p + 1 is still a prompt token
+                n_pl = min(computed + n_base, req.num_prompt_tokens - 1) - computed
+                prompt_lp_jobs.append((rid, row, computed, n_pl))
             row += n_new
         if self.lora is not None:
             self.lora.set_batch(row_lora)
@@ -303,6 +310,7 @@ class ModelRunner:
         sampled: dict[str, int] = {}
         lp = None
         d2h = 0
+        prompt_lp = self._prompt_logprobs(prompt_lp_jobs) if prompt_lp_jobs else None
         if logits_rows:
             if self.capture_hidden:
                 rows = self._last_hidden_rows.detach().float().cpu()
@@ -346,4 +354,33 @@ class ModelRunner:
         req_ids = [s[0] for s in step.scheduled]
         lp_by_req = dict(zip(sample_reqs, lp)) if lp is not None else None
         return StepResult(req_ids, [sampled.get(r) for r in req_ids],
-                          [lp_by_req.get(r) for r in req_ids] if lp_by_req is not None else None)
+                          [lp_by_req.get(r) for r in req_ids] if lp_by_req is not None else None,
+                          prompt_logprobs=prompt_lp)
+
+    def _prompt_logprobs(self, jobs: list[tuple[str, int, int, int]]) -> dict:
+        """Log-probabilities of the prompt tokens computed in this step: the final-norm hidden rows of the
+        step are still in the staging buffer; they go through the LM head in blocks of 512 rows (a block of
+        fp32 logits over a 128k vocabulary is 256 MB), and only the chosen and top-k entries leave the device
+        (vllm/v1/worker/gpu_model_runner.py ``_get_prompt_logprobs_dict``)."""
+        hidden = self.model.rt.hidden
+        out: dict[str, list] = {}
+        for rid, row0, pos0, n in jobs:
+            req = self.requests[rid]
+            k = int(req.sampling_params.prompt_logprobs)
+            targets = torch.as_tensor(req.token_ids[pos0 + 1: pos0 + 1 + n], dtype=torch.long, device=hidden.device)
+            items = out.setdefault(rid, [])
+            for b in range(0, n, 512):
+                e = min(n, b + 512)
+                lsm = torch.log_softmax(self.model.compute_logits(hidden[row0 + b: row0 + e]).float(), dim=-1)
+                chosen = lsm.gather(1, targets[b:e, None]).squeeze(1).tolist()
+                if k > 0:
+                    top_v, top_i = lsm.topk(min(k, lsm.shape[1]), dim=-1)
+                    top_v, top_i = top_v.tolist(), top_i.tolist()
+                tg = targets[b:e].tolist()
+                for j in range(e - b):
+                    d = {int(tg[j]): float(chosen[j])}
+                    if k > 0:
+                        for t, v in zip(top_i[j], top_v[j]):
+                            d.setdefault(int(t), float(v))
+                    items.append((pos0 + b + j + 1, d))
+        return out
