@@ -103,7 +103,7 @@ class KVCacheManager:
         blocks = []
         # never reuse the whole prompt: the last token must be recomputed to produce logits
         usable = (req.num_tokens - 1) // self.block_size
-        for h in block_hashes(req.all_token_ids, self.block_size, req.cache_salt)[:usable]:
+        for h in self._hashes(req, usable):
             b = self.pool.lookup(h)
             if b is None:
                 break
@@ -113,6 +113,8 @@ class KVCacheManager:
     def allocate_slots(self, req: Request, num_new_tokens: int, cached_blocks: Optional[list[int]] = None) -> bool:
         """Make sure ``req`` owns enough blocks for ``num_computed_tokens + num_new_tokens`` tokens.
         Returns False (and changes nothing) if the pool cannot provide them."""
+        if not cached_blocks and (req.num_computed_tokens + num_new_tokens) <= len(req.block_ids) * self.block_size:
+            return True                    # the common decode step: the last block still has room
         cached_blocks = cached_blocks or []
         have = len(req.block_ids) + len(cached_blocks)
         need_total = (req.num_computed_tokens + len(cached_blocks) * 0 + num_new_tokens + self.block_size - 1) // self.block_size
@@ -126,16 +128,36 @@ class KVCacheManager:
         req.block_ids.extend(self.pool.allocate(need))
         return True
 
+    def _hashes(self, req: Request, num_blocks: int) -> list[bytes]:
+        """Chained hashes of the request's first ``num_blocks`` full blocks. The chain is kept on the request
+        and only extended: tokens are append-only, so a block's hash never changes once it is full."""
+        chain = req.block_hash_chain
+        bs = self.block_size
+        if len(chain) < num_blocks:
+            prev = chain[-1] if chain else req.cache_salt
+            for i in range(len(chain), num_blocks):
+                m = hashlib.sha256(prev)
+                m.update(b",".join(str(req.token_at(j)).encode() for j in range(i * bs, (i + 1) * bs)))
+                prev = m.digest()
+                chain.append(prev)
+        return chain[:num_blocks]
+
     def cache_full_blocks(self, req: Request) -> None:
+        """Publish the blocks that became full since the last call (per-step cost: O(new blocks))."""
         if not self.enable_caching:
             return
         full = req.num_computed_tokens // self.block_size
-        for i, h in enumerate(block_hashes(req.all_token_ids[:full * self.block_size], self.block_size, req.cache_salt)):
-            self.pool.cache_block(req.block_ids[i], h)
+        if full <= req.num_published_blocks:
+            return
+        hashes = self._hashes(req, full)
+        for i in range(req.num_published_blocks, full):
+            self.pool.cache_block(req.block_ids[i], hashes[i])
+        req.num_published_blocks = full
 
     def free(self, req: Request) -> None:
         self.pool.release(req.block_ids)
         req.block_ids = []
+        req.num_published_blocks = 0       # the next owner of these block ids starts over; the hash chain stays
 
     def usage(self) -> float:
         return self.pool.usage()

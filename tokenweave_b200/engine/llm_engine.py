@@ -129,7 +129,11 @@ class LLMEngine:
         return self.core.scheduler.num_unfinished()
 
     # ---- stepping ---------------------------------------------------------------------------
-    def step(self) -> list[RequestOutput]:
+    def step(self, final_only: bool = False) -> list[RequestOutput]:
+        """One engine iteration. Returns a snapshot of every request that produced a token or finished;
+        with ``final_only`` only finished requests are materialised (what the offline API consumes —
+        the counterpart of ``RequestOutputKind.FINAL_ONLY`` in vllm/sampling_params.py), which keeps the
+        per-step host cost independent of the lengths generated so far."""
         touched = self.core.step()
         if self.stat_logger is not None and self.core.last_stats is not None:
             self.stat_logger.record(self.core.last_stats)
@@ -147,7 +151,10 @@ class LLMEngine:
                 hit = detok.update(child.output_token_ids[len(detok.token_ids):])
                 if hit is not None and not child.status.finished:
                     self.core.scheduler.finish_request(child, RequestStatus.FINISHED_STOPPED, hit)
-            outputs[pid] = self._make_output(parent)
+            outputs[pid] = parent
+        if final_only:
+            outputs = {pid: p for pid, p in outputs.items() if all(c.status.finished for c in p.children)}
+        outputs = {pid: self._make_output(p) for pid, p in outputs.items()}
         done = [pid for pid, out in outputs.items() if out.finished]
         for pid in done:
             parent = self.parents.pop(pid)

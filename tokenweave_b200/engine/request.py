@@ -26,7 +26,7 @@ FINISH_REASON = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_
                  RequestStatus.FINISHED_ABORTED: "abort"}
 
 
-@dataclass
+@dataclass(eq=False)        # identity semantics: membership tests in the queues must not compare token lists
 class Request:
     request_id: str
     prompt_token_ids: list[int]
@@ -42,6 +42,8 @@ class Request:
     spec_token_ids: list[int] = field(default_factory=list)   # drafts to verify in the next step
     lora_request: Optional[object] = None                     # tokenweave_b200.lora.LoRARequest
     prompt_logprobs: dict = field(default_factory=dict)       # prompt position -> {token id: log-probability}
+    block_hash_chain: list = field(default_factory=list)      # prefix-cache hashes of the full blocks so far
+    num_published_blocks: int = 0                             # leading blocks already offered to the prefix cache
     stop_reason: Optional[object] = None
     first_scheduled_time: Optional[float] = None
     first_token_time: Optional[float] = None

@@ -205,8 +205,10 @@ class Scheduler:
 
     def _propose_drafts(self, req: Request) -> None:
         """n-gram drafts for the next step of a greedy decoding request (empty when nothing matches)."""
+        if not self.spec.enabled:
+            return
         from .spec_decode import clamp_drafts, ngram_propose, spec_eligible
-        if not self.spec.enabled or not spec_eligible(req.sampling_params):
+        if not spec_eligible(req.sampling_params):
             return
         drafts = ngram_propose(req.all_token_ids, self.spec.num_speculative_tokens, self.spec.prompt_lookup_max,
                                self.spec.prompt_lookup_min)

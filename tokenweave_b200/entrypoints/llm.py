@@ -75,7 +75,7 @@ class LLM:
             from tqdm import tqdm
             bar = tqdm(total=len(request_ids), desc="Processed prompts")
         while self.llm_engine.has_unfinished_requests():
-            for out in self.llm_engine.step():
+            for out in self.llm_engine.step(final_only=True):
                 if out.finished:
                     final[out.request_id] = out
                     if bar is not None:

@@ -246,6 +246,21 @@ class ModelRunner:
             req = self.requests[rid]
             req.block_ids.extend(new_blocks)
             drafts = list(rest[0]) if rest and rest[0] else []
+            if n_new == 1 and not drafts and req.sampling_params.prompt_logprobs is None:
+                # decode fast path (most rows of a serving step): scalars only, no array temporaries
+                ids[row] = req.token_ids[computed]
+                positions[row] = computed
+                slots[row] = req.block_ids[computed // bs] * bs + computed % bs
+                q_lens.append(1)
+                kv_lens.append(computed + 1)
+                tables[b] = req.block_ids
+                if computed + 1 >= len(req.token_ids):
+                    logits_rows.append(row)
+                    sample_reqs.append(rid)
+                if self.lora is not None:
+                    row_lora.append(req.lora_id)
+                row += 1
+                continue
             n_base = n_new - len(drafts)             # tokens of the request itself; the drafts follow them
             ids[row:row + n_base] = req.token_ids[computed:computed + n_base]
             if drafts:
