@@ -86,6 +86,17 @@ class LLMEngine:
                 sp.guided_choice_token_ids = [list(self.tokenizer.encode(c, add_special_tokens=False))
                                               for c in sp.guided_choice]
                 sp.eos_token_id = self.eos_token_id
+            if (sp.guided_regex or sp.guided_json is not None) and not sp.guided_pattern:
+                from . import structured
+                if self.eos_token_id is None:
+                    raise ValueError("structured output ends a request through the end-of-sequence token; "
+                                     "the model configuration or tokenizer must define one")
+                if sp is params:
+                    sp = params.clone()
+                sp.guided_pattern = structured.constraint_pattern(sp)
+                structured.DFA(sp.guided_pattern)          # syntax errors surface here, not on the workers
+                sp.eos_token_id = self.eos_token_id
+                sp.ignore_eos = False
             if sp.min_tokens > 0 and sp.eos_token_id is None and not sp.ignore_eos:
                 if sp is params:
                     sp = params.clone()          # the caller's object stays untouched

@@ -13,6 +13,10 @@ class ByteTokenizer:
     eos_token_id = 257
     vocab_size = 258
 
+    def token_bytes(self, token_id: int) -> bytes:
+        """The bytes a token adds to the output text (structured output walks these)."""
+        return bytes([token_id]) if 0 <= token_id < 256 else b""
+
     def encode(self, text: str, add_special_tokens: bool = True) -> list[int]:
         ids = list(text.encode("utf-8"))
         return ([self.bos_token_id] + ids) if add_special_tokens else ids

@@ -26,11 +26,19 @@ logger = init_logger(__name__)
 _SAMPLING_FIELDS = ("n", "temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty",
                     "repetition_penalty", "seed", "stop", "stop_token_ids", "max_tokens", "min_tokens", "ignore_eos",
                     "skip_special_tokens", "logit_bias", "allowed_token_ids", "bad_words_token_ids", "guided_choice",
-                    "prompt_logprobs")
+                    "prompt_logprobs", "guided_regex", "guided_json")
 
 
 def sampling_params_from_request(body: dict, default_max_tokens: int = 16) -> SamplingParams:
     kw = {k: body[k] for k in _SAMPLING_FIELDS if body.get(k) is not None}
+    # OpenAI's response_format: {"type": "json_object"} or {"type": "json_schema", "json_schema": {"schema": {...}}}
+    rf = body.get("response_format")
+    if isinstance(rf, dict) and "guided_json" not in kw and "guided_regex" not in kw:
+        if rf.get("type") == "json_object":
+            kw["guided_json"] = {}
+        elif rf.get("type") == "json_schema":
+            js = rf.get("json_schema") or {}
+            kw["guided_json"] = js.get("schema", js)
     if "max_completion_tokens" in body and body["max_completion_tokens"] is not None:
         kw["max_tokens"] = body["max_completion_tokens"]
     kw.setdefault("max_tokens", default_max_tokens)

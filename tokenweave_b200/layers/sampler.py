@@ -23,11 +23,20 @@ class SamplerOutput:
 
 
 def apply_penalties(logits: torch.Tensor, params: Sequence[SamplingParams], prompt_tokens: Sequence[Sequence[int]],
-                    output_tokens: Sequence[Sequence[int]]) -> torch.Tensor:
+                    output_tokens: Sequence[Sequence[int]], guided=None) -> torch.Tensor:
+    """Edits the logits rows in place. ``guided(sp, generated tokens)`` returns the token ids a structured-output
+    constraint allows next (None: the request has no such constraint)."""
     V = logits.shape[1]
     for i, sp in enumerate(params):
         if not sp.needs_penalties:
             continue
+        allowed_next = guided(sp, output_tokens[i]) if guided is not None else None
+        if allowed_next is not None:
+            # regex / JSON-schema constraint (vllm/v1/structured_output: the grammar bitmask applied to the logits)
+            keep = torch.as_tensor([t for t in allowed_next if 0 <= t < V], dtype=torch.long, device=logits.device)
+            masked = torch.full_like(logits[i], float("-inf"))
+            masked[keep] = logits[i, keep]
+            logits[i] = masked
         out_ids = torch.as_tensor(list(output_tokens[i]), dtype=torch.long, device=logits.device)
         if sp.repetition_penalty != 1.0:
             seen = torch.as_tensor(list(prompt_tokens[i]) + list(output_tokens[i]), dtype=torch.long, device=logits.device)
@@ -111,6 +120,23 @@ class Sampler:
         import random
         self._rng = random.Random(seed)      # row seeds of unseeded requests; identical on every TP rank
         self.use_fused_kernel = use_fused_kernel
+        self.vocab_provider = None           # () -> list of token byte strings; set by the model runner
+        self._trie = None
+
+    def _guided(self, sp: SamplingParams, generated) -> Optional[list]:
+        """Allowed next tokens under the request's regex / JSON-schema constraint."""
+        from ..engine import structured
+        pattern = structured.constraint_pattern(sp)
+        if pattern is None:
+            return None
+        if self._trie is None:
+            if self.vocab_provider is None:
+                raise RuntimeError("structured output needs the tokenizer's vocabulary on the worker")
+            self._trie = structured.TokenTrie(self.vocab_provider())
+        fsm = structured.get_fsm(pattern, self._trie, sp.eos_token_id)
+        allowed = fsm.allowed_tokens(fsm.state_after(generated))
+        # a dead end (only reachable if a token outside the mask was forced in): let the request end
+        return allowed if allowed else ([sp.eos_token_id] if sp.eos_token_id is not None else None)
 
     def _row_seeds(self, params: Sequence[SamplingParams], output_tokens) -> list[int]:
         seeds = []
@@ -133,7 +159,7 @@ class Sampler:
         B, V = logits.shape
         want_logprobs = any(sp.logprobs is not None for sp in params)
         if any(sp.needs_penalties for sp in params):
-            logits = apply_penalties(logits.clone(), params, prompt_tokens, output_tokens)
+            logits = apply_penalties(logits.clone(), params, prompt_tokens, output_tokens, guided=self._guided)
         raw_logprobs = torch.log_softmax(logits, dim=-1) if want_logprobs else None
         if all(sp.greedy for sp in params):
             ids = ops.argmax(logits)

@@ -36,6 +36,12 @@ class SamplingParams:
     # ``guided_choice_token_ids``; generation stops when a choice is complete.
     guided_choice: Optional[list[str]] = None
     guided_choice_token_ids: Optional[list[list[int]]] = None
+    # Structured output (``GuidedDecodingParams.regex`` / ``.json`` of the reference): the generated text must
+    # match the regular expression, or be a JSON document satisfying the schema (a dict or its JSON text;
+    # ``{}`` admits any JSON value). The engine lowers both to ``guided_pattern``; see engine/structured.py.
+    guided_regex: Optional[str] = None
+    guided_json: Union[None, str, dict] = None
+    guided_pattern: Optional[str] = None
 
     def __post_init__(self):
         if self.logit_bias is not None:
@@ -68,7 +74,8 @@ class SamplingParams:
         """True when the logits must be edited before sampling (penalties, biases, masks)."""
         return (self.presence_penalty != 0.0 or self.frequency_penalty != 0.0 or self.repetition_penalty != 1.0
                 or bool(self.logit_bias) or self.allowed_token_ids is not None or bool(self.bad_words_token_ids)
-                or self.min_tokens > 0 or bool(self.guided_choice_token_ids))
+                or self.min_tokens > 0 or bool(self.guided_choice_token_ids)
+                or bool(self.guided_regex) or self.guided_json is not None or bool(self.guided_pattern))
 
     def clone(self) -> "SamplingParams":
         import copy

@@ -80,6 +80,7 @@ class ModelRunner:
         self.model: Optional[DecoderModel] = None
         self.requests: dict[str, _CachedRequest] = {}
         self.sampler = Sampler(seed=config.seed)
+        self.sampler.vocab_provider = self._token_bytes       # structured output: built on first use
         self.block_size = config.cache.block_size
         self.max_tokens = config.scheduler.max_num_batched_tokens
         tw = config.tokenweave
@@ -142,6 +143,14 @@ class ModelRunner:
         self._graphs.clear()
         self._graph_seen.clear()
         self._graph_pool = None
+
+    def _token_bytes(self) -> list:
+        """Bytes every vocabulary entry contributes to the text, from the same tokenizer the front end uses."""
+        from ..engine.structured import token_bytes_table
+        from ..engine.tokenizer import load_tokenizer
+        cfg = self.config
+        tok = load_tokenizer(cfg.tokenizer or (cfg.model.path if cfg.model.path else "byte"))
+        return token_bytes_table(tok, cfg.model.vocab_size)
 
     # ---- one step ---------------------------------------------------------------------------
     def _update_states(self, step: StepData) -> None:
