@@ -194,6 +194,14 @@ class ParallelConfig:
     distributed_executor_backend: str = "auto"
     disable_custom_all_reduce: bool = True
     nvls: bool = True                     # allow multimem transport when the hardware offers it
+    # data parallelism: independent engine replicas, each a TP group on its own GPUs
+    # (replica r uses devices [r * tp, (r + 1) * tp))
+    data_parallel_size: int = 1
+    data_parallel_rank: int = 0
+
+    @property
+    def device_offset(self) -> int:
+        return self.data_parallel_rank * self.tensor_parallel_size
 
 
 @dataclass
@@ -266,6 +274,8 @@ class EngineArgs:
     max_model_len: Optional[int] = None
     tensor_parallel_size: int = 1
     distributed_executor_backend: str = "auto"
+    data_parallel_size: int = 1           # engine replicas behind one front end (entrypoints/api_server.py)
+    data_parallel_rank: int = 0           # which replica this engine is: its GPUs start at rank * tensor_parallel_size
     block_size: int = 128
     gpu_memory_utilization: float = 0.90
     num_gpu_blocks_override: Optional[int] = None
@@ -320,7 +330,8 @@ class EngineArgs:
             cache=CacheConfig(self.block_size, self.gpu_memory_utilization, self.num_gpu_blocks_override,
                               self.enable_prefix_caching),
             parallel=ParallelConfig(self.tensor_parallel_size, self.distributed_executor_backend,
-                                    self.disable_custom_all_reduce),
+                                    self.disable_custom_all_reduce, data_parallel_size=self.data_parallel_size,
+                                    data_parallel_rank=self.data_parallel_rank),
             scheduler=SchedulerConfig(budget, self.max_num_seqs, self.enable_chunked_prefill, max_len),
             tokenweave=TokenWeaveConfig(mode=self.tokenweave_mode, config_path=self.tokenweave_config,
                                         overlap_threshold=self.tokenweave_threshold,

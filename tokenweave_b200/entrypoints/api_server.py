@@ -94,7 +94,8 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
     try:
         from ..utils.metrics import PrometheusStatLogger
         prom = PrometheusStatLogger(name)
-        engine.engine.stat_logger = prom
+        for e in getattr(engine, "replicas", [engine]):        # every data-parallel replica reports into it
+            e.engine.stat_logger = prom
     except Exception:       # prometheus_client missing: /metrics answers 501
         prom = None
 
@@ -303,7 +304,11 @@ def main() -> None:
         args.enable_lora = True
     if args.tensor_parallel_size > 1 and args.distributed_executor_backend == "auto":
         args.distributed_executor_backend = "mp"
-    engine = AsyncLLMEngine.from_engine_args(args)
+    if args.data_parallel_size > 1:
+        from ..engine.data_parallel import DataParallelEngine
+        engine = DataParallelEngine.from_engine_args(args)
+    else:
+        engine = AsyncLLMEngine.from_engine_args(args)
     import uvicorn
     try:
         uvicorn.run(build_app(engine, ns.served_model_name, lora_modules), host=ns.host, port=ns.port, log_level="info")

@@ -35,7 +35,7 @@ def _worker_main(config: EngineConfig, rank: int, init_method: str, mq_handle: t
     try:
         from ..worker.worker import Worker
         mq = MessageQueue.attach(mq_handle, rank)
-        worker = Worker(config, rank, rank, init_method)
+        worker = Worker(config, rank, config.parallel.device_offset + rank, init_method)
         worker.init_device()
         worker.load_model()
         ready_conn.send(("READY", rank))

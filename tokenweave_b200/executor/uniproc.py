@@ -27,7 +27,7 @@ class UniProcExecutor(Executor):
             if config.parallel.tensor_parallel_size != 1:
                 raise ValueError("the in-process executor runs one rank; use the 'mp' or "
                                  "'external_launcher' backend for tensor parallelism")
-            rank = local_rank = 0
+            rank, local_rank = 0, config.parallel.device_offset
         self.rank = rank
         self.worker = Worker(config, rank, local_rank)
         self.worker.init_device()
