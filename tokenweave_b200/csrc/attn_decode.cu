@@ -209,6 +209,27 @@ attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restri
 
 using namespace tw;
 
+// Reduction of split-KV partial results (also used by the tensor-core decode kernel).
+extern "C" int tw_attn_decode_merge(const float* part_o, const float* part_ml, const int* tok_row, int n_tok,
+                                    int hq, int D, int splits, void* out, long long ldo, cudaStream_t stream) {
+  if (n_tok <= 0 || splits <= 1) return 0;
+  auto ob = reinterpret_cast<__nv_bfloat16*>(out);
+  if (D == 128)
+    attn_decode_merge_kernel<128><<<dim3(n_tok, hq), 128, 0, stream>>>(part_o, part_ml, tok_row, hq, splits, ob, ldo);
+  else if (D == 64)
+    attn_decode_merge_kernel<64><<<dim3(n_tok, hq), 64, 0, stream>>>(part_o, part_ml, tok_row, hq, splits, ob, ldo);
+  else {
+    set_last_error("attn_decode_merge: head_dim must be 64 or 128 (got %d)", D);
+    return 1;
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error("attn_decode_merge launch failed: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
+
 // part_o: [n_tok, hq, splits, D] fp32, part_ml: [n_tok, hq, splits, 2] fp32 (used when splits > 1).
 extern "C" int tw_attn_decode(const void* q, long long ldq, const void* k_cache, const void* v_cache, int page,
                               void* out, long long ldo, const int* tok_row, const int* tok_seq,

@@ -77,6 +77,15 @@ int tw_attn_decode(const void* q, long long ldq, const void* k_cache, const void
                    const int* block_table, int max_blocks, int hq, int hkv, int D, float scale, int splits,
                    float* part_o, float* part_ml, cudaStream_t stream);
 
+int tw_attn_decode_merge(const float* part_o, const float* part_ml, const int* tok_row, int n_tok, int hq, int D,
+                         int splits, void* out, long long ldo, cudaStream_t stream);
+// tensor-core variant for grouped-query models with head size 128 (attn_decode_tc.cu)
+int tw_attn_decode_tc(const void* q, long long ldq, const void* k_cache, const void* v_cache, int num_blocks,
+                      int page, void* out, long long ldo, const int* tok_row, const int* tok_seq,
+                      const int* tok_kvlen, int n_tok, const int* block_table, int max_blocks, int hq, int hkv,
+                      int D, float scale, int splits, float* part_o, float* part_ml, uint32_t* status,
+                      cudaStream_t stream);
+
 // ---- mixture of experts (moe.cu) ----
 int tw_moe_router(const void* x, long long ldx, const void* wg, float* topk_w, int* topk_ids, float* logits_out,
                   int T, int H, int E, int topk, int renormalize, cudaStream_t stream);

@@ -10,6 +10,8 @@ from __future__ import annotations
 
 from typing import Optional
 
+import os
+
 import torch
 
 from . import _native, gemm_table, reference
@@ -402,6 +404,19 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
 _decode_ws: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
+# Decode attention kernel: "simt" (attn_decode.cu) or "tc" (attn_decode_tc.cu: tcgen05, grouped-query models
+# with head size 128, sequences of 256 keys and more). TW_DECODE_TC=1 selects "tc".
+_decode_variant = "tc" if os.environ.get("TW_DECODE_TC", "0") == "1" else "simt"
+
+
+def set_decode_variant(name: Optional[str]) -> None:
+    """``"tc"`` / ``"simt"``; None restores the environment's choice."""
+    global _decode_variant
+    if name not in (None, "tc", "simt"):
+        raise ValueError(name)
+    _decode_variant = name or ("tc" if os.environ.get("TW_DECODE_TC", "0") == "1" else "simt")
+
+
 def decode_splits(n_tok: int, hkv: int, max_kv_len: int, sm_count: int = 148) -> int:
     """How many ways the keys are split so that a small decode batch still fills the machine."""
     ctas = n_tok * hkv
@@ -420,7 +435,14 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o
         return
     _check_bf16(q, k_cache, v_cache, out)
     page = k_cache.shape[1]
-    splits = decode_splits(n_tok, hkv, max_kv_len, sm_count)
+    use_tc = (_decode_variant == "tc" and head_dim == 128 and hq // hkv <= 16 and max_kv_len >= 256
+              and 8 <= page <= 128 and 128 % page == 0)
+    if use_tc:
+        # one 192-thread CTA per SM: split until the machine is full, two key tiles per split at least
+        ctas, tiles = n_tok * hkv, (max_kv_len + 127) // 128
+        splits = 1 if ctas >= sm_count else max(1, min((sm_count + ctas - 1) // ctas, tiles // 2, 32))
+    else:
+        splits = decode_splits(n_tok, hkv, max_kv_len, sm_count)
     part_o = part_ml = None
     if splits > 1:
         key = (q.device.index, n_tok * hq * splits * head_dim)
@@ -432,6 +454,12 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o
                 _decode_ws.clear()
             _decode_ws[key] = ws
         part_o, part_ml = ws
+    if use_tc:
+        _native.call("tw_attn_decode_tc", q.data_ptr(), _row_stride(q), k_cache.data_ptr(), v_cache.data_ptr(),
+                     k_cache.shape[0], page, out.data_ptr(), _row_stride(out), tok_row.data_ptr(), tok_seq.data_ptr(),
+                     tok_kvlen.data_ptr(), n_tok, block_table.data_ptr(), block_table.shape[1], hq, hkv, head_dim,
+                     scale, splits, _p(part_o), _p(part_ml), status_word(q.device).data_ptr(), _stream())
+        return
     _native.call("tw_attn_decode", q.data_ptr(), _row_stride(q), k_cache.data_ptr(), v_cache.data_ptr(), page,
                  out.data_ptr(), _row_stride(out), tok_row.data_ptr(), tok_seq.data_ptr(), tok_kvlen.data_ptr(),
                  n_tok, block_table.data_ptr(), block_table.shape[1], hq, hkv, head_dim, scale, splits,

@@ -38,6 +38,8 @@ _SIGNATURES = {
                         f32, vp, vp],
     "tw_attn_decode": [vp, ll, vp, vp, i32, vp, ll, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp, vp,
                        vp],
+    "tw_attn_decode_tc": [vp, ll, vp, vp, i32, i32, vp, ll, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp, vp,
+                          vp, vp],
     "tw_moe_router": [vp, ll, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "tw_moe_align": [vp, i32, i32, i32, vp, vp, vp, i32, vp, vp],
     "tw_moe_scatter": [vp, ll, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],
