@@ -201,7 +201,9 @@ def test_attn_prefill(hq, hkv, D, page, seqs, variant):
     (6, 1, 128, 64, [300] * 40),
     (4, 2, 64, 16, [129, 4096]),
 ])
-def test_attn_decode(hq, hkv, D, page, kvs):
+@pytest.mark.parametrize("variant", ["simt", None])     # None: the library's choice (tensor cores where they apply)
+def test_attn_decode(hq, hkv, D, page, kvs, variant):
+    ops.set_decode_variant(variant)
     seqs = [(1, kv) for kv in kvs]
     kc, vc, bt, cu, kv_lens = _make_paged(seqs, hkv, D, page)
     T = len(kvs)
@@ -210,8 +212,12 @@ def test_attn_decode(hq, hkv, D, page, kvs):
     expect = ref.paged_attention(q, kc, vc, cu, kv_lens, bt, hq, hkv, D, scale)
     out = torch.zeros_like(q)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    ops.attn_decode(q, kc, vc, out, i32(list(range(T))), i32(list(range(T))), i32(kv_lens), T, bt, hq, hkv, D,
-                    scale, max(kvs))
+    try:
+        ops.attn_decode(q, kc, vc, out, i32(list(range(T))), i32(list(range(T))), i32(kv_lens), T, bt, hq, hkv, D,
+                        scale, max(kvs))
+        torch.cuda.synchronize()
+    finally:
+        ops.set_decode_variant(None)
     close(out, expect, atol=2e-2, rtol=3e-2)
 
 

@@ -196,8 +196,9 @@ class ModelRunner:
             if m is None:
                 parts.append(None)
                 continue
-            hkv = self.model.layers[0].attn.hkv
-            splits = ops.decode_splits(m.num_single, hkv, m.max_kv_len, self.model.rt.sm_count)
+            a = self.model.layers[0].attn
+            splits = ops.decode_plan(m.num_single, a.hq, a.hkv, a.head_dim, self.block_size, m.max_kv_len,
+                                     self.model.rt.sm_count)
             parts.append((m.num_actual_tokens, m.num_seqs, m.num_tiles, m.num_single, m.block_table.shape[1], splits))
         return tuple(parts)
 
