@@ -23,7 +23,7 @@ SHAPES = [  # batch, keys per sequence, query heads, KV heads (per rank), page
 ]
 
 
-def run_case(B, kv, hq, hkv, page, D=128):
+def run_case(B, kv, hq, hkv, page, variants=("simt", "tc"), D=128):
     mb = (kv + page - 1) // page
     nb = B * mb + 2
     kc = torch.randn(nb, page, hkv, D, device=DEV, dtype=BF)
@@ -35,7 +35,7 @@ def run_case(B, kv, hq, hkv, page, D=128):
     out = torch.zeros_like(q)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
     res, first = {}, None
-    for var in ("simt", "tc"):
+    for var in variants:
         ops.set_decode_variant(var)
         launch = lambda: ops.attn_decode(q, kc, vc, out, rows, rows, lens, B, bt, hq, hkv, D, D ** -0.5, kv)  # noqa: E731
         for _ in range(3):
@@ -55,17 +55,23 @@ def run_case(B, kv, hq, hkv, page, D=128):
     ops.set_decode_variant(None)
     ops.check_status()
     kv_bytes = 2 * B * kv * hkv * D * 2
-    return dict(batch=B, kv_len=kv, q_heads=hq, kv_heads=hkv, page=page, simt_us=round(res["simt"], 1),
-                tc_us=round(res["tc"], 1), speedup=round(res["simt"] / res["tc"], 2),
-                simt_tb_s=round(kv_bytes / res["simt"] / 1e6, 2), tc_tb_s=round(kv_bytes / res["tc"] / 1e6, 2),
-                max_abs_diff=float((out.float() - first.float()).abs().max()))
+    row = dict(batch=B, kv_len=kv, q_heads=hq, kv_heads=hkv, page=page)
+    for var in variants:
+        row[var + "_us"] = round(res[var], 1)
+        row[var + "_tb_s"] = round(kv_bytes / res[var] / 1e6, 2)
+    row["speedup"] = round(res[variants[0]] / res[variants[-1]], 2)        # first variant over last
+    row["max_abs_diff"] = float((out.float() - first.float()).abs().max())
+    return row
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--csv", default=None, help="also write the rows to <results dir>/<NAME>.csv")
+    ap.add_argument("--variants", default="simt,tc",
+                    help="kernels to time, in order: simt, tc (one CTA per work item), tcp (persistent CTAs)")
     ns = ap.parse_args()
-    rows = [run_case(*s) for s in SHAPES]
+    variants = tuple(ns.variants.split(","))
+    rows = [run_case(*s, variants=variants) for s in SHAPES]
     for r in rows:
         print(json.dumps(r), flush=True)
     if ns.csv:

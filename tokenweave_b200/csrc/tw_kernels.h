@@ -85,6 +85,11 @@ int tw_attn_decode_tc(const void* q, long long ldq, const void* k_cache, const v
                       const int* tok_kvlen, int n_tok, const int* block_table, int max_blocks, int hq, int hkv,
                       int D, float scale, int splits, float* part_o, float* part_ml, uint32_t* status,
                       cudaStream_t stream);
+int tw_attn_decode_tc_persistent(const void* q, long long ldq, const void* k_cache, const void* v_cache,
+                                 int num_blocks, int page, void* out, long long ldo, const int* tok_row,
+                                 const int* tok_seq, const int* tok_kvlen, int n_tok, const int* block_table,
+                                 int max_blocks, int hq, int hkv, int D, float scale, int splits, float* part_o,
+                                 float* part_ml, int max_ctas, uint32_t* status, cudaStream_t stream);
 
 // ---- mixture of experts (moe.cu) ----
 int tw_moe_router(const void* x, long long ldx, const void* wg, float* topk_w, int* topk_ids, float* logits_out,

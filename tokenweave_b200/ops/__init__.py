@@ -405,16 +405,23 @@ _decode_ws: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
 # Decode attention kernel: "tc" (attn_decode_tc.cu: tcgen05; used for grouped-query models with head size 128
 # once a sequence of the step has 256 keys, 1.4 to 1.8 times faster than the SIMT kernel on B200) or "simt"
-# (attn_decode.cu, every other case). TW_DECODE_TC=0 forces "simt".
-_decode_variant = "tc" if os.environ.get("TW_DECODE_TC", "1") == "1" else "simt"
+# (attn_decode.cu, every other case). TW_DECODE_TC=0 forces "simt". "tcp" is the persistent form of "tc"
+# (one CTA per SM walks the work items; TW_DECODE_TC=persistent): written and compiled, not yet run on a GPU,
+# so nothing selects it by default.
+def _env_decode_variant() -> str:
+    v = os.environ.get("TW_DECODE_TC", "1")
+    return "tcp" if v == "persistent" else "tc" if v == "1" else "simt"
+
+
+_decode_variant = _env_decode_variant()
 
 
 def set_decode_variant(name: Optional[str]) -> None:
-    """``"tc"`` / ``"simt"``; None restores the environment's choice."""
+    """``"tc"`` / ``"tcp"`` / ``"simt"``; None restores the environment's choice."""
     global _decode_variant
-    if name not in (None, "tc", "simt"):
+    if name not in (None, "tc", "tcp", "simt"):
         raise ValueError(name)
-    _decode_variant = name or ("tc" if os.environ.get("TW_DECODE_TC", "1") == "1" else "simt")
+    _decode_variant = name or _env_decode_variant()
 
 
 def decode_splits(n_tok: int, hkv: int, max_kv_len: int, sm_count: int = 148) -> int:
@@ -441,14 +448,19 @@ def decode_splits_tc(ctas: int, tiles: int, sm_count: int = 148) -> int:
 
 
 def decode_plan(n_tok: int, hq: int, hkv: int, head_dim: int, page: int, max_kv_len: int,
-                sm_count: int = 148) -> tuple[bool, int]:
-    """(tensor-core kernel?, key splits) for a decode launch: everything that shapes the launch besides the
-    tensor sizes, so a CUDA-graph signature that includes it replays the launch it captured."""
-    use_tc = (_decode_variant == "tc" and head_dim == 128 and hq // hkv <= 16 and max_kv_len >= 256
+                sm_count: int = 148) -> tuple[str, int]:
+    """(kernel, key splits) for a decode launch: everything that shapes the launch besides the tensor sizes,
+    so a CUDA-graph signature that includes it replays the launch it captured."""
+    use_tc = (_decode_variant in ("tc", "tcp") and head_dim == 128 and hq // hkv <= 16 and max_kv_len >= 256
               and 8 <= page <= 128 and 128 % page == 0)
+    tiles = (max_kv_len + 127) // 128
+    if use_tc and _decode_variant == "tcp":
+        # persistent CTAs: items of about four key tiles balance the SMs without whole-wave effects
+        ctas = n_tok * hkv
+        return "tcp", 1 if ctas >= 6 * sm_count else max(1, min(tiles // 4, 32))
     if use_tc:
-        return True, decode_splits_tc(n_tok * hkv, (max_kv_len + 127) // 128, sm_count)
-    return False, decode_splits(n_tok, hkv, max_kv_len, sm_count)
+        return "tc", decode_splits_tc(n_tok * hkv, tiles, sm_count)
+    return "simt", decode_splits(n_tok, hkv, max_kv_len, sm_count)
 
 
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
@@ -460,7 +472,7 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o
         return
     _check_bf16(q, k_cache, v_cache, out)
     page = k_cache.shape[1]
-    use_tc, splits = decode_plan(n_tok, hq, hkv, head_dim, page, max_kv_len, sm_count)
+    kernel, splits = decode_plan(n_tok, hq, hkv, head_dim, page, max_kv_len, sm_count)
     part_o = part_ml = None
     if splits > 1:
         key = (q.device.index, n_tok * hq * splits * head_dim)
@@ -472,11 +484,18 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o
                 _decode_ws.clear()
             _decode_ws[key] = ws
         part_o, part_ml = ws
-    if use_tc:
+    if kernel == "tc":
         _native.call("tw_attn_decode_tc", q.data_ptr(), _row_stride(q), k_cache.data_ptr(), v_cache.data_ptr(),
                      k_cache.shape[0], page, out.data_ptr(), _row_stride(out), tok_row.data_ptr(), tok_seq.data_ptr(),
                      tok_kvlen.data_ptr(), n_tok, block_table.data_ptr(), block_table.shape[1], hq, hkv, head_dim,
                      scale, splits, _p(part_o), _p(part_ml), status_word(q.device).data_ptr(), _stream())
+        return
+    if kernel == "tcp":
+        _native.call("tw_attn_decode_tc_persistent", q.data_ptr(), _row_stride(q), k_cache.data_ptr(),
+                     v_cache.data_ptr(), k_cache.shape[0], page, out.data_ptr(), _row_stride(out), tok_row.data_ptr(),
+                     tok_seq.data_ptr(), tok_kvlen.data_ptr(), n_tok, block_table.data_ptr(), block_table.shape[1], hq,
+                     hkv, head_dim, scale, splits, _p(part_o), _p(part_ml), sm_count if sm_count != 148 else 0,
+                     status_word(q.device).data_ptr(), _stream())
         return
     _native.call("tw_attn_decode", q.data_ptr(), _row_stride(q), k_cache.data_ptr(), v_cache.data_ptr(), page,
                  out.data_ptr(), _row_stride(out), tok_row.data_ptr(), tok_seq.data_ptr(), tok_kvlen.data_ptr(),

@@ -40,6 +40,8 @@ _SIGNATURES = {
                        vp],
     "tw_attn_decode_tc": [vp, ll, vp, vp, i32, i32, vp, ll, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp, vp,
                           vp, vp],
+    "tw_attn_decode_tc_persistent": [vp, ll, vp, vp, i32, i32, vp, ll, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32,
+                                     i32, vp, vp, i32, vp, vp],
     "tw_moe_router": [vp, ll, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "tw_moe_align": [vp, i32, i32, i32, vp, vp, vp, i32, vp, vp],
     "tw_moe_scatter": [vp, ll, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],
