@@ -1,9 +1,6 @@
 """TokenWeave config files, split planner and split metadata."""
 import json
 
-import numpy as np
-import pytest
-
 from tokenweave_b200.tokenweave.config import CONFIG_DIR, TokenWeavePlanner, load_config
 from tokenweave_b200.worker.split_metadata import split_batch
 from tokenweave_b200.layers.attention import plan_attention

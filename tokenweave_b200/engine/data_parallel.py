@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import dataclasses
 import itertools
-from typing import AsyncIterator, Optional, Union
+from typing import AsyncIterator, Union
 
 from ..config import EngineArgs
 from ..outputs import RequestOutput
