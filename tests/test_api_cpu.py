@@ -2,6 +2,7 @@
 import argparse
 import json
 
+import pytest
 import torch
 
 from tokenweave_b200 import LLM, SamplingParams
@@ -144,3 +145,31 @@ def test_guided_choice_generates_exactly_one_of_the_choices():
     assert ids in ([5, 6, 7], [9, 9])
     llm.shutdown()
     raw.shutdown()
+
+
+def test_classify_with_a_sequence_classification_checkpoint(tmp_path):
+    from tokenweave_b200 import LLM
+    from tokenweave_b200.config import MODEL_PRESETS, ModelConfig
+    from tokenweave_b200.models.loader import save_hf_checkpoint
+    from tw_testing import hf_config_dict, make_hf_state, naive_logits
+    cfg = ModelConfig(name="tiny-llama", **MODEL_PRESETS["tiny-llama"])
+    st = make_hf_state(cfg, seed=8)
+    head = torch.randn(3, cfg.hidden_size, generator=torch.Generator().manual_seed(1)) * 0.2
+    ckpt = {k: v for k, v in st.items() if k != "lm_head.weight"}
+    ckpt["score.weight"] = head
+    hf = hf_config_dict(cfg)
+    hf["architectures"] = ["LlamaForSequenceClassification"]
+    save_hf_checkpoint(ckpt, hf, str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", skip_tokenizer_init=True, block_size=16,
+              max_num_batched_tokens=64)
+    prompts = [list(range(7, 90)), [5, 6, 7]]
+    outs = llm.classify(prompts)
+    for o, p in zip(outs, prompts):
+        want = torch.softmax(naive_logits(cfg, {**st, "lm_head.weight": head}, p)[-1], -1)
+        assert len(o.probs) == 3 and abs(sum(o.probs) - 1.0) < 1e-5
+        assert torch.allclose(torch.tensor(o.probs), want, atol=1e-4)
+    llm.shutdown()
+    plain = LLM("tiny-llama", dtype="float32", device="cpu", skip_tokenizer_init=True, block_size=16)
+    with pytest.raises(ValueError):
+        plain.classify([[1, 2, 3]])
+    plain.shutdown()

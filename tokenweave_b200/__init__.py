@@ -4,7 +4,8 @@ token-split compute/communication overlap and fused all-reduce + RMSNorm."""
 __version__ = "0.1.0"
 
 from .sampling_params import BeamSearchParams, SamplingParams  # noqa: E402,F401
-from .outputs import (BeamSearchOutput, BeamSearchSequence, CompletionOutput, PoolingOutput,  # noqa: E402,F401
+from .outputs import (BeamSearchOutput, BeamSearchSequence, ClassificationOutput, CompletionOutput,  # noqa: E402,F401
+                      PoolingOutput,
                       RequestOutput)
 
 

@@ -13,7 +13,7 @@ from typing import Any, Optional, Sequence, Union
 
 from ..config import EngineArgs, ModelConfig
 from ..engine.llm_engine import LLMEngine
-from ..outputs import BeamSearchOutput, BeamSearchSequence, PoolingOutput, RequestOutput
+from ..outputs import BeamSearchOutput, BeamSearchSequence, ClassificationOutput, PoolingOutput, RequestOutput
 from ..sampling_params import BeamSearchParams, SamplingParams
 from ..utils.logging import init_logger
 
@@ -155,6 +155,33 @@ class LLM:
     def embed(self, prompts: Union[PromptType, Sequence[PromptType]]) -> list["PoolingOutput"]:
         """L2-normalised :meth:`encode` (``LLM.embed`` of the reference)."""
         return self.encode(prompts, normalize=True)
+
+    def classify(self, prompts: Union[PromptType, Sequence[PromptType]]) -> list["ClassificationOutput"]:
+        """Class probabilities for checkpoints with a sequence-classification head (``score.weight`` of the
+        ``*ForSequenceClassification`` layouts): the head is applied to the last token's final-norm hidden
+        state and soft-maxed (``LLM.classify`` of the reference, pooler ``PoolingType.LAST`` + softmax)."""
+        import torch
+        head = self._classifier_head()
+        res = []
+        for o in self.encode(prompts):
+            probs = torch.softmax(o.data.float() @ head.t(), dim=-1)
+            res.append(ClassificationOutput(o.request_id, o.prompt_token_ids, probs.tolist()))
+        return res
+
+    def _classifier_head(self):
+        head = getattr(self, "_score_head", None)
+        if head is None:
+            from ..models.loader import iter_checkpoint
+            path = self.llm_engine.config.model.path
+            if path is not None:
+                for name, tensor in iter_checkpoint(path):
+                    if name in ("score.weight", "classifier.weight"):
+                        head = tensor.float()
+                        break
+            if head is None:
+                raise ValueError("classify() needs a checkpoint with a sequence-classification head (score.weight)")
+            self._score_head = head
+        return head
 
     def score(self, text_1: Union[PromptType, Sequence[PromptType]], text_2: Union[PromptType, Sequence[PromptType]]) -> list[float]:
         """Cosine similarity of the embeddings of ``text_1`` and ``text_2`` (one-to-many or pairwise), the

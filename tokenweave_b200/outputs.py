@@ -60,3 +60,11 @@ class PoolingOutput:
     request_id: str
     prompt_token_ids: list[int]
     data: "object"
+
+
+@dataclass
+class ClassificationOutput:
+    """Result of ``LLM.classify``: class probabilities from the checkpoint's sequence-classification head."""
+    request_id: str
+    prompt_token_ids: list[int]
+    probs: list[float]
