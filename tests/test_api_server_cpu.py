@@ -106,6 +106,23 @@ def test_bad_requests_are_rejected_and_the_server_keeps_serving(client):
     assert m.status_code == 200 and "tokenweave:generation_tokens_total" in m.text
 
 
+def test_embeddings_endpoint_matches_the_offline_api(client):
+    import torch
+    from tokenweave_b200 import LLM
+    r = client.post("/v1/embeddings", json={"input": ["hello world", "abc"]})
+    assert r.status_code == 200, r.text
+    data = r.json()["data"]
+    assert [d["index"] for d in data] == [0, 1] and r.json()["usage"]["prompt_tokens"] == 12 + 4
+    llm = LLM("tiny-llama", dtype="float32", device="cpu", block_size=16, max_num_batched_tokens=128, seed=1)
+    want = llm.embed(["hello world", "abc"])
+    llm.shutdown()
+    for d, w in zip(data, want):
+        assert torch.allclose(torch.tensor(d["embedding"]), w.data, atol=1e-5)
+    raw = client.post("/v1/embeddings", json={"input": [256, 104, 105], "normalize": False}).json()["data"][0]["embedding"]
+    assert abs(sum(x * x for x in raw) ** 0.5 - 1.0) > 1e-3          # not normalised
+    assert client.post("/classify", json={"input": "x"}).status_code == 400     # no classification head here
+
+
 def test_adapter_selected_by_model_name(tmp_path):
     from starlette.testclient import TestClient
     from tokenweave_b200.config import MODEL_PRESETS, ModelConfig

@@ -91,6 +91,11 @@ class EngineCore:
             for rid, items in result.prompt_logprobs.items():
                 if rid in by_id:
                     by_id[rid].prompt_logprobs.update(items)      # keyed by position: a recompute overwrites
+        if result.pooled:
+            for s in sched.scheduled:
+                vec = result.pooled.get(s.request.request_id)
+                if vec is not None and s.request.pooled is None:
+                    s.request.pooled = vec
         touched = self.scheduler.update_from_output(
             sched, ModelRunnerOutput(result.req_ids, result.sampled_token_ids, result.logprobs))
         self._last_logprobs = dict(zip(result.req_ids, result.logprobs)) if result.logprobs else {}

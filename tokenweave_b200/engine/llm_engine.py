@@ -192,7 +192,7 @@ class LLMEngine:
             got = parent.children[0].prompt_logprobs        # the children share the prompt
             plp = [None] + [got.get(p) for p in range(1, len(parent.prompt_token_ids))]
         return RequestOutput(parent.request_id, parent.prompt, parent.prompt_token_ids, comps, finished, metrics,
-                             prompt_logprobs=plp)
+                             prompt_logprobs=plp, pooled=parent.children[0].pooled)
 
     def shutdown(self) -> None:
         self.core.shutdown()

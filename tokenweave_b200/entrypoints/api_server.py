@@ -228,6 +228,63 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
                 usage[k] += v
         return {"id": rid, "object": "text_completion", "created": created, "model": name, "choices": choices, "usage": usage}
 
+    # ---- /v1/embeddings, /classify -------------------------------------------------------------
+    async def pooled_vectors(body: dict, rid: str):
+        """Last-token hidden state of every input (text, token ids, or a list of either)."""
+        prompts = normalise_prompts(body.get("input", body.get("prompt")))
+        if tokenizer is None and any(isinstance(p, str) for p in prompts):
+            raise ValueError("text inputs need a tokenizer; send token ids")
+        sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, detokenize=False, pooling=True)
+        return await run_all(prompts, sp, rid, pick_adapter(body))
+
+    @app.post("/v1/embeddings")
+    async def embeddings(req: Request):
+        body = await req.json()
+        rid = "embd-" + uuid.uuid4().hex
+        try:
+            outs = await pooled_vectors(body, rid)
+        except (ValueError, TypeError) as e:
+            return error(400, str(e))
+        except EngineDeadError as e:
+            return error(500, str(e), "server_error")
+        data, n_tok = [], 0
+        for i, out in enumerate(outs):
+            vec = out.pooled
+            if body.get("normalize", True):
+                vec = vec / vec.norm().clamp_min(1e-12)
+            data.append({"object": "embedding", "index": i, "embedding": vec.tolist()})
+            n_tok += len(out.prompt_token_ids)
+        return {"id": rid, "object": "list", "model": name, "data": data,
+                "usage": {"prompt_tokens": n_tok, "total_tokens": n_tok}}
+
+    score_head = {}
+
+    @app.post("/classify")
+    async def classify(req: Request):
+        body = await req.json()
+        import torch
+        if "w" not in score_head:
+            from ..models.loader import iter_checkpoint
+            path = engine.engine.config.model.path
+            for tname, tensor in (iter_checkpoint(path) if path else ()):
+                if tname in ("score.weight", "classifier.weight"):
+                    score_head["w"] = tensor.float()
+                    break
+        if "w" not in score_head:
+            return error(400, "the served checkpoint has no sequence-classification head (score.weight)")
+        rid = "cls-" + uuid.uuid4().hex
+        try:
+            outs = await pooled_vectors(body, rid)
+        except (ValueError, TypeError) as e:
+            return error(400, str(e))
+        except EngineDeadError as e:
+            return error(500, str(e), "server_error")
+        data = []
+        for i, out in enumerate(outs):
+            probs = torch.softmax(out.pooled.float() @ score_head["w"].t(), dim=-1)
+            data.append({"index": i, "label": int(probs.argmax()), "probs": probs.tolist()})
+        return {"id": rid, "object": "list", "model": name, "data": data}
+
     # ---- /v1/chat/completions -----------------------------------------------------------------
     def chat_prompt(messages: list, add_generation_prompt: bool = True) -> str:
         if hasattr(tokenizer, "apply_chat_template") and getattr(tokenizer, "chat_template", None):

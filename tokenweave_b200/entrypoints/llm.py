@@ -138,15 +138,11 @@ class LLM:
         if isinstance(prompts, (str, dict)) or (isinstance(prompts, list) and prompts and isinstance(prompts[0], int)):
             prompts = [prompts]
         prompts = list(prompts)
-        self.collective_rpc("set_capture_hidden", True)
-        try:
-            outs = self.generate(prompts, SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, detokenize=False))
-            captured = self.collective_rpc("take_captured_hidden")[0]
-        finally:
-            self.collective_rpc("set_capture_hidden", False)
+        outs = self.generate(prompts, SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, detokenize=False,
+                                                     pooling=True))
         res = []
         for o in outs:
-            vec = captured[o.request_id]
+            vec = o.pooled
             if normalize:
                 vec = vec / vec.norm().clamp_min(1e-12)
             res.append(PoolingOutput(request_id=o.request_id, prompt_token_ids=o.prompt_token_ids, data=vec))

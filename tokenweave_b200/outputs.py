@@ -39,6 +39,7 @@ class RequestOutput:
     # with ``SamplingParams.prompt_logprobs``: one entry per prompt token, None for the first, then
     # ``{token id: log-probability}`` holding the prompt token itself and the k most likely tokens there
     prompt_logprobs: Optional[list] = None
+    pooled: Optional[object] = None      # with ``SamplingParams.pooling``: fp32 hidden state (host tensor)
 
 
 @dataclass

@@ -25,6 +25,9 @@ class SamplingParams:
     # log-probability of every prompt token given its prefix, plus the k most likely tokens at each position
     # (vllm/sampling_params.py ``prompt_logprobs``); such a request does not reuse cached prefixes
     prompt_logprobs: Optional[int] = None
+    # pooling request: the final-norm hidden state at the last prompt token comes back in
+    # ``RequestOutput.pooled`` (what ``LLM.encode`` and the server's embedding endpoint use)
+    pooling: bool = False
     detokenize: bool = True
     skip_special_tokens: bool = True
     logit_bias: Optional[dict] = None                   # token id -> additive bias (clamped to [-100, 100])

@@ -60,6 +60,7 @@ class StepResult:
     device_time_ms: Optional[float] = None
     # request id -> [(prompt position, {token id: log-probability})] for the prompt positions of this step
     prompt_logprobs: Optional[dict] = None
+    pooled: Optional[dict] = None        # request id -> final-norm hidden state (host fp32) of pooling requests
 
 
 @dataclass
@@ -100,6 +101,7 @@ class ModelRunner:
         self.lora = None                     # LoRAManager when the engine was built with enable_lora
         self.capture_hidden = False          # pooling requests: keep the final-norm hidden row of every sampled position
         self.captured_hidden: dict = {}
+        self._want_pooled = False            # this step samples for a request with SamplingParams.pooling
         self._h2d_done = torch.cuda.Event() if pin else None   # guards reuse of the pinned staging buffers
         # CUDA graphs: a step whose shape signature has been seen before is replayed from a captured graph
         self.use_graphs = bool(tw.use_cuda_graphs) and pin
@@ -207,7 +209,7 @@ class ModelRunner:
         if n_logits == 0:
             return None, None
         rows = hidden.index_select(0, self._rows_dev[:n_logits])
-        if self.capture_hidden:
+        if self.capture_hidden or self._want_pooled:
             self._last_hidden_rows = rows
         logits = self.model.compute_logits(rows)
         return logits, (ops.argmax(logits) if greedy else None)
@@ -328,7 +330,9 @@ class ModelRunner:
             self._rows_host[:n_logits] = torch.as_tensor(logits_rows, dtype=torch.long)
             self._rows_dev[:n_logits].copy_(self._rows_host[:n_logits], non_blocking=True)
         lora_active = self.lora is not None and self.lora.active      # row gathers of a step are not graph-stable
-        if self.use_graphs and not self.capture_logits and not self.capture_hidden and not lora_active:
+        self._want_pooled = any(r.sampling_params.pooling for r in reqs)
+        if (self.use_graphs and not self.capture_logits and not self.capture_hidden and not lora_active
+                and not self._want_pooled):
             logits, greedy_ids = self._run_graphed(self._signature(step_in, n_logits, greedy), step_in, n_logits, greedy)
         else:
             logits, greedy_ids = self._forward_and_logits(step_in, n_logits, greedy)
@@ -336,6 +340,11 @@ class ModelRunner:
         lp = None
         d2h = 0
         prompt_lp = self._prompt_logprobs(prompt_lp_jobs) if prompt_lp_jobs else None
+        pooled = None
+        if logits_rows and self._want_pooled:
+            host_rows = self._last_hidden_rows.detach().float().cpu()
+            pooled = {rid: host_rows[i].clone() for i, (rid, r) in enumerate(zip(sample_reqs, reqs))
+                      if r.sampling_params.pooling}
         if logits_rows:
             if self.capture_hidden:
                 rows = self._last_hidden_rows.detach().float().cpu()
@@ -380,7 +389,7 @@ class ModelRunner:
         lp_by_req = dict(zip(sample_reqs, lp)) if lp is not None else None
         return StepResult(req_ids, [sampled.get(r) for r in req_ids],
                           [lp_by_req.get(r) for r in req_ids] if lp_by_req is not None else None,
-                          prompt_logprobs=prompt_lp)
+                          prompt_logprobs=prompt_lp, pooled=pooled)
 
     def _prompt_logprobs(self, jobs: list[tuple[str, int, int, int]]) -> dict:
         """Log-probabilities of the prompt tokens computed in this step: the final-norm hidden rows of the
