@@ -67,10 +67,12 @@ class IncrementalDetokenizer:
         window_new = self.tokenizer.decode(self.token_ids[start:], skip_special_tokens=self.skip_special)
         if window_new.endswith("�"):
             return None              # incomplete UTF-8 sequence: wait for the next token
-        self.text += window_new[len(window_old):]
+        delta = window_new[len(window_old):]
+        self.text += delta
         self._emitted_prefix = len(self.token_ids)
         for s in self.stop:
-            pos = self.text.find(s)
+            # a new match must touch the text that was just added
+            pos = self.text.find(s, max(0, len(self.text) - len(delta) - len(s) + 1))
             if pos >= 0:
                 self.text = self.text[:pos]
                 return s
