@@ -110,3 +110,78 @@ def test_prompt_too_long_rejected():
     s, _ = make(max_len=32)
     with pytest.raises(ValueError):
         s.add_request(req(0, 40))
+
+
+# ---- randomised runs: invariants that must hold for any arrival pattern ---------------------------
+def _fuzz_once(seed, caching, spec_k):
+    import random
+    from tokenweave_b200.engine.spec_decode import SpecDecodeConfig
+    rng = random.Random(seed)
+    block = rng.choice([4, 16])
+    num_blocks = rng.randrange(12, 40)
+    budget = rng.choice([16, 48, 96])
+    kv = KVCacheManager(num_blocks, block, caching)
+    spec = SpecDecodeConfig(num_speculative_tokens=spec_k)
+    s = Scheduler(SchedulerConfig(budget, rng.randrange(2, 7), True, 512), kv, spec)
+    capacity = (num_blocks - 1) * block
+    pending = []
+    for i in range(rng.randrange(4, 14)):
+        n = rng.randrange(1, min(120, capacity // 2))
+        shared = [1, 2, 3, 4] * (n // 8)                 # common prefixes so that the prefix cache gets hits
+        ids = (shared + [rng.randrange(5, 50) for _ in range(n)])[:n]
+        pending.append(Request(str(i), ids, SamplingParams(max_tokens=rng.randrange(1, 12), temperature=0,
+                                                            stop_token_ids=[49] if rng.random() < 0.3 else None)))
+    expected_prompt = {r.request_id: list(r.prompt_token_ids) for r in pending}
+    finished, steps = {}, 0
+    while pending or s.has_unfinished_requests():
+        steps += 1
+        assert steps < 3000, "the scheduler stopped making progress"
+        for _ in range(rng.randrange(0, 3)):
+            if pending:
+                s.add_request(pending.pop())
+        if not s.has_unfinished_requests():
+            continue
+        out = s.schedule()
+        assert out.total_num_tokens <= budget
+        assert len({x.request.request_id for x in out.scheduled}) == len(out.scheduled)
+        owned = [b for r in s.running for b in r.block_ids]
+        if not caching:
+            assert len(owned) == len(set(owned)), "a block is owned twice"
+        for x in out.scheduled:
+            r = x.request
+            assert x.num_new_tokens >= 1
+            assert len(r.block_ids) * block >= x.num_computed_tokens + x.num_new_tokens, "not enough slots"
+        toks = []
+        for x in out.scheduled:
+            if x.spec_token_ids:        # the model confirms a random number of drafts, then emits one more token
+                keep = rng.randrange(0, len(x.spec_token_ids) + 1)
+                toks.append(list(x.spec_token_ids[:keep]) + [rng.randrange(5, 50)])
+            else:
+                toks.append(rng.randrange(5, 50))
+        touched = s.update_from_output(out, ModelRunnerOutput([x.request.request_id for x in out.scheduled], toks))
+        for r in touched:
+            if r.status.finished:
+                finished[r.request_id] = r
+        if rng.random() < 0.05 and s.running:      # a client walks away
+            victim = rng.choice(s.running)
+            s.abort_request(victim.request_id)
+            finished[victim.request_id] = victim
+    assert set(finished) == set(expected_prompt)
+    for rid, r in finished.items():
+        assert r.prompt_token_ids == expected_prompt[rid]
+        if r.status != RequestStatus.FINISHED_ABORTED:
+            assert 1 <= len(r.output_token_ids) <= r.sampling_params.max_tokens
+            if r.status == RequestStatus.FINISHED_STOPPED:
+                assert r.output_token_ids[-1] == 49 and 49 not in r.output_token_ids[:-1]
+            else:
+                assert len(r.output_token_ids) == r.sampling_params.max_tokens
+        assert r.block_ids == []
+    # every block is back in the pool and nothing holds a reference
+    assert kv.pool.num_free == num_blocks - 1
+    assert all(c == 0 for c in kv.pool.ref[1:])
+
+
+@pytest.mark.parametrize("caching,spec_k", [(False, 0), (True, 0), (False, 3), (True, 2)])
+def test_random_workloads_keep_the_invariants(caching, spec_k):
+    for seed in range(60):
+        _fuzz_once(seed * 7 + spec_k, caching, spec_k)
