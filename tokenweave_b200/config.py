@@ -198,10 +198,17 @@ class ParallelConfig:
     # (replica r uses devices [r * tp, (r + 1) * tp))
     data_parallel_size: int = 1
     data_parallel_rank: int = 0
+    # pipeline parallelism: the layers are cut into this many consecutive stages of tensor_parallel_size ranks
+    pipeline_parallel_size: int = 1
+
+    @property
+    def world_size(self) -> int:
+        """Ranks of one engine replica."""
+        return self.tensor_parallel_size * self.pipeline_parallel_size
 
     @property
     def device_offset(self) -> int:
-        return self.data_parallel_rank * self.tensor_parallel_size
+        return self.data_parallel_rank * self.world_size
 
 
 @dataclass
@@ -274,6 +281,7 @@ class EngineArgs:
     max_model_len: Optional[int] = None
     tensor_parallel_size: int = 1
     distributed_executor_backend: str = "auto"
+    pipeline_parallel_size: int = 1       # pipeline stages (consecutive layer ranges), each a tensor-parallel group
     data_parallel_size: int = 1           # engine replicas behind one front end (entrypoints/api_server.py)
     data_parallel_rank: int = 0           # which replica this engine is: its GPUs start at rank * tensor_parallel_size
     block_size: int = 128
@@ -331,7 +339,8 @@ class EngineArgs:
                               self.enable_prefix_caching),
             parallel=ParallelConfig(self.tensor_parallel_size, self.distributed_executor_backend,
                                     self.disable_custom_all_reduce, data_parallel_size=self.data_parallel_size,
-                                    data_parallel_rank=self.data_parallel_rank),
+                                    data_parallel_rank=self.data_parallel_rank,
+                                    pipeline_parallel_size=self.pipeline_parallel_size),
             scheduler=SchedulerConfig(budget, self.max_num_seqs, self.enable_chunked_prefill, max_len),
             tokenweave=TokenWeaveConfig(mode=self.tokenweave_mode, config_path=self.tokenweave_config,
                                         overlap_threshold=self.tokenweave_threshold,

@@ -45,7 +45,7 @@ class Executor:
 def make_executor(config: EngineConfig) -> Executor:
     import os
     backend = config.parallel.distributed_executor_backend
-    tp = config.parallel.tensor_parallel_size
+    tp = config.parallel.world_size          # ranks of the replica: tensor-parallel x pipeline-parallel
     if backend == "auto":
         if tp == 1:
             backend = "uni"

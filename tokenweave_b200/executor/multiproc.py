@@ -75,7 +75,7 @@ def _worker_main(config: EngineConfig, rank: int, init_method: str, mq_handle: t
 class MultiprocExecutor(Executor):
     def __init__(self, config: EngineConfig):
         super().__init__(config)
-        self.world = config.parallel.tensor_parallel_size
+        self.world = config.parallel.world_size
         ctx = mp.get_context(envs.TW_WORKER_MULTIPROC_METHOD)
         from ..parallel.state import TPState  # noqa: F401  (import check before spawning)
         import socket

@@ -20,13 +20,13 @@ class UniProcExecutor(Executor):
             rank = int(os.environ.get("RANK", "0"))
             local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
             world = int(os.environ.get("WORLD_SIZE", "1"))
-            if world != config.parallel.tensor_parallel_size:
-                raise ValueError(f"WORLD_SIZE={world} does not match tensor_parallel_size="
-                                 f"{config.parallel.tensor_parallel_size}")
+            if world != config.parallel.world_size:
+                raise ValueError(f"WORLD_SIZE={world} does not match tensor_parallel_size x pipeline_parallel_size="
+                                 f"{config.parallel.world_size}")
         else:
-            if config.parallel.tensor_parallel_size != 1:
+            if config.parallel.world_size != 1:
                 raise ValueError("the in-process executor runs one rank; use the 'mp' or "
-                                 "'external_launcher' backend for tensor parallelism")
+                                 "'external_launcher' backend for tensor or pipeline parallelism")
             rank, local_rank = 0, config.parallel.device_offset
         self.rank = rank
         self.worker = Worker(config, rank, local_rank)
@@ -35,12 +35,12 @@ class UniProcExecutor(Executor):
 
     def determine_num_blocks(self) -> int:
         n = self.worker.determine_num_blocks()
-        if self.config.parallel.tensor_parallel_size > 1:
+        if self.config.parallel.world_size > 1:
             import torch
             import torch.distributed as dist
             from ..parallel.state import get_tp
             t = torch.tensor([n], dtype=torch.int64)
-            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=get_tp().cpu_group)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=get_tp().world_cpu_group)       # all stages agree
             n = int(t.item())
         return n
 

@@ -27,7 +27,7 @@ from ..layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowPa
 from ..layers.moe import FusedMoE
 from ..ops import reference
 from ..parallel.comm import TPCommunicator
-from ..parallel.state import get_tp
+from ..parallel.state import get_tp, recv_from_prev_stage, send_to_next_stage
 from ..parallel.symm_mem import SymmetricBuffer, create_symmetric_buffer
 from ..tokenweave import schedule
 from ..tokenweave.config import SplitPlan
@@ -177,10 +177,23 @@ class DecoderModel(nn.Module):
         self.cfg = cfg
         dt = cfg.dtype
         self.embed_tokens = VocabEmbedding(cfg.vocab_size, cfg.hidden_size, embedding_parallel, dtype=dt, device=device)
-        self.layers = nn.ModuleList([DecoderLayer(cfg, device=device) for _ in range(cfg.num_layers)])
+        # pipeline parallelism: this process holds a consecutive range of the layers (all of them at one stage;
+        # early stages take the remainder, vllm/distributed/utils.py ``get_pp_indices``)
+        tp = get_tp()
+        per, extra = divmod(cfg.num_layers, tp.pp_size)
+        self.first_layer = tp.pp_rank * per + min(tp.pp_rank, extra)
+        self.end_layer = self.first_layer + per + (1 if tp.pp_rank < extra else 0)
+        if self.end_layer == self.first_layer:
+            raise ValueError(f"{cfg.num_layers} layers cannot fill {tp.pp_size} pipeline stages")
+        self.layers = nn.ModuleList([DecoderLayer(cfg, device=device) for _ in range(self.first_layer, self.end_layer)])
         for i, layer in enumerate(self.layers):
-            layer.layer_idx = i
+            layer.layer_idx = self.first_layer + i
         self.norm_w = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dt, device=device), requires_grad=False)
+        # A stage that is not the last closes its last layer with the NEXT stage's first input norm (the fused
+        # collective applies the following block's norm), so it keeps a copy of that weight.
+        self.boundary_norm_w = None
+        if not tp.is_last_stage:
+            self.boundary_norm_w = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dt, device=device), requires_grad=False)
         self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, dtype=dt, device=device)
         self.rt: Optional[Runtime] = None
         self.tw_mode = "overlap"
@@ -213,28 +226,38 @@ class DecoderModel(nn.Module):
         assert Tp <= rt.hidden.shape[0], "step exceeds the staging buffer"
         hidden, residual = rt.hidden, rt.residual
         eps = cfg.rms_norm_eps
-        if Tp > T:
-            hidden[T:Tp].zero_()
-        self.embed_tokens(step.input_ids, out=hidden[:T])
-        pending = self.embed_tokens.parallel and self.tw_mode not in ("no_ar", "no_ar_no_ln")
-        if pending:
-            residual[:Tp].zero_()
-        else:
+        stage = get_tp()
+        if stage.is_first_stage:
             if Tp > T:
-                residual[T:Tp].zero_()
-            ops.rmsnorm_copy_(hidden[:T], residual[:T], self.layers[0].input_norm_w, eps)
+                hidden[T:Tp].zero_()
+            self.embed_tokens(step.input_ids, out=hidden[:T])
+            pending = self.embed_tokens.parallel and self.tw_mode not in ("no_ar", "no_ar_no_ln")
+            if pending:
+                residual[:Tp].zero_()
+            else:
+                if Tp > T:
+                    residual[T:Tp].zero_()
+                ops.rmsnorm_copy_(hidden[:T], residual[:T], self.layers[0].input_norm_w, eps)
+        else:
+            # the previous stage left the normalised input of our first layer and the residual stream (whatever
+            # its layout across the tensor-parallel ranks: the peer with the same TP rank holds the same rows)
+            recv_from_prev_stage(hidden[:Tp], residual[:Tp])
+            pending = False
+        close_w = self.norm_w if stage.is_last_stage else self.boundary_norm_w
         if plan.overlap:
-            schedule.run_overlap(self.layers, self.norm_w, hidden, residual, step.meta0, step.meta1, plan, rt.comm,
+            schedule.run_overlap(self.layers, close_w, hidden, residual, step.meta0, step.meta1, plan, rt.comm,
                                  rt, eps, pending)
         elif self.tw_mode == "fused_gemm":
-            schedule.run_fused_gemm(self.layers, self.norm_w, hidden, residual, step.meta, plan, rt.comm, rt, eps,
+            schedule.run_fused_gemm(self.layers, close_w, hidden, residual, step.meta, plan, rt.comm, rt, eps,
                                     pending)
         elif self.tw_mode in ("overlap", "fuse_only"):
-            schedule.run_fuse_only(self.layers, self.norm_w, hidden, residual, step.meta, plan, rt.comm, rt, eps,
+            schedule.run_fuse_only(self.layers, close_w, hidden, residual, step.meta, plan, rt.comm, rt, eps,
                                    pending)
         else:
-            schedule.run_baseline(self.layers, self.norm_w, hidden, residual, step.meta, plan, rt.comm, rt, eps,
+            schedule.run_baseline(self.layers, close_w, hidden, residual, step.meta, plan, rt.comm, rt, eps,
                                   self.tw_mode, pending)
+        if not stage.is_last_stage:
+            send_to_next_stage(hidden[:Tp], residual[:Tp])
         return hidden[:T]
 
     @torch.inference_mode()
@@ -300,9 +323,14 @@ class DecoderModel(nn.Module):
                 self.lm_head.weight_loader(self.lm_head.weight, tensor)
             elif n.startswith("layers."):
                 _, idx, rest = n.split(".", 2)
-                if int(idx) >= len(self.layers):
+                li = int(idx)
+                if li == self.end_layer and self.boundary_norm_w is not None and rest == "input_layernorm.weight":
+                    self.boundary_norm_w.data.copy_(tensor)       # the next stage's first input norm
+                    loaded.add(name)
                     continue
-                self._load_layer_weight(self.layers[int(idx)], rest, tensor)
+                if not self.first_layer <= li < self.end_layer:
+                    continue
+                self._load_layer_weight(self.layers[li - self.first_layer], rest, tensor)
             else:
                 continue
             loaded.add(name)

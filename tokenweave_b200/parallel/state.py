@@ -1,9 +1,12 @@
 """Process-group state: one process per GPU, ``torch.distributed`` (NCCL on GPUs, gloo on CPU) for
 the plumbing, a gloo twin group for host-side control messages.
 
-Counterpart of vllm/distributed/parallel_state.py:802-949. Only tensor parallelism is modelled:
-the TokenWeave path of the reference runs TP=4/8 with PP=DP=1 (its V1 multiprocess executor asserts
-world_size == tp, vllm/v1/executor/multiproc_executor.py:56-59).
+Counterpart of vllm/distributed/parallel_state.py:802-949. The job's ranks form ``pp`` pipeline stages
+of ``tp`` tensor-parallel ranks each (stage ``s`` = global ranks ``[s * tp, (s + 1) * tp)``, the layout of
+``parallel_state.py:906-933``). ``TPState.rank`` / ``world_size`` / ``group`` always describe the
+tensor-parallel group of this process, so everything written for TP runs unchanged inside a stage;
+activations cross stage boundaries with point-to-point sends between equal tensor-parallel ranks.
+The TokenWeave runs of the reference use TP = 4 / 8 with PP = 1.
 """
 from __future__ import annotations
 
@@ -25,6 +28,20 @@ class TPState:
     group: Optional[dist.ProcessGroup] = None       # device collectives (NCCL / gloo)
     cpu_group: Optional[dist.ProcessGroup] = None   # host control plane (gloo)
     owns_process_group: bool = False
+    # pipeline parallelism (1 stage: everything below is the identity)
+    pp_rank: int = 0
+    pp_size: int = 1
+    global_rank: int = 0
+    global_size: int = 1
+    world_cpu_group: Optional[dist.ProcessGroup] = None   # host control plane over all stages
+
+    @property
+    def is_first_stage(self) -> bool:
+        return self.pp_rank == 0
+
+    @property
+    def is_last_stage(self) -> bool:
+        return self.pp_rank == self.pp_size - 1
 
 
 _STATE = TPState()
@@ -66,9 +83,15 @@ def _generation_store(init_method: str, rank: int, world_size: int, timeout_s: f
 
 
 def init_distributed(rank: int, world_size: int, local_rank: Optional[int] = None, device: str = "auto",
-                     init_method: Optional[str] = None, timeout_s: float = 600.0) -> TPState:
-    """Join (or create) the job's process group and bind this process to its GPU."""
+                     init_method: Optional[str] = None, timeout_s: float = 600.0,
+                     tp_size: Optional[int] = None) -> TPState:
+    """Join (or create) the job's process group and bind this process to its GPU. ``tp_size`` smaller than
+    ``world_size`` makes ``world_size / tp_size`` pipeline stages."""
     global _STATE
+    tp_size = world_size if tp_size is None else tp_size
+    if world_size % tp_size:
+        raise ValueError(f"world size {world_size} is not a multiple of the tensor-parallel size {tp_size}")
+    pp_size = world_size // tp_size
     local_rank = rank if local_rank is None else local_rank
     use_cuda = (device == "cuda") or (device == "auto" and torch.cuda.is_available())
     if use_cuda:
@@ -97,8 +120,45 @@ def init_distributed(rank: int, world_size: int, local_rank: Optional[int] = Non
             owns = True
         group = dist.group.WORLD
         cpu_group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s)) if use_cuda else group
-    _STATE = TPState(rank, world_size, local_rank, dev, group, cpu_group, owns)
+    if pp_size == 1:
+        _STATE = TPState(rank, world_size, local_rank, dev, group, cpu_group, owns, global_rank=rank,
+                         global_size=world_size, world_cpu_group=cpu_group)
+        return _STATE
+    # several stages: one tensor-parallel group (and its gloo twin) per stage; every rank creates all of them,
+    # in the same order, as torch.distributed requires
+    world_cpu, tp_group, tp_cpu = cpu_group, None, None
+    if tp_size > 1:
+        for s in range(pp_size):
+            ranks = list(range(s * tp_size, (s + 1) * tp_size))
+            g = dist.new_group(ranks, backend="nccl" if use_cuda else "gloo", timeout=datetime.timedelta(seconds=timeout_s))
+            cg = dist.new_group(ranks, backend="gloo", timeout=datetime.timedelta(seconds=timeout_s)) if use_cuda else g
+            if rank in ranks:
+                tp_group, tp_cpu = g, cg
+    _STATE = TPState(rank % tp_size, tp_size, local_rank, dev, tp_group, tp_cpu, owns, pp_rank=rank // tp_size,
+                     pp_size=pp_size, global_rank=rank, global_size=world_size, world_cpu_group=world_cpu)
     return _STATE
+
+
+def send_to_next_stage(*tensors: torch.Tensor) -> None:
+    """Hand tensors to the same tensor-parallel rank of the next pipeline stage (blocking sends, in order)."""
+    dst = _STATE.global_rank + _STATE.world_size
+    for t in tensors:
+        dist.send(t, dst=dst)
+
+
+def recv_from_prev_stage(*tensors: torch.Tensor) -> None:
+    src = _STATE.global_rank - _STATE.world_size
+    for t in tensors:
+        dist.recv(t, src=src)
+
+
+def broadcast_from_last_stage(obj):
+    """The step result lives on the last stage; every rank of the job gets a copy (host control plane)."""
+    if _STATE.pp_size == 1:
+        return obj
+    box = [obj]
+    dist.broadcast_object_list(box, src=(_STATE.pp_size - 1) * _STATE.world_size, group=_STATE.world_cpu_group)
+    return box[0]
 
 
 def set_single_process(device: torch.device) -> TPState:
@@ -120,8 +180,9 @@ def cpu_barrier() -> None:
 
 
 def broadcast_object(obj, src: int = 0):
+    """Broadcast inside the tensor-parallel group; ``src`` is a rank of that group."""
     if _STATE.world_size == 1:
         return obj
     box = [obj]
-    dist.broadcast_object_list(box, src=src, group=_STATE.cpu_group)
+    dist.broadcast_object_list(box, src=dist.get_global_rank(_STATE.cpu_group, src), group=_STATE.cpu_group)
     return box[0]

@@ -76,7 +76,7 @@ def _exchange_fds(tp: TPState, my_fd: Optional[int], tag: str, root_only: bool =
     base = [None]
     if tp.rank == 0:
         base[0] = os.path.join("/tmp", f"tw_symm_{uuid.uuid4().hex[:12]}_{tag}")
-    dist.broadcast_object_list(base, src=0, group=tp.cpu_group)
+    dist.broadcast_object_list(base, src=dist.get_global_rank(tp.cpu_group, 0), group=tp.cpu_group)
     path = lambda r: f"{base[0]}_{r}.sock"
     expect = (0 if tp.rank == 0 else 1) if root_only else tp.world_size - 1
     got: dict[int, int] = {}

@@ -21,7 +21,7 @@ from ..config import EngineConfig
 from ..layers.attention import AttentionMetadata, build_attention_metadata
 from ..layers.sampler import Sampler
 from ..models.decoder import DecoderModel, StepInput
-from ..parallel.state import get_tp
+from ..parallel.state import broadcast_from_last_stage, get_tp
 from ..sampling_params import SamplingParams
 from ..tokenweave.config import TokenWeavePlanner
 from ..utils.logging import init_logger
@@ -104,7 +104,7 @@ class ModelRunner:
         self._want_pooled = False            # this step samples for a request with SamplingParams.pooling
         self._h2d_done = torch.cuda.Event() if pin else None   # guards reuse of the pinned staging buffers
         # CUDA graphs: a step whose shape signature has been seen before is replayed from a captured graph
-        self.use_graphs = bool(tw.use_cuda_graphs) and pin
+        self.use_graphs = bool(tw.use_cuda_graphs) and pin and self.tp.pp_size == 1    # stage hand-offs are not captured
         self._meta_dev = [torch.zeros(1 << 20, dtype=torch.int32, device=device) if self.use_graphs else None
                           for _ in range(2)]
         # logits rows per step: one per sequence, plus one per draft token under speculative decoding
@@ -322,6 +322,19 @@ class ModelRunner:
         if self.timing_events is not None:
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             ev[0].record()
+        if self.tp.pp_size > 1 and not self.tp.is_last_stage:
+            # an inner pipeline stage: run the local layers (the model hands its output to the next stage); the
+            # sampled tokens come back from the last stage with the rest of the step's result
+            self.model(step_in)
+            if ev is not None:
+                ev[1].record()
+                self.timing_events.append(ev)
+            self.h2d_bytes_last_step, self.d2h_bytes_last_step = h2d, 0
+            result = broadcast_from_last_stage(None)
+            for rid, tok in zip(result.req_ids, result.sampled_token_ids):
+                if tok is not None:
+                    self.requests[rid].token_ids.extend(list(tok) if isinstance(tok, (list, tuple)) else [int(tok)])
+            return result
         n_logits = len(logits_rows)
         reqs = [self.requests[r] for r in sample_reqs]
         greedy = bool(reqs) and all(r.sampling_params.greedy and not r.sampling_params.needs_penalties
@@ -387,9 +400,12 @@ class ModelRunner:
         self.h2d_bytes_last_step, self.d2h_bytes_last_step = h2d, d2h
         req_ids = [s[0] for s in step.scheduled]
         lp_by_req = dict(zip(sample_reqs, lp)) if lp is not None else None
-        return StepResult(req_ids, [sampled.get(r) for r in req_ids],
-                          [lp_by_req.get(r) for r in req_ids] if lp_by_req is not None else None,
-                          prompt_logprobs=prompt_lp, pooled=pooled)
+        result = StepResult(req_ids, [sampled.get(r) for r in req_ids],
+                            [lp_by_req.get(r) for r in req_ids] if lp_by_req is not None else None,
+                            prompt_logprobs=prompt_lp, pooled=pooled)
+        if self.tp.pp_size > 1:
+            result = broadcast_from_last_stage(result)       # every stage's scheduler sees the same result
+        return result
 
     def _prompt_logprobs(self, jobs: list[tuple[str, int, int, int]]) -> dict:
         """Log-probabilities of the prompt tokens computed in this step: the final-norm hidden rows of the

@@ -30,10 +30,11 @@ class Worker:
         self.profiler = None
 
     def init_device(self) -> None:
-        world = self.config.parallel.tensor_parallel_size
+        world = self.config.parallel.world_size
         dev_kind = self.config.resolved_device()
         if world > 1:
-            tp = pstate.init_distributed(self.rank, world, self.local_rank, dev_kind, self.init_method)
+            tp = pstate.init_distributed(self.rank, world, self.local_rank, dev_kind, self.init_method,
+                                         tp_size=self.config.parallel.tensor_parallel_size)
         else:
             if dev_kind == "cuda":
                 torch.cuda.set_device(self.local_rank)
