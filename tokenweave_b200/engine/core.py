@@ -101,7 +101,10 @@ class EngineCore:
         self._last_logprobs = dict(zip(result.req_ids, result.logprobs)) if result.logprobs else {}
         self.last_stats = StepStats(num_tokens=sched.total_num_tokens, num_running=len(self.scheduler.running),
                                     num_waiting=len(self.scheduler.waiting), kv_usage=self.kv.usage(),
-                                    num_generated=self.scheduler.last_emitted)
+                                    num_generated=self.scheduler.last_emitted,
+                                    prefix_cache_queries=self.kv.prefix_queries, prefix_cache_hits=self.kv.prefix_hits,
+                                    num_draft_tokens=self.scheduler.num_draft_tokens,
+                                    num_accepted_tokens=self.scheduler.num_accepted_tokens)
         return touched
 
     def shutdown(self) -> None:

@@ -95,6 +95,8 @@ class KVCacheManager:
         self.block_size = block_size
         self.pool = BlockPool(num_blocks, enable_caching)
         self.enable_caching = enable_caching
+        self.prefix_queries = 0        # blocks looked up / found in the prefix cache since start
+        self.prefix_hits = 0
 
     def get_computed_blocks(self, req: Request) -> tuple[list[int], int]:
         """Longest cached prefix of the request's prompt: (block ids, number of tokens)."""
@@ -108,6 +110,8 @@ class KVCacheManager:
             if b is None:
                 break
             blocks.append(b)
+        self.prefix_queries += usable
+        self.prefix_hits += len(blocks)
         return blocks, len(blocks) * self.block_size
 
     def allocate_slots(self, req: Request, num_new_tokens: int, cached_blocks: Optional[list[int]] = None) -> bool:

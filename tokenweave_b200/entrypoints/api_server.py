@@ -105,8 +105,11 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
     def finished_metrics(out: RequestOutput) -> None:
         if prom is not None and out.finished:
             m = out.metrics
+            n_out = max((len(c.token_ids) for c in out.outputs), default=0)
+            tpot = ((m.finished_time - m.first_token_time) / (n_out - 1)
+                    if m.finished_time and m.first_token_time and n_out > 1 else None)
             prom.record_finished((m.first_token_time - m.arrival_time) if m.first_token_time else None,
-                                 (m.finished_time - m.arrival_time) if m.finished_time else None)
+                                 (m.finished_time - m.arrival_time) if m.finished_time else None, tpot)
 
     @app.get("/health")
     async def health():

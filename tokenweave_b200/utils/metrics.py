@@ -17,6 +17,11 @@ class StepStats:
     num_waiting: int = 0
     kv_usage: float = 0.0
     num_generated: int = 0
+    # cumulative counters of the engine (prefix cache in blocks, speculative decoding in tokens)
+    prefix_cache_queries: int = 0
+    prefix_cache_hits: int = 0
+    num_draft_tokens: int = 0
+    num_accepted_tokens: int = 0
 
 
 class LoggingStatLogger:
@@ -36,8 +41,14 @@ class LoggingStatLogger:
         now = time.monotonic()
         if now - self._t0 >= self.interval_s:
             dt = now - self._t0
-            logger.info("throughput: prompt %.1f tok/s, generation %.1f tok/s | running %d, waiting %d | KV usage %.1f%%",
-                        self._prompt / dt, self._gen / dt, stats.num_running, stats.num_waiting, 100 * stats.kv_usage)
+            extra = ""
+            if stats.prefix_cache_queries:
+                extra += " | prefix cache hit rate %.1f%%" % (100.0 * stats.prefix_cache_hits / stats.prefix_cache_queries)
+            if stats.num_draft_tokens:
+                extra += " | draft acceptance %.1f%%" % (100.0 * stats.num_accepted_tokens / stats.num_draft_tokens)
+            logger.info("throughput: prompt %.1f tok/s, generation %.1f tok/s | running %d, waiting %d | KV usage %.1f%%%s",
+                        self._prompt / dt, self._gen / dt, stats.num_running, stats.num_waiting, 100 * stats.kv_usage,
+                        extra)
             self._t0, self._prompt, self._gen = now, 0, 0
 
 
@@ -60,6 +71,15 @@ class PrometheusStatLogger:
                                  buckets=[0.01, 0.025, 0.05, 0.1, 0.25, 0.5, 1, 2.5, 5, 10]).labels(**labels)
         self.e2e = pc.Histogram("tokenweave:e2e_request_latency_seconds", "request latency", list(labels), registry=reg,
                                 buckets=[0.1, 0.5, 1, 2.5, 5, 10, 30, 60, 120]).labels(**labels)
+        self.tpot = pc.Histogram("tokenweave:time_per_output_token_seconds", "mean time per output token after the first",
+                                 list(labels), registry=reg,
+                                 buckets=[0.005, 0.01, 0.02, 0.03, 0.05, 0.075, 0.1, 0.2, 0.5, 1]).labels(**labels)
+        counter = lambda name, doc: pc.Counter(name, doc, list(labels), registry=reg).labels(**labels)  # noqa: E731
+        self.prefix_queries = counter("tokenweave:prefix_cache_queries_total", "blocks looked up in the prefix cache")
+        self.prefix_hits = counter("tokenweave:prefix_cache_hits_total", "blocks found in the prefix cache")
+        self.draft_tokens = counter("tokenweave:spec_decode_num_draft_tokens_total", "draft tokens proposed")
+        self.accepted_tokens = counter("tokenweave:spec_decode_num_accepted_tokens_total", "draft tokens confirmed")
+        self._seen = [0, 0, 0, 0]       # last cumulative values, to turn them into increments
 
     def record(self, stats: StepStats) -> None:
         self.running.set(stats.num_running)
@@ -68,9 +88,16 @@ class PrometheusStatLogger:
         self.prompt_tokens.inc(max(0, stats.num_tokens - stats.num_generated))
         self.gen_tokens.inc(stats.num_generated)
         self.step_tokens.observe(stats.num_tokens)
+        now = [stats.prefix_cache_queries, stats.prefix_cache_hits, stats.num_draft_tokens, stats.num_accepted_tokens]
+        for c, new, old in zip((self.prefix_queries, self.prefix_hits, self.draft_tokens, self.accepted_tokens),
+                               now, self._seen):
+            c.inc(max(0, new - old))
+        self._seen = now
 
-    def record_finished(self, ttft_s: Optional[float], e2e_s: Optional[float]) -> None:
+    def record_finished(self, ttft_s: Optional[float], e2e_s: Optional[float], tpot_s: Optional[float] = None) -> None:
         if ttft_s is not None:
             self.ttft.observe(ttft_s)
         if e2e_s is not None:
             self.e2e.observe(e2e_s)
+        if tpot_s is not None:
+            self.tpot.observe(tpot_s)
