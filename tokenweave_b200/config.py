@@ -263,6 +263,7 @@ class EngineConfig:
     speculative: Any = None               # engine.spec_decode.SpecDecodeConfig (n-gram drafts for greedy requests)
     enable_lora: bool = False             # serve requests through LoRA adapters (tokenweave_b200.lora)
     max_loras: int = 8                    # adapters resident per worker (least recently used is evicted)
+    kv_transfer: Any = None               # engine.kv_connector.KVTransferConfig (blocks shared through storage)
 
     def resolved_device(self) -> str:
         if self.device != "auto":
@@ -302,6 +303,9 @@ class EngineArgs:
     enable_sleep_mode: bool = False       # weights and KV cache on the VMM allocator: LLM.sleep() frees their memory
     # {"method": "ngram", "num_speculative_tokens": k, "prompt_lookup_max": n, "prompt_lookup_min": m}, or just k
     speculative_config: Any = None
+    # {"kv_connector": "SharedStorageConnector", "kv_role": "kv_producer" | "kv_consumer" | "kv_both",
+    #  "kv_connector_extra_config": {"shared_storage_path": dir}}: KV blocks published to / fetched from storage
+    kv_transfer_config: Any = None
     enable_lora: bool = False
     max_loras: int = 8
     # TokenWeave
@@ -336,7 +340,7 @@ class EngineArgs:
         return EngineConfig(
             model=model,
             cache=CacheConfig(self.block_size, self.gpu_memory_utilization, self.num_gpu_blocks_override,
-                              self.enable_prefix_caching),
+                              self.enable_prefix_caching or self.kv_transfer_config is not None),   # the connector keys blocks by prefix hash
             parallel=ParallelConfig(self.tensor_parallel_size, self.distributed_executor_backend,
                                     self.disable_custom_all_reduce, data_parallel_size=self.data_parallel_size,
                                     data_parallel_rank=self.data_parallel_rank,
@@ -354,7 +358,12 @@ class EngineArgs:
             load_format=load_format, quantization=self.quantization, seed=self.seed, device=self.device, enforce_eager=self.enforce_eager,
             tokenizer=self.tokenizer, skip_tokenizer_init=self.skip_tokenizer_init,
             disable_log_stats=self.disable_log_stats, enable_sleep_mode=self.enable_sleep_mode,
-            speculative=self._speculative(), enable_lora=self._lora_checked(model), max_loras=self.max_loras)
+            speculative=self._speculative(), enable_lora=self._lora_checked(model), max_loras=self.max_loras,
+            kv_transfer=self._kv_transfer())
+
+    def _kv_transfer(self):
+        from .engine.kv_connector import KVTransferConfig
+        return KVTransferConfig.from_user(self.kv_transfer_config)
 
     def _lora_checked(self, model) -> bool:
         if self.enable_lora and self.tokenweave_mode == "fused_gemm":

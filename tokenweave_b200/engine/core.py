@@ -37,6 +37,14 @@ class EngineCore:
         self.kv = KVCacheManager(num_blocks, config.cache.block_size, config.cache.enable_prefix_caching)
         self.scheduler = Scheduler(config.scheduler, self.kv, config.speculative)
         self._sent_blocks: dict[str, int] = {}     # blocks of each request already known to the workers
+        # KV connector: the scheduler side only asks which blocks the store can supply; the workers move the data
+        self.kv_transfer = config.kv_transfer
+        if self.kv_transfer is not None:
+            from .kv_connector import SharedStorageConnector
+            lookup = SharedStorageConnector(self.kv_transfer, 0, config.parallel.world_size)
+            self.kv.track_published = self.kv_transfer.can_save
+            if self.kv_transfer.can_load:
+                self.scheduler.connector = lookup
         self.last_stats: Optional[StepStats] = None
 
     def _on_executor_failure(self) -> None:
@@ -82,6 +90,8 @@ class EngineCore:
                 self.executor.execute_model(self._to_step_data(sched))
             return []
         try:
+            if sched.kv_loads:
+                self.executor.collective_rpc("load_kv_blocks", list(sched.kv_loads))
             result: StepResult = self.executor.execute_model(self._to_step_data(sched))
         except ExecutorFailure as e:
             self.dead = True
@@ -99,6 +109,14 @@ class EngineCore:
         touched = self.scheduler.update_from_output(
             sched, ModelRunnerOutput(result.req_ids, result.sampled_token_ids, result.logprobs))
         self._last_logprobs = dict(zip(result.req_ids, result.logprobs)) if result.logprobs else {}
+        if self.kv.newly_published:
+            # blocks that became full in this step are in the workers' caches now: publish them to the store
+            saves, self.kv.newly_published = self.kv.newly_published, []
+            try:
+                self.executor.collective_rpc("save_kv_blocks", saves)
+            except ExecutorFailure as e:
+                self.dead = True
+                raise EngineDeadError(str(e)) from e
         self.last_stats = StepStats(num_tokens=sched.total_num_tokens, num_running=len(self.scheduler.running),
                                     num_waiting=len(self.scheduler.waiting), kv_usage=self.kv.usage(),
                                     num_generated=self.scheduler.last_emitted,

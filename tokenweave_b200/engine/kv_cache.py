@@ -97,6 +97,8 @@ class KVCacheManager:
         self.enable_caching = enable_caching
         self.prefix_queries = 0        # blocks looked up / found in the prefix cache since start
         self.prefix_hits = 0
+        self.track_published = False   # a KV connector wants to know which blocks became full
+        self.newly_published: list[tuple[int, bytes]] = []     # (block id, hash) since the engine last took them
 
     def get_computed_blocks(self, req: Request) -> tuple[list[int], int]:
         """Longest cached prefix of the request's prompt: (block ids, number of tokens)."""
@@ -156,7 +158,13 @@ class KVCacheManager:
         hashes = self._hashes(req, full)
         for i in range(req.num_published_blocks, full):
             self.pool.cache_block(req.block_ids[i], hashes[i])
+            if self.track_published:
+                self.newly_published.append((req.block_ids[i], hashes[i]))
         req.num_published_blocks = full
+
+    def prefix_hashes(self, req: Request) -> list[bytes]:
+        """Hashes of the prompt blocks a request may take from a cache (never the block of its last token)."""
+        return self._hashes(req, (req.num_tokens - 1) // self.block_size)
 
     def free(self, req: Request) -> None:
         self.pool.release(req.block_ids)

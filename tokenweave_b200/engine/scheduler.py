@@ -35,6 +35,8 @@ class SchedulerOutput:
     finished_req_ids: list[str] = field(default_factory=list)
     preempted_req_ids: list[str] = field(default_factory=list)
     step_id: int = 0
+    # KV connector: (block id, block hash) pairs the workers fill from the external store before the step runs
+    kv_loads: list = field(default_factory=list)
 
     @property
     def empty(self) -> bool:
@@ -55,6 +57,7 @@ class Scheduler:
         self.config = config
         self.kv = kv
         self.spec = spec if spec is not None else SpecDecodeConfig()
+        self.connector = None              # engine.kv_connector.SharedStorageConnector of a consuming engine
         self.num_draft_tokens = 0          # statistics of speculative decoding
         self.num_accepted_tokens = 0
         self.last_emitted = 0
@@ -133,14 +136,25 @@ class Scheduler:
                 if req.num_computed_tokens == 0 and req.sampling_params.prompt_logprobs is None:
                     # (prompt log-probabilities need the hidden state of every prompt position: no cache hits)
                     cached, n_cached = self.kv.get_computed_blocks(req)
-                remaining = req.num_tokens - req.num_computed_tokens - n_cached
+                # blocks the local cache does not have may be in the external store (the hook of
+                # vllm/v1/core/sched/scheduler.py:319-367): they are loaded into fresh blocks before the step
+                ext_hashes: list = []
+                if (self.connector is not None and req.num_computed_tokens == 0
+                        and req.sampling_params.prompt_logprobs is None):
+                    want = self.kv.prefix_hashes(req)[len(cached):]
+                    ext_hashes = want[:self.connector.num_matched(want)]
+                n_ext = len(ext_hashes) * self.kv.block_size
+                remaining = req.num_tokens - req.num_computed_tokens - n_cached - n_ext
                 n = min(remaining, budget)
                 if n < remaining and not self.config.enable_chunked_prefill:
                     break
                 req.num_computed_tokens += n_cached
-                if not self.kv.allocate_slots(req, n, cached):
+                if not self.kv.allocate_slots(req, n_ext + n, cached):
                     req.num_computed_tokens -= n_cached
                     break
+                for j, h in enumerate(ext_hashes):
+                    out.kv_loads.append((req.block_ids[len(cached) + j], h))
+                req.num_computed_tokens += n_ext
                 self.waiting.popleft()
                 req.status = RequestStatus.RUNNING
                 if req.first_scheduled_time is None:

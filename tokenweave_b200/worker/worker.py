@@ -179,6 +179,36 @@ class Worker:
         if self.device.type == "cuda":
             torch.cuda.synchronize()
 
+    # ---- KV connector (engine/kv_connector.py): blocks to / from the external store -------------------------
+    def _kv_connector(self):
+        if getattr(self, "_connector", None) is None:
+            from ..engine.kv_connector import SharedStorageConnector
+            tp = pstate.get_tp()
+            self._connector = SharedStorageConnector(self.config.kv_transfer, tp.global_rank, tp.global_size)
+        return self._connector
+
+    def save_kv_blocks(self, items: list) -> None:
+        """items: (block id, block hash); this rank's slice of every local layer goes into one file per block."""
+        conn = self._kv_connector()
+        layers = self.runner.model.layers
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)       # the step that filled the blocks has completed
+        for block, h in items:
+            if conn.available(h):
+                continue
+            k = torch.stack([layer.attn.k_cache[block] for layer in layers])
+            v = torch.stack([layer.attn.v_cache[block] for layer in layers])
+            conn.save_block(h, k, v)
+
+    def load_kv_blocks(self, items: list) -> None:
+        conn = self._kv_connector()
+        layers = self.runner.model.layers
+        for block, h in items:
+            k, v = conn.load_block(h)
+            for i, layer in enumerate(layers):
+                layer.attn.k_cache[block].copy_(k[i], non_blocking=True)
+                layer.attn.v_cache[block].copy_(v[i], non_blocking=True)
+
     def set_capture_hidden(self, on: bool) -> None:
         """Pooling support: keep the final-norm hidden state at every request's first sampled position."""
         self.runner.capture_hidden = bool(on)
