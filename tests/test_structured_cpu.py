@@ -243,3 +243,27 @@ def test_token_bytes_of_common_vocabulary_spellings():
     # sentencepiece: word-boundary marker and byte fallback
     sp = Fake(["▁the", "<0x0A>", "ab", "▁", "</s>"], special=[4])
     assert token_bytes_table(sp, 5) == [b" the", b"\n", b"ab", b" ", b""]
+
+
+def test_constrained_text_is_always_well_formed_utf8():
+    rng = random.Random(5)
+    for pattern in [r'"[^"\\]*"', r"a.{0,6}b", json_schema_to_regex({"type": "string", "maxLength": 5})]:
+        dfa = DFA(pattern)
+        accepted = 0
+        for _ in range(300):
+            s, out = 0, bytearray()
+            for _ in range(40):
+                if dfa.accepting[s] and rng.random() < 0.3:
+                    break
+                nxt = [b for b in range(256) if dfa.step(s, b) >= 0]
+                if not nxt:
+                    break
+                high = [b for b in nxt if b >= 0x80]
+                b = rng.choice(high) if high and rng.random() < 0.6 else rng.choice(nxt)
+                out.append(b)
+                s = dfa.step(s, b)
+            if dfa.accepting[s]:
+                accepted += 1
+                out.decode("utf-8")                 # raises on half a character, overlong forms, surrogates
+        assert accepted > 20
+    assert DFA(r"[^a]").fullmatch("é") and DFA(r".").fullmatch("😀") and not DFA(r".").fullmatch(b"\xc3")

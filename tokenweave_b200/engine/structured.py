@@ -18,8 +18,9 @@ end-of-sequence token is allowed exactly in accepting states, which is also how 
 Supported syntax: literals, ``.``, escapes ``\\d \\w \\s \\D \\W \\S \\n \\t \\r \\xHH \\uHHHH`` and escaped
 punctuation, classes ``[a-z0-9_]`` / ``[^...]``, groups ``( )`` and ``(?: )``, alternation, ``* + ?`` and
 ``{m} {m,} {m,n}`` (a lazy ``?`` suffix is accepted and ignored; ``^`` / ``$`` at the ends are ignored since
-the whole output must match). Characters outside ASCII are matched as their UTF-8 byte sequences; ``.`` and
-negated classes accept any byte of a multi-byte character.
+the whole output must match). ``\\d \\w \\s`` are the ASCII classes. Characters outside ASCII are matched as their
+UTF-8 byte sequences; ``.`` and negated classes accept any whole, well-formed multi-byte character, so a
+constrained output is always valid UTF-8.
 """
 from __future__ import annotations
 
@@ -48,6 +49,26 @@ _CHAR_ESC = {"n": "\n", "t": "\t", "r": "\r", "f": "\f", "v": "\v", "0": "\0", "
 
 class RegexError(ValueError):
     pass
+
+
+def _range_mask(lo: int, hi: int) -> int:
+    return sum(1 << b for b in range(lo, hi + 1))
+
+
+def _utf8_multibyte():
+    """AST of one well-formed multi-byte UTF-8 character (no overlong forms, no surrogates, up to U+10FFFF), so
+    that ``.`` and negated classes never let half a character through."""
+    tail = ("set", _range_mask(0x80, 0xBF))
+    seq = lambda *parts: ("cat", [p if isinstance(p, tuple) else ("set", p) for p in parts])  # noqa: E731
+    return ("alt", [
+        seq(_range_mask(0xC2, 0xDF), tail),
+        seq(1 << 0xE0, _range_mask(0xA0, 0xBF), tail),
+        seq(_range_mask(0xE1, 0xEC) | _range_mask(0xEE, 0xEF), tail, tail),
+        seq(1 << 0xED, _range_mask(0x80, 0x9F), tail),
+        seq(1 << 0xF0, _range_mask(0x90, 0xBF), tail, tail),
+        seq(_range_mask(0xF1, 0xF3), tail, tail, tail),
+        seq(1 << 0xF4, _range_mask(0x80, 0x8F), tail, tail),
+    ])
 
 
 # ---- parser: pattern -> AST ------------------------------------------------------------------------------------
@@ -159,7 +180,7 @@ class _Parser:
         if c == "[":
             return self._class()
         if c == ".":
-            return ("set", ALL & ~(1 << 0x0A))
+            return ("alt", [("set", _ASCII & ~(1 << 0x0A)), _utf8_multibyte()])
         if c == "\\":
             e = self._escape(False)
             return ("set", e) if isinstance(e, int) else self._literal(e)
@@ -205,8 +226,8 @@ class _Parser:
             else:
                 wide.append(lo)
         if negate:
-            # complement over ASCII; every byte of a multi-byte character passes
-            return ("set", (_ASCII & ~mask) | _HIGH)
+            # complement over ASCII, plus any whole multi-byte character (non-ASCII members are not excluded)
+            return ("alt", [("set", _ASCII & ~mask), _utf8_multibyte()])
         if not wide:
             return ("set", mask)
         return ("alt", ([("set", mask)] if mask else []) + [self._literal(ch) for ch in wide])
