@@ -6,7 +6,8 @@ Endpoints: ``GET /health``, ``GET /v1/models``, ``POST /v1/completions``, ``POST
 (both with ``"stream": true`` server-sent events), ``POST /tokenize``, ``POST /detokenize``,
 ``GET /metrics`` (Prometheus text). A lean counterpart of vllm/entrypoints/openai/api_server.py and
 serving_completion.py / serving_chat.py: the request fields that map onto ``SamplingParams`` are
-honoured, the rest of the OpenAI schema (tools, response formats, multimodal parts) is not served.
+honoured, including ``response_format`` and function calling (``tools`` / ``tool_choice``, entrypoints/tool_calls.py);
+multimodal message parts are not served.
 Tensor-parallel serving uses the multiprocess executor (one worker process per GPU).
 """
 import argparse
@@ -289,10 +290,20 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
         return {"id": rid, "object": "list", "model": name, "data": data}
 
     # ---- /v1/chat/completions -----------------------------------------------------------------
-    def chat_prompt(messages: list, add_generation_prompt: bool = True) -> str:
+    def chat_prompt(messages: list, add_generation_prompt: bool = True, tools: Optional[list] = None) -> str:
         if hasattr(tokenizer, "apply_chat_template") and getattr(tokenizer, "chat_template", None):
-            return tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt)
-        text = "".join(f"{m['role']}: {m['content']}\n" for m in messages)
+            kw = {"tools": tools} if tools else {}
+            return tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt,
+                                                 **kw)
+        text = ""
+        if tools:
+            from .tool_calls import describe_tools
+            text = "system: " + describe_tools(tools) + "\n"
+        for m in messages:
+            content = m.get("content")
+            if content is None and m.get("tool_calls"):
+                content = json.dumps([c.get("function", c) for c in m["tool_calls"]])
+            text += f"{m['role']}: {content}\n"
         return text + ("assistant: " if add_generation_prompt else "")
 
     @app.post("/v1/chat/completions")
@@ -303,14 +314,51 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
         msgs = body.get("messages")
         if not isinstance(msgs, list) or not msgs:
             return error(400, "messages must be a non-empty list")
+        tools = body.get("tools") if body.get("tool_choice") != "none" else None
+        tool_choice = body.get("tool_choice", "auto" if tools else None)
         try:
+            from . import tool_calls as tc
             sp = sampling_params_from_request(body, default_max_tokens=256)
-            prompt = chat_prompt(msgs, body.get("add_generation_prompt", True))
+            forced = tc.forced_schema(tools, tool_choice) if tools else None
+            if forced is not None:
+                sp.guided_json, sp.guided_regex = forced, None      # the call's arguments always parse
+            prompt = chat_prompt(msgs, body.get("add_generation_prompt", True), tools)
             lora = pick_adapter(body)
         except (ValueError, TypeError, KeyError) as e:
             return error(400, str(e))
         rid = "chatcmpl-" + uuid.uuid4().hex
         created = int(time.time())
+
+        def message_of(comp) -> tuple[dict, Optional[str]]:
+            """Assistant message (with tool calls where the text holds some) and the finish reason."""
+            if not tools:
+                return {"role": "assistant", "content": comp.text}, comp.finish_reason
+            if forced is not None:
+                try:
+                    calls, content = tc.calls_from_forced(comp.text, tools, tool_choice), None
+                except (ValueError, KeyError, TypeError):      # cut off by max_tokens before the JSON closed
+                    calls, content = [], comp.text
+            else:
+                content, calls = tc.calls_from_text(comp.text, tools)
+            msg = {"role": "assistant", "content": content}
+            if calls:
+                msg["tool_calls"] = calls
+            return msg, ("tool_calls" if calls and comp.finish_reason == "stop" else comp.finish_reason)
+
+        if body.get("stream") and tools:
+            # calls are recognised on the complete text: one chunk with the whole message, then the end marker
+            async def sse_tools() -> AsyncIterator[str]:
+                try:
+                    out = (await run_all([prompt], sp, rid, lora))[0]
+                    for c in out.outputs:
+                        msg, fin = message_of(c)
+                        chunk = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": name,
+                                 "choices": [{"index": c.index, "delta": msg, "finish_reason": fin}]}
+                        yield f"data: {json.dumps(chunk)}\n\n"
+                except (EngineDeadError, ValueError) as e:
+                    yield f"data: {json.dumps({'error': {'message': str(e)}})}\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(sse_tools(), media_type="text/event-stream")
         if body.get("stream"):
             async def sse() -> AsyncIterator[str]:
                 sent = {}
@@ -341,8 +389,11 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
             return error(400, str(e))
         except EngineDeadError as e:
             return error(500, str(e), "server_error")
-        choices = [{"index": c.index, "message": {"role": "assistant", "content": c.text},
-                    "logprobs": _logprobs_block(c, tokenizer), "finish_reason": c.finish_reason} for c in out.outputs]
+        choices = []
+        for c in out.outputs:
+            msg, fin = message_of(c)
+            choices.append({"index": c.index, "message": msg, "logprobs": _logprobs_block(c, tokenizer),
+                            "finish_reason": fin})
         return {"id": rid, "object": "chat.completion", "created": created, "model": name, "choices": choices,
                 "usage": _usage(out)}
 
