@@ -173,3 +173,19 @@ def test_classify_with_a_sequence_classification_checkpoint(tmp_path):
     with pytest.raises(ValueError):
         plain.classify([[1, 2, 3]])
     plain.shutdown()
+
+
+def test_truncate_prompt_tokens_and_priority_argument():
+    llm = LLM("tiny-llama", dtype="float32", device="cpu", skip_tokenizer_init=True, block_size=16,
+              max_num_batched_tokens=64, scheduling_policy="priority", max_num_seqs=1)
+    long_prompt = list(range(5, 105))
+    sp = SamplingParams(temperature=0, max_tokens=3, ignore_eos=True, truncate_prompt_tokens=20)
+    a = llm.generate([long_prompt], sp)[0]
+    b = llm.generate([long_prompt[-20:]], SamplingParams(temperature=0, max_tokens=3, ignore_eos=True))[0]
+    assert a.prompt_token_ids == long_prompt[-20:] and a.outputs[0].token_ids == b.outputs[0].token_ids
+    # one sequence at a time: the urgent request finishes first although it was submitted last
+    outs = llm.generate([[1, 2, 3], [4, 5, 6], [7, 8, 9]], SamplingParams(temperature=0, max_tokens=2, ignore_eos=True),
+                        priority=[2, 1, 0])
+    t = [o.metrics.finished_time for o in outs]
+    assert t[2] < t[1] < t[0]
+    llm.shutdown()

@@ -185,3 +185,28 @@ def _fuzz_once(seed, caching, spec_k):
 def test_random_workloads_keep_the_invariants(caching, spec_k):
     for seed in range(60):
         _fuzz_once(seed * 7 + spec_k, caching, spec_k)
+
+
+def test_priority_policy_orders_admission_and_preemption():
+    kv = KVCacheManager(num_blocks=12, block_size=16, enable_caching=False)
+    s = Scheduler(SchedulerConfig(64, 8, True, 1024, "priority"), kv)
+    for i, prio in enumerate([5, 1, 3, 1]):
+        r = req(i, 40, max_tokens=50)
+        r.priority = prio
+        s.add_request(r)
+    assert [r.request_id for r in s.waiting] == ["1", "3", "2", "0"]        # by priority, arrival among equals
+    out, _ = run_step(s)
+    assert [x.request.request_id for x in out.scheduled] == ["1", "3"]      # 40 + 24 tokens of the 64-token budget
+    for _ in range(3):
+        run_step(s)
+    assert {r.request_id for r in s.running} >= {"1", "3", "2"}
+    # the pool (11 usable blocks) runs dry while three requests decode: the least urgent of them is the victim
+    victims = []
+    for _ in range(40):
+        out, _ = run_step(s)
+        victims += out.preempted_req_ids
+        if victims:
+            break
+    assert victims and victims[0] == "2" and "1" not in victims and "3" not in victims
+    with pytest.raises(ValueError):
+        Scheduler(SchedulerConfig(64, 8, True, 1024, "lottery"), kv).add_request(req(9, 4))

@@ -217,6 +217,7 @@ class SchedulerConfig:
     max_num_seqs: int = 256
     enable_chunked_prefill: bool = True
     max_model_len: int = 8192
+    policy: str = "fcfs"                  # "fcfs" | "priority" (lower value first, arrival order among equals)
 
 
 @dataclass
@@ -292,6 +293,7 @@ class EngineArgs:
     max_num_batched_tokens: Optional[int] = None
     max_num_seqs: int = 256
     enable_chunked_prefill: bool = True
+    scheduling_policy: str = "fcfs"       # "fcfs" | "priority": requests carry a priority, lower values run first
     enforce_eager: bool = True
     enable_expert_parallel: bool = False
     disable_custom_all_reduce: bool = True
@@ -345,7 +347,8 @@ class EngineArgs:
                                     self.disable_custom_all_reduce, data_parallel_size=self.data_parallel_size,
                                     data_parallel_rank=self.data_parallel_rank,
                                     pipeline_parallel_size=self.pipeline_parallel_size),
-            scheduler=SchedulerConfig(budget, self.max_num_seqs, self.enable_chunked_prefill, max_len),
+            scheduler=SchedulerConfig(budget, self.max_num_seqs, self.enable_chunked_prefill, max_len,
+                                      self.scheduling_policy),
             tokenweave=TokenWeaveConfig(mode=self.tokenweave_mode, config_path=self.tokenweave_config,
                                         overlap_threshold=self.tokenweave_threshold,
                                         transport=self.tokenweave_transport,

@@ -54,7 +54,7 @@ class LLMEngine:
 
     # ---- requests ---------------------------------------------------------------------------
     def add_request(self, request_id: str, prompt: Union[str, list[int], dict], params: SamplingParams,
-                    lora_request=None) -> None:
+                    lora_request=None, priority: int = 0) -> None:
         if lora_request is not None and not self.config.enable_lora:
             raise ValueError("pass enable_lora=True to serve LoRA adapters")
         text: Optional[str] = None
@@ -67,6 +67,8 @@ class LLMEngine:
             text, ids = prompt, self._encode(prompt)
         else:
             ids = list(prompt)
+        if params.truncate_prompt_tokens is not None:
+            ids = list(ids)[-params.truncate_prompt_tokens:]        # keep the end of the prompt (left truncation)
         vocab = self.config.model.vocab_size
         if any((t < 0 or t >= vocab) for t in ids):
             raise ValueError(f"request {request_id}: token id outside [0, {vocab})")
@@ -102,7 +104,8 @@ class LLMEngine:
                     sp = params.clone()          # the caller's object stays untouched
                 sp.eos_token_id = self.eos_token_id     # the sampler masks it until min_tokens is reached
             cid = request_id if params.n == 1 else f"{i}_{request_id}"
-            child = Request(cid, list(ids), sp, eos_token_id=self.eos_token_id, prompt=text, lora_request=lora_request)
+            child = Request(cid, list(ids), sp, eos_token_id=self.eos_token_id, prompt=text, lora_request=lora_request,
+                            priority=priority)
             parent.children.append(child)
             detok = None
             if self.tokenizer is not None and params.detokenize:

@@ -42,6 +42,7 @@ class Request:
     spec_token_ids: list[int] = field(default_factory=list)   # drafts to verify in the next step
     lora_request: Optional[object] = None                     # tokenweave_b200.lora.LoRARequest
     prompt_logprobs: dict = field(default_factory=dict)       # prompt position -> {token id: log-probability}
+    priority: int = 0                                         # scheduling_policy="priority": lower values first
     pooled: Optional[object] = None                           # pooling requests: hidden state at the last prompt token
     block_hash_chain: list = field(default_factory=list)      # prefix-cache hashes of the full blocks so far
     num_published_blocks: int = 0                             # leading blocks already offered to the prefix cache

@@ -74,8 +74,17 @@ class Scheduler:
         if req.num_prompt_tokens >= self.config.max_model_len:
             raise ValueError(f"prompt of {req.num_prompt_tokens} tokens does not fit max_model_len "
                              f"{self.config.max_model_len}")
+        if self.config.policy not in ("fcfs", "priority"):
+            raise ValueError(f"unknown scheduling policy {self.config.policy!r}")
         self.requests[req.request_id] = req
-        self.waiting.append(req)
+        if self.config.policy == "priority":
+            # keep the queue ordered by (priority, arrival); vllm/v1/core/sched/scheduler.py "priority" policy
+            i = len(self.waiting)
+            while i > 0 and self.waiting[i - 1].priority > req.priority:
+                i -= 1
+            self.waiting.insert(i, req)
+        else:
+            self.waiting.append(req)
 
     def abort_request(self, request_id: str) -> None:
         req = self.requests.get(request_id)
@@ -116,7 +125,14 @@ class Scheduler:
                     n += len(drafts)
                 req.spec_token_ids = []
             while not self.kv.allocate_slots(req, n):
-                victim = self.running.pop()     # most recently admitted
+                if self.config.policy == "priority":
+                    # the least urgent running request goes first, the most recently admitted among equals
+                    worst = max(range(len(self.running)), key=lambda j: (self.running[j].priority, j))
+                    victim = self.running.pop(worst)
+                    if worst < i:
+                        i -= 1                  # the list shifted under the cursor
+                else:
+                    victim = self.running.pop()     # most recently admitted
                 self._preempt(victim)
                 preempted.append(victim)
                 if victim is req:

@@ -41,10 +41,11 @@ class LLM:
     def generate(self, prompts: Union[PromptType, Sequence[PromptType], None] = None,
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  prompt_token_ids: Optional[Sequence[list[int]]] = None, use_tqdm: bool = False,
-                 lora_request=None) -> list[RequestOutput]:
+                 lora_request=None, priority: Optional[Sequence[int]] = None) -> list[RequestOutput]:
         """Generate completions; results come back in prompt order. A prompt is text, a list of token
         ids, or ``{"prompt": ..., "prompt_token_ids": [...]}``. ``lora_request``: a
-        :class:`tokenweave_b200.lora.LoRARequest` for all prompts, or one (or None) per prompt."""
+        :class:`tokenweave_b200.lora.LoRARequest` for all prompts, or one (or None) per prompt.
+        ``priority``: one integer per prompt (lower runs first) under ``scheduling_policy="priority"``."""
         if prompts is None:
             if prompt_token_ids is None:
                 raise ValueError("give prompts or prompt_token_ids")
@@ -61,10 +62,13 @@ class LLM:
         loras = lora_request if isinstance(lora_request, (list, tuple)) else [lora_request] * len(prompts)
         if len(loras) != len(prompts):
             raise ValueError("one LoRARequest per prompt (or a single one for all)")
+        prios = list(priority) if priority is not None else [0] * len(prompts)
+        if len(prios) != len(prompts):
+            raise ValueError("one priority per prompt")
         ids = []
-        for p, sp, lr in zip(prompts, sampling_params, loras):
+        for p, sp, lr, pr in zip(prompts, sampling_params, loras, prios):
             rid = str(next(self._counter))
-            self.llm_engine.add_request(rid, p, sp, lora_request=lr)
+            self.llm_engine.add_request(rid, p, sp, lora_request=lr, priority=int(pr))
             ids.append(rid)
         return self._run_engine(ids, use_tqdm)
 

@@ -28,6 +28,7 @@ class SamplingParams:
     # pooling request: the final-norm hidden state at the last prompt token comes back in
     # ``RequestOutput.pooled`` (what ``LLM.encode`` and the server's embedding endpoint use)
     pooling: bool = False
+    truncate_prompt_tokens: Optional[int] = None      # keep only the last k prompt tokens
     detokenize: bool = True
     skip_special_tokens: bool = True
     logit_bias: Optional[dict] = None                   # token id -> additive bias (clamped to [-100, 100])
@@ -57,6 +58,8 @@ class SamplingParams:
             self.stop = [self.stop]
         self.stop = list(self.stop or [])
         self.stop_token_ids = list(self.stop_token_ids or [])
+        if self.truncate_prompt_tokens is not None and self.truncate_prompt_tokens < 1:
+            raise ValueError("truncate_prompt_tokens must be at least 1")
         if self.n < 1:
             raise ValueError("n must be at least 1")
         if self.temperature < 0:
