@@ -295,10 +295,15 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
           *reinterpret_cast<__nv_bfloat16*>(p_buf + g * 128 + ((kc ^ (g & 7)) * 16) + ke * 2) = __float2bfloat16(pv);
         }
       }
-      if (rescale) {
-        // O^T accumulated so far refers to the old maxima: scale column g by alpha[g]
+      // Every tile waits for the previous tile's P.V, needed or not: the parity wait only tells "the phase
+      // before the current one has completed", so a thread that skipped a phase could take the completion of
+      // tile j - 2 for that of tile j (late V tiles make that happen) and read O too early in the epilogue.
+      if (j > 0) {
         if (ok) ok = mbar_wait(o_done, (j - 1) & 1);
         tc_fence_after_sync();
+      }
+      if (rescale) {
+        // O^T accumulated so far refers to the old maxima: scale column g by alpha[g]
         uint32_t ov[16];
         tmem_ld_32x16(t_lane + COL_O, ov);
         tmem_wait_ld();
@@ -668,9 +673,11 @@ attn_decode_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmK, const 
             *reinterpret_cast<__nv_bfloat16*>(p_buf + g * 128 + ((kc ^ (g & 7)) * 16) + ke * 2) = __float2bfloat16(pv);
           }
         }
-        if (rescale) {
+        if (j > 0) {        // keeps every thread's view of o_done's phase exact (see the one-item kernel)
           if (ok) ok = mbar_wait(o_done, (jt - 1) & 1);
           tc_fence_after_sync();
+        }
+        if (rescale) {
           uint32_t ov[16];
           tmem_ld_32x16(t_lane + COL_O, ov);
           tmem_wait_ld();
