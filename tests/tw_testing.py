@@ -67,13 +67,16 @@ def hf_config_dict(cfg):
     return d
 
 
-def naive_logits(cfg, st, ids):
-    """Dense fp32 forward of one sequence (no paging, no sharding): logits for every position."""
+def naive_logits(cfg, st, ids, cos_sin=None):
+    """Dense fp32 forward of one sequence (no paging, no sharding): logits for every position. ``cos_sin``:
+    optional ([T, D/2] cos, [T, D/2] sin) tables for rope variants; the default is plain rope."""
     x = st["model.embed_tokens.weight"].float()[ids]
     T, D, half = len(ids), cfg.head_dim, cfg.head_dim // 2
     inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, half, dtype=torch.float64) * 2 / D))
     fr = torch.outer(torch.arange(T, dtype=torch.float64), inv)
     cos, sin = fr.cos().float()[:, None, :], fr.sin().float()[:, None, :]
+    if cos_sin is not None:
+        cos, sin = cos_sin[0][:, None, :], cos_sin[1][:, None, :]
 
     def norm(v, w):
         return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * w.float()

@@ -205,11 +205,41 @@ def build_cos_sin_cache(head_dim: int, max_pos: int, theta: float,
             inv_freq = scaled
         elif kind == "linear":
             inv_freq = inv_freq / float(rope_scaling["factor"])
+        elif kind in ("longrope", "su"):
+            # Phi-3 LongRoPE (vllm/model_executor/layers/rotary_embedding.py ``Phi3LongRoPEScaledRotaryEmbedding``):
+            # per-frequency rescale factors, one list for contexts inside the original window and one beyond it.
+            # Both tables are stored back to back - rows [0, original) "short", rows [original, original + max_pos)
+            # "long" - and ``longrope_offset`` tells the runner by how much to shift the positions of a step that
+            # reaches beyond the original window.
+            orig = int(rope_scaling.get("original_max_position_embeddings", max_pos))
+            scale = max_pos / orig
+            mscale = 1.0 if scale <= 1.0 else math.sqrt(1.0 + math.log(scale) / math.log(orig))
+            att = rope_scaling.get("attention_factor")
+            if att is not None:
+                mscale = float(att)
+            if "short_factor" not in rope_scaling or "long_factor" not in rope_scaling:
+                raise ValueError("longrope needs the short_factor and long_factor lists")
+            tables = []
+            for factors, rows in ((rope_scaling["short_factor"], orig), (rope_scaling["long_factor"], max_pos)):
+                f = torch.tensor(factors, dtype=torch.float64)
+                if f.numel() != half:
+                    raise ValueError(f"longrope factor lists need {half} entries, got {f.numel()}")
+                fr = torch.outer(torch.arange(rows, dtype=torch.float64), inv_freq / f)
+                tables.append(torch.cat([fr.cos(), fr.sin()], dim=-1) * mscale)
+            return torch.cat(tables, 0).float().to(device)
         else:
-            raise ValueError(f"unsupported rope_scaling type {kind!r} (default, linear, dynamic, yarn, llama3)")
+            raise ValueError(f"unsupported rope_scaling type {kind!r} (default, linear, dynamic, yarn, llama3, longrope)")
     t = torch.arange(max_pos, dtype=torch.float64)
     freqs = torch.outer(t, inv_freq)
     return (torch.cat([freqs.cos(), freqs.sin()], dim=-1) * mscale).float().to(device)
+
+
+def longrope_offset(rope_scaling: Optional[dict], max_pos: int) -> int:
+    """Rows to add to the positions of a step that reaches beyond the original context window (0 for every
+    other rope variant): the "long" table starts there."""
+    if not rope_scaling or rope_scaling.get("rope_type", rope_scaling.get("type")) not in ("longrope", "su"):
+        return 0
+    return int(rope_scaling.get("original_max_position_embeddings", max_pos))
 
 
 def rope_kv_write_(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor],

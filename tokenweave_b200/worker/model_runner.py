@@ -102,6 +102,8 @@ class ModelRunner:
         self.capture_hidden = False          # pooling requests: keep the final-norm hidden row of every sampled position
         self.captured_hidden: dict = {}
         self._want_pooled = False            # this step samples for a request with SamplingParams.pooling
+        from ..ops.reference import longrope_offset
+        self._longrope_offset = longrope_offset(config.model.rope_scaling, config.model.max_model_len)
         self._h2d_done = torch.cuda.Event() if pin else None   # guards reuse of the pinned staging buffers
         # CUDA graphs: a step whose shape signature has been seen before is replayed from a captured graph
         self.use_graphs = bool(tw.use_cuda_graphs) and pin and self.tp.pp_size == 1    # stage hand-offs are not captured
@@ -300,6 +302,10 @@ class ModelRunner:
         if self.lora is not None:
             self.lora.set_batch(row_lora)
 
+        if self._longrope_offset and T and int(positions[:T].max()) > self._longrope_offset:
+            # LongRoPE: a step that reaches beyond the original window rotates all its tokens with the "long"
+            # factors, which sit behind the "short" rows of the rotary table (slots were computed above)
+            positions = positions + np.int32(self._longrope_offset)
         plan = self.planner.plan(T)
         ids_dev = self._ids_dev[:T]
         ids_dev.copy_(self._ids_host[:T], non_blocking=True)
