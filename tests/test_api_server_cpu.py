@@ -162,3 +162,20 @@ def test_async_engine_abort_frees_the_request(engine):
             await asyncio.sleep(0.01)
         return False
     assert asyncio.run(run())
+
+
+def test_score_version_and_stop_string_options(client):
+    assert client.get("/ping").json() == {"status": "ok"} and "version" in client.get("/version").json()
+    r = client.post("/v1/score", json={"text_1": "hello", "text_2": ["hello", "something else"]})
+    assert r.status_code == 200, r.text
+    scores = [d["score"] for d in r.json()["data"]]
+    assert abs(scores[0] - 1.0) < 1e-5 and scores[1] < 0.9999
+    assert client.post("/score", json={"text_1": ["a", "b"], "text_2": ["c"]}).status_code == 400
+    # stop strings: cut before the match by default, kept with include_stop_str_in_output
+    body = {"prompt": "stop test", "max_tokens": 12, "temperature": 0, "ignore_eos": True}
+    full = client.post("/v1/completions", json=body).json()["choices"][0]["text"]
+    needle = full[4:6]
+    cut = client.post("/v1/completions", json={**body, "stop": [needle]}).json()["choices"][0]
+    kept = client.post("/v1/completions", json={**body, "stop": [needle], "include_stop_str_in_output": True}).json()["choices"][0]
+    assert cut["finish_reason"] == "stop" and full.startswith(cut["text"]) and needle not in cut["text"]
+    assert kept["text"] == cut["text"] + needle

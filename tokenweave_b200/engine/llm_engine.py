@@ -109,7 +109,8 @@ class LLMEngine:
             parent.children.append(child)
             detok = None
             if self.tokenizer is not None and params.detokenize:
-                detok = IncrementalDetokenizer(self.tokenizer, ids, params.skip_special_tokens, params.stop)
+                detok = IncrementalDetokenizer(self.tokenizer, ids, params.skip_special_tokens, params.stop,
+                                               params.include_stop_str_in_output)
             parent.detoks.append(detok)
             parent.logprobs.append([])
             parent.cum_logprob.append(0.0)

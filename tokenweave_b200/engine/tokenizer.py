@@ -49,10 +49,11 @@ class IncrementalDetokenizer:
     """Keeps the text of a request up to date as tokens arrive and checks stop strings."""
 
     def __init__(self, tokenizer, prompt_ids: list[int], skip_special_tokens: bool = True,
-                 stop: Optional[list[str]] = None):
+                 stop: Optional[list[str]] = None, include_stop: bool = False):
         self.tokenizer = tokenizer
         self.skip_special = skip_special_tokens
         self.stop = stop or []
+        self.include_stop = include_stop     # keep the matched stop string at the end of the text
         self.token_ids: list[int] = []
         self.text = ""
         self._emitted_prefix = 0     # tokens already turned into stable text
@@ -74,6 +75,6 @@ class IncrementalDetokenizer:
             # a new match must touch the text that was just added
             pos = self.text.find(s, max(0, len(self.text) - len(delta) - len(s) + 1))
             if pos >= 0:
-                self.text = self.text[:pos]
+                self.text = self.text[:pos + (len(s) if self.include_stop else 0)]
                 return s
         return None

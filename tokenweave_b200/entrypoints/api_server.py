@@ -27,7 +27,8 @@ logger = init_logger(__name__)
 _SAMPLING_FIELDS = ("n", "temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty",
                     "repetition_penalty", "seed", "stop", "stop_token_ids", "max_tokens", "min_tokens", "ignore_eos",
                     "skip_special_tokens", "logit_bias", "allowed_token_ids", "bad_words_token_ids", "guided_choice",
-                    "prompt_logprobs", "guided_regex", "guided_json")
+                    "prompt_logprobs", "guided_regex", "guided_json", "include_stop_str_in_output",
+                    "truncate_prompt_tokens")
 
 
 def sampling_params_from_request(body: dict, default_max_tokens: int = 16) -> SamplingParams:
@@ -115,6 +116,15 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
     @app.get("/health")
     async def health():
         return JSONResponse({"status": "ok"}) if engine.is_running else error(503, "engine is not running", "server_error")
+
+    @app.get("/ping")
+    async def ping():
+        return await health()
+
+    @app.get("/version")
+    async def version():
+        from .. import __version__
+        return {"version": __version__}
 
     @app.get("/v1/models")
     async def models():
@@ -261,6 +271,29 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
         return {"id": rid, "object": "list", "model": name, "data": data,
                 "usage": {"prompt_tokens": n_tok, "total_tokens": n_tok}}
 
+    @app.post("/score")
+    @app.post("/v1/score")
+    async def score(req: Request):
+        """Cosine similarity of ``text_1`` with every entry of ``text_2`` (or pairwise for equally long lists)."""
+        body = await req.json()
+        one = lambda x: isinstance(x, str) or (isinstance(x, list) and x and isinstance(x[0], int))   # noqa: E731
+        a = [body.get("text_1")] if one(body.get("text_1")) else list(body.get("text_1") or [])
+        b = [body.get("text_2")] if one(body.get("text_2")) else list(body.get("text_2") or [])
+        if len(a) == 1 and len(b) > 1:
+            a = a * len(b)
+        if not a or len(a) != len(b):
+            return error(400, "score takes one-to-many or equally long lists in text_1 / text_2")
+        rid = "score-" + uuid.uuid4().hex
+        try:
+            outs = await pooled_vectors({**body, "input": a + b}, rid)
+        except (ValueError, TypeError) as e:
+            return error(400, str(e))
+        except EngineDeadError as e:
+            return error(500, str(e), "server_error")
+        vecs = [o.pooled / o.pooled.norm().clamp_min(1e-12) for o in outs]
+        data = [{"index": i, "object": "score", "score": float((vecs[i] * vecs[len(a) + i]).sum())} for i in range(len(a))]
+        return {"id": rid, "object": "list", "model": name, "data": data}
+
     score_head = {}
 
     @app.post("/classify")
@@ -405,6 +438,7 @@ def main() -> None:
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--served-model-name", default=None)
+    ap.add_argument("--chat-template", default=None, help="a Jinja chat template (file or literal) replacing the tokenizer's")
     ap.add_argument("--lora-modules", nargs="*", default=[], metavar="NAME=PATH",
                     help="adapters to serve; a request selects one by its name in the model field (needs --enable-lora)")
     EngineArgs.add_cli_args(ap)
@@ -420,6 +454,10 @@ def main() -> None:
         engine = DataParallelEngine.from_engine_args(args)
     else:
         engine = AsyncLLMEngine.from_engine_args(args)
+    if ns.chat_template and engine.engine.tokenizer is not None:
+        import os as _os
+        tpl = open(ns.chat_template).read() if _os.path.exists(ns.chat_template) else ns.chat_template
+        engine.engine.tokenizer.chat_template = tpl
     import uvicorn
     try:
         uvicorn.run(build_app(engine, ns.served_model_name, lora_modules), host=ns.host, port=ns.port, log_level="info")

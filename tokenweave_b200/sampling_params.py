@@ -18,6 +18,7 @@ class SamplingParams:
     seed: Optional[int] = None
     stop: Union[None, str, list[str]] = None
     stop_token_ids: Optional[list[int]] = None
+    include_stop_str_in_output: bool = False
     max_tokens: Optional[int] = 16
     min_tokens: int = 0
     ignore_eos: bool = False
