@@ -32,6 +32,15 @@ _VARS: dict[str, Callable[[], Any]] = {
     "TW_RPC_TIMEOUT_S": lambda: float(os.getenv("TW_RPC_TIMEOUT_S", "180")),
     # trace every Python function call of the package to this file (debugging aid)
     "TW_TRACE_FUNCTION": lambda: os.getenv("TW_TRACE_FUNCTION"),
+    # decode attention kernel: "1" tensor cores where they apply (default), "0" the SIMT kernel everywhere,
+    # "persistent" the tensor-core kernel with one CTA per SM walking the work items (read by ops at import)
+    "TW_DECODE_TC": lambda: os.getenv("TW_DECODE_TC", "1"),
+    # vocabulary-parallel instead of replicated embedding table
+    "TW_EMBEDDING_PARALLEL": lambda: os.getenv("TW_EMBEDDING_PARALLEL", "0") == "1",
+    # libnccl for the ctypes binding (parallel/pynccl.py); default: the one torch ships
+    "TW_NCCL_SO_PATH": lambda: os.getenv("TW_NCCL_SO_PATH"),
+    # where the artifact scripts write their CSV / JSON results
+    "TW_RESULTS_DIR": lambda: os.getenv("TW_RESULTS_DIR", "results"),
     # port range start for rendezvous when none is given
     "TW_PORT": lambda: int(os.getenv("TW_PORT", "29611")),
 }
