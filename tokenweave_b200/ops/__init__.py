@@ -475,13 +475,15 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o
     kernel, splits = decode_plan(n_tok, hq, hkv, head_dim, page, max_kv_len, sm_count)
     part_o = part_ml = None
     if splits > 1:
-        key = (q.device.index, n_tok * hq * splits * head_dim)
+        # Partial results live in buffers whose sizes are powers of two and which are never freed: a captured
+        # CUDA graph keeps the raw addresses, so a buffer may not go away while any graph could replay, and
+        # rounding keeps the number of buffers small (launches of one stream use them one after the other).
+        partials = 1 << max(0, (n_tok * hq * splits - 1).bit_length())
+        key = (q.device.index, partials, head_dim)
         ws = _decode_ws.get(key)
         if ws is None:
-            ws = (torch.empty(n_tok * hq * splits * head_dim, dtype=torch.float32, device=q.device),
-                  torch.empty(n_tok * hq * splits * 2, dtype=torch.float32, device=q.device))
-            if len(_decode_ws) > 64:
-                _decode_ws.clear()
+            ws = (torch.empty(partials * head_dim, dtype=torch.float32, device=q.device),
+                  torch.empty(partials * 2, dtype=torch.float32, device=q.device))
             _decode_ws[key] = ws
         part_o, part_ml = ws
     if kernel == "tc":
