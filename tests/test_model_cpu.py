@@ -198,3 +198,41 @@ def test_fp8_quantised_model_tracks_the_full_precision_model():
     assert cos.min() > 0.98, cos
     with pytest.raises(ValueError):
         _engine("tiny-llama", quantization="int3")
+
+
+def test_fp8_checkpoint_loads_and_matches_online_quantisation(tmp_path):
+    """A checkpoint that stores e4m3 weights with per-channel scales (plus static activation scales, which are
+    ignored) runs on the fp8 path without a flag and gives what quantising the original weights online gives."""
+    from tokenweave_b200.ops import reference as ref
+    cfg = ModelConfig(name="tiny-llama", **MODEL_PRESETS["tiny-llama"])
+    st = make_hf_state(cfg, seed=12)
+    plain, quant = str(tmp_path / "plain"), str(tmp_path / "fp8")
+    save_hf_checkpoint(st, hf_config_dict(cfg), plain)
+    q_state = {}
+    for name, t in st.items():
+        if name.endswith("_proj.weight"):
+            q, s = ref.quant_fp8(t)
+            q_state[name] = q
+            q_state[name[: -len(".weight")] + ".weight_scale"] = s.reshape(-1, 1)
+            q_state[name[: -len(".weight")] + ".input_scale"] = torch.tensor(1.0)
+        else:
+            q_state[name] = t
+    hf = hf_config_dict(cfg)
+    hf["quantization_config"] = {"quant_method": "fp8", "activation_scheme": "static"}
+    save_hf_checkpoint(q_state, hf, quant)
+    prompts = _prompts(cfg.vocab_size, [60, 9])
+    logits = []
+    for path, kw in ((quant, {}), (plain, {"quantization": "fp8"})):
+        llm = _engine(path, **kw)
+        assert llm.llm_engine.config.quantization == "fp8"
+        r = _runner(llm)
+        r.capture_logits = True
+        llm.generate(prompts, SamplingParams(temperature=0, max_tokens=1))
+        got = {rid: row for reqs, lg in r.captured_logits for rid, row in zip(reqs, lg)}
+        logits.append(torch.stack([got[str(i)] for i in range(len(prompts))]))
+        llm.shutdown()
+    torch.testing.assert_close(logits[0], logits[1], atol=1e-4, rtol=1e-4)
+    bad = dict(hf_config_dict(cfg), quantization_config={"quant_method": "gptq", "bits": 4})
+    save_hf_checkpoint(st, bad, str(tmp_path / "gptq"))
+    with pytest.raises(ValueError, match="only fp8"):
+        _engine(str(tmp_path / "gptq"))

@@ -47,6 +47,7 @@ class ModelConfig:
     expert_parallel: bool = False       # MoE: whole experts per rank instead of tensor-sharded experts
     init_std: float = 0.02
     path: Optional[str] = None           # checkpoint directory (None: random init)
+    checkpoint_quantization: Optional[str] = None    # "fp8" when the checkpoint's config says its weights are fp8
 
     @property
     def is_moe(self) -> bool:
@@ -96,7 +97,25 @@ class ModelConfig:
             qk_norm=arch == "qwen3",
             num_experts=cfg.get("num_local_experts", 0), num_experts_per_tok=cfg.get("num_experts_per_tok", 2),
             max_model_len=max_len,
-            tie_word_embeddings=cfg.get("tie_word_embeddings", False), dtype=dt, eos_token_id=eos, path=path)
+            tie_word_embeddings=cfg.get("tie_word_embeddings", False), dtype=dt, eos_token_id=eos, path=path,
+            checkpoint_quantization=ModelConfig._quant_of(cfg))
+
+    @staticmethod
+    def _quant_of(cfg: dict) -> Optional[str]:
+        """"fp8" for checkpoints quantised to fp8 (``quant_method`` fp8, or compressed-tensors with 8-bit float
+        weights); other schemes are not served."""
+        qc = cfg.get("quantization_config") or {}
+        method = str(qc.get("quant_method", "")).lower()
+        if not method:
+            return None
+        if method == "fp8":
+            return "fp8"
+        if method == "compressed-tensors":
+            groups = (qc.get("config_groups") or {}).values()
+            if groups and all((g.get("weights") or {}).get("type") == "float" and (g.get("weights") or {}).get("num_bits") == 8
+                              for g in groups):
+                return "fp8"
+        raise ValueError(f"checkpoint quantised with {method!r}: only fp8 checkpoints are served")
 
     @staticmethod
     def from_pretrained(path: str) -> "ModelConfig":
@@ -331,6 +350,8 @@ class EngineArgs:
             model.expert_parallel = True
         max_len = model.max_model_len
         budget = self.max_num_batched_tokens or (8192 if self.enable_chunked_prefill else max(max_len, 8192))
+        if self.quantization is None and model.checkpoint_quantization is not None:
+            self.quantization = model.checkpoint_quantization        # an fp8 checkpoint runs on the fp8 GEMMs
         if self.quantization not in (None, "fp8"):
             raise ValueError(f"unknown quantization {self.quantization!r} (supported: fp8)")
         if self.quantization and self.tokenweave_mode == "fused_gemm":

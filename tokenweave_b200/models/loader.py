@@ -43,6 +43,54 @@ def iter_checkpoint(path: str) -> Iterator[tuple[str, torch.Tensor]]:
         del state
 
 
+_FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
+_SCALE_SUFFIXES = (".weight_scale", ".weight_scale_inv")
+_DROPPED_SUFFIXES = (".input_scale", ".k_scale", ".v_scale", ".q_scale", ".kv_scale")
+
+
+def dequantize_fp8(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """fp8 weight x its scale in fp32: per tensor (one value), per output channel (``[N]`` / ``[N, 1]``) or per
+    block (``[ceil(N / b), ceil(K / b)]``, the 128 x 128 block layout of block-quantised checkpoints)."""
+    w, s = weight.float(), scale.float()
+    if s.numel() == 1:
+        return w * s.reshape(())
+    if s.ndim == 1 or (s.ndim == 2 and s.shape[1] == 1):
+        return w * s.reshape(-1, 1)
+    if s.ndim == 2:
+        br, bc = -(-w.shape[0] // s.shape[0]), -(-w.shape[1] // s.shape[1])
+        full = s.repeat_interleave(br, 0)[: w.shape[0]].repeat_interleave(bc, 1)[:, : w.shape[1]]
+        return w * full
+    raise ValueError(f"fp8 scale of shape {tuple(s.shape)} for a weight of shape {tuple(w.shape)}")
+
+
+def dequantized_stream(weights: Iterator[tuple[str, torch.Tensor]]) -> Iterator[tuple[str, torch.Tensor]]:
+    """Pass-through for ordinary checkpoints. For fp8 checkpoints (``weight`` stored as e4m3 next to a
+    ``weight_scale`` / ``weight_scale_inv``; the FP8 and compressed-tensors layouts the reference reads in
+    vllm/model_executor/layers/quantization/fp8.py) every weight comes out as fp32 = fp8 x scale (the parameter copy rounds it to the model's dtype), whichever of
+    the two tensors the file lists first; static activation and KV scales are dropped (activations are quantised
+    dynamically here). With ``quantization="fp8"`` the layers are then re-quantised per output channel, which
+    reproduces a per-channel checkpoint exactly."""
+    pending_w: dict[str, torch.Tensor] = {}
+    pending_s: dict[str, torch.Tensor] = {}
+    for name, t in weights:
+        if name.endswith(_DROPPED_SUFFIXES):
+            continue
+        stem = None
+        if name.endswith(_SCALE_SUFFIXES):
+            stem = name.rsplit(".", 1)[0]
+            pending_s[stem] = t
+        elif name.endswith(".weight") and t.dtype in _FP8_DTYPES:
+            stem = name[: -len(".weight")]
+            pending_w[stem] = t
+        else:
+            yield name, t
+            continue
+        if stem in pending_w and stem in pending_s:
+            yield stem + ".weight", dequantize_fp8(pending_w.pop(stem), pending_s.pop(stem))
+    for stem, w in pending_w.items():          # an fp8 tensor without a scale: its values are the weights
+        yield stem + ".weight", w.float()
+
+
 def load_model_weights(model, config: EngineConfig) -> None:
     fmt = config.load_format
     if fmt == "dummy" or (fmt == "auto" and not config.model.path):
@@ -50,7 +98,7 @@ def load_model_weights(model, config: EngineConfig) -> None:
     else:
         if not config.model.path:
             raise ValueError(f"load_format={fmt!r} needs a checkpoint directory")
-        loaded = model.load_weights(iter_checkpoint(config.model.path))
+        loaded = model.load_weights(dequantized_stream(iter_checkpoint(config.model.path)))
         logger.info("loaded %d tensors from %s", len(loaded), config.model.path)
     if config.quantization == "fp8":
         quantize_linears_fp8_(model)
