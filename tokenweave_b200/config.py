@@ -271,7 +271,7 @@ class EngineConfig:
     parallel: ParallelConfig = field(default_factory=ParallelConfig)
     scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
     tokenweave: TokenWeaveConfig = field(default_factory=TokenWeaveConfig)
-    load_format: str = "auto"             # "auto" | "dummy" | "safetensors"
+    load_format: str = "auto"             # "auto" | "dummy" | "safetensors" | "sharded_state"
     quantization: Optional[str] = None    # None | "fp8" (e4m3 weights per channel, dynamic per-token activations)
     seed: int = 0
     device: str = "auto"                  # "auto" | "cuda" | "cpu"

@@ -95,6 +95,25 @@ def load_model_weights(model, config: EngineConfig) -> None:
     fmt = config.load_format
     if fmt == "dummy" or (fmt == "auto" and not config.model.path):
         model.init_dummy_weights(config.seed)
+    elif fmt == "sharded_state":
+        # every rank reads back exactly the parameters it wrote with ``LLM.save_sharded_state``: no resharding,
+        # no name mapping (vllm/model_executor/model_loader/loader.py ``ShardedStateLoader``)
+        from safetensors.torch import load_file
+        from ..parallel.state import get_tp
+        fname = os.path.join(config.model.path or "", f"rank_{get_tp().global_rank}.safetensors")
+        if not os.path.exists(fname):
+            raise FileNotFoundError(f"load_format='sharded_state' needs {fname} (written by LLM.save_sharded_state)")
+        state = load_file(fname)
+        params = dict(model.named_parameters())
+        missing = sorted(set(params) - set(state))
+        if missing:
+            raise ValueError(f"{fname} lacks {len(missing)} parameters of this rank (first: {missing[0]}); it was "
+                             f"saved under another parallel layout")
+        for n, p_ in params.items():
+            if tuple(state[n].shape) != tuple(p_.shape):
+                raise ValueError(f"{fname}: {n} has shape {tuple(state[n].shape)}, this rank expects {tuple(p_.shape)}")
+            p_.data.copy_(state[n])
+        logger.info("loaded %d sharded tensors from %s", len(params), fname)
     else:
         if not config.model.path:
             raise ValueError(f"load_format={fmt!r} needs a checkpoint directory")

@@ -223,6 +223,13 @@ class Worker:
         os.makedirs(path, exist_ok=True)
         state = {n: p.detach().cpu().contiguous() for n, p in self.runner.model.named_parameters()}
         save_file(state, os.path.join(path, f"rank_{self.rank}.safetensors"))
+        src = self.config.model.path
+        if self.rank == 0 and src and os.path.isdir(src) and os.path.abspath(src) != os.path.abspath(path):
+            import shutil      # the directory then loads on its own with load_format="sharded_state"
+            for name in os.listdir(src):
+                if name.endswith(".json") or name.startswith("tokenizer") or name.endswith(".model"):
+                    if "safetensors.index" not in name:
+                        shutil.copy(os.path.join(src, name), os.path.join(path, name))
 
     def load_sharded_state(self, path: str) -> None:
         from safetensors.torch import load_file
