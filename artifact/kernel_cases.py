@@ -35,10 +35,15 @@ def main() -> None:
                     help="attn_prefill: -1 library default, 0 auto, 1 one head per CTA, 2 head pairs")
     ap.add_argument("--attn-ring", type=int, default=0, help="attn_prefill head pairs: K/V tile slots (0 = all that fit)")
     ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--decode-variant", default=None, choices=["simt", "tc", "tcp"],
+                    help="attn_decode: SIMT kernel (attn_decode_kernel), tensor cores (attn_decode_tc_kernel) or their "
+                         "persistent form; default: the library's choice")
     args = ap.parse_args()
     from tokenweave_b200 import ops
     from tokenweave_b200.ops import _native
     _native.load().tw_attn_set_variant(args.attn_variant)
+    if args.decode_variant:
+        ops.set_decode_variant(args.decode_variant)
     _native.load().tw_attn_set_ring(args.attn_ring)
     torch.cuda.set_device(0)
     dev, BF = "cuda", torch.bfloat16
