@@ -45,6 +45,13 @@ class TPState:
 
 
 _STATE = TPState()
+_SUBGROUPS: list = []       # groups made by new_group here, destroyed (newest first) before the world group
+
+
+def _new_group(*args, **kwargs):
+    g = dist.new_group(*args, **kwargs)
+    _SUBGROUPS.append(g)
+    return g
 
 
 def get_tp() -> TPState:
@@ -119,7 +126,7 @@ def init_distributed(rank: int, world_size: int, local_rank: Optional[int] = Non
             dist.init_process_group(**kwargs)
             owns = True
         group = dist.group.WORLD
-        cpu_group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s)) if use_cuda else group
+        cpu_group = _new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s)) if use_cuda else group
     if pp_size == 1:
         _STATE = TPState(rank, world_size, local_rank, dev, group, cpu_group, owns, global_rank=rank,
                          global_size=world_size, world_cpu_group=cpu_group)
@@ -130,8 +137,8 @@ def init_distributed(rank: int, world_size: int, local_rank: Optional[int] = Non
     if tp_size > 1:
         for s in range(pp_size):
             ranks = list(range(s * tp_size, (s + 1) * tp_size))
-            g = dist.new_group(ranks, backend="nccl" if use_cuda else "gloo", timeout=datetime.timedelta(seconds=timeout_s))
-            cg = dist.new_group(ranks, backend="gloo", timeout=datetime.timedelta(seconds=timeout_s)) if use_cuda else g
+            g = _new_group(ranks, backend="nccl" if use_cuda else "gloo", timeout=datetime.timedelta(seconds=timeout_s))
+            cg = _new_group(ranks, backend="gloo", timeout=datetime.timedelta(seconds=timeout_s)) if use_cuda else g
             if rank in ranks:
                 tp_group, tp_cpu = g, cg
     _STATE = TPState(rank % tp_size, tp_size, local_rank, dev, tp_group, tp_cpu, owns, pp_rank=rank // tp_size,
@@ -168,9 +175,24 @@ def set_single_process(device: torch.device) -> TPState:
 
 
 def destroy_distributed() -> None:
+    """Leave the job's process groups. Every rank first meets the others on the host control plane, so no
+    rank tears its sockets down while a peer still has traffic (or a gloo worker thread) on them; the
+    sub-groups go before the world group they were carved from."""
     global _STATE
     if _STATE.owns_process_group and dist.is_initialized():
+        try:
+            if _STATE.world_cpu_group is not None:
+                dist.barrier(group=_STATE.world_cpu_group, async_op=True).wait(datetime.timedelta(seconds=20))
+        except Exception:            # a peer that died or hangs: do not wait for it
+            pass
+        while _SUBGROUPS:
+            g = _SUBGROUPS.pop()
+            try:
+                dist.destroy_process_group(g)
+            except Exception:
+                pass
         dist.destroy_process_group()
+    _SUBGROUPS.clear()
     _STATE = TPState()
 
 
