@@ -189,3 +189,42 @@ def test_truncate_prompt_tokens_and_priority_argument():
     t = [o.metrics.finished_time for o in outs]
     assert t[2] < t[1] < t[0]
     llm.shutdown()
+
+
+def test_a_non_zero_device_status_word_stops_the_engine_before_tokens_are_emitted():
+    """The runner reads the status word together with the sampled ids; a kernel that gave up on a wait must
+    end the engine instead of letting tokens computed from un-reduced data through. The word is faked here
+    (there is no device on this box): the second step reports a peer time-out."""
+    from tokenweave_b200.engine.core import EngineDeadError
+    llm = _llm()
+    runner = llm.llm_engine.core.executor.worker.runner
+    calls = {"n": 0}
+
+    def fake_status():
+        calls["n"] += 1
+        return torch.tensor([2 if calls["n"] >= 2 else 0], dtype=torch.int32)
+    runner._status_src = fake_status
+    with pytest.raises(EngineDeadError, match="peer"):
+        llm.generate(["abc"], SamplingParams(temperature=0, max_tokens=5, ignore_eos=True))
+    assert calls["n"] == 2
+    assert llm.llm_engine.core.dead
+    # only the first step's token was recorded; the failed step emitted nothing
+    req = next(iter(llm.llm_engine.core.scheduler.requests.values()))
+    assert len(req.output_token_ids) == 1
+    with pytest.raises(EngineDeadError):
+        llm.generate(["abc"], SamplingParams(max_tokens=1))
+    # the workers can put their communication state back collectively (a no-op for one CPU rank)
+    llm.llm_engine.core.executor.collective_rpc("reset_comm_state")
+
+
+def test_kv_fingerprint_keeps_models_apart(tmp_path):
+    from tokenweave_b200.engine.kv_connector import KVTransferConfig, SharedStorageConnector
+    cfg = KVTransferConfig(shared_storage_path=str(tmp_path))
+    a = SharedStorageConnector(cfg, 0, 1, "modelA")
+    b = SharedStorageConnector(cfg, 0, 1, "modelB")
+    k = torch.zeros(2, 16, 1, 8)
+    a.save_block(b"\x01" * 8, k, k)
+    assert a.available(b"\x01" * 8) and not b.available(b"\x01" * 8)
+    with pytest.raises(ValueError, match="shape"):
+        a.load_block(b"\x01" * 8, (3, 16, 1, 8))
+    assert a.load_block(b"\x01" * 8, (2, 16, 1, 8))[0].shape == k.shape

@@ -34,6 +34,10 @@ def _prefill_tokens(llm, prompts, sp):
     return outs, total
 
 
+def _stored(store):
+    return sorted(f for _, _, names in os.walk(store) for f in names)
+
+
 def test_consumer_reuses_the_producers_blocks(tmp_path):
     cfg = ModelConfig(name="tiny-llama", **MODEL_PRESETS["tiny-llama"])
     st = make_hf_state(cfg, seed=31)
@@ -49,7 +53,8 @@ def test_consumer_reuses_the_producers_blocks(tmp_path):
     outs, computed = _prefill_tokens(producer, [p1], sp)
     assert computed == len(p1) + 3                       # prompt + the decode steps
     producer.shutdown()
-    files = sorted(os.listdir(store))
+    files = _stored(store)
+    assert len(os.listdir(store)) == 1                   # one sub-directory: the fingerprint of this KV layout
     assert len(files) == len(p1) // 16 and all(f.endswith(".r0of1.pt") for f in files)
 
     consumer = LLM(ckpt, kv_transfer_config=_cfg("kv_consumer", store), **args)
@@ -62,7 +67,7 @@ def test_consumer_reuses_the_producers_blocks(tmp_path):
             seq.append(int(naive_logits(cfg, st, seq)[-1].argmax()))
         assert out.outputs[0].token_ids == seq[len(p):]
     assert outs2[1].outputs[0].token_ids == outs[0].outputs[0].token_ids
-    assert sorted(os.listdir(store)) == files            # a consumer writes nothing
+    assert _stored(store) == files                       # a consumer writes nothing
     consumer.shutdown()
 
 
@@ -103,4 +108,4 @@ def test_connector_under_tp2(tmp_path):
     for _ in range(4):
         seq.append(int(naive_logits(cfg, st, seq)[-1].argmax()))
     run_ranks(_tp_rank, 2, ckpt, store, p1, p2, seq[len(p2):])
-    assert len(os.listdir(store)) == 2 * 6           # six blocks, one file per rank
+    assert len(_stored(store)) == 2 * 6              # six blocks, one file per rank

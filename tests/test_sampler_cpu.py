@@ -87,6 +87,16 @@ def test_logprobs_hold_the_sampled_token_and_the_top_n():
         assert math.isclose(v, float(ref[t]), abs_tol=1e-6)
 
 
+def test_logprobs_are_the_models_own_even_when_penalties_and_masks_change_the_choice():
+    logits = torch.tensor([[1.0, 5.0, 3.0, 2.0]])
+    ref = torch.log_softmax(logits[0], -1)
+    out = Sampler()(logits.clone(), [SamplingParams(temperature=0, logprobs=2, logit_bias={1: -100.0})], [None], [[]], [[]])
+    assert int(out.token_ids[0]) == 2                      # the bias moved the choice away from token 1
+    lp = out.logprobs[0]
+    assert math.isclose(lp[2], float(ref[2]), abs_tol=1e-6)
+    assert math.isclose(lp[1], float(ref[1]), abs_tol=1e-6)     # token 1 is still the model's most likely one
+
+
 def test_logit_bias_allowed_tokens_bad_words_min_tokens():
     logits = torch.tensor([[1.0, 5.0, 3.0, 2.0, 0.0, -1.0]])
     s = Sampler()

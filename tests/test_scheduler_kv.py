@@ -113,7 +113,7 @@ def test_prompt_too_long_rejected():
 
 
 # ---- randomised runs: invariants that must hold for any arrival pattern ---------------------------
-def _fuzz_once(seed, caching, spec_k):
+def _fuzz_once(seed, caching, spec_k, policy="fcfs"):
     import random
     from tokenweave_b200.engine.spec_decode import SpecDecodeConfig
     rng = random.Random(seed)
@@ -122,7 +122,7 @@ def _fuzz_once(seed, caching, spec_k):
     budget = rng.choice([16, 48, 96])
     kv = KVCacheManager(num_blocks, block, caching)
     spec = SpecDecodeConfig(num_speculative_tokens=spec_k)
-    s = Scheduler(SchedulerConfig(budget, rng.randrange(2, 7), True, 512), kv, spec)
+    s = Scheduler(SchedulerConfig(budget, rng.randrange(2, 7), True, 512, policy), kv, spec)
     capacity = (num_blocks - 1) * block
     pending = []
     for i in range(rng.randrange(4, 14)):
@@ -131,6 +131,7 @@ def _fuzz_once(seed, caching, spec_k):
         ids = (shared + [rng.randrange(5, 50) for _ in range(n)])[:n]
         pending.append(Request(str(i), ids, SamplingParams(max_tokens=rng.randrange(1, 12), temperature=0,
                                                             stop_token_ids=[49] if rng.random() < 0.3 else None)))
+        pending[-1].priority = rng.randrange(0, 4) if policy == "priority" else 0
     expected_prompt = {r.request_id: list(r.prompt_token_ids) for r in pending}
     finished, steps = {}, 0
     while pending or s.has_unfinished_requests():
@@ -144,6 +145,9 @@ def _fuzz_once(seed, caching, spec_k):
         out = s.schedule()
         assert out.total_num_tokens <= budget
         assert len({x.request.request_id for x in out.scheduled}) == len(out.scheduled)
+        # a request preempted in this step runs no tokens in it, and what runs is in the running list
+        assert not {x.request.request_id for x in out.scheduled} & set(out.preempted_req_ids)
+        assert all(x.request in s.running for x in out.scheduled)
         owned = [b for r in s.running for b in r.block_ids]
         if not caching:
             assert len(owned) == len(set(owned)), "a block is owned twice"
@@ -185,6 +189,36 @@ def _fuzz_once(seed, caching, spec_k):
 def test_random_workloads_keep_the_invariants(caching, spec_k):
     for seed in range(60):
         _fuzz_once(seed * 7 + spec_k, caching, spec_k)
+
+
+@pytest.mark.parametrize("caching,spec_k", [(False, 0), (True, 2)])
+def test_random_workloads_under_the_priority_policy(caching, spec_k):
+    for seed in range(60):
+        _fuzz_once(seed * 11 + spec_k, caching, spec_k, policy="priority")
+
+
+def test_priority_victim_already_scheduled_in_the_step_is_taken_out():
+    """A less urgent request that got its tokens earlier in the step loses them (and its blocks) when a more
+    urgent one behind it in the running list cannot grow: it must not stay among the step's scheduled requests."""
+    kv = KVCacheManager(num_blocks=7, block_size=16, enable_caching=False)       # 6 usable blocks
+    s = Scheduler(SchedulerConfig(64, 8, True, 1024, "priority"), kv)
+    a, b = req(0, 34, max_tokens=40), req(1, 47, max_tokens=40)
+    a.priority, b.priority = 5, 0
+    s.add_request(a)
+    run_step(s)
+    s.add_request(b)
+    seen = False
+    for _ in range(6):
+        out = s.schedule()
+        ids = [x.request.request_id for x in out.scheduled]
+        assert not set(ids) & set(out.preempted_req_ids)
+        assert out.total_num_tokens == sum(x.num_new_tokens for x in out.scheduled) <= 64
+        owned = [blk for r in s.running for blk in r.block_ids]
+        assert len(owned) == len(set(owned))
+        seen = seen or out.preempted_req_ids == ["0"]
+        s.update_from_output(out, ModelRunnerOutput(ids, [7] * len(ids)))
+    assert seen, "the case never preempted the less urgent request"
+    assert a.status == RequestStatus.PREEMPTED or a in s.running
 
 
 def test_priority_policy_orders_admission_and_preemption():

@@ -237,7 +237,7 @@ extern "C" int tw_attn_decode(const void* q, long long ldq, const void* k_cache,
                               int hq, int hkv, int D, float scale, int splits, float* part_o,
                               float* part_ml, cudaStream_t stream) {
   if (n_tok <= 0) return 0;
-  if ((D != 128 && D != 64) || hq % hkv != 0 || hq / hkv > DEC_GMAX) {
+  if ((D != 128 && D != 64) || hkv <= 0 || hq <= 0 || hq % hkv != 0 || hq / hkv > DEC_GMAX) {
     set_last_error("attn_decode: unsupported shape (D=%d, hq=%d, hkv=%d)", D, hq, hkv);
     return 1;
   }
@@ -324,7 +324,7 @@ extern "C" int tw_attn_decode_noalloc(const void* q, long long ldq, const void* 
                                       const int* block_table, int max_blocks, int hq, int hkv, int D,
                                       float scale, int splits, cudaStream_t stream) {
   if (n_tok <= 0) return 0;
-  if ((D != 128 && D != 64) || hkv <= 0 || hq % hkv != 0 || hq / hkv > DEC_GMAX) {
+  if ((D != 128 && D != 64) || hkv <= 0 || hq <= 0 || hq % hkv != 0 || hq / hkv > DEC_GMAX) {
     set_last_error("attn_decode_noalloc: unsupported shape (D=%d, hq=%d, hkv=%d)", D, hq, hkv);
     return 1;
   }

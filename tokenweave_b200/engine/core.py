@@ -11,6 +11,7 @@ from typing import Optional
 from ..config import EngineConfig
 from ..executor import Executor, make_executor
 from ..executor.base import ExecutorFailure
+from ..ops import KernelStatusError
 from ..utils.logging import init_logger
 from ..utils.metrics import StepStats
 from ..worker.model_runner import NewRequestData, StepData, StepResult
@@ -40,8 +41,8 @@ class EngineCore:
         # KV connector: the scheduler side only asks which blocks the store can supply; the workers move the data
         self.kv_transfer = config.kv_transfer
         if self.kv_transfer is not None:
-            from .kv_connector import SharedStorageConnector
-            lookup = SharedStorageConnector(self.kv_transfer, 0, config.parallel.world_size)
+            from .kv_connector import SharedStorageConnector, kv_fingerprint
+            lookup = SharedStorageConnector(self.kv_transfer, 0, config.parallel.world_size, kv_fingerprint(config))
             self.kv.track_published = self.kv_transfer.can_save
             if self.kv_transfer.can_load:
                 self.scheduler.connector = lookup
@@ -96,6 +97,12 @@ class EngineCore:
         except ExecutorFailure as e:
             self.dead = True
             raise EngineDeadError(str(e)) from e
+        except KernelStatusError as e:
+            # an in-process worker read a non-zero device status word with the step's result: the collectives
+            # of this step did not complete, nothing of it is emitted, and the signal pads / tile flags are in an
+            # unknown state until the workers run ``reset_comm_state`` together
+            self.dead = True
+            raise EngineDeadError(f"a kernel reported a failed wait: {e}") from e
         if result.prompt_logprobs:
             by_id = {s.request.request_id: s.request for s in sched.scheduled}
             for rid, items in result.prompt_logprobs.items():

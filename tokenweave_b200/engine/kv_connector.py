@@ -60,12 +60,16 @@ class SharedStorageConnector:
     """``rank`` / ``world`` are the global rank and size of the replica's worker group; the scheduler side uses
     rank 0 and only asks :meth:`num_matched`."""
 
-    def __init__(self, cfg: KVTransferConfig, rank: int = 0, world: int = 1):
+    def __init__(self, cfg: KVTransferConfig, rank: int = 0, world: int = 1, fingerprint: str = ""):
+        """``fingerprint`` names what must agree between the engines that share the directory (model, dtype,
+        block size, layer count, parallel layout): it becomes a sub-directory, so two models that point at the
+        same path never exchange blocks."""
         self.cfg, self.rank, self.world = cfg, rank, world
-        os.makedirs(cfg.shared_storage_path, exist_ok=True)
+        self.root = os.path.join(cfg.shared_storage_path, fingerprint) if fingerprint else cfg.shared_storage_path
+        os.makedirs(self.root, exist_ok=True)
 
     def _file(self, block_hash: bytes, rank: int) -> str:
-        return os.path.join(self.cfg.shared_storage_path, f"{block_hash.hex()}.r{rank}of{self.world}.pt")
+        return os.path.join(self.root, f"{block_hash.hex()}.r{rank}of{self.world}.pt")
 
     def available(self, block_hash: bytes) -> bool:
         return all(os.path.exists(self._file(block_hash, r)) for r in range(self.world))
@@ -88,6 +92,20 @@ class SharedStorageConnector:
         torch.save({"k": k.cpu().contiguous(), "v": v.cpu().contiguous()}, tmp)
         os.replace(tmp, path)
 
-    def load_block(self, block_hash: bytes) -> tuple[torch.Tensor, torch.Tensor]:
-        d = torch.load(self._file(block_hash, self.rank), map_location="cpu")
-        return d["k"], d["v"]
+    def load_block(self, block_hash: bytes, expect_shape=None) -> tuple[torch.Tensor, torch.Tensor]:
+        """Tensors only (``weights_only``): the directory is written by other processes. ``expect_shape`` is
+        the ``[layers, page, kv_heads, head_dim]`` shape the caller's cache needs."""
+        d = torch.load(self._file(block_hash, self.rank), map_location="cpu", weights_only=True)
+        k, v = d["k"], d["v"]
+        if expect_shape is not None and (tuple(k.shape) != tuple(expect_shape) or tuple(v.shape) != tuple(expect_shape)):
+            raise ValueError(f"stored KV block has shape {tuple(k.shape)}, this engine needs {tuple(expect_shape)}")
+        return k, v
+
+
+def kv_fingerprint(config) -> str:
+    """Identity of a KV layout: engines whose fingerprints differ keep their blocks apart."""
+    import hashlib
+    m, par = config.model, config.parallel
+    key = (m.name, m.architecture, m.num_layers, m.hidden_size, m.num_kv_heads, m.head_dim, str(m.dtype),
+           config.cache.block_size, par.tensor_parallel_size, getattr(par, "pipeline_parallel_size", 1))
+    return hashlib.sha256(repr(key).encode()).hexdigest()[:16]

@@ -131,6 +131,13 @@ class Scheduler:
                     victim = self.running.pop(worst)
                     if worst < i:
                         i -= 1                  # the list shifted under the cursor
+                        # the victim already has its tokens in this step: take them out again (its blocks are
+                        # about to be freed) and hand the tokens back to the budget
+                        for k, sr in enumerate(out.scheduled):
+                            if sr.request is victim:
+                                budget += sr.num_new_tokens
+                                del out.scheduled[k]
+                                break
                 else:
                     victim = self.running.pop()     # most recently admitted
                 self._preempt(victim)

@@ -43,8 +43,12 @@ def _worker_main(config: EngineConfig, rank: int, init_method: str, mq_handle: t
         ready_conn.send(("FAILED", traceback.format_exc()))
         return
     parent = os.getppid()
-    fail_at = int(os.environ.get("TW_TEST_FAIL_AT_STEP", "-1"))      # host-side fault injection for tests
-    exit_at = int(os.environ.get("TW_TEST_EXIT_AT_STEP", "-1"))
+    # Host-side fault injection for tests. Honoured by CPU workers only: a GPU rank that exits while its
+    # symmetric buffer is bound to an NVLink multicast object can fault its peers' GPUs.
+    fail_at = exit_at = -1
+    if worker.device.type == "cpu":
+        fail_at = int(os.environ.get("TW_TEST_FAIL_AT_STEP", "-1"))
+        exit_at = int(os.environ.get("TW_TEST_EXIT_AT_STEP", "-1"))
     fault_rank = int(os.environ.get("TW_TEST_FAULT_RANK", "0"))
     steps = 0
     while True:

@@ -158,9 +158,11 @@ class Sampler:
                  generators: Sequence[Optional[torch.Generator]], prompt_tokens=None, output_tokens=None) -> SamplerOutput:
         B, V = logits.shape
         want_logprobs = any(sp.logprobs is not None for sp in params)
+        # reported log-probabilities are the model's own: taken before penalties, logit bias and masks touch the
+        # logits (vllm/v1/sample/sampler.py:36-47 computes its raw_logprobs first as well)
+        raw_logprobs = torch.log_softmax(logits.float(), dim=-1) if want_logprobs else None
         if any(sp.needs_penalties for sp in params):
             logits = apply_penalties(logits.clone(), params, prompt_tokens, output_tokens, guided=self._guided)
-        raw_logprobs = torch.log_softmax(logits, dim=-1) if want_logprobs else None
         if all(sp.greedy for sp in params):
             ids = ops.argmax(logits)
         elif logits.is_cuda and self.use_fused_kernel:

@@ -46,6 +46,29 @@ class TPCommunicator:
     def _mc(self) -> Optional[int]:
         return self.buf.multicast_ptr if self.use_mc else None
 
+    def reset_after_failure(self) -> None:
+        """Collective recovery after a kernel reported a failed wait: every rank calls this together.
+
+        A barrier that ran out leaves raised flags behind, a fused GEMM that gave up leaves tile counters and
+        shard epochs half-way; the next kernel would read them as its own. All ranks drain their device, meet
+        on the host, zero their signal pad, flag words, epochs and status word, and meet again before any
+        kernel runs."""
+        from .state import cpu_barrier
+        if self.tp.device.type == "cuda":
+            torch.cuda.synchronize(self.tp.device)
+        cpu_barrier()
+        if self.in_kernel:
+            self.buf.reset_signal_pads()
+            flags = getattr(self, "flags", None)
+            if flags is not None:
+                flags.tensor.zero_()
+                flags.reset_signal_pads()
+                self._epochs.zero_()
+        if self.tp.device.type == "cuda":
+            ops.reset_status(self.tp.device)
+            torch.cuda.synchronize(self.tp.device)
+        cpu_barrier()
+
     # ---- the product op -----------------------------------------------------------------
     def fused_allreduce_add_rmsnorm_(self, x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
                                      eps: float, max_ctas: int = 16, mode: int = 0, rows_in_flight: int = 0) -> None:

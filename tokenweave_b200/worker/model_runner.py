@@ -114,6 +114,9 @@ class ModelRunner:
         n_rows = max(config.scheduler.max_num_seqs, 1) * (1 + k_spec)
         self._rows_dev = torch.zeros(n_rows, dtype=torch.long, device=device)
         self._rows_host = torch.zeros(n_rows, dtype=torch.long, pin_memory=pin)
+        # the word kernels OR their error codes into travels to the host with the sampled ids of every step
+        self._status_src = (lambda: ops.status_word(device)) if pin else None
+        self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pin)
         self._graphs: dict = {}
         self._graph_seen: dict = {}
         self._graph_pool = None
@@ -380,8 +383,13 @@ class ModelRunner:
                                    [r.token_ids[r.num_prompt_tokens:] for r in reqs])
             if ev is not None:
                 ev[1].record()
+            if self._status_src is not None:
+                self._status_host.copy_(self._status_src(), non_blocking=True)
             toks = out.token_ids.tolist()            # the device -> host synchronisation point of the step
             d2h = len(toks) * 4
+            if self._status_src is not None:
+                d2h += 4
+                self._raise_on_device_status()
             lp = out.logprobs
             i = 0
             while i < len(toks):
@@ -412,6 +420,15 @@ class ModelRunner:
         if self.tp.pp_size > 1:
             result = broadcast_from_last_stage(result)       # every stage's scheduler sees the same result
         return result
+
+    def _raise_on_device_status(self) -> None:
+        """Called right after the step's device -> host synchronisation: a kernel that gave up on a bounded
+        wait (a peer that never signalled, a tile flag that never came) has left un-reduced data behind, so
+        the step's tokens must not be emitted. The word is sticky (kernels OR into it), so a failure in a
+        step that sampled nothing is seen at the next step that does."""
+        code = int(self._status_host[0])
+        if code != 0:
+            raise ops.KernelStatusError(code)
 
     def _prompt_logprobs(self, jobs: list[tuple[str, int, int, int]]) -> dict:
         """Log-probabilities of the prompt tokens computed in this step: the final-norm hidden rows of the

@@ -95,6 +95,14 @@ class Worker:
             ops.check_status(self.device)
         return True
 
+    def reset_comm_state(self) -> None:
+        """Collective: put signal pads, tile flags, epochs and the status word back to their start state after a
+        step ended with a non-zero status word (``EngineCore`` is dead by then; a supervisor that wants to go on
+        calls this on all workers and builds a new core on the same executor)."""
+        rt = self.runner.model.rt if self.runner is not None and self.runner.model is not None else None
+        if rt is not None:
+            rt.comm.reset_after_failure()
+
     # ---- profiling hooks (LLM.start_profile / stop_profile) ----
     def profile(self, start: bool) -> None:
         trace_dir = envs.TW_TORCH_PROFILER_DIR
@@ -182,9 +190,10 @@ class Worker:
     # ---- KV connector (engine/kv_connector.py): blocks to / from the external store -------------------------
     def _kv_connector(self):
         if getattr(self, "_connector", None) is None:
-            from ..engine.kv_connector import SharedStorageConnector
+            from ..engine.kv_connector import SharedStorageConnector, kv_fingerprint
             tp = pstate.get_tp()
-            self._connector = SharedStorageConnector(self.config.kv_transfer, tp.global_rank, tp.global_size)
+            self._connector = SharedStorageConnector(self.config.kv_transfer, tp.global_rank, tp.global_size,
+                                                     kv_fingerprint(self.config))
         return self._connector
 
     def save_kv_blocks(self, items: list) -> None:
@@ -203,8 +212,9 @@ class Worker:
     def load_kv_blocks(self, items: list) -> None:
         conn = self._kv_connector()
         layers = self.runner.model.layers
+        want = (len(layers),) + tuple(layers[0].attn.k_cache.shape[1:])
         for block, h in items:
-            k, v = conn.load_block(h)
+            k, v = conn.load_block(h, want)
             for i, layer in enumerate(layers):
                 layer.attn.k_cache[block].copy_(k[i], non_blocking=True)
                 layer.attn.v_cache[block].copy_(v[i], non_blocking=True)
