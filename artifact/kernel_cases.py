@@ -32,7 +32,11 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--attn-variant", type=int, default=-1,
-                    help="attn_prefill: -1 library default, 0 auto, 1 one head per CTA, 2 head pairs")
+                    help="attn_prefill: -1 library default, 0 auto, 1 one head per CTA, 2 head pairs, 3 persistent with split key range")
+    ap.add_argument("--q-tokens", type=int, default=0,
+                    help="attn_prefill: only the last N tokens are queries (a chunk of a longer prompt, or the second "
+                         "token subset of the overlap schedule); 0 = all")
+    ap.add_argument("--max-ctas", type=int, default=0, help="attn_prefill variant 3: SM budget (0 = all)")
     ap.add_argument("--attn-ring", type=int, default=0, help="attn_prefill head pairs: K/V tile slots (0 = all that fit)")
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--decode-variant", default=None, choices=["simt", "tc", "tcp"],
@@ -82,13 +86,15 @@ def main() -> None:
         T, hq, hkv, D, page = args.tokens, args.heads, args.kv_heads, args.head_dim, 128
         nb = T // page + 1
         kc, vc = torch.randn(nb, page, hkv, D, device=dev).to(BF), torch.randn(nb, page, hkv, D, device=dev).to(BF)
-        q = torch.randn(T, hq * D, device=dev).to(BF)
+        Tq = args.q_tokens or T
+        q = torch.randn(Tq, hq * D, device=dev).to(BF)
         out = torch.empty_like(q)
         i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
-        tiles = list(range(0, T, 128))[::-1]
-        meta = (i32([0, T]), i32([T]), torch.arange(nb, dtype=torch.int32, device=dev).view(1, -1), i32([0] * len(tiles)), i32(tiles))
-        fn = lambda: ops.attn_prefill(q, kc, vc, out, meta[0], meta[1], meta[2], meta[3], meta[4], len(tiles), hq, hkv, D, D ** -0.5)
-        flops = 4 * T * T * hq * D // 2
+        tiles = list(range(0, Tq, 128))[::-1]
+        meta = (i32([0, Tq]), i32([T]), torch.arange(nb, dtype=torch.int32, device=dev).view(1, -1), i32([0] * len(tiles)), i32(tiles))
+        fn = lambda: ops.attn_prefill(q, kc, vc, out, meta[0], meta[1], meta[2], meta[3], meta[4], len(tiles), hq, hkv, D, D ** -0.5,
+                                      max_ctas=args.max_ctas)
+        flops = 4 * hq * D * (T * T - (T - Tq) * (T - Tq)) // 2
     elif args.case == "attn_decode":
         B, kv, hq, hkv, D, page = 256, 2048, args.heads, args.kv_heads, 128, 128
         nb = B * (kv // page) + 1

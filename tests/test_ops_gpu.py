@@ -172,9 +172,12 @@ def _make_paged(seqs, hkv, D, page, extra_blocks=3):
     (4, 2, 64, 32, [(333, 333), (64, 500), (1, 130)]),
     (6, 1, 128, 128, [(513, 1300)]),
 ])
-@pytest.mark.parametrize("variant", [1, 2])      # one head per CTA / two heads of a KV group per CTA
+# one head per CTA / two heads of a KV group per CTA / persistent CTAs with the key range split between the
+# softmax groups (on every SM, and on 3 CTAs so that each walks several items in both directions)
+@pytest.mark.parametrize("variant", [1, 2, 3, (3, 3)])
 def test_attn_prefill(hq, hkv, D, page, seqs, variant):
     from tokenweave_b200.ops import _native
+    variant, max_ctas = variant if isinstance(variant, tuple) else (variant, 0)
     _native.load().tw_attn_set_variant(variant)
     kc, vc, bt, cu, kv_lens = _make_paged(seqs, hkv, D, page)
     T = cu[-1]
@@ -188,10 +191,13 @@ def test_attn_prefill(hq, hkv, D, page, seqs, variant):
             tile_q0.append(q0)
     out = torch.zeros_like(q)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    ops.attn_prefill(q, kc, vc, out, i32(cu), i32(kv_lens), bt, i32(tile_seq), i32(tile_q0), len(tile_seq), hq,
-                     hkv, D, scale)
-    torch.cuda.synchronize()
-    _native.load().tw_attn_set_variant(-1)
+    try:
+        ops.attn_prefill(q, kc, vc, out, i32(cu), i32(kv_lens), bt, i32(tile_seq), i32(tile_q0), len(tile_seq), hq,
+                         hkv, D, scale, max_ctas=max_ctas)
+        torch.cuda.synchronize()
+        ops.check_status()
+    finally:
+        _native.load().tw_attn_set_variant(-1)
     close(out, expect, atol=2e-2, rtol=3e-2)
 
 

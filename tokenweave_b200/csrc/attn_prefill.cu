@@ -17,41 +17,11 @@
 //               across tiles and is rescaled only when the running maximum grows by more than 2^8
 //               (the stale maximum is a valid softmax reference; P stays below 256).
 // Every wait is bounded; a timeout reports TW_ERR_MBAR_TIMEOUT and leaves by the tear-down.
-#include "tw_common.cuh"
+#include "attn_prefill_common.cuh"
 #include "tw_host.h"
 #include "tw_kernels.h"
 
 namespace tw {
-
-constexpr int ATT_BM = 128;      // query rows per CTA
-constexpr int ATT_BN = 128;      // keys per tile
-constexpr int ATT_SOFTMAX_THREADS = 256;
-constexpr int ATT_THREADS = 64 + ATT_SOFTMAX_THREADS;
-constexpr int ATT_HALF_BYTES = 128 * 128;  // a [128 rows x 64 bf16] swizzled half tile
-
-// 2^x in one MUFU instruction (ex2.approx with flush-to-zero; exp2f() without fast-math wraps the same
-// instruction in range fix-ups that cost four more issue slots per element). Inputs here are <= 8 or -inf.
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-struct AttnParams {
-  __nv_bfloat16* out;
-  long long ldo;
-  const int* cu_q;         // [B+1] first query row of each sequence
-  const int* kv_lens;      // [B] keys visible to the last query of the sequence
-  const int* block_table;  // [B, max_blocks]
-  const int* tile_seq;     // [num_tiles] sequence of each query tile
-  const int* tile_q0;      // [num_tiles] first query (within the sequence) of the tile
-  int max_blocks;
-  int page;                // tokens per cache page
-  int hq, hkv;
-  int ring;                // head-pair kernel: K/V tile slots in use
-  float scale_log2;        // softmax scale * log2(e)
-  uint32_t* status;
-};
 
 template <int D>
 struct AttnSmem {
@@ -708,6 +678,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 }
 
 constexpr int ATTN_DEFAULT_VARIANT = 0;
+constexpr bool ATTN_AUTO_SPLIT = false;   // what "automatic" picks: the persistent split kernel, or the per-tile kernels
 static int g_attn_variant = ATTN_DEFAULT_VARIANT;   // 0 auto, 1 one head per CTA, 2 head pairs
 static int g_attn_ring = 0;                          // 0: as many K/V slots as fit
 
@@ -777,7 +748,7 @@ extern "C" int tw_attn_prefill(const void* q, long long ldq, int T, const void* 
                                int num_blocks, int page, void* out, long long ldo, const int* cu_q,
                                const int* kv_lens, const int* block_table, int max_blocks,
                                const int* tile_seq, const int* tile_q0, int num_tiles, int hq, int hkv,
-                               int D, float scale, uint32_t* status, cudaStream_t stream) {
+                               int D, float scale, int max_ctas, uint32_t* status, cudaStream_t stream) {
   if (num_tiles <= 0 || T <= 0) return 0;
   if (D != 128 && D != 64) {
     set_last_error("attn_prefill: head_dim must be 64 or 128 (got %d)", D);
@@ -820,6 +791,10 @@ extern "C" int tw_attn_prefill(const void* q, long long ldq, int T, const void* 
   p.ring = 3;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  // Persistent kernel with the key range of an item split between the softmax groups (variant 3): the
+  // only one that honours an SM budget.
+  if (g_attn_variant == 3 || (g_attn_variant == 0 && ATTN_AUTO_SPLIT))
+    return launch_prefill_split(D, tmQ, tmK, tmV, p, num_tiles, max_ctas, stream);
   // Query heads that share a KV head go two to a CTA when the group size is even.
   const bool pair = ((hq / hkv) % 2 == 0) && g_attn_variant != 1;
   if (pair)
@@ -830,6 +805,7 @@ extern "C" int tw_attn_prefill(const void* q, long long ldq, int T, const void* 
 }
 
 // Kernel choice for tuning runs and tests: 0 automatic, 1 one head per CTA, 2 head pairs where legal,
+// 3 persistent CTAs with the key range split between the softmax groups,
 // negative: back to the library default.
 extern "C" int tw_attn_set_ring(int slots) {
   g_attn_ring = slots;

@@ -387,8 +387,10 @@ def sample(logits: torch.Tensor, packed_params: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------
 def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                  cu_q: torch.Tensor, kv_lens: torch.Tensor, block_table: torch.Tensor, tile_seq: torch.Tensor,
-                 tile_q0: torch.Tensor, num_tiles: int, hq: int, hkv: int, head_dim: int, scale: float) -> None:
-    """Tensor-core causal attention for the 128-query tiles listed in (tile_seq, tile_q0)."""
+                 tile_q0: torch.Tensor, num_tiles: int, hq: int, hkv: int, head_dim: int, scale: float,
+                 max_ctas: int = 0) -> None:
+    """Tensor-core causal attention for the 128-query tiles listed in (tile_seq, tile_q0), heaviest tile first.
+    ``max_ctas`` bounds the SMs the persistent kernel occupies (0: all)."""
     if num_tiles == 0:
         return
     _check_bf16(q, k_cache, v_cache, out)
@@ -396,8 +398,8 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     _native.call("tw_attn_prefill", q.data_ptr(), _row_stride(q), q.shape[0], k_cache.data_ptr(),
                  v_cache.data_ptr(), num_blocks, page, out.data_ptr(), _row_stride(out), cu_q.data_ptr(),
                  kv_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], tile_seq.data_ptr(),
-                 tile_q0.data_ptr(), num_tiles, hq, hkv, head_dim, scale, status_word(q.device).data_ptr(),
-                 _stream())
+                 tile_q0.data_ptr(), num_tiles, hq, hkv, head_dim, scale, max_ctas,
+                 status_word(q.device).data_ptr(), _stream())
 
 
 _decode_ws: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
