@@ -14,6 +14,11 @@ eps 1e-5, seed per rank. Columns (microseconds, median, cold L2, max over ranks)
   simple_fusion  RS, norm, AG as three phases of one kernel
   fused[c]       the product kernel on c CTAs, c in --ctas ("fused_best" = min over c)
   roofline_us    T*H*2 bytes over the measured 770 GB/s per direction; frac = roofline / fused_best
+  ref_*          with --reference-kernels: the reference's OWN kernels (csrc/tokenweave_fused_kernels.cu and
+                 csrc/tokenweave_artifact_kernels.cu, unchanged, built by baseline/build_ref_kernels.py) on the same
+                 box, same inputs, same timing loop, driven as artifact/figure_4_10/bench.py:136-160 drives them:
+                 ref_fused[c] / ref_fused_best (fused_rs_ln_ag_cta), ref_mm_ar (multimem_ar_cta),
+                 ref_simple_fusion (simple_fusion_rs_ln_ag_cta)
 Each fused result is checked against NCCL all-reduce + reference RMSNorm with atol = rtol = 4e-2.
 """
 from __future__ import annotations
@@ -64,6 +69,9 @@ def main() -> None:
     ap.add_argument("--burst", type=int, default=20,
                     help="also time this many back-to-back launches per event pair (steady-state latency per launch, "
                          "warm L2, no host in between: how the kernels run inside a model step); 0 disables")
+    ap.add_argument("--reference-kernels", action="store_true",
+                    help="also time the reference's own kernels from baseline/_ref/tw_ref_kernels (their device waits "
+                         "have no bound: they run only after this build's kernel passed on every rank for the same T)")
     ap.add_argument("--out", default=os.path.join(RESULTS_DIR, "fused_microbench"))
     args = ap.parse_args()
     if args.transport == "p2p":
@@ -77,6 +85,18 @@ def main() -> None:
     H, W, rank = args.hidden, tp.world_size, tp.rank
     Tmax = max(args.tokens)
     buf = create_symmetric_buffer(Tmax, H, torch.bfloat16, tp)
+    ref_ops = ref_buf = None
+    if args.reference_kernels and W > 1:
+        lib = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref",
+                           "tw_ref_kernels", "tw_ref_kernels.so")
+        if not os.path.exists(lib):
+            raise SystemExit(f"{lib} is missing: run python baseline/build_ref_kernels.py first")
+        torch.ops.load_library(lib)
+        ref_ops = torch.ops.tw_ref
+        # a symmetric buffer of its own, through PyTorch's rendezvous as the reference does (llama.py:437-441)
+        ref_buf = create_symmetric_buffer(Tmax, H, torch.bfloat16, tp, provider="torch")
+        if not ref_buf.has_multicast:
+            raise SystemExit("the reference's kernels need the NVLS multicast mapping")
     comm = TPCommunicator(buf, tp, wait_budget_ms=5000)
     g = torch.Generator(device="cuda").manual_seed(1000 + rank)
     gw = torch.Generator(device="cuda").manual_seed(7)
@@ -146,6 +166,42 @@ def main() -> None:
             if W > 1:
                 row["nccl_ar_norm_burst"] = burst_us(nccl_norm, args.burst)
         row["best_ctas"] = min(fused, key=fused.get)
+        if ref_ops is not None and ok:
+            # the reference kernel works on this rank's shard rows and is given the multicast address of the shard
+            rview = ref_buf.tensor[:T]
+            rres = res0.clone()
+            off = rank * rpr * H * 2
+            mc, pads = ref_buf.multicast_ptr + off, ref_buf.signal_pads_dev
+            sl = slice(rank * rpr, (rank + 1) * rpr)
+
+            def ref_refill():
+                rview.copy_(x)
+
+            def ref_fused_fn(c):
+                ref_ops.fused_rs_ln_ag_cta(rview[sl], rres[sl], w, mc, pads, rank, W, c, 1e-5)
+            ref_refill()
+            rres.copy_(res0)
+            torch.cuda.synchronize()
+            dist.barrier()
+            ref_fused_fn(16)
+            torch.cuda.synchronize()
+            rok = torch.tensor([int(torch.allclose(rview.float(), expect.float(), atol=4e-2, rtol=4e-2))], device="cuda")
+            dist.all_reduce(rok, op=dist.ReduceOp.MIN)
+            row["ref_correct"] = bool(rok.item())
+            rkw = dict(warmup=args.warmup, iters=args.iters, before=ref_refill, sync_ranks=args.sync_ranks)
+            rf = {c: time_us(lambda: ref_fused_fn(c), **rkw) for c in args.ctas}
+            for c, v in rf.items():
+                row[f"ref_fused_{c}"] = v
+            row["ref_fused_best"] = min(rf.values())
+            row["ref_mm_ar"] = min(time_us(lambda: ref_ops.multimem_ar_cta(rview[sl], mc, pads, rank, W, c), **rkw)
+                                   for c in args.ctas)
+            row["ref_simple_fusion"] = min(
+                time_us(lambda: ref_ops.simple_fusion_rs_ln_ag_cta(rview[sl], rres[sl], w, mc, pads, rank, W, c, 1e-5), **rkw)
+                for c in args.ctas)
+            if args.burst > 0:
+                cb = min(rf, key=rf.get)
+                row["ref_fused_burst"] = burst_us(lambda: ref_fused_fn(cb), args.burst)
+            row["vs_ref_fused"] = row["ref_fused_best"] / row["fused_best"]
         roof = T * H * 2 / (NVLINK_GBS_MEASURED * 1e9) * 1e6 if W > 1 else 0.0
         row["roofline_us"] = roof
         row["roofline_frac"] = (roof / row["fused_best"]) if W > 1 else None

@@ -50,8 +50,10 @@ def parse_args():
     ap.add_argument("--mode", default="overlap",
                     choices=["overlap", "fuse_only", "fused_gemm", "baseline_nccl", "baseline_multimem", "no_ar"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the result invalid)")
-    ap.add_argument("--cuda-graphs", action="store_true",
-                    help="replay the step from a CUDA graph (captured during warm-up; needs --warmup >= 3)")
+    ap.add_argument("--cuda-graphs", dest="cuda_graphs", action="store_true", default=None,
+                    help="replay the step from a CUDA graph (captured during warm-up; the default when --warmup >= 3)")
+    ap.add_argument("--no-cuda-graphs", dest="cuda_graphs", action="store_false",
+                    help="launch every kernel of the timed steps eagerly")
     return ap.parse_args()
 
 
@@ -107,29 +109,82 @@ class ClockSampler:
 
 
 def run_reference(args) -> None:
-    """The unmodified reference (a vLLM fork) installed under baseline/_ref, through LLM.generate."""
+    """The unmodified reference (a vLLM fork) installed under baseline/_ref, through its own ``LLM.generate``:
+    the same prompts, ``max_tokens=1``, eager mode, custom all-reduce off, dummy weights - the settings of its
+    artifact/figure_2_11/bench.py:52-124 - timed with the same barrier + synchronize bracket as this build's arm.
+    Prints the ``unavailable`` line when the fork is not installed (its build needs packages and git clones this
+    image cannot supply; ``baseline/REFERENCE_INSTALL.txt`` has the record)."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    reason = None
+    rank = int(os.environ.get("RANK", "0"))
+
+    def unavailable(reason: str) -> None:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": reason}))
+
     if not os.path.isdir(os.path.join(ref_dir, "vllm")):
         note = os.path.join(ROOT, "baseline", "REFERENCE_INSTALL.txt")
         reason = "reference not installed under baseline/_ref"
         if os.path.exists(note):
             reason = open(note).read().strip().splitlines()[0]
-    else:
-        try:
-            sys.path.insert(0, ref_dir)
-            import vllm  # noqa: F401
-            import vllm._C  # noqa: F401  (the compiled kernels the TokenWeave path needs)
-        except Exception as e:  # pragma: no cover
-            reason = f"reference under baseline/_ref does not import: {type(e).__name__}: {str(e)[:120]}"
-    if reason is None:
-        reason = "reference imports but its stock path was not wired to this bench"
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": reason}))
+        return unavailable(reason)
+    if args.gpus > 1 and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # the fork spawns its own tensor-parallel workers; under a torchrun launch only rank 0 drives it
+        if rank != 0:
+            return
+        for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_PORT", "TORCHELASTIC_RUN_ID"):
+            os.environ.pop(k, None)
+    try:
+        sys.path.insert(0, ref_dir)
+        import torch
+        import vllm
+        import vllm._C  # noqa: F401  (the compiled kernels the TokenWeave path needs)
+        from vllm import LLM as RefLLM, SamplingParams as RefSamplingParams
+    except Exception as e:
+        return unavailable(f"reference under baseline/_ref does not import: {type(e).__name__}: {str(e)[:120]}")
+    T = args.prompt_len
+    hf_names = {"llama-3.3-70b": "meta-llama/Llama-3.3-70B-Instruct", "qwen2.5-72b": "Qwen/Qwen2.5-72B-Instruct",
+                "mixtral-8x22b": "mistralai/Mixtral-8x22B-Instruct-v0.1"}
+    try:
+        llm = RefLLM(model=hf_names.get(args.model, args.model), tensor_parallel_size=args.gpus, load_format="dummy",
+                     enforce_eager=True, disable_custom_all_reduce=True, enable_chunked_prefill=True,
+                     enable_prefix_caching=False, max_num_batched_tokens=T, max_model_len=T + 64, dtype="bfloat16",
+                     skip_tokenizer_init=True, seed=0)
+    except Exception as e:
+        return unavailable(f"reference engine did not start: {type(e).__name__}: {str(e)[:120]}")
+    g = torch.Generator().manual_seed(1234)
+    vocab = llm.llm_engine.model_config.get_vocab_size()
+    prompts = [torch.randint(0, vocab, (T,), generator=g).tolist() for _ in range(args.steps + args.warmup)]
+    sp = RefSamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, detokenize=False)
+    for i in range(args.warmup):
+        llm.generate(prompt_token_ids=[prompts[i]], sampling_params=sp, use_tqdm=False)
+    sampler = ClockSampler(True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    wall = 0.0
+    for i in range(args.steps):
+        flush.zero_()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        llm.generate(prompt_token_ids=[prompts[args.warmup + i]], sampling_params=sp, use_tqdm=False)
+        torch.cuda.synchronize()
+        wall += time.perf_counter() - t0
+    clocks = sampler.stop(set(range(args.gpus)))
+    value = T * args.steps / wall
+    base = BASELINE_TOKENS_PER_S.get(T) if args.model == "llama-3.3-70b" else None
+    print(json.dumps({
+        "metric": "prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": wall * 1e3 / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": (value / base) if base else None, "dtype": "bf16",
+        "data": "synthetic random token ids, random-init weights (load_format=dummy)",
+        "config": {"model": args.model, "global_batch": 1, "seq_len": T, "parallelism": f"tp{args.gpus}",
+                   "timing": "host clock around LLM.generate (the fork runs its workers in other processes)"},
+        "clocks": clocks, "e2e": {"value": value, "unit": "tokens/s"}, "impl": "reference"}), flush=True)
 
 
 def main() -> None:
     args = parse_args()
+    if args.cuda_graphs is None:
+        # eager on the first sight of a step shape, capture on the second, replay from the third on
+        args.cuda_graphs = args.warmup >= 3
     if args.impl == "reference":
         run_reference(args)
         return
@@ -223,6 +278,8 @@ def main() -> None:
                    "l2": "per-rank weights (>= 17 GB) exceed the 126 MB L2; a 256 MB buffer is zeroed between steps",
                    "baseline": "TokenWeave on 8xH100, same prompt length (artifact/csvs/figure_11a.csv)"},
         "clocks": clocks,
+        # device time in SM cycles: compares runs whose clocks differ under the power cap (ms x median SM MHz)
+        "cycles_per_step": (dev_ms / args.steps * 1e-3 * clocks["sm_mhz"] * 1e6) if clocks.get("sm_mhz") else None,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": wall_ms / args.steps,
                 "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps},
         "gpu_launches": launches,

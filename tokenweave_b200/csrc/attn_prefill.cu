@@ -678,7 +678,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 }
 
 constexpr int ATTN_DEFAULT_VARIANT = 0;
-constexpr bool ATTN_AUTO_SPLIT = false;   // what "automatic" picks: the persistent split kernel, or the per-tile kernels
+constexpr bool ATTN_AUTO_SPLIT = true;   // what "automatic" picks: the persistent split kernel, or the per-tile kernels
 static int g_attn_variant = ATTN_DEFAULT_VARIANT;   // 0 auto, 1 one head per CTA, 2 head pairs
 static int g_attn_ring = 0;                          // 0: as many K/V slots as fit
 

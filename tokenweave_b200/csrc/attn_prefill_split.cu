@@ -15,7 +15,12 @@
 //   * P never touches shared memory: the softmax threads write bf16 probabilities back into the upper
 //     half of their S columns (tcgen05.st) and the P V product reads its A operand from tensor memory
 //     (tcgen05.mma with a TMEM operand), which frees 64 KB for a deeper K/V ring and removes the
-//     shared-memory stores and the proxy fence of every tile.
+//     shared-memory stores and the proxy fence of every tile. A row's 128 scores are read from tensor
+//     memory once (four loads in flight, one wait) and the softmax runs from registers with the packed
+//     two-wide fp32 instructions and the three-input maximum of sm_100.
+// Tried and dropped: softmax steps of 64 keys with S double-buffered per group (Q K^T of the next step
+// then never waits for the softmax). An M = 128 MMA with N = 64 takes as long as one with N = 128, so
+// the Q K^T time doubled and the kernel was 40 % slower.
 // Replaces the FlashAttention-2 varlen call the reference makes on Blackwell
 // (vllm/v1/attention/backends/flash_attn.py:713-733, vllm/attention/utils/fa_utils.py:29-34).
 //

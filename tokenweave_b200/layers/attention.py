@@ -134,7 +134,9 @@ class Attention(nn.Module):
         self.k_cache, self.v_cache = k_cache, v_cache
 
     def forward(self, qkv: torch.Tensor, cos_sin: torch.Tensor, meta: AttentionMetadata,
-                out: torch.Tensor) -> torch.Tensor:
+                out: torch.Tensor, max_ctas: int = 0) -> torch.Tensor:
+        """``max_ctas``: SM budget of the prefill kernel (0: all), so that a collective running on the
+        second stream keeps its SMs during attention as it does during the GEMMs."""
         n = meta.num_actual_tokens
         if n == 0:
             return out
@@ -146,7 +148,8 @@ class Attention(nn.Module):
                                                 meta.block_table, self.hq, self.hkv, self.head_dim, self.scale)
             return out
         ops.attn_prefill(q, self.k_cache, self.v_cache, out, meta.cu_q, meta.kv_lens, meta.block_table,
-                         meta.tile_seq, meta.tile_q0, meta.num_tiles, self.hq, self.hkv, self.head_dim, self.scale)
+                         meta.tile_seq, meta.tile_q0, meta.num_tiles, self.hq, self.hkv, self.head_dim, self.scale,
+                         max_ctas=max_ctas)
         ops.attn_decode(q, self.k_cache, self.v_cache, out, meta.tok_row, meta.tok_seq, meta.tok_kvlen,
                         meta.num_single, meta.block_table, self.hq, self.hkv, self.head_dim, self.scale,
                         meta.max_kv_len)

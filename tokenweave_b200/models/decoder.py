@@ -126,7 +126,7 @@ class DecoderLayer(nn.Module):
         if segs:
             from ..lora import LoRAManager
             LoRAManager.apply(segs, self.layer_idx, "qkv_proj", rows[:n], qkv)
-        attn_out = self.attn(qkv, rt.cos_sin, meta, rt.attn_out[:n])
+        attn_out = self.attn(qkv, rt.cos_sin, meta, rt.attn_out[:n], max_ctas=max_ctas)
         if segs:
             # the o_proj output overwrites rows[:n], which is also nothing the delta needs: the delta reads attn_out
             self.o_proj(attn_out, out=rows[:n], max_ctas=max_ctas)
