@@ -48,7 +48,8 @@ def parse_args():
     ap.add_argument("--model", default="llama-3.3-70b")
     ap.add_argument("--prompt-len", type=int, default=8192)
     ap.add_argument("--mode", default="overlap",
-                    choices=["overlap", "fuse_only", "fused_gemm", "baseline_nccl", "baseline_multimem", "no_ar"])
+                    choices=["overlap", "fuse_only", "fused_gemm", "baseline_nccl", "baseline_custom_ar", "baseline_multimem",
+                             "no_ar"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the result invalid)")
     ap.add_argument("--cuda-graphs", dest="cuda_graphs", action="store_true", default=None,
                     help="replay the step from a CUDA graph (captured during warm-up; the default when --warmup >= 3)")

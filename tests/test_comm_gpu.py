@@ -136,6 +136,96 @@ def test_fused_and_collectives_two_gpus(transport):
     run_ranks(_comm_worker, 2, transport, timeout=300)
 
 
+@pytest.mark.parametrize("world", [4, 8])
+@pytest.mark.parametrize("transport", ["multimem", "p2p"])
+def test_fused_and_collectives_four_and_eight_gpus(world, transport):
+    _need_gpus(world)
+    run_ranks(_comm_worker, world, transport, timeout=300)
+
+
+def _custom_ar_worker(rank, world):
+    """The peer-to-peer all-reduce baseline and the package's own NCCL communicator against torch.distributed,
+    on integer-valued data so that every path must agree bit for bit (the scheme of the reference's
+    tests/distributed/test_custom_all_reduce.py:24-120), eagerly and replayed from a CUDA graph."""
+    import torch.distributed as dist
+    from tokenweave_b200 import ops
+    from tokenweave_b200.parallel import state as pstate
+    from tokenweave_b200.parallel.comm import TPCommunicator
+    from tokenweave_b200.parallel.symm_mem import create_symmetric_buffer
+    tp = pstate.init_distributed(rank, world, rank, "cuda")
+    errors = []
+    try:
+        H = 8192
+        buf = create_symmetric_buffer(2048, H, torch.bfloat16, tp)
+        comm = TPCommunicator(buf, tp, wait_budget_ms=3000)
+        assert comm.enable_pynccl(), "the ctypes NCCL communicator did not come up"
+        g = torch.Generator(device="cuda").manual_seed(3 + rank)
+        for enabled in (True, False):
+            if enabled:
+                comm.enable_custom_all_reduce()
+            else:
+                comm.custom_ar_enabled = False
+            # one-shot (16 KB, 128 KB), two-shot (1 MB, 8 MB), beyond the limit (32 MB: NCCL)
+            for T in (1, 8, 64, 512, 2048):
+                x = torch.randint(0, 4, (T, H), device="cuda", generator=g).to(torch.bfloat16)
+                want = x.clone()
+                dist.all_reduce(want, group=tp.group)
+                view = buf.tensor[:T]
+                view.copy_(x)
+                torch.cuda.synchronize(); dist.barrier(group=tp.group)
+                comm.custom_all_reduce_(view)
+                torch.cuda.synchronize(); dist.barrier(group=tp.group)
+                if not torch.equal(view, want):
+                    errors.append(f"custom all-reduce (enabled={enabled}) T={T}: differs from NCCL")
+        comm.enable_custom_all_reduce()
+        # the package's NCCL path, and both captured in one CUDA graph
+        y = torch.randint(0, 4, (64, H), device="cuda", generator=g).to(torch.bfloat16)
+        want = y.clone()
+        dist.all_reduce(want, group=tp.group)
+        z = y.clone()
+        comm.nccl_all_reduce_(z)
+        if not torch.equal(z, want):
+            errors.append("pynccl all-reduce differs from torch.distributed")
+        parts = torch.empty(world * 1024, device="cuda")
+        comm.nccl_all_gather(parts, torch.full((1024,), float(rank), device="cuda"))
+        if parts.view(world, 1024)[:, 7].tolist() != [float(r) for r in range(world)]:
+            errors.append("pynccl all-gather order")
+        view = buf.tensor[:64]
+        z.copy_(y)
+        view.copy_(y)
+        torch.cuda.synchronize(); dist.barrier(group=tp.group)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            comm.custom_all_reduce_(view)
+            comm.nccl_all_reduce_(z)
+        for _ in range(3):
+            view.copy_(y)
+            z.copy_(y)
+            torch.cuda.synchronize(); dist.barrier(group=tp.group)
+            graph.replay()
+            torch.cuda.synchronize(); dist.barrier(group=tp.group)
+            if not (torch.equal(view, want) and torch.equal(z, want)):
+                errors.append("graph replay of custom all-reduce / pynccl differs")
+        ops.check_status()
+        del graph
+    except Exception:
+        import traceback
+        errors.append(traceback.format_exc())
+    torch.cuda.synchronize()
+    dist.barrier(group=tp.group)
+    if comm.pynccl is not None:
+        comm.pynccl.destroy()
+    buf.close()
+    pstate.destroy_distributed()
+    assert not errors, "\n".join(errors)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_custom_all_reduce_and_pynccl_match_nccl_exactly(world):
+    _need_gpus(world)
+    run_ranks(_custom_ar_worker, world, timeout=300)
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     """A wait on a flag nobody sets runs out of its budget, the kernel returns and the host reads the
     status word; the context stays usable."""

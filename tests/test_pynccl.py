@@ -52,8 +52,9 @@ def _rank(rank, world):
     pstate.destroy_distributed()
 
 
-@pytest.mark.skip(reason="communicator path written against nccl.h, not yet run on GPUs")
-def test_collectives_on_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    run_ranks(_rank, 2)
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_collectives_against_known_sums(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    run_ranks(_rank, world)

@@ -48,6 +48,8 @@ def _rank(rank, world, path, prompts, mode, expect_path, transport):
             mode, extra = mode[:-3], dict(enable_expert_parallel=True)
         elif mode.endswith("+fp8"):
             mode, extra = mode[:-4], dict(quantization="fp8")
+        if mode == "baseline_custom_ar":
+            extra = dict(disable_custom_all_reduce=False)
         logits, llm = _generate(path, prompts, tensor_parallel_size=world,
                                 distributed_executor_backend="external_launcher", tokenweave_mode=mode,
                                 tokenweave_threshold=1024, **extra)
@@ -81,10 +83,23 @@ def _rank(rank, world, path, prompts, mode, expect_path, transport):
                                                  ("tiny-qwen2", "fused_gemm", "p2p"),
                                                  ("tiny-mixtral", "fused_gemm", "multimem"),
                                                  ("tiny-mixtral", "overlap+ep", "multimem"),
-                                                 ("tiny-llama-d128", "overlap+fp8", "multimem")])
+                                                 ("tiny-llama-d128", "overlap+fp8", "multimem"),
+                                                 ("tiny-llama-d128", "baseline_custom_ar", "multimem")])
 def test_tp2_matches_single_gpu(tmp_path, arch, mode, transport):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+    _tp_matches_single_gpu(tmp_path, arch, mode, transport, 2)
+
+
+@pytest.mark.parametrize("world", [4, 8])
+@pytest.mark.parametrize("mode,transport", [("overlap", "multimem"), ("fuse_only", "p2p"), ("fused_gemm", "multimem"),
+                                            ("baseline_custom_ar", "multimem"), ("baseline_nccl", "multimem")])
+def test_tp4_tp8_match_single_gpu(tmp_path, world, mode, transport):
+    """Eight query heads over 4 and 8 ranks (KV heads replicated), every schedule against one GPU."""
+    _tp_matches_single_gpu(tmp_path, "tiny-llama-h8", mode, transport, world)
+
+
+def _tp_matches_single_gpu(tmp_path, arch, mode, transport, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     cfg = ModelConfig(name=arch, **MODEL_PRESETS[arch])
     st = make_hf_state(cfg, seed=5, dtype=torch.bfloat16)
     hf = hf_config_dict(cfg)
@@ -95,7 +110,7 @@ def test_tp2_matches_single_gpu(tmp_path, arch, mode, transport):
     llm.shutdown()
     ep = str(tmp_path / "expect.pt")
     torch.save(expect, ep)
-    run_ranks(_rank, 2, str(tmp_path), prompts, mode, ep, transport, timeout=300)
+    run_ranks(_rank, world, str(tmp_path), prompts, mode, ep, transport, timeout=300)
 
 
 def _graph_rank(rank, world, path, prompts, mode):
@@ -130,16 +145,18 @@ def _graph_rank(rank, world, path, prompts, mode):
     assert err is None, err
 
 
-@pytest.mark.parametrize("mode", ["overlap", "fuse_only"])
-def test_tp2_cuda_graph_replay_matches_eager(tmp_path, mode):
-    """Both streams of the overlap schedule and the in-kernel collectives under CUDA-graph capture and replay."""
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    arch = "tiny-llama-d128"
+@pytest.mark.parametrize("world,mode", [(2, "overlap"), (2, "fuse_only"), (2, "baseline_nccl"), (4, "overlap"),
+                                        (8, "overlap"), (8, "fuse_only")])
+def test_tp_cuda_graph_replay_matches_eager(tmp_path, world, mode):
+    """Both streams of the overlap schedule and the in-kernel collectives under CUDA-graph capture and replay
+    (``baseline_nccl``: NCCL through the package's own communicator inside the graph)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    arch = "tiny-llama-d128" if world == 2 else "tiny-llama-h8"
     cfg = ModelConfig(name=arch, **MODEL_PRESETS[arch])
     st = make_hf_state(cfg, seed=5, dtype=torch.bfloat16)
     hf = hf_config_dict(cfg)
     hf["torch_dtype"] = "bfloat16"
     save_hf_checkpoint(st, hf, str(tmp_path))
     prompts = _prompts(cfg.vocab_size, [700, 300, 333, 40])
-    run_ranks(_graph_rank, 2, str(tmp_path), prompts, mode, timeout=300)
+    run_ranks(_graph_rank, world, str(tmp_path), prompts, mode, timeout=300)

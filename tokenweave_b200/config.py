@@ -136,6 +136,10 @@ MODEL_PRESETS: dict[str, dict[str, Any]] = {
     "tiny-llama-d128": dict(architecture="llama", hidden_size=512, num_layers=2, num_q_heads=4, num_kv_heads=2,
                             head_dim=128, intermediate_size=1024, vocab_size=2048, rms_norm_eps=1e-5,
                             rope_theta=500000.0, max_model_len=4096),
+    # eight query heads: shards over 8 tensor-parallel ranks (the two KV heads are then replicated four times)
+    "tiny-llama-h8": dict(architecture="llama", hidden_size=1024, num_layers=2, num_q_heads=8, num_kv_heads=2,
+                          head_dim=128, intermediate_size=2048, vocab_size=2048, rms_norm_eps=1e-5,
+                          rope_theta=500000.0, max_model_len=4096),
     "tiny-qwen2": dict(architecture="qwen2", hidden_size=512, num_layers=2, num_q_heads=4, num_kv_heads=2,
                        head_dim=128, intermediate_size=1024, vocab_size=2048, rms_norm_eps=1e-6,
                        rope_theta=1e6, qkv_bias=True, max_model_len=4096),
@@ -248,6 +252,8 @@ class TokenWeaveConfig:
       "fuse_only"         fused kernel, no split
       "baseline_multimem" in-kernel all-reduce, separate add+RMSNorm kernel
       "baseline_nccl"     NCCL all-reduce, separate add+RMSNorm kernel
+      "baseline_custom_ar" peer-to-peer one-shot / two-shot all-reduce for messages up to 8 MB when
+                          ``disable_custom_all_reduce=False`` (NCCL otherwise), separate add+RMSNorm kernel
       "no_ar"             communication deleted (numerically wrong upper bound); also the cost-attribution
                           variants "no_ar1", "no_ar2", "no_ln1", "no_ln2", "no_ar_no_ln"
     """

@@ -37,6 +37,9 @@ _VARS: dict[str, Callable[[], Any]] = {
     "TW_DECODE_TC": lambda: os.getenv("TW_DECODE_TC", "1"),
     # vocabulary-parallel instead of replicated embedding table
     "TW_EMBEDDING_PARALLEL": lambda: os.getenv("TW_EMBEDDING_PARALLEL", "0") == "1",
+    # NCCL baseline collectives and the logits gather through the package's own communicator (parallel/pynccl.py)
+    # instead of torch.distributed; "0" leaves the process group in charge
+    "TW_USE_PYNCCL": lambda: os.getenv("TW_USE_PYNCCL", "1") == "1",
     # libnccl for the ctypes binding (parallel/pynccl.py); default: the one torch ships
     "TW_NCCL_SO_PATH": lambda: os.getenv("TW_NCCL_SO_PATH"),
     # where the artifact scripts write their CSV / JSON results

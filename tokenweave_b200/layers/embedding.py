@@ -66,6 +66,7 @@ class ParallelLMHead(nn.Module):
         self.vocab_start = tp.rank * self.per_rank
         self.weight = nn.Parameter(torch.zeros(self.per_rank, hidden, dtype=dtype, device=device),
                                    requires_grad=False)
+        self.comm = None       # TPCommunicator of the runtime: its private NCCL communicator gathers the logits
 
     def forward(self, hidden: torch.Tensor) -> torch.Tensor:
         """fp32 logits ``[rows, vocab_size]`` on every rank."""
@@ -74,7 +75,10 @@ class ParallelLMHead(nn.Module):
         if tp.world_size > 1:
             rows, cols = local.shape
             gathered = torch.empty(tp.world_size * rows, cols, dtype=local.dtype, device=local.device)
-            dist.all_gather_into_tensor(gathered, local.contiguous(), group=tp.group)
+            if self.comm is not None:
+                self.comm.nccl_all_gather(gathered.view(-1), local.contiguous().view(-1))
+            else:
+                dist.all_gather_into_tensor(gathered, local.contiguous(), group=tp.group)
             local = gathered.view(tp.world_size, rows, cols).permute(1, 0, 2).reshape(rows, -1)
         return local[:, : self.vocab_size].float()
 

@@ -199,10 +199,18 @@ class DecoderModel(nn.Module):
         self.tw_mode = "overlap"
 
     # ---- runtime -------------------------------------------------------------------------
-    def setup_runtime(self, max_tokens: int, tw_cfg, provider: Optional[str] = None) -> Runtime:
+    def setup_runtime(self, max_tokens: int, tw_cfg, provider: Optional[str] = None,
+                      disable_custom_all_reduce: bool = True) -> Runtime:
         device = self.norm_w.device
         self.rt = Runtime(self.cfg, max_tokens, device, tw_cfg, provider)
         self.tw_mode = tw_cfg.mode
+        # library baselines: NCCL through the package's own communicator (graph-capturable, on the current
+        # stream) for "baseline_nccl" and the logits gather; peer-to-peer all-reduce when the engine allows it
+        from .. import envs
+        if envs.TW_USE_PYNCCL and self.rt.comm.enable_pynccl():
+            self.lm_head.comm = self.rt.comm
+        if not disable_custom_all_reduce:
+            self.rt.comm.enable_custom_all_reduce()
         return self.rt
 
     def kv_cache_bytes_per_block(self, block_size: int) -> int:

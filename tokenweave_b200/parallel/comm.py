@@ -38,6 +38,35 @@ class TPCommunicator:
         self.use_mc = self.in_kernel and buf.has_multicast and transport in ("auto", "multimem")
         if transport == "multimem" and self.in_kernel and not buf.has_multicast:
             raise RuntimeError("multimem transport requested but the symmetric buffer has no multicast mapping")
+        self.pynccl = None                      # NcclCommunicator of this group (enable_pynccl)
+        self.custom_ar_enabled = False          # the "custom all-reduce" baseline may be used (enable_custom_all_reduce)
+        self.custom_ar_max_bytes = 8 << 20
+        self._car_out: Optional[torch.Tensor] = None
+
+    # ---- library baselines --------------------------------------------------------------------
+    def enable_pynccl(self) -> bool:
+        """A private NCCL communicator (ctypes, ``parallel/pynccl.py``) for the library-only baseline and the
+        logits gather: collectives go onto the current stream without the process-group layer, so they can
+        be captured in CUDA graphs (vllm/distributed/device_communicators/pynccl.py:109-217). Collective:
+        every rank of the group calls it. Returns False (and leaves ``torch.distributed`` in charge) on CPU,
+        for one rank, or when the library cannot be loaded."""
+        if self.pynccl is not None:
+            return True
+        if self.world == 1 or self.tp.device.type != "cuda":
+            return False
+        from .pynccl import NcclCommunicator
+        from .state import broadcast_object
+        try:
+            self.pynccl = NcclCommunicator(self.tp.rank, self.world, self.tp.device, broadcast_object)
+        except OSError:
+            self.pynccl = None
+        return self.pynccl is not None
+
+    def enable_custom_all_reduce(self, max_bytes: int = 8 << 20) -> None:
+        """Allows :meth:`custom_all_reduce_` to use peer loads / stores (the engine option
+        ``disable_custom_all_reduce=False``)."""
+        self.custom_ar_enabled = self.in_kernel
+        self.custom_ar_max_bytes = max_bytes
 
     @property
     def world(self) -> int:
@@ -94,8 +123,8 @@ class TPCommunicator:
                      torch.cuda.current_stream().cuda_stream)
 
     # ---- stand-alone collectives on rows of the symmetric buffer ---------------------------
-    def _collective(self, x: torch.Tensor, op: int, max_ctas: int) -> None:
-        _native.call("tw_collective", self._mc(), self.buf.peer_ptrs_dev, self.buf.signal_pads_dev, self.tp.rank,
+    def _collective(self, x: torch.Tensor, op: int, max_ctas: int, peer_only: bool = False) -> None:
+        _native.call("tw_collective", None if peer_only else self._mc(), self.buf.peer_ptrs_dev, self.buf.signal_pads_dev, self.tp.rank,
                      self.world, CHANNEL_COLLECTIVE, self.budget_ns, ops.status_word(x.device).data_ptr(),
                      self.buf.byte_offset(x), x.numel() * x.element_size(), op, max_ctas,
                      torch.cuda.current_stream().cuda_stream)
@@ -150,8 +179,51 @@ class TPCommunicator:
 
     # ---- NCCL baseline ------------------------------------------------------------------
     def nccl_all_reduce_(self, x: torch.Tensor) -> None:
-        if self.world > 1:
+        if self.world == 1:
+            return
+        if self.pynccl is not None and x.is_contiguous():
+            self.pynccl.all_reduce(x)
+        else:
             dist.all_reduce(x, group=self.tp.group)
+
+    def nccl_all_gather(self, out: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """``out`` ([world * n]) receives every rank's ``x`` ([n]) in rank order."""
+        if self.pynccl is not None and x.is_contiguous() and out.is_contiguous():
+            self.pynccl.all_gather(out, x)
+        else:
+            dist.all_gather_into_tensor(out, x, group=self.tp.group)
+        return out
+
+    # ---- custom all-reduce baseline ---------------------------------------------------------
+    def custom_all_reduce_(self, x: torch.Tensor) -> None:
+        """The reference's "custom all-reduce" (csrc/custom_all_reduce.cuh:296-364, size policy :558-589; Python
+        side vllm/distributed/device_communicators/custom_all_reduce.py:48-301) for rows of the symmetric
+        buffer, in place: peer loads and stores with a flag barrier, no NVLS. One-shot (every rank pulls the whole
+        message from every peer) below 512 KiB for up to 4 ranks and below 256 KiB for up to 8, two-shot
+        (reduce-scatter + all-gather over peer pointers) up to ``custom_ar_max_bytes``, NCCL beyond that or
+        when the option is off. The reference registers the buffers of a captured graph with its peers
+        (``register_graph_buffers``, custom_all_reduce.py:193); here the activations already live in symmetric
+        memory every rank can address, so there is nothing to register and the calls replay from a graph as
+        they are."""
+        if self.world == 1:
+            return
+        nbytes = x.numel() * x.element_size()
+        ok = (self.custom_ar_enabled and x.dtype == torch.bfloat16 and x.is_contiguous() and self.world in (2, 4, 6, 8)
+              and nbytes <= self.custom_ar_max_bytes and nbytes % (16 * self.world) == 0)
+        if not ok:
+            self.nccl_all_reduce_(x)
+            return
+        one_shot = (self.world <= 4 and nbytes < 512 * 1024) or (self.world <= 8 and nbytes < 256 * 1024)
+        if one_shot:
+            if self._car_out is None:
+                self._car_out = torch.empty(512 * 1024 // 2, dtype=torch.bfloat16, device=x.device)
+            out = self._car_out[: x.numel()]
+            self.oneshot_all_reduce(x, out)
+            # every rank has read every peer's copy before any rank overwrites its own: the one-shot kernel
+            # ends with a barrier
+            x.view(-1).copy_(out)
+        else:
+            self._collective(x, OP_ALL_REDUCE, 36, peer_only=True)
 
     # ---- GEMM fused with its collective (one kernel each) ----------------------------------
     FLAG_WORDS_PER_REGION = 256      # 128 tile counters (+128 "done" counters share the range), then epochs

@@ -6,9 +6,10 @@ them are ordered on the GPU.
 * ``run_overlap``    two token subsets; the compute stream runs one subset's attention / MLP while the
                      communication stream runs the other subset's fused kernel on a few SMs
                      (reference: tokenweave_overlap, tokenweave_utils.py:175-340).
-* ``run_baseline``   all-reduce (NCCL or in-kernel multimem) followed by a separate add+RMSNorm kernel,
-                     or no communication at all (the artifact's baseline_ring / baseline_multimem /
-                     no_ar variants, artifact/llama_src_files/pl_*.py).
+* ``run_baseline``   all-reduce (NCCL, the peer-to-peer "custom all-reduce", or in-kernel multimem) followed
+                     by a separate add+RMSNorm kernel, or no communication at all (the artifact's
+                     baseline_ring / baseline_multimem / no_ar variants, artifact/llama_src_files/pl_*.py;
+                     ``baseline_custom_ar`` is stock vLLM with ``disable_custom_all_reduce=False``).
 
 On entry the rows of ``hidden`` hold ``rmsnorm(x) * input_layernorm[0]`` and ``residual`` holds ``x``
 (or ``hidden`` holds vocab-parallel partial embeddings and ``residual`` zeros, with ``first_pending``
@@ -101,6 +102,8 @@ def run_baseline(layers: Sequence, final_norm_w: torch.Tensor, hidden: torch.Ten
         if which not in skip_ar:
             if base == "baseline_nccl":
                 comm.nccl_all_reduce_(hidden[:T])
+            elif base == "baseline_custom_ar":
+                comm.custom_all_reduce_(hidden[:T])
             elif base == "baseline_multimem":
                 comm.all_reduce_(h, plan.attention_ctas)
         if which not in skip_ln:

@@ -131,7 +131,8 @@ class ModelRunner:
         t0 = time.monotonic()
         with (weights_pool if weights_pool is not None else contextlib.nullcontext()):
             self.model = build_model(self.config, self.device, embedding_parallel)
-        self.model.setup_runtime(self.max_tokens, self.config.tokenweave)
+        self.model.setup_runtime(self.max_tokens, self.config.tokenweave,
+                                 disable_custom_all_reduce=self.config.parallel.disable_custom_all_reduce)
         if self.config.enable_lora:
             from ..lora import LoRAManager
             self.lora = LoRAManager(self.model, self.config.max_loras)

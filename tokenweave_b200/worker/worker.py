@@ -256,6 +256,9 @@ class Worker:
             self.runner.release_graphs()
         if self.runner is not None and self.runner.model is not None and self.runner.model.rt is not None:
             try:
+                if self.runner.model.rt.comm.pynccl is not None:
+                    self.runner.model.rt.comm.pynccl.destroy()
+                    self.runner.model.rt.comm.pynccl = None
                 self.runner.model.rt.staging.close()
             except Exception as e:       # tear-down must not mask the caller's error
                 logger.warning("symmetric buffer tear-down failed: %s", e)
