@@ -290,6 +290,10 @@ class EngineConfig:
     enable_lora: bool = False             # serve requests through LoRA adapters (tokenweave_b200.lora)
     max_loras: int = 8                    # adapters resident per worker (least recently used is evicted)
     kv_transfer: Any = None               # engine.kv_connector.KVTransferConfig (blocks shared through storage)
+    # scheduler + executor in a process of their own behind ZMQ / msgpack (engine/core_client.py); the front end
+    # (tokeniser, detokeniser, output assembly) then overlaps with scheduling and kernel launches
+    engine_core_process: bool = False
+    engine_core_timeout_s: float = 300.0  # a step result that takes longer than this means the core is stuck
 
     def resolved_device(self) -> str:
         if self.device != "auto":
@@ -333,6 +337,7 @@ class EngineArgs:
     # {"kv_connector": "SharedStorageConnector", "kv_role": "kv_producer" | "kv_consumer" | "kv_both",
     #  "kv_connector_extra_config": {"shared_storage_path": dir}}: KV blocks published to / fetched from storage
     kv_transfer_config: Any = None
+    engine_core_process: bool = False     # run scheduler + executor in their own process (ZMQ + msgpack boundary)
     enable_lora: bool = False
     max_loras: int = 8
     # TokenWeave
@@ -389,7 +394,7 @@ class EngineArgs:
             tokenizer=self.tokenizer, skip_tokenizer_init=self.skip_tokenizer_init,
             disable_log_stats=self.disable_log_stats, enable_sleep_mode=self.enable_sleep_mode,
             speculative=self._speculative(), enable_lora=self._lora_checked(model), max_loras=self.max_loras,
-            kv_transfer=self._kv_transfer())
+            kv_transfer=self._kv_transfer(), engine_core_process=self.engine_core_process)
 
     def _kv_transfer(self):
         from .engine.kv_connector import KVTransferConfig

@@ -39,7 +39,11 @@ class LLMEngine:
         self.config = config
         self.tokenizer = None if config.skip_tokenizer_init else load_tokenizer(config.tokenizer or
                                                                                (config.model.path if config.model.path else "byte"))
-        self.core = EngineCore(config, executor)
+        if config.engine_core_process and executor is None:
+            from .core_client import MPEngineCoreClient
+            self.core = MPEngineCoreClient(config)
+        else:
+            self.core = EngineCore(config, executor)
         self.parents: dict[str, _Parent] = {}
         self.child_to_parent: dict[str, tuple[str, int]] = {}
         self.stat_logger = None if config.disable_log_stats else LoggingStatLogger()

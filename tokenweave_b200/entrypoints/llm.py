@@ -201,10 +201,10 @@ class LLM:
         return self.llm_engine.core.executor.collective_rpc(method, *args, **kwargs)
 
     def start_profile(self) -> None:
-        self.llm_engine.core.executor.profile(True)
+        self.collective_rpc("profile", True)
 
     def stop_profile(self) -> None:
-        self.llm_engine.core.executor.profile(False)
+        self.collective_rpc("profile", False)
 
     def chat(self, messages, sampling_params: Optional[SamplingParams] = None, add_generation_prompt: bool = True,
              use_tqdm: bool = False) -> list[RequestOutput]:
@@ -234,7 +234,11 @@ class LLM:
         self.collective_rpc("sleep", level)
 
     def reset_prefix_cache(self) -> bool:
-        return self.llm_engine.core.scheduler.kv.pool.reset_prefix_cache()
+        core = self.llm_engine.core
+        if not hasattr(core.scheduler, "kv"):
+            # the scheduler lives in the core process: it drops its prefix cache there
+            return bool(core.rpc_core("reset_prefix_cache"))
+        return core.scheduler.kv.pool.reset_prefix_cache()
 
     def wake_up(self) -> None:
         self.collective_rpc("wake_up")
