@@ -35,11 +35,8 @@ def _paged(kvs, hkv, D, page, seed):
     (16, 1, 64, [512, 1500], 148),                      # sixteen query heads per KV head: N is full
     (6, 2, 128, [1024] * 40, 148),                      # odd group size
 ])
-@pytest.mark.parametrize("variant", [
-    "tc",
-    # the persistent form: sm_count = 1 there means ONE CTA walks every work item
-    pytest.param("tcp", marks=pytest.mark.skip(reason="persistent variant: compiled, not yet run on a GPU")),
-])
+# "tcp" is the persistent form: sm_count = 1 there means ONE CTA walks every work item
+@pytest.mark.parametrize("variant", ["tc", "tcp"])
 def test_tc_decode_matches_reference(hq, hkv, page, kvs, sm_count, variant):
     D = 128
     kc, vc, bt = _paged(kvs, hkv, D, page, seed=len(kvs) + hq)

@@ -75,21 +75,35 @@ def test_phi3_packed_checkpoint_and_mistral_config(tmp_path):
         torch.testing.assert_close(got[str(i)], naive_logits(cfg, st, p)[-1], atol=2e-4, rtol=2e-4)
     llm.shutdown()
 
-    mcfg = ModelConfig(name="tiny-mistral", **dict(MODEL_PRESETS["tiny-llama"], architecture="mistral", rope_theta=1e6))
+    # a window (24 keys) shorter than the prompts, and a soft cap on the scores: prefill in chunks, then decode
+    mcfg = ModelConfig(name="tiny-mistral", **dict(MODEL_PRESETS["tiny-llama"], architecture="mistral", rope_theta=1e6,
+                                                   sliding_window=24, attn_logit_softcapping=5.0))
     hf = hf_config_dict(mcfg)
     del hf["rope_theta"]
-    hf.update(rope_parameters={"rope_type": "default", "rope_theta": 1e6}, sliding_window=256, max_position_embeddings=2048)
+    hf.update(rope_parameters={"rope_type": "default", "rope_theta": 1e6}, max_position_embeddings=2048)
     mst = make_hf_state(mcfg, seed=6)
     save_hf_checkpoint(mst, hf, str(tmp_path / "mistral"))
-    llm = _engine(str(tmp_path / "mistral"))
+    llm = _engine(str(tmp_path / "mistral"), max_num_batched_tokens=32)
     m = llm.llm_engine.config.model
-    assert (m.architecture, m.rope_theta, m.max_model_len) == ("mistral", 1e6, 256)
+    assert (m.architecture, m.rope_theta, m.max_model_len, m.sliding_window, m.attn_logit_softcapping) == \
+        ("mistral", 1e6, 2048, 24, 5.0)
     r = _runner(llm)
     r.capture_logits = True
-    llm.generate(prompts, SamplingParams(temperature=0, max_tokens=1))
-    got = {rid: row for reqs, logits in r.captured_logits for rid, row in zip(reqs, logits)}
+    prompts = _prompts(mcfg.vocab_size, [70, 9])
+    outs = llm.generate(prompts, SamplingParams(temperature=0, max_tokens=3))
+    first = {}
+    for reqs, logits in r.captured_logits:
+        for rid, row in zip(reqs, logits):
+            first.setdefault(rid, row)
     for i, p in enumerate(prompts):
-        torch.testing.assert_close(got[str(i)], naive_logits(mcfg, mst, p)[-1], atol=2e-4, rtol=2e-4)
+        torch.testing.assert_close(first[outs[i].request_id], naive_logits(mcfg, mst, p)[-1], atol=2e-4, rtol=2e-4)
+        seq = list(p)
+        for _ in range(3):
+            seq.append(int(naive_logits(mcfg, mst, seq)[-1].argmax()))
+        assert outs[i].outputs[0].token_ids == seq[len(p):]
+    # the window matters for this prompt: full attention gives other logits
+    full = ModelConfig(name="x", **dict(MODEL_PRESETS["tiny-llama"], architecture="mistral", rope_theta=1e6))
+    assert (naive_logits(full, mst, prompts[0])[-1] - first[outs[0].request_id]).abs().max() > 1e-3
     llm.shutdown()
 
 

@@ -201,6 +201,51 @@ def test_attn_prefill(hq, hkv, D, page, seqs, variant):
     close(out, expect, atol=2e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("window,softcap", [(200, 0.0), (0, 7.5), (77, 30.0), (5000, 0.0)])
+@pytest.mark.parametrize("hq,hkv,D,page,seqs", [
+    (8, 2, 128, 16, [(200, 1000), (1, 77), (128, 640), (5, 5)]),
+    (4, 4, 64, 32, [(333, 333), (64, 500)]),
+    (16, 2, 128, 128, [(1024, 1024), (700, 2048)]),
+])
+def test_attn_sliding_window_and_softcap(hq, hkv, D, page, seqs, window, softcap):
+    """Prefill tiles and single-query tokens under a sliding window and / or a soft cap on the scores."""
+    kc, vc, bt, cu, kv_lens = _make_paged(seqs, hkv, D, page)
+    T = cu[-1]
+    q = rnd(T, hq * D, scale=2.0)
+    scale = D ** -0.5
+    expect = ref.paged_attention(q, kc, vc, cu, kv_lens, bt, hq, hkv, D, scale, window=window, softcap=softcap)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    tile_seq, tile_q0, tok_row, tok_seq, tok_kv = [], [], [], [], []
+    for b, (ql, kv) in enumerate(seqs):
+        if ql >= 16:
+            for q0 in range(0, ql, 128):
+                tile_seq.append(b)
+                tile_q0.append(q0)
+        else:
+            for i in range(ql):
+                tok_row.append(cu[b] + i)
+                tok_seq.append(b)
+                tok_kv.append(kv - ql + i + 1)
+    out = torch.zeros_like(q)
+    ops.attn_prefill(q, kc, vc, out, i32(cu), i32(kv_lens), bt, i32(tile_seq), i32(tile_q0), len(tile_seq), hq, hkv, D,
+                     scale, window=window, softcap=softcap)
+    if tok_row:
+        ops.attn_decode(q, kc, vc, out, i32(tok_row), i32(tok_seq), i32(tok_kv), len(tok_row), bt, hq, hkv, D, scale,
+                        max(tok_kv), window=window, softcap=softcap)
+    torch.cuda.synchronize()
+    ops.check_status()
+    close(out, expect, atol=2e-2, rtol=3e-2)
+    # every row as a single-query token through the decode kernel (split-KV included)
+    rows = list(range(T))
+    seq_of = [b for b, (ql, _) in enumerate(seqs) for _ in range(ql)]
+    kv_of = [kv - ql + i + 1 for (ql, kv) in seqs for i in range(ql)]
+    out2 = torch.zeros_like(q)
+    ops.attn_decode(q, kc, vc, out2, i32(rows), i32(seq_of), i32(kv_of), T, bt, hq, hkv, D, scale, max(kv_of),
+                    window=window, softcap=softcap)
+    torch.cuda.synchronize()
+    close(out2, expect, atol=2e-2, rtol=3e-2)
+
+
 @pytest.mark.parametrize("hq,hkv,D,page,kvs", [
     (8, 1, 128, 16, [1, 31, 32, 33, 700]),
     (64, 8, 128, 128, [5000, 77]),

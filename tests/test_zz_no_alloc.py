@@ -59,7 +59,7 @@ def _run_both(lib, new, old, seed, kvs, hq, hkv, D, page, splits):
     part_ml = torch.empty(n * hq * splits * 2, dtype=torch.float32, device="cuda")
     rc = old(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), page, ref_out.data_ptr(), ref_out.stride(0),
              rows.data_ptr(), seqs.data_ptr(), kvl.data_ptr(), n, bt.data_ptr(), bt.shape[1], hq, hkv, D, scale,
-             splits, part_o.data_ptr(), part_ml.data_ptr(), stream)
+             splits, part_o.data_ptr(), part_ml.data_ptr(), 0, 0.0, stream)     # no sliding window, no soft cap
     assert rc == 0, lib.tw_last_error()
     out = torch.zeros_like(q)
     rc = new(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), page, out.data_ptr(), out.stride(0),

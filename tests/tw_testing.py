@@ -62,6 +62,10 @@ def hf_config_dict(cfg):
              intermediate_size=cfg.intermediate_size, vocab_size=cfg.vocab_size, rms_norm_eps=cfg.rms_norm_eps,
              rope_theta=cfg.rope_theta, max_position_embeddings=cfg.max_model_len, torch_dtype="float32",
              attention_bias=cfg.qkv_bias)
+    if getattr(cfg, "sliding_window", 0):
+        d["sliding_window"] = cfg.sliding_window
+    if getattr(cfg, "attn_logit_softcapping", 0.0):
+        d["attn_logit_softcapping"] = cfg.attn_logit_softcapping
     if cfg.num_experts:
         d.update(num_local_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok)
     return d
@@ -102,7 +106,13 @@ def naive_logits(cfg, st, ids, cos_sin=None):
         rep = cfg.num_q_heads // cfg.num_kv_heads
         k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
         s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(D)
-        s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        cap = getattr(cfg, "attn_logit_softcapping", 0.0)
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        hidden_keys = torch.triu(torch.ones(T, T, dtype=torch.bool), 1)
+        if getattr(cfg, "sliding_window", 0):
+            hidden_keys |= torch.tril(torch.ones(T, T, dtype=torch.bool), -cfg.sliding_window)
+        s = s.masked_fill(hidden_keys, float("-inf"))
         o = torch.einsum("hqk,khd->qhd", s.softmax(-1), v).reshape(T, -1)
         x = x + o @ st[p + "self_attn.o_proj.weight"].float().t()
         h = norm(x, st[p + "post_attention_layernorm.weight"])

@@ -38,6 +38,8 @@ class ModelConfig:
     rope_scaling: Optional[dict] = None
     qkv_bias: bool = False
     qk_norm: bool = False                # RMSNorm over head_dim on every q and k head before rope (Qwen3)
+    sliding_window: int = 0              # a query sees the last N keys only (Mistral-7B v0.1: 4096); 0 = full attention
+    attn_logit_softcapping: float = 0.0  # attention scores pass through cap * tanh(s / cap) (Gemma-2 style); 0 = off
     num_experts: int = 0                 # 0 = dense MLP
     num_experts_per_tok: int = 2
     max_model_len: int = 8192
@@ -83,9 +85,7 @@ class ModelConfig:
                 cfg.setdefault("rope_scaling", rp)
         max_len = cfg.get("max_position_embeddings", 8192)
         window = cfg.get("sliding_window")
-        if window and cfg.get("use_sliding_window", True) and window < max_len:
-            # no sliding-window attention kernel: serve the span in which full and windowed attention agree
-            max_len = int(window)
+        window = int(window) if window and cfg.get("use_sliding_window", True) and window < max_len else 0
         return ModelConfig(
             name=name or cfg.get("_name_or_path", arch), architecture=arch, hidden_size=cfg["hidden_size"],
             num_layers=cfg["num_hidden_layers"], num_q_heads=heads,
@@ -94,7 +94,8 @@ class ModelConfig:
             rms_norm_eps=cfg.get("rms_norm_eps", 1e-6 if arch in ("qwen2", "qwen3") else 1e-5),
             rope_theta=cfg.get("rope_theta") or (1e6 if arch in ("qwen2", "qwen3", "mixtral") else 10000.0),
             rope_scaling=cfg.get("rope_scaling"), qkv_bias=cfg.get("attention_bias", arch == "qwen2"),
-            qk_norm=arch == "qwen3",
+            qk_norm=arch == "qwen3", sliding_window=window,
+            attn_logit_softcapping=float(cfg.get("attn_logit_softcapping") or 0.0),
             num_experts=cfg.get("num_local_experts", 0), num_experts_per_tok=cfg.get("num_experts_per_tok", 2),
             max_model_len=max_len,
             tie_word_embeddings=cfg.get("tie_word_embeddings", False), dtype=dt, eos_token_id=eos, path=path,

@@ -28,7 +28,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
                    const int* __restrict__ tok_seq, const int* __restrict__ tok_kvlen,
                    const int* __restrict__ block_table, int max_blocks, int page, int hq, int hkv,
                    float scale_log2, int splits, __nv_bfloat16* __restrict__ out, long long ldo,
-                   float* __restrict__ part_o, float* __restrict__ part_ml) {
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int window, float softcap_log2) {
+  // window: the query (at position kv_len - 1) sees the last `window` keys only (0: all of them).
+  // softcap_log2: soft cap of the scores times log2(e) (0: off); scores here are already in the log2 domain.
   constexpr int EPL = D / 32;  // output elements per lane
   const int G = hq / hkv;
   const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -49,11 +51,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
   }
   __syncthreads();
 
-  // keys of this split, in whole 32-key chunks
+  // keys of this split, in whole 32-key chunks (under a sliding window the chunks before it are skipped)
+  const int key_lo = window > 0 ? max(0, kv_len - window) : 0;
+  const int chunk_lo = key_lo / 32;
   const int chunks_total = (kv_len + 31) / 32;
-  const int chunks_per_split = (chunks_total + splits - 1) / splits;
-  const int chunk_begin = split * chunks_per_split;
+  const int chunks_per_split = (chunks_total - chunk_lo + splits - 1) / splits;
+  const int chunk_begin = chunk_lo + split * chunks_per_split;
   const int chunk_end = min(chunks_total, chunk_begin + chunks_per_split);
+  const float cap_inv = softcap_log2 > 0.f ? 1.f / softcap_log2 : 0.f;
 
   float m[DEC_GMAX], l[DEC_GMAX], o[DEC_GMAX][EPL];
 #pragma unroll
@@ -66,7 +71,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
 
   for (int ch = chunk_begin + warp; ch < chunk_end; ch += DEC_WARPS) {
     const int key = ch * 32 + lane;
-    const bool valid = key < kv_len;
+    const bool valid = key < kv_len && key >= key_lo;
     long long row_off = 0;  // element offset of this lane's key row inside the caches
     if (valid) {
       const int blk = table[key / page];
@@ -99,7 +104,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
     float pr[DEC_GMAX];
 #pragma unroll
     for (int g = 0; g < DEC_GMAX; ++g) {
-      const float sv = valid ? s[g] : -INFINITY;
+      float sv = s[g];
+      if (softcap_log2 > 0.f) sv = softcap_log2 * tanhf(sv * cap_inv);
+      sv = valid ? sv : -INFINITY;
       const float mc = warp_max(sv);
       const float mn = fmaxf(m[g], mc);
       const float alpha = exp2f(m[g] - mn);  // 0 on the first chunk (m = -inf)
@@ -235,8 +242,9 @@ extern "C" int tw_attn_decode(const void* q, long long ldq, const void* k_cache,
                               void* out, long long ldo, const int* tok_row, const int* tok_seq,
                               const int* tok_kvlen, int n_tok, const int* block_table, int max_blocks,
                               int hq, int hkv, int D, float scale, int splits, float* part_o,
-                              float* part_ml, cudaStream_t stream) {
+                              float* part_ml, int window, float softcap, cudaStream_t stream) {
   if (n_tok <= 0) return 0;
+  const float softcap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   if ((D != 128 && D != 64) || hkv <= 0 || hq <= 0 || hq % hkv != 0 || hq / hkv > DEC_GMAX) {
     set_last_error("attn_decode: unsupported shape (D=%d, hq=%d, hkv=%d)", D, hq, hkv);
     return 1;
@@ -255,14 +263,14 @@ extern "C" int tw_attn_decode(const void* q, long long ldq, const void* k_cache,
   if (D == 128) {
     attn_decode_kernel<128><<<grid, DEC_WARPS * 32, 0, stream>>>(qb, ldq, kb, vb, tok_row, tok_seq, tok_kvlen,
                                                                  block_table, max_blocks, page, hq, hkv,
-                                                                 scale_log2, splits, ob, ldo, part_o, part_ml);
+                                                                 scale_log2, splits, ob, ldo, part_o, part_ml, window, softcap_log2);
     if (splits > 1)
       attn_decode_merge_kernel<128><<<dim3(n_tok, hq), 128, 0, stream>>>(part_o, part_ml, tok_row, hq, splits,
                                                                          ob, ldo);
   } else {
     attn_decode_kernel<64><<<grid, DEC_WARPS * 32, 0, stream>>>(qb, ldq, kb, vb, tok_row, tok_seq, tok_kvlen,
                                                                 block_table, max_blocks, page, hq, hkv,
-                                                                scale_log2, splits, ob, ldo, part_o, part_ml);
+                                                                scale_log2, splits, ob, ldo, part_o, part_ml, window, softcap_log2);
     if (splits > 1)
       attn_decode_merge_kernel<64><<<dim3(n_tok, hq), 64, 0, stream>>>(part_o, part_ml, tok_row, hq, splits,
                                                                        ob, ldo);
@@ -324,6 +332,8 @@ extern "C" int tw_attn_decode_noalloc(const void* q, long long ldq, const void* 
                                       const int* block_table, int max_blocks, int hq, int hkv, int D,
                                       float scale, int splits, cudaStream_t stream) {
   if (n_tok <= 0) return 0;
+  const int window = 0;               // full causal attention, no soft cap
+  const float softcap_log2 = 0.f;
   if ((D != 128 && D != 64) || hkv <= 0 || hq <= 0 || hq % hkv != 0 || hq / hkv > DEC_GMAX) {
     set_last_error("attn_decode_noalloc: unsupported shape (D=%d, hq=%d, hkv=%d)", D, hq, hkv);
     return 1;
@@ -350,14 +360,14 @@ extern "C" int tw_attn_decode_noalloc(const void* q, long long ldq, const void* 
   if (D == 128) {
     attn_decode_kernel<128><<<grid, DEC_WARPS * 32, 0, stream>>>(qb, ldq, kb, vb, tok_row, tok_seq, tok_kvlen,
                                                                  block_table, max_blocks, page, hq, hkv,
-                                                                 scale_log2, splits, ob, ldo, part_o, part_ml);
+                                                                 scale_log2, splits, ob, ldo, part_o, part_ml, window, softcap_log2);
     if (splits > 1)
       attn_decode_merge_kernel<128><<<dim3(n_tok, hq), 128, 0, stream>>>(part_o, part_ml, tok_row, hq, splits,
                                                                          ob, ldo);
   } else {
     attn_decode_kernel<64><<<grid, DEC_WARPS * 32, 0, stream>>>(qb, ldq, kb, vb, tok_row, tok_seq, tok_kvlen,
                                                                 block_table, max_blocks, page, hq, hkv,
-                                                                scale_log2, splits, ob, ldo, part_o, part_ml);
+                                                                scale_log2, splits, ob, ldo, part_o, part_ml, window, softcap_log2);
     if (splits > 1)
       attn_decode_merge_kernel<64><<<dim3(n_tok, hq), 64, 0, stream>>>(part_o, part_ml, tok_row, hq, splits,
                                                                        ob, ldo);

@@ -748,7 +748,8 @@ extern "C" int tw_attn_prefill(const void* q, long long ldq, int T, const void* 
                                int num_blocks, int page, void* out, long long ldo, const int* cu_q,
                                const int* kv_lens, const int* block_table, int max_blocks,
                                const int* tile_seq, const int* tile_q0, int num_tiles, int hq, int hkv,
-                               int D, float scale, int max_ctas, uint32_t* status, cudaStream_t stream) {
+                               int D, float scale, int max_ctas, int window, float softcap, uint32_t* status,
+                               cudaStream_t stream) {
   if (num_tiles <= 0 || T <= 0) return 0;
   if (D != 128 && D != 64) {
     set_last_error("attn_prefill: head_dim must be 64 or 128 (got %d)", D);
@@ -790,10 +791,14 @@ extern "C" int tw_attn_prefill(const void* q, long long ldq, int T, const void* 
   p.hkv = hkv;
   p.ring = 3;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window > 0 ? window : 0;
+  p.softcap = softcap > 0.f ? softcap : 0.f;
+  p.scale = scale;
   p.status = status;
   // Persistent kernel with the key range of an item split between the softmax groups (variant 3): the
   // only one that honours an SM budget.
-  if (g_attn_variant == 3 || (g_attn_variant == 0 && ATTN_AUTO_SPLIT))
+  // (sliding window and soft cap exist in that kernel only)
+  if (g_attn_variant == 3 || (g_attn_variant == 0 && ATTN_AUTO_SPLIT) || p.window > 0 || p.softcap > 0.f)
     return launch_prefill_split(D, tmQ, tmK, tmV, p, num_tiles, max_ctas, stream);
   // Query heads that share a KV head go two to a CTA when the group size is even.
   const bool pair = ((hq / hkv) % 2 == 0) && g_attn_variant != 1;

@@ -32,6 +32,9 @@ struct AttnParams {
   int hq, hkv;
   int ring;                // head-pair kernel: K/V tile slots in use
   float scale_log2;        // softmax scale * log2(e)
+  int window;              // sliding window: a query at position p sees keys (p - window, p]; 0 = unlimited
+  float softcap;           // logits soft cap: s -> cap * tanh(s / cap) on the scaled scores; 0 = off
+  float scale;             // softmax scale (needed with the soft cap)
   uint32_t* status;
 };
 

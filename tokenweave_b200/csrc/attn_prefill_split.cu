@@ -94,9 +94,17 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   return d;
 }
 
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // One work item: a 128-query tile of one head.
 struct SplitItem {
-  int head, kvh, seq, q_begin, q0, rows_valid, pos0, kv_len, n_tiles, n_a;   // group A: tiles [0, n_a), B: [n_a, n_tiles)
+  // key tiles [j_lo, j_lo + n_tiles) are needed (j_lo > 0 only under a sliding window);
+  // group A takes the first n_a of them, group B the rest
+  int head, kvh, seq, q_begin, q0, rows_valid, pos0, kv_len, j_lo, n_tiles, n_a;
 };
 
 __device__ __forceinline__ SplitItem split_item(const AttnParams& p, int idx) {
@@ -112,7 +120,9 @@ __device__ __forceinline__ SplitItem split_item(const AttnParams& p, int idx) {
   it.rows_valid = min(ATT_BM, q_len - it.q0);
   it.pos0 = it.kv_len - q_len + it.q0;                       // absolute position of the tile's first query
   const int kv_end = min(it.kv_len, it.pos0 + it.rows_valid);  // keys [0, kv_end) are needed
-  it.n_tiles = (kv_end + ATT_BN - 1) / ATT_BN;
+  // under a sliding window the tile's first query sees nothing before key pos0 - window + 1
+  it.j_lo = p.window > 0 ? max(0, it.pos0 - p.window + 1) / ATT_BN : 0;
+  it.n_tiles = (kv_end + ATT_BN - 1) / ATT_BN - it.j_lo;
   it.n_a = (it.n_tiles + 1) / 2;
   return it;
 }
@@ -129,7 +139,9 @@ __device__ __forceinline__ void split_pair_sync(int quarter) {
   asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory");
 }
 
-template <int D>
+// OPTS: sliding window and logits soft cap compiled in (a separate instantiation, so that the plain causal
+// kernel keeps its register budget).
+template <int D, bool OPTS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_prefill_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                           const __grid_constant__ CUtensorMap tmV, const AttnParams p, const int total_items) {
@@ -227,10 +239,10 @@ attn_prefill_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         };
         const int n_b = it.n_tiles - it.n_a;
         for (int t = 0; t < it.n_a && ok; ++t) {
-          ok = load_tile(0, &tmK, t);
-          if (ok && t < n_b) ok = load_tile(1, &tmK, it.n_a + t);
-          if (ok) ok = load_tile(0, &tmV, t);
-          if (ok && t < n_b) ok = load_tile(1, &tmV, it.n_a + t);
+          ok = load_tile(0, &tmK, it.j_lo + t);
+          if (ok && t < n_b) ok = load_tile(1, &tmK, it.j_lo + it.n_a + t);
+          if (ok) ok = load_tile(0, &tmV, it.j_lo + t);
+          if (ok && t < n_b) ok = load_tile(1, &tmV, it.j_lo + it.n_a + t);
         }
         ++items_done;
       }
@@ -322,15 +334,20 @@ attn_prefill_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       const SplitItem it = split_item(p, idx);
       const int n_b = it.n_tiles - it.n_a;
       const int n_mine = g == 0 ? it.n_a : n_b;
-      const int j0 = g == 0 ? 0 : it.n_a;
+      const int j0 = it.j_lo + (g == 0 ? 0 : it.n_a);
+      const float cap_mul = (OPTS && p.softcap > 0.f) ? p.softcap / p.scale : 0.f;
+      const float cap_in = (OPTS && p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
       const int pos = it.pos0 + min(r, it.rows_valid - 1);   // padding rows copy the last valid row's mask
+      const int pos_w = (OPTS && p.window > 0) ? pos - p.window + 1 : 0;    // first key this row sees
       float m_ref = -INFINITY;   // softmax reference (a stale running maximum), log2 domain
       float l_sum = 0.f;
       for (int t = 0; t < n_mine; ++t) {
         if (ok) ok = mbar_wait(&s_full[g], cnt & 1);
         tc_fence_after_sync();
         const int k_base = (j0 + t) * ATT_BN;
-        const bool need_mask = (k_base + ATT_BN - 1) > __shfl_sync(0xffffffffu, pos, 0);
+        // warp-uniform: lane 0 holds the warp's smallest position, lane 31 its largest
+        bool need_mask = (k_base + ATT_BN - 1) > __shfl_sync(0xffffffffu, pos, 0);
+        if (OPTS) need_mask = need_mask || k_base < __shfl_sync(0xffffffffu, pos_w, 31);
         // The row's 128 scores come to registers in one go (four loads in flight, one wait): the latency of
         // tensor-memory loads is paid once per tile, and everything below runs from registers.
         uint32_t s0[32], s1[32], s2[32], s3[32];
@@ -339,13 +356,23 @@ attn_prefill_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         tmem_ld_32x32(t_s + 64, s2);
         tmem_ld_32x32(t_s + 96, s3);
         tmem_wait_ld();
+        if (OPTS && p.softcap > 0.f) {
+          // s -> cap * tanh(s * scale / cap), kept in units of the raw scores (the scale is applied below)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            s0[i] = __float_as_uint(cap_mul * fast_tanh(__uint_as_float(s0[i]) * cap_in));
+            s1[i] = __float_as_uint(cap_mul * fast_tanh(__uint_as_float(s1[i]) * cap_in));
+            s2[i] = __float_as_uint(cap_mul * fast_tanh(__uint_as_float(s2[i]) * cap_in));
+            s3[i] = __float_as_uint(cap_mul * fast_tanh(__uint_as_float(s3[i]) * cap_in));
+          }
+        }
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            if (k_base + i > pos) s0[i] = __float_as_uint(-INFINITY);
-            if (k_base + 32 + i > pos) s1[i] = __float_as_uint(-INFINITY);
-            if (k_base + 64 + i > pos) s2[i] = __float_as_uint(-INFINITY);
-            if (k_base + 96 + i > pos) s3[i] = __float_as_uint(-INFINITY);
+            if (k_base + i > pos || (OPTS && k_base + i < pos_w)) s0[i] = __float_as_uint(-INFINITY);
+            if (k_base + 32 + i > pos || (OPTS && k_base + 32 + i < pos_w)) s1[i] = __float_as_uint(-INFINITY);
+            if (k_base + 64 + i > pos || (OPTS && k_base + 64 + i < pos_w)) s2[i] = __float_as_uint(-INFINITY);
+            if (k_base + 96 + i > pos || (OPTS && k_base + 96 + i < pos_w)) s3[i] = __float_as_uint(-INFINITY);
           }
         }
         // row maximum: three-input max, one chain per chunk
@@ -487,11 +514,11 @@ attn_prefill_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   }
 }
 
-template <int D>
+template <int D, bool OPTS>
 static int launch_split_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p,
                           int num_tiles, int max_ctas, cudaStream_t stream) {
   using S = SplitSmem<D>;
-  auto kern = attn_prefill_split_kernel<D>;
+  auto kern = attn_prefill_split_kernel<D, OPTS>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -518,8 +545,11 @@ static int launch_split_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, const 
 
 int launch_prefill_split(int D, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
                          const AttnParams& p, int num_tiles, int max_ctas, cudaStream_t stream) {
-  return D == 128 ? launch_split_t<128>(tmQ, tmK, tmV, p, num_tiles, max_ctas, stream)
-                  : launch_split_t<64>(tmQ, tmK, tmV, p, num_tiles, max_ctas, stream);
+  if (p.window > 0 || p.softcap > 0.f)
+    return D == 128 ? launch_split_t<128, true>(tmQ, tmK, tmV, p, num_tiles, max_ctas, stream)
+                    : launch_split_t<64, true>(tmQ, tmK, tmV, p, num_tiles, max_ctas, stream);
+  return D == 128 ? launch_split_t<128, false>(tmQ, tmK, tmV, p, num_tiles, max_ctas, stream)
+                  : launch_split_t<64, false>(tmQ, tmK, tmV, p, num_tiles, max_ctas, stream);
 }
 
 }  // namespace tw

@@ -71,14 +71,14 @@ int tw_merge_attn_states(void* out, float* out_lse, const void* a_out, const flo
 int tw_attn_prefill(const void* q, long long ldq, int T, const void* k_cache, const void* v_cache,
                     int num_blocks, int page, void* out, long long ldo, const int* cu_q, const int* kv_lens,
                     const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
-                    int num_tiles, int hq, int hkv, int D, float scale, int max_ctas, uint32_t* status,
-                    cudaStream_t stream);
+                    int num_tiles, int hq, int hkv, int D, float scale, int max_ctas, int window, float softcap,
+                    uint32_t* status, cudaStream_t stream);
 int tw_attn_set_variant(int variant);
 int tw_attn_set_ring(int slots);
 int tw_attn_decode(const void* q, long long ldq, const void* k_cache, const void* v_cache, int page, void* out,
                    long long ldo, const int* tok_row, const int* tok_seq, const int* tok_kvlen, int n_tok,
                    const int* block_table, int max_blocks, int hq, int hkv, int D, float scale, int splits,
-                   float* part_o, float* part_ml, cudaStream_t stream);
+                   float* part_o, float* part_ml, int window, float softcap, cudaStream_t stream);
 
 int tw_attn_decode_merge(const float* part_o, const float* part_ml, const int* tok_row, int n_tok, int hq, int D,
                          int splits, void* out, long long ldo, cudaStream_t stream);

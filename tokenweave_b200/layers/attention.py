@@ -122,10 +122,14 @@ def build_attention_metadata(q_lens: Sequence[int], kv_lens: Sequence[int], posi
 class Attention(nn.Module):
     """Owns the layer's KV cache and runs rope -> cache write -> attention on packed qkv rows."""
 
-    def __init__(self, num_q_heads: int, num_kv_heads: int, head_dim: int, scale: Optional[float] = None):
+    def __init__(self, num_q_heads: int, num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
+                 sliding_window: int = 0, logit_softcap: float = 0.0):
         super().__init__()
         self.hq, self.hkv, self.head_dim = num_q_heads, num_kv_heads, head_dim
         self.scale = scale if scale is not None else head_dim ** -0.5
+        # options of the reference's attention backend (vllm/v1/attention/backends/flash_attn.py:517-538): a query
+        # sees the last `sliding_window` keys only (0: all); scores pass through cap * tanh(s / cap) (0: off)
+        self.window, self.softcap = int(sliding_window or 0), float(logit_softcap or 0.0)
         self.k_cache: Optional[torch.Tensor] = None   # [blocks, page, hkv, D]
         self.v_cache: Optional[torch.Tensor] = None
         self.qk_norm: Optional[tuple] = None          # (q weight [D], k weight [D], eps): per-head RMSNorm before rope
@@ -145,12 +149,13 @@ class Attention(nn.Module):
         q = qkv[:, : self.hq * self.head_dim]
         if not qkv.is_cuda:
             out[:n] = reference.paged_attention(q[:n], self.k_cache, self.v_cache, meta.cu_q_cpu, meta.kv_lens_cpu,
-                                                meta.block_table, self.hq, self.hkv, self.head_dim, self.scale)
+                                                meta.block_table, self.hq, self.hkv, self.head_dim, self.scale,
+                                                window=self.window, softcap=self.softcap)
             return out
         ops.attn_prefill(q, self.k_cache, self.v_cache, out, meta.cu_q, meta.kv_lens, meta.block_table,
                          meta.tile_seq, meta.tile_q0, meta.num_tiles, self.hq, self.hkv, self.head_dim, self.scale,
-                         max_ctas=max_ctas)
+                         max_ctas=max_ctas, window=self.window, softcap=self.softcap)
         ops.attn_decode(q, self.k_cache, self.v_cache, out, meta.tok_row, meta.tok_seq, meta.tok_kvlen,
                         meta.num_single, meta.block_table, self.hq, self.hkv, self.head_dim, self.scale,
-                        meta.max_kv_len)
+                        meta.max_kv_len, window=self.window, softcap=self.softcap)
         return out

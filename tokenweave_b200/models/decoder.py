@@ -89,7 +89,8 @@ class DecoderLayer(nn.Module):
         H, D = cfg.hidden_size, cfg.head_dim
         self.qkv_proj = QKVParallelLinear(H, D, cfg.num_q_heads, cfg.num_kv_heads, cfg.qkv_bias, dtype=dt, device=device)
         self.o_proj = RowParallelLinear(cfg.num_q_heads * D, H, False, dtype=dt, device=device)
-        self.attn = Attention(self.qkv_proj.q_heads, self.qkv_proj.kv_heads, D)
+        self.attn = Attention(self.qkv_proj.q_heads, self.qkv_proj.kv_heads, D, sliding_window=cfg.sliding_window,
+                              logit_softcap=cfg.attn_logit_softcapping)
         if cfg.qk_norm:
             # one weight vector per projection, shared by all heads (and therefore by all ranks)
             self.q_norm_w = nn.Parameter(torch.ones(D, dtype=dt, device=device), requires_grad=False)

@@ -388,9 +388,11 @@ def sample(logits: torch.Tensor, packed_params: torch.Tensor) -> torch.Tensor:
 def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                  cu_q: torch.Tensor, kv_lens: torch.Tensor, block_table: torch.Tensor, tile_seq: torch.Tensor,
                  tile_q0: torch.Tensor, num_tiles: int, hq: int, hkv: int, head_dim: int, scale: float,
-                 max_ctas: int = 0) -> None:
+                 max_ctas: int = 0, window: int = 0, softcap: float = 0.0) -> None:
     """Tensor-core causal attention for the 128-query tiles listed in (tile_seq, tile_q0), heaviest tile first.
-    ``max_ctas`` bounds the SMs the persistent kernel occupies (0: all)."""
+    ``max_ctas`` bounds the SMs the persistent kernel occupies (0: all). ``window`` > 0: sliding-window
+    attention, a query at position p sees keys (p - window, p]; ``softcap`` > 0: scores pass through
+    ``cap * tanh(s / cap)`` (the options of vllm/v1/attention/backends/flash_attn.py:517-538)."""
     if num_tiles == 0:
         return
     _check_bf16(q, k_cache, v_cache, out)
@@ -398,7 +400,7 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     _native.call("tw_attn_prefill", q.data_ptr(), _row_stride(q), q.shape[0], k_cache.data_ptr(),
                  v_cache.data_ptr(), num_blocks, page, out.data_ptr(), _row_stride(out), cu_q.data_ptr(),
                  kv_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], tile_seq.data_ptr(),
-                 tile_q0.data_ptr(), num_tiles, hq, hkv, head_dim, scale, max_ctas,
+                 tile_q0.data_ptr(), num_tiles, hq, hkv, head_dim, scale, max_ctas, int(window), float(softcap),
                  status_word(q.device).data_ptr(), _stream())
 
 
@@ -450,10 +452,11 @@ def decode_splits_tc(ctas: int, tiles: int, sm_count: int = 148) -> int:
 
 
 def decode_plan(n_tok: int, hq: int, hkv: int, head_dim: int, page: int, max_kv_len: int,
-                sm_count: int = 148) -> tuple[str, int]:
+                sm_count: int = 148, plain: bool = True) -> tuple[str, int]:
     """(kernel, key splits) for a decode launch: everything that shapes the launch besides the tensor sizes,
-    so a CUDA-graph signature that includes it replays the launch it captured."""
-    use_tc = (_decode_variant in ("tc", "tcp") and head_dim == 128 and hq // hkv <= 16 and max_kv_len >= 256
+    so a CUDA-graph signature that includes it replays the launch it captured. ``plain`` is False under a
+    sliding window or a soft cap, which only the SIMT kernel implements."""
+    use_tc = (plain and _decode_variant in ("tc", "tcp") and head_dim == 128 and hq // hkv <= 16 and max_kv_len >= 256
               and 8 <= page <= 128 and 128 % page == 0)
     tiles = (max_kv_len + 127) // 128
     if use_tc and _decode_variant == "tcp":
@@ -468,13 +471,16 @@ def decode_plan(n_tok: int, hq: int, hkv: int, head_dim: int, page: int, max_kv_
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                 tok_row: torch.Tensor, tok_seq: torch.Tensor, tok_kvlen: torch.Tensor, n_tok: int,
                 block_table: torch.Tensor, hq: int, hkv: int, head_dim: int, scale: float, max_kv_len: int,
-                sm_count: int = 148) -> None:
-    """Single-query attention for the listed tokens; splits the keys when the grid would be small."""
+                sm_count: int = 148, window: int = 0, softcap: float = 0.0) -> None:
+    """Single-query attention for the listed tokens; splits the keys when the grid would be small.
+    ``window`` / ``softcap`` as in :func:`attn_prefill`."""
     if n_tok == 0:
         return
     _check_bf16(q, k_cache, v_cache, out)
     page = k_cache.shape[1]
-    kernel, splits = decode_plan(n_tok, hq, hkv, head_dim, page, max_kv_len, sm_count)
+    plain = window <= 0 and softcap <= 0
+    kernel, splits = decode_plan(n_tok, hq, hkv, head_dim, page, min(max_kv_len, window) if window > 0 else max_kv_len,
+                                 sm_count, plain)
     part_o = part_ml = None
     if splits > 1:
         # Partial results live in buffers whose sizes are powers of two and which are never freed: a captured
@@ -504,7 +510,7 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o
     _native.call("tw_attn_decode", q.data_ptr(), _row_stride(q), k_cache.data_ptr(), v_cache.data_ptr(), page,
                  out.data_ptr(), _row_stride(out), tok_row.data_ptr(), tok_seq.data_ptr(), tok_kvlen.data_ptr(),
                  n_tok, block_table.data_ptr(), block_table.shape[1], hq, hkv, head_dim, scale, splits,
-                 _p(part_o), _p(part_ml), _stream())
+                 _p(part_o), _p(part_ml), int(window), float(softcap), _stream())
 
 
 # ---------------------------------------------------------------------------------------------

@@ -35,9 +35,9 @@ _SIGNATURES = {
     "tw_swap_pages": [vp, vp, ll, vp, i32, vp],
     "tw_merge_attn_states": [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
     "tw_attn_prefill": [vp, ll, i32, vp, vp, i32, i32, vp, ll, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32,
-                        f32, i32, vp, vp],
+                        f32, i32, i32, f32, vp, vp],
     "tw_attn_decode": [vp, ll, vp, vp, i32, vp, ll, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp, vp,
-                       vp],
+                       i32, f32, vp],
     "tw_attn_decode_tc": [vp, ll, vp, vp, i32, i32, vp, ll, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp, vp,
                           vp, vp],
     "tw_attn_decode_tc_persistent": [vp, ll, vp, vp, i32, i32, vp, ll, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32,

@@ -293,9 +293,11 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, vocab_start: int = 0,
 # attention
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: Sequence[int],
                     kv_lens: Sequence[int], block_table: torch.Tensor, hq: int, hkv: int, head_dim: int,
-                    scale: float) -> torch.Tensor:
+                    scale: float, window: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """Causal varlen attention over a paged cache. ``q``: [T, hq*D]; caches [blocks, page, hkv, D];
-    sequence b owns query rows ``cu_q[b]:cu_q[b+1]`` whose last row sees ``kv_lens[b]`` keys."""
+    sequence b owns query rows ``cu_q[b]:cu_q[b+1]`` whose last row sees ``kv_lens[b]`` keys. ``window`` > 0:
+    a query at position p sees keys (p - window, p] only; ``softcap`` > 0: scores become
+    ``softcap * tanh(score / softcap)`` before the softmax."""
     T = q.shape[0]
     D = head_dim
     page = k_cache.shape[1]
@@ -315,9 +317,14 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         k = k.repeat_interleave(group, dim=1)
         v = v.repeat_interleave(group, dim=1)
         s = torch.einsum("qhd,khd->hqk", qb, k) * scale
+        if softcap > 0:
+            s = softcap * torch.tanh(s / softcap)
         qpos = torch.arange(kv_len - q_len, kv_len, device=q.device).unsqueeze(-1)
         kpos = torch.arange(kv_len, device=q.device).unsqueeze(0)
-        s = s.masked_fill((kpos > qpos).unsqueeze(0), float("-inf"))
+        hidden_keys = kpos > qpos
+        if window > 0:
+            hidden_keys = hidden_keys | (kpos <= qpos - window)
+        s = s.masked_fill(hidden_keys.unsqueeze(0), float("-inf"))
         p = torch.softmax(s, dim=-1)
         o = torch.einsum("hqk,khd->qhd", p, v)
         out[qs:qe] = o.reshape(q_len, hq * D).to(q.dtype)

@@ -67,6 +67,7 @@ def tp_world_size() -> int:
 
 
 _init_generation = 0
+_BASE_STORES: dict = {}
 
 
 def _generation_store(init_method: str, rank: int, world_size: int, timeout_s: float):
@@ -84,8 +85,14 @@ def _generation_store(init_method: str, rank: int, world_size: int, timeout_s: f
     gen = _init_generation
     _init_generation += 1
     agent_store = os.environ.get("TORCHELASTIC_USE_AGENT_STORE", "") == "True"
-    base = dist.TCPStore(host, int(port), world_size, is_master=(rank == 0 and not agent_store),
-                         timeout=datetime.timedelta(seconds=timeout_s), wait_for_workers=False)
+    # one store (server on rank 0, one client connection elsewhere) per address for the life of the process:
+    # a second engine in the same process finds it again instead of binding the port a second time
+    key = (host, int(port), rank, world_size)
+    base = _BASE_STORES.get(key)
+    if base is None:
+        base = dist.TCPStore(host, int(port), world_size, is_master=(rank == 0 and not agent_store),
+                             timeout=datetime.timedelta(seconds=timeout_s), wait_for_workers=False)
+        _BASE_STORES[key] = base
     return dist.PrefixStore(f"tw_init_{gen}", base)
 
 

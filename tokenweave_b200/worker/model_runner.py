@@ -205,8 +205,9 @@ class ModelRunner:
                 parts.append(None)
                 continue
             a = self.model.layers[0].attn
-            splits = ops.decode_plan(m.num_single, a.hq, a.hkv, a.head_dim, self.block_size, m.max_kv_len,
-                                     self.model.rt.sm_count)
+            splits = ops.decode_plan(m.num_single, a.hq, a.hkv, a.head_dim, self.block_size,
+                                     min(m.max_kv_len, a.window) if a.window > 0 else m.max_kv_len,
+                                     self.model.rt.sm_count, a.window <= 0 and a.softcap <= 0)
             parts.append((m.num_actual_tokens, m.num_seqs, m.num_tiles, m.num_single, m.block_table.shape[1], splits))
         return tuple(parts)
 
