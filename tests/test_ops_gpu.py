@@ -419,3 +419,47 @@ def test_gemm_fp8_swiglu(M, I, K):
     out = ops.gemm_fp8(aq, wq, a_s, w_s, swiglu=True)
     assert out.shape == (M, I)
     close(out, ref.gemm_fp8(aq, wq, a_s, w_s, swiglu=True))
+
+
+@pytest.mark.parametrize("T,H", [(7, 64), (300, 8192), (33, 5120)])
+def test_int8_quant_and_fused_norm(T, H):
+    x = rnd(T, H, scale=3.0)
+    q, s = ops.quant_int8(x)
+    q_ref, s_ref = ref.quant_int8(x)
+    torch.testing.assert_close(s, s_ref, rtol=1e-6, atol=0)
+    assert (q.int() - q_ref.int()).abs().max().item() <= 1 and (q != q_ref).float().mean().item() < 1e-3
+    static = torch.tensor([0.05], device=DEV)
+    q2, _ = ops.quant_int8(x, static)
+    assert (q2.int() - ref.quant_int8(x, static)[0].int()).abs().max().item() <= 1
+    w = rnd(H, scale=0.1) + 1
+    res = rnd(T, H)
+    res2 = res.clone()
+    q3, s3 = ops.rmsnorm_quant_int8(x, w, 1e-5, residual=res2)
+    summed = x + res
+    assert torch.equal(res2, summed)
+    y = ref.rmsnorm(summed, w, 1e-5)
+    q3_ref, s3_ref = ref.quant_int8(y)
+    torch.testing.assert_close(s3, s3_ref, rtol=2e-2, atol=1e-6)
+    assert (q3.int() - q3_ref.int()).abs().max().item() <= 2
+
+
+def test_gather_cache_convert_fp8_permute_cols():
+    seqs = [(1, 300), (1, 17), (1, 128), (1, 1)]
+    hkv, D, page = 2, 128, 16
+    kc, _, bt, _, kv_lens = _make_paged(seqs, hkv, D, page)
+    cu = torch.tensor([0] + list(torch.tensor(kv_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    got = ops.gather_cache(kc, bt, cu, sum(kv_lens))
+    assert torch.equal(got, ref.gather_cache(kc, bt, kv_lens))
+    # bf16 -> e4m3 -> bf16 with a scale: what an fp8 KV cache stores and returns
+    x = rnd(64, 16, hkv, D)
+    f8 = ops.convert_fp8(x, scale=0.5)
+    assert f8.dtype == torch.float8_e4m3fn
+    want = (x.float() / 0.5).clamp(-448, 448).to(torch.float8_e4m3fn)
+    assert (f8.float() - want.float()).abs().max().item() <= 0.07 * want.float().abs().max().item()
+    back = ops.convert_fp8(f8, scale=0.5)
+    torch.testing.assert_close(back.float(), f8.float() * 0.5, rtol=1e-2, atol=1e-3)
+    torch.testing.assert_close(back.float(), x.float(), rtol=0.07, atol=0.03)
+    # column permutation
+    m = rnd(37, 1000)
+    perm = torch.randperm(1000, device=DEV).to(torch.int32)
+    assert torch.equal(ops.permute_cols(m, perm), m[:, perm.long()])

@@ -34,10 +34,19 @@ __device__ __forceinline__ uint16_t to_e4m3x2(float a, float b) {
   return static_cast<uint16_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
 }
 
+// Two int8 values per call: round to nearest even, saturate to [-128, 127] (float_to_int8_rn of the
+// reference, csrc/quantization/compressed_tensors/int8_quant_kernels.cu:13-28).
+__device__ __forceinline__ uint16_t to_int8x2(float a, float b) {
+  const int ia = max(-128, min(127, __float2int_rn(a)));
+  const int ib = max(-128, min(127, __float2int_rn(b)));
+  return static_cast<uint16_t>((ia & 0xff) | ((ib & 0xff) << 8));
+}
+
+// INT8: the output is symmetric int8 (row maximum maps to 127) instead of e4m3 (row maximum maps to 448).
 // MODE 0: quantise x. MODE 1: y = rmsnorm(x) * w, quantise y. MODE 2: x += residual, residual = x,
 // y = rmsnorm(x) * w, quantise y. DYNAMIC: scale[t] = max|y[t, :]| / 448 is computed and written;
 // otherwise every row uses scales[0]. Each thread owns VPT vectors of 8 elements.
-template <int VPT, int MODE, bool DYNAMIC>
+template <int VPT, int MODE, bool DYNAMIC, bool INT8>
 __global__ void __launch_bounds__(1024)
 quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ res,
                  const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ out, float* __restrict__ scales,
@@ -114,7 +123,7 @@ quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict_
     float scale = static_scale;
     if (DYNAMIC) {
       amax = block_max(amax, scratch);
-      scale = fmaxf(amax / FP8_E4M3_MAX, 1e-10f);
+      scale = fmaxf(amax / (INT8 ? 127.f : FP8_E4M3_MAX), 1e-10f);
       if (threadIdx.x == 0) scales[t] = scale;
     }
     // one IEEE reciprocal per row, then a multiply per element (the reference's is_scale_inverted form,
@@ -130,15 +139,20 @@ quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict_
         const float2 a = unpack_bf16x2(u[0]), b = unpack_bf16x2(u[1]);
         const float2 c = unpack_bf16x2(u[2]), d = unpack_bf16x2(u[3]);
         uint2 o;
-        o.x = to_e4m3x2(a.x * rscale, a.y * rscale) | (static_cast<uint32_t>(to_e4m3x2(b.x * rscale, b.y * rscale)) << 16);
-        o.y = to_e4m3x2(c.x * rscale, c.y * rscale) | (static_cast<uint32_t>(to_e4m3x2(d.x * rscale, d.y * rscale)) << 16);
+        if (INT8) {
+          o.x = to_int8x2(a.x * rscale, a.y * rscale) | (static_cast<uint32_t>(to_int8x2(b.x * rscale, b.y * rscale)) << 16);
+          o.y = to_int8x2(c.x * rscale, c.y * rscale) | (static_cast<uint32_t>(to_int8x2(d.x * rscale, d.y * rscale)) << 16);
+        } else {
+          o.x = to_e4m3x2(a.x * rscale, a.y * rscale) | (static_cast<uint32_t>(to_e4m3x2(b.x * rscale, b.y * rscale)) << 16);
+          o.y = to_e4m3x2(c.x * rscale, c.y * rscale) | (static_cast<uint32_t>(to_e4m3x2(d.x * rscale, d.y * rscale)) << 16);
+        }
         orow[v] = o;
       }
     }
   }
 }
 
-template <int MODE, bool DYNAMIC>
+template <int MODE, bool DYNAMIC, bool INT8 = false>
 static int launch_quant(const void* x, void* res, const void* w, void* out, float* scales, int T, int H,
                         long long ldx, long long ldr, long long ldo, float eps, int max_ctas, cudaStream_t stream) {
   const int nvec = H / 8;
@@ -162,8 +176,8 @@ static int launch_quant(const void* x, void* res, const void* w, void* out, floa
   auto ob = reinterpret_cast<uint8_t*>(out);
 #define TW_QUANT_CASE(V)                                                                              \
   case V:                                                                                             \
-    quant_fp8_kernel<V, MODE, DYNAMIC><<<grid, threads, 0, stream>>>(xb, rb, wb, ob, scales, T, H, ldx, \
-                                                                     ldr, ldo, eps);                  \
+    quant_fp8_kernel<V, MODE, DYNAMIC, INT8><<<grid, threads, 0, stream>>>(xb, rb, wb, ob, scales, T, H, ldx, \
+                                                                           ldr, ldo, eps);                  \
     break;
   switch (vpt) {
     TW_QUANT_CASE(1)
@@ -212,4 +226,35 @@ extern "C" int tw_rmsnorm_quant_fp8(const void* x, void* residual, const void* w
                    : launch_quant<2, false>(x, residual, w, out, scales, T, H, ldx, ldr, ldo, eps, max_ctas, stream);
   return dynamic ? launch_quant<1, true>(x, nullptr, w, out, scales, T, H, ldx, 0, ldo, eps, max_ctas, stream)
                  : launch_quant<1, false>(x, nullptr, w, out, scales, T, H, ldx, 0, ldo, eps, max_ctas, stream);
+}
+
+// Symmetric int8: out[t, :] = clamp(round(x[t, :] / scale), -128, 127); dynamic != 0: scale[t] = max|x[t, :]| / 127
+// is written to scales[t], otherwise scales[0] is used for every row (the reference's static_scaled_int8_quant /
+// dynamic_scaled_int8_quant, csrc/quantization/compressed_tensors/int8_quant_kernels.cu).
+extern "C" int tw_quant_int8(const void* x, long long ldx, void* out, long long ldo, float* scales, int T, int H,
+                             int dynamic, int max_ctas, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0) {
+    set_last_error("quant_int8: width and strides must be multiples of 8");
+    return 1;
+  }
+  return dynamic ? launch_quant<0, true, true>(x, nullptr, nullptr, out, scales, T, H, ldx, 0, ldo, 0.f, max_ctas, stream)
+                 : launch_quant<0, false, true>(x, nullptr, nullptr, out, scales, T, H, ldx, 0, ldo, 0.f, max_ctas, stream);
+}
+
+// (add +) RMSNorm fused with int8 quantisation; arguments as tw_rmsnorm_quant_fp8 (the reference's
+// rms_norm_dynamic_per_token_quant with an int8 output, csrc/quantization/fused_kernels/).
+extern "C" int tw_rmsnorm_quant_int8(const void* x, void* residual, const void* w, void* out, long long ldo,
+                                     float* scales, int T, int H, long long ldx, long long ldr, float eps,
+                                     int dynamic, int max_ctas, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0 || (residual != nullptr && ldr % 8 != 0)) {
+    set_last_error("rmsnorm_quant_int8: width and strides must be multiples of 8");
+    return 1;
+  }
+  if (residual != nullptr)
+    return dynamic ? launch_quant<2, true, true>(x, residual, w, out, scales, T, H, ldx, ldr, ldo, eps, max_ctas, stream)
+                   : launch_quant<2, false, true>(x, residual, w, out, scales, T, H, ldx, ldr, ldo, eps, max_ctas, stream);
+  return dynamic ? launch_quant<1, true, true>(x, nullptr, w, out, scales, T, H, ldx, 0, ldo, eps, max_ctas, stream)
+                 : launch_quant<1, false, true>(x, nullptr, w, out, scales, T, H, ldx, 0, ldo, eps, max_ctas, stream);
 }

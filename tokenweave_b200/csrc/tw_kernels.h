@@ -67,6 +67,18 @@ int tw_swap_pages(const void* src, void* dst, long long page_bytes, const long l
 int tw_merge_attn_states(void* out, float* out_lse, const void* a_out, const float* a_lse, const void* b_out,
                          const float* b_lse, int T, int H, int D, cudaStream_t stream);
 
+// ---- int8 quantisation (quant_fp8.cu) and cache utilities (cache_ops.cu) ----
+int tw_quant_int8(const void* x, long long ldx, void* out, long long ldo, float* scales, int T, int H, int dynamic,
+                  int max_ctas, cudaStream_t stream);
+int tw_rmsnorm_quant_int8(const void* x, void* residual, const void* w, void* out, long long ldo, float* scales,
+                          int T, int H, long long ldx, long long ldr, float eps, int dynamic, int max_ctas,
+                          cudaStream_t stream);
+int tw_gather_cache(const void* cache, void* dst, const int* block_table, const int* cu_seq, int batch,
+                    int max_blocks, int page, int row_elems, cudaStream_t stream);
+int tw_convert_fp8(const void* src, void* dst, long long n, float scale, int to_fp8, cudaStream_t stream);
+int tw_permute_cols(const void* in, void* out, const int* perm, int rows, int cols, long long ld_in,
+                    long long ld_out, cudaStream_t stream);
+
 // ---- attention (attn_prefill.cu, attn_decode.cu) ----
 int tw_attn_prefill(const void* q, long long ldq, int T, const void* k_cache, const void* v_cache,
                     int num_blocks, int page, void* out, long long ldo, const int* cu_q, const int* kv_lens,

@@ -17,7 +17,8 @@ from . import _native, gemm_table, reference
 
 __all__ = [
     "gemm", "rmsnorm", "rmsnorm_copy_", "add_rmsnorm_", "rope_kv_write_", "swiglu", "embedding", "argmax",
-    "quant_fp8", "rmsnorm_quant_fp8", "gemm_fp8", "activation", "copy_pages", "swap_pages", "merge_attn_states", "attn_prefill", "attn_decode", "moe_router", "moe_align", "moe_scatter", "moe_combine", "status_word",
+    "quant_fp8", "rmsnorm_quant_fp8", "quant_int8", "rmsnorm_quant_int8", "gather_cache", "convert_fp8", "permute_cols",
+    "gemm_fp8", "activation", "copy_pages", "swap_pages", "merge_attn_states", "attn_prefill", "attn_decode", "moe_router", "moe_align", "moe_scatter", "moe_combine", "status_word",
     "check_status", "reset_status", "STATUS_CODES", "KernelStatusError",
 ]
 
@@ -277,6 +278,94 @@ def activation(x: torch.Tensor, kind: str, out: Optional[torch.Tensor] = None, p
     _check_bf16(x, out)
     _native.call("tw_activation", x.data_ptr(), _row_stride(x), out.data_ptr(), _row_stride(out), T, d, code,
                  float(param), _stream())
+    return out
+
+
+def quant_int8(x: torch.Tensor, scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+               max_ctas: int = 0):
+    """bf16 ``[T, H]`` -> (int8 ``[T, H]``, fp32 scales), symmetric. ``scale`` None: dynamic per-token scales
+    ``max|row| / 127``; else the given one-element tensor for every row (the reference's
+    ``dynamic_scaled_int8_quant`` / ``static_scaled_int8_quant``)."""
+    T, H = x.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.int8, device=x.device)
+    if not x.is_cuda:
+        q, s = reference.quant_int8(x, scale)
+        out.copy_(q)
+        return out, s
+    _check_bf16(x)
+    scales = torch.empty(T, dtype=torch.float32, device=x.device) if scale is None else scale
+    _native.call("tw_quant_int8", x.data_ptr(), _row_stride(x), out.data_ptr(), _row_stride(out), scales.data_ptr(),
+                 T, H, int(scale is None), max_ctas, _stream())
+    return out, scales
+
+
+def rmsnorm_quant_int8(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None,
+                       scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, max_ctas: int = 0):
+    """``q = int8(rmsnorm(x [+ residual]) * weight / scale)``; with ``residual`` the sum is written back to
+    ``residual`` first. Returns ``(q, scales)`` like :func:`quant_int8`."""
+    T, H = x.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.int8, device=x.device)
+    if not x.is_cuda:
+        if residual is not None:
+            residual.copy_((x + residual))
+            y = reference.rmsnorm(residual, weight, eps)
+        else:
+            y = reference.rmsnorm(x, weight, eps)
+        q, s = reference.quant_int8(y, scale)
+        out.copy_(q)
+        return out, s
+    _check_bf16(x, weight)
+    scales = torch.empty(T, dtype=torch.float32, device=x.device) if scale is None else scale
+    _native.call("tw_rmsnorm_quant_int8", x.data_ptr(), None if residual is None else residual.data_ptr(),
+                 weight.data_ptr(), out.data_ptr(), _row_stride(out), scales.data_ptr(), T, H, _row_stride(x),
+                 0 if residual is None else _row_stride(residual), eps, int(scale is None), max_ctas, _stream())
+    return out, scales
+
+
+def gather_cache(cache: torch.Tensor, block_table: torch.Tensor, cu_seq: torch.Tensor, total_rows: int,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The cache rows of every sequence (``cu_seq``: ``[batch + 1]`` int32 prefix sums of the lengths, on the
+    cache's device), in block-table order, as one contiguous ``[total_rows, kv_heads, D]`` tensor."""
+    page = cache.shape[1]
+    if out is None:
+        out = torch.empty(total_rows, *cache.shape[2:], dtype=cache.dtype, device=cache.device)
+    if not cache.is_cuda:
+        lens = (cu_seq[1:] - cu_seq[:-1]).tolist()
+        out.copy_(reference.gather_cache(cache, block_table, lens))
+        return out
+    _check_bf16(cache)
+    row_elems = cache[0, 0].numel()
+    _native.call("tw_gather_cache", cache.data_ptr(), out.data_ptr(), block_table.data_ptr(), cu_seq.data_ptr(),
+                 block_table.shape[0], block_table.shape[1], page, row_elems, _stream())
+    return out
+
+
+def convert_fp8(src: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 -> e4m3 (``src / scale``) or e4m3 -> bf16 (``src * scale``), by the dtype of ``src``: how a KV cache
+    is stored in / read back from fp8 (``convert_fp8`` of the reference's cache kernels)."""
+    to_fp8 = src.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty(src.shape, dtype=FP8 if to_fp8 else torch.bfloat16, device=src.device)
+    if not src.is_cuda:
+        out.copy_((src.float() / scale).clamp(-448, 448).to(FP8) if to_fp8 else (src.float() * scale).to(torch.bfloat16))
+        return out
+    assert src.is_contiguous() and out.is_contiguous()
+    _native.call("tw_convert_fp8", src.data_ptr(), out.data_ptr(), src.numel(), float(scale), int(to_fp8), _stream())
+    return out
+
+
+def permute_cols(x: torch.Tensor, perm: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[:, j] = x[:, perm[j]]`` for a 16-bit matrix (``permute_cols`` of the reference)."""
+    if out is None:
+        out = torch.empty_like(x)
+    if not x.is_cuda:
+        out.copy_(x[:, perm.long()])
+        return out
+    assert x.element_size() == 2 and perm.dtype == torch.int32 and perm.numel() == x.shape[1]
+    _native.call("tw_permute_cols", x.data_ptr(), out.data_ptr(), perm.data_ptr(), x.shape[0], x.shape[1],
+                 _row_stride(x), _row_stride(out), _stream())
     return out
 
 

@@ -30,6 +30,11 @@ _SIGNATURES = {
     "tw_gemm_fp8": [vp, ll, vp, ll, ll, vp, ll, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp, vp],
     "tw_quant_fp8": [vp, ll, vp, ll, vp, i32, i32, i32, i32, vp],
     "tw_rmsnorm_quant_fp8": [vp, vp, vp, vp, ll, vp, i32, i32, ll, ll, f32, i32, i32, vp],
+    "tw_quant_int8": [vp, ll, vp, ll, vp, i32, i32, i32, i32, vp],
+    "tw_rmsnorm_quant_int8": [vp, vp, vp, vp, ll, vp, i32, i32, ll, ll, f32, i32, i32, vp],
+    "tw_gather_cache": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
+    "tw_convert_fp8": [vp, vp, ll, f32, i32, vp],
+    "tw_permute_cols": [vp, vp, vp, i32, i32, ll, ll, vp],
     "tw_activation": [vp, ll, vp, ll, i32, i32, i32, f32, vp],
     "tw_copy_pages": [vp, ll, vp, i32, vp],
     "tw_swap_pages": [vp, vp, ll, vp, i32, vp],

@@ -59,6 +59,28 @@ def swiglu(x: torch.Tensor) -> torch.Tensor:
 FP8_MAX = 448.0
 
 
+def quant_int8(x: torch.Tensor, scale: Optional[torch.Tensor] = None):
+    """(int8 tensor, scales): symmetric, per-token ``max|row| / 127`` when ``scale`` is None, else the given scalar;
+    round to nearest even and saturate."""
+    xf = x.float()
+    if scale is None:
+        s = (xf.abs().amax(dim=-1) / 127.0).clamp_min(1e-10)
+        q = torch.round(xf * s.reciprocal().unsqueeze(-1)).clamp(-128, 127).to(torch.int8)
+        return q, s
+    q = torch.round(xf * scale.float().reshape(()).reciprocal()).clamp(-128, 127).to(torch.int8)
+    return q, scale
+
+
+def gather_cache(cache: torch.Tensor, block_table: torch.Tensor, seq_lens: Sequence[int]) -> torch.Tensor:
+    """Rows of every sequence, in block-table order, concatenated: ``[sum(seq_lens), kv_heads, D]``."""
+    page = cache.shape[1]
+    parts = []
+    for b, n in enumerate(seq_lens):
+        blocks = block_table[b, : (n + page - 1) // page].long()
+        parts.append(cache.index_select(0, blocks).reshape(-1, *cache.shape[2:])[:n])
+    return torch.cat(parts, 0) if parts else cache.new_zeros((0, *cache.shape[2:]))
+
+
 def quant_fp8(x: torch.Tensor, scale: Optional[torch.Tensor] = None):
     """(e4m3 tensor, scales): per-token ``max|row| / 448`` when ``scale`` is None, else the given scalar."""
     xf = x.float()
