@@ -39,6 +39,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, nargs="+", default=[256, 512, 1024, 2048, 3072, 4096, 6144, 8192, 16384])
     ap.add_argument("--sm-budgets", type=int, nargs="+", default=[148, 140, 132])
     ap.add_argument("--iters", type=int, default=8)
+    ap.add_argument("--shapes", nargs="*", default=None,
+                    help="restrict the run to these weight shapes, each as N,K,swiglu (e.g. 1280,8192,0)")
     ap.add_argument("--out", default=os.path.join(ROOT, "tokenweave_b200", "gemm_configs", "NVIDIA_B200.json"))
     args = ap.parse_args()
     from tokenweave_b200 import ops
@@ -57,6 +59,9 @@ def main() -> None:
             for s in shapes_for(cfg, tp):
                 if s not in todo:
                     todo.append(s)
+    if args.shapes:
+        want = {tuple(int(v) for v in sh.split(",")) for sh in args.shapes}
+        todo = [t for t in todo if t in want]
     table = {}
     if os.path.exists(args.out):
         with open(args.out) as f:
@@ -72,7 +77,9 @@ def main() -> None:
             for sms in args.sm_budgets:
                 best = None
                 for kernel in (2, 1):
-                    widths = range(256, 63, -64) if (kernel == 2 or sw) else range(256, 63, -32)
+                    # CTA pairs also have tiles wider than one MMA (plain epilogue only): 320 .. 512 columns
+                    widths = (list(range(512, 63, -64)) if (kernel == 2 and not sw) else
+                              range(256, 63, -64) if (kernel == 2 or sw) else range(256, 63, -32))
                     for bn in widths:
                         lib.tw_gemm_set_kernel_override(kernel)
                         lib.tw_gemm_set_tile_override(bn)

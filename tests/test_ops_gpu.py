@@ -39,6 +39,26 @@ def test_gemm_plain(M, N, K):
     close(out, ref.gemm(a, w))
 
 
+@pytest.mark.parametrize("bn", [320, 384, 448, 512])
+@pytest.mark.parametrize("M,N,K,max_ctas", [(4096, 1280, 1024, 0), (1000, 1280, 512, 0), (512, 1000, 256, 6), (300, 640, 1088, 0)])
+def test_gemm_pair_wide_tiles(M, N, K, max_ctas, bn):
+    """CTA-pair kernel with tiles wider than one MMA (two MMAs per k-step, one accumulator), bias included."""
+    from tokenweave_b200.ops import _native, gemm_table
+    lib = _native.load()
+    a, w, bias = rnd(M, K), rnd(N, K, scale=1 / math.sqrt(K)), rnd(N)
+    gemm_table.set_enabled(False)
+    lib.tw_gemm_set_kernel_override(2)
+    lib.tw_gemm_set_tile_override(bn)
+    try:
+        out = ops.gemm(a, w, bias=bias, max_ctas=max_ctas)
+        torch.cuda.synchronize()
+    finally:
+        lib.tw_gemm_set_kernel_override(0)
+        lib.tw_gemm_set_tile_override(0)
+        gemm_table.set_enabled(True)
+    close(out, ref.gemm(a, w, bias))
+
+
 def test_gemm_bias_rowscale_strided_out():
     M, N, K = 513, 1280, 1024
     a, w, bias = rnd(M, K), rnd(N, K, scale=1 / math.sqrt(K)), rnd(N)
@@ -463,3 +483,24 @@ def test_gather_cache_convert_fp8_permute_cols():
     m = rnd(37, 1000)
     perm = torch.randperm(1000, device=DEV).to(torch.int32)
     assert torch.equal(ops.permute_cols(m, perm), m[:, perm.long()])
+
+
+@pytest.mark.parametrize("T,pair", [(4096, True), (4096, False), (5000, True), (300, True)])
+def test_moe_layer_grouped_gemm_on_cta_pairs(T, pair):
+    """The MoE layer end to end: with enough rows per expert the groups are padded to 256 rows and the grouped
+    GEMMs run on CTA pairs; both forms must agree with the loop-over-experts reference."""
+    from tokenweave_b200.layers.moe import FusedMoE
+    from tokenweave_b200.parallel.state import set_single_process
+    set_single_process(torch.device(DEV))
+    H, I, E = 1024, 512, 8
+    moe = FusedMoE(E, 2, H, I, dtype=BF, device=DEV)
+    moe.pair_tiles = pair
+    moe.gate.data.copy_(rnd(E, H, scale=1 / math.sqrt(H)))
+    moe.w13.data.copy_(rnd(E, 2 * I, H, scale=1 / math.sqrt(H)))
+    moe.w2.data.copy_(rnd(E, H, I, scale=1 / math.sqrt(I)))
+    x = rnd(T, H)
+    out = moe(x)
+    torch.cuda.synchronize()
+    tw, ids, _ = ops.moe_router(x, moe.gate, 2)
+    want = ref.moe_experts(x, moe.w13, moe.w2, tw, ids)
+    close(out, want, atol=3e-2, rtol=3e-2)

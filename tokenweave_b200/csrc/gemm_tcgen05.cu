@@ -434,6 +434,22 @@ static GemmPlan choose_plan(int M, int N, int K, int sms, bool swiglu, bool grou
         best = GemmPlan{true, bn};
       }
     }
+    // Wide tiles (one accumulator, two MMAs per k-step): worth it when they bring a skinny N down to ONE wave
+    // where the narrower tiles need two or more (the tile cost per column keeps falling with the width, but
+    // with one accumulator the epilogue of a tile no longer hides behind the next tile's main loop).
+    if (!swiglu) {
+      for (int bn = 320; bn <= 512; bn += 64) {
+        if (g_bn_override > 0 && bn != g_bn_override) continue;
+        const long long tiles = static_cast<long long>(num_m2) * ((N + bn - 1) / bn);
+        if (tiles > pairs && g_bn_override != bn) continue;
+        const long long waves = (tiles + pairs - 1) / pairs;
+        const double cost = waves * (tile_cost_pair(bn) * kb_eff + 0.1 * bn) * 1.02;
+        if (cost < best_cost * 0.999) {
+          best_cost = cost;
+          best = GemmPlan{true, bn};
+        }
+      }
+    }
   }
   return best;
 }
@@ -455,7 +471,8 @@ extern "C" int tw_gemm_set_kernel_override(int kind) {
 
 extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
                                  void* C, long long ldc, const void* bias, const float* row_scale, int M, int N,
-                                 int K, int swiglu, int up_row_offset, int bn, int max_ctas, uint32_t* status,
+                                 int K, int swiglu, int up_row_offset, int bn, int max_ctas, const int* tile_expert,
+                                 const int* num_m_tiles_dev, int n_per_expert, uint32_t* status,
                                  cudaStream_t stream);
 
 // Shared launcher body. A is [M,K] with row stride lda, B is [rows_b, K] with row stride ldb
@@ -464,7 +481,9 @@ static int gemm_dispatch(bool fp8, const void* A, long long lda, const void* B, 
                          void* C, long long ldc, const void* bias, const float* row_scale, const float* col_scale,
                          int M, int N, int K, int swiglu, int up_row_offset, const int* tile_expert,
                          const int* num_m_tiles_dev, int n_per_expert, int max_ctas, int plan_hint,
-                         uint32_t* status, cudaStream_t stream) {
+                         uint32_t* status, cudaStream_t stream, int group_tile_rows = 128) {
+  // group_tile_rows: rows per entry of tile_expert (grouped mode). 256: the caller padded every expert to 256
+  // rows, so the CTA-pair kernel can take the groups; 128: single-CTA tiles.
   // plan_hint: 0 = cost model; otherwise kernel * 1000 + tile width (kernel 1 = single-CTA tiles,
   // 2 = CTA pairs), as produced by the tuning table.
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -480,16 +499,20 @@ static int gemm_dispatch(bool fp8, const void* A, long long lda, const void* B, 
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
   // the cost model sees k-blocks: an fp8 problem has K / 128 of them; CTA pairs are bf16-only
+  if (tile_expert != nullptr && group_tile_rows == 256 && !fp8 && sms >= 2)
+    return tw_gemm_bf16_pair(A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, M, N, K, swiglu, up_row_offset, 256, sms,
+                             tile_expert, num_m_tiles_dev, n_per_expert, status, stream);
   GemmPlan plan = choose_plan(M, N, fp8 ? K / 2 : K, sms, swiglu != 0, tile_expert != nullptr || fp8);
   if (plan_hint > 0) {
     const int kind = plan_hint / 1000, bn = plan_hint % 1000;
-    const bool pair_ok = !fp8 && kind == 2 && tile_expert == nullptr && sms >= 2 && bn % 64 == 0;
-    const bool single_ok = kind == 1 && bn % (swiglu ? 64 : 32) == 0;
-    if (bn >= 64 && bn <= 256 && (pair_ok || single_ok)) plan = GemmPlan{pair_ok, bn};
+    const bool pair_ok = !fp8 && kind == 2 && tile_expert == nullptr && sms >= 2 && bn % 64 == 0 &&
+                         (bn <= 256 || (bn <= 512 && !swiglu));
+    const bool single_ok = kind == 1 && bn % (swiglu ? 64 : 32) == 0 && bn <= 256;
+    if (bn >= 64 && (pair_ok || single_ok)) plan = GemmPlan{pair_ok, bn};
   }
   if (plan.pair)
     return tw_gemm_bf16_pair(A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, M, N, K, swiglu, up_row_offset, plan.bn,
-                             sms, status, stream);
+                             sms, nullptr, nullptr, 0, status, stream);
   const int BN = plan.bn;
   const int out_cols = swiglu ? BN / 2 : BN;
   const int num_n = (N + out_cols - 1) / out_cols;
@@ -553,6 +576,20 @@ extern "C" int tw_gemm_bf16(const void* A, long long lda, const void* B, long lo
   return gemm_dispatch(false, A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, nullptr, M, N, K, swiglu,
                        up_row_offset, tile_expert, num_m_tiles_dev, n_per_expert, max_ctas, plan_hint, status,
                        stream);
+}
+
+// Grouped GEMM over experts padded to 256 rows each: tile_expert has one entry per 256-row tile and the groups
+// run on CTA pairs (cta_group::2, M = 256 per tile).
+extern "C" int tw_gemm_bf16_grouped256(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
+                                       void* C, long long ldc, const float* row_scale, int M, int N, int K, int swiglu,
+                                       int up_row_offset, const int* tile_expert, const int* num_m_tiles_dev,
+                                       int n_per_expert, int max_ctas, uint32_t* status, cudaStream_t stream) {
+  if (tile_expert == nullptr) {
+    set_last_error("tw_gemm_bf16_grouped256: needs the tile -> expert map");
+    return 1;
+  }
+  return gemm_dispatch(false, A, lda, B, ldb, rows_b, C, ldc, nullptr, row_scale, nullptr, M, N, K, swiglu,
+                       up_row_offset, tile_expert, num_m_tiles_dev, n_per_expert, max_ctas, 0, status, stream, 256);
 }
 
 // e4m3 x e4m3 -> bf16: C = (A * B^T) * row_scale[m] * col_scale[n] + bias[n] (scales fp32, either may be

@@ -13,6 +13,11 @@
 // Barriers: full[s] lives in the leader and counts the bytes of both CTAs; empty[s] and acc_full[a]
 // exist in both CTAs and are signalled by the leader's tcgen05.commit (one commit per CTA);
 // acc_empty[a] lives in the leader and collects one arrival per epilogue warp of both CTAs.
+// Wide tiles (256 < BN <= 512, plain epilogue only): one accumulator of BN columns, two MMAs of BN / 2
+// columns per k-step. A skinny N (the QKV projection under 8-way tensor parallelism has N = 1280) then
+// fits one wave of 256 x 320 tiles where 256-wide tiles need two waves at half occupancy. Each CTA holds
+// a quarter of the tile's B rows per MMA: rows [r q, r q + q) and [2 q + r q, 2 q + r q + q) of the tile,
+// q = BN / 4, r the CTA's rank, so that the columns of the two MMAs come out in order.
 // Every wait is bounded (TW_ERR_MBAR_TIMEOUT); the pair leaves together through a cluster barrier.
 #include <string.h>
 
@@ -38,6 +43,11 @@ struct Gemm2Params {
   const float* row_scale;
   int M, N, K;
   int num_m_tiles, num_n_tiles;   // in 256-row pair tiles
+  // grouped mode (mixture of experts): pair tile m belongs to expert tile_expert[m], whose weights start
+  // n_per_expert rows into B; the number of valid pair tiles is read from device memory
+  const int* tile_expert;
+  const int* num_m_tiles_dev;
+  int n_per_expert;
   int up_row_offset;
   int bn, stages;
   int kb_per_stage;
@@ -122,7 +132,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int b_half_bytes = HALF_N * G2_BK * 2;
   const int stage_bytes = KBPS * (G2_A_BYTES + b_half_bytes);
   const int OUT_COLS = SWIGLU ? BN / 2 : BN;
-  const uint32_t IDESC = make_idesc_bf16(2 * G2_BM, BN, 0, 0);
+  const bool WIDE = BN > 256;                      // two MMAs of BN / 2 columns per k-step, one accumulator
+  const int MMA_N = WIDE ? BN / 2 : BN;
+  const int NUM_ACC = WIDE ? 1 : 2;
+  const uint32_t IDESC = make_idesc_bf16(2 * G2_BM, MMA_N, 0, 0);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -165,7 +178,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_m = p.num_m_tiles, num_n = p.num_n_tiles;
+  int num_m = p.num_m_tiles;
+  if (p.num_m_tiles_dev != nullptr) num_m = min(num_m, *p.num_m_tiles_dev);
+  const int num_n = p.num_n_tiles;
   const int total_tiles = num_m * num_n;
   const int num_kb = ((p.K + G2_BK - 1) / G2_BK + KBPS - 1) / KBPS;   // pipeline iterations per tile
   const int pair = blockIdx.x >> 1;
@@ -180,9 +195,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         int m_tile, n_tile;
         pair_tile_coords(t, num_m, num_n, m_tile, n_tile);
         const int m0 = m_tile * 2 * G2_BM + rank * G2_BM;
+        const int e_row0 = p.tile_expert != nullptr ? p.tile_expert[m_tile] * p.n_per_expert : 0;
         int b_row0;
-        if (SWIGLU) b_row0 = n_tile * OUT_COLS + (rank ? p.up_row_offset : 0);   // leader: gate rows, peer: up rows
-        else b_row0 = n_tile * BN + rank * HALF_N;
+        if (SWIGLU) b_row0 = e_row0 + n_tile * OUT_COLS + (rank ? p.up_row_offset : 0);   // leader: gate rows, peer: up rows
+        else b_row0 = e_row0 + n_tile * BN + rank * HALF_N;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             report_error(p.status, TW_ERR_MBAR_TIMEOUT);
@@ -197,7 +213,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             // a k-block past the end of K reads zeros (out-of-bounds fill) and adds nothing
             const int kx = (kb * KBPS + s) * G2_BK;
             tma_load_2d_pair(sa + s * G2_A_BYTES, &tmA, leader_full, kx, m0);
-            tma_load_2d_pair(sb + s * b_half_bytes, &tmB, leader_full, kx, b_row0);
+            if (WIDE) {
+              // this CTA's quarter of the B rows of each of the two MMAs (the tensor map's box is BN / 4 rows)
+              const int q = BN / 4;
+              tma_load_2d_pair(sb + s * b_half_bytes, &tmB, leader_full, kx, e_row0 + n_tile * BN + rank * q);
+              tma_load_2d_pair(sb + s * b_half_bytes + q * G2_BK * 2, &tmB, leader_full, kx,
+                               e_row0 + n_tile * BN + 2 * q + rank * q);
+            } else {
+              tma_load_2d_pair(sb + s * b_half_bytes, &tmB, leader_full, kx, b_row0);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -228,8 +252,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const uint64_t a_desc = make_smem_desc_sw128(sa + s * G2_A_BYTES, 16, 1024);
             const uint64_t b_desc = make_smem_desc_sw128(sb + s * b_half_bytes, 16, 1024);
 #pragma unroll
-            for (int k = 0; k < G2_BK / 16; ++k)
+            for (int k = 0; k < G2_BK / 16; ++k) {
               umma_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+              if (WIDE) {
+                // second half of the columns: the next BN / 4 rows of this CTA's B tile (and of the peer's)
+                const uint64_t b2 = make_smem_desc_sw128(sb + s * b_half_bytes + (BN / 4) * G2_BK * 2, 16, 1024);
+                umma_ss_pair(d_tmem + MMA_N, a_desc + 2 * k, b2 + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+              }
+            }
           }
           // the stage is free in BOTH CTAs once these MMAs have read it
           const uint32_t e_local = smem_u32(&empty_bar[stage]);
@@ -245,8 +275,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const uint32_t f_local = smem_u32(&acc_full[acc]);
         umma_commit_pair(map_to_cta(f_local, 0));
         umma_commit_pair(map_to_cta(f_local, 1));
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1;
+        if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
       }
     }
   } else {
@@ -318,8 +347,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1;
+      if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
     }
   }
 
@@ -385,14 +413,17 @@ extern "C" int tw_gemm_set_pair_kbps(int kbps) {
   return 0;
 }
 
-// Same contract as tw_gemm_bf16 without the grouped mode. `bn` is the tile width (multiple of 64,
-// <= 256), `max_ctas` bounds the SMs used (rounded down to an even number).
+// Same contract as tw_gemm_bf16. `bn` is the tile width (multiple of 64, <= 256, or up to 512 without SwiGLU),
+// `max_ctas` bounds the SMs used (rounded down to an even number). Grouped mode: tile_expert has one entry per
+// 256-row tile of A (the caller pads every expert to 256 rows).
 extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
                                  void* C, long long ldc, const void* bias, const float* row_scale, int M, int N,
-                                 int K, int swiglu, int up_row_offset, int bn, int max_ctas, uint32_t* status,
+                                 int K, int swiglu, int up_row_offset, int bn, int max_ctas, const int* tile_expert,
+                                 const int* num_m_tiles_dev, int n_per_expert, uint32_t* status,
                                  cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldc % 8) != 0 || bn % 64 != 0 || bn < 64 || bn > 256) {
+  if ((K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldc % 8) != 0 || bn % 64 != 0 || bn < 64 || bn > 512 ||
+      (bn > 256 && swiglu)) {
     set_last_error("tw_gemm_bf16_pair: bad strides or tile width (K=%d, bn=%d)", K, bn);
     return 1;
   }
@@ -406,9 +437,11 @@ extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, lo
   const int num_m = (M + 2 * G2_BM - 1) / (2 * G2_BM);
   const int out_cols = swiglu ? bn / 2 : bn;
   const int num_n = (N + out_cols - 1) / out_cols;
-  const int kbps = (g_pair_kbps == 2 && K >= 256) ? 2 : 1;
+  int kbps = (g_pair_kbps == 2 && K >= 256) ? 2 : 1;
+  // wide tiles: two k-blocks per stage only while three such stages fit (216 KB of pipeline at most)
+  if (bn > 256 && (216 * 1024) / (2 * (G2_A_BYTES + (bn / 2) * G2_BK * 2)) < 3) kbps = 1;
   const int stage_bytes = kbps * (G2_A_BYTES + (bn / 2) * G2_BK * 2);
-  int stages = G2_SMEM_BUDGET / stage_bytes;
+  int stages = (bn > 256 ? 216 * 1024 : G2_SMEM_BUDGET) / stage_bytes;
   if (stages > G2_MAX_STAGES) stages = G2_MAX_STAGES;
 
   CUtensorMap tmA, tmB;
@@ -421,7 +454,7 @@ extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, lo
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows_b};
     uint64_t strides[1] = {(uint64_t)ldb * 2};
-    uint32_t box[2] = {G2_BK, (uint32_t)(bn / 2)};
+    uint32_t box[2] = {G2_BK, (uint32_t)(bn > 256 ? bn / 4 : bn / 2)};     // wide tiles: two loads of a quarter each
     if (!make_tensor_map_bf16(&tmB, B, 2, dims, strides, box)) return 1;
   }
   Gemm2Params p;
@@ -435,6 +468,9 @@ extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, lo
   p.num_m_tiles = num_m;
   p.num_n_tiles = num_n;
   p.up_row_offset = up_row_offset;
+  p.tile_expert = tile_expert;
+  p.num_m_tiles_dev = num_m_tiles_dev;
+  p.n_per_expert = n_per_expert;
   p.bn = bn;
   p.stages = stages;
   p.kb_per_stage = kbps;

@@ -17,6 +17,10 @@ int tw_gemm_bf16(const void* A, long long lda, const void* B, long long ldb, lon
                  long long ldc, const void* bias, const float* row_scale, int M, int N, int K, int swiglu,
                  int up_row_offset, const int* tile_expert, const int* num_m_tiles_dev, int n_per_expert,
                  int max_ctas, int plan_hint, uint32_t* status, cudaStream_t stream);
+int tw_gemm_bf16_grouped256(const void* A, long long lda, const void* B, long long ldb, long long rows_b, void* C,
+                            long long ldc, const float* row_scale, int M, int N, int K, int swiglu, int up_row_offset,
+                            const int* tile_expert, const int* num_m_tiles_dev, int n_per_expert, int max_ctas,
+                            uint32_t* status, cudaStream_t stream);
 int tw_gemm_set_tile_override(int bn);
 int tw_gemm_set_kernel_override(int kind);
 

@@ -20,7 +20,9 @@ from .. import ops
 from ..ops import reference
 from ..parallel.state import get_tp
 
-TILE_ROWS = 128
+TILE_ROWS = 128          # rows every expert's group is padded to ...
+TILE_ROWS_PAIR = 256     # ... or, once an expert gets 512 rows or more on average, this: the groups then run on
+                         # CTA pairs (256-row tcgen05 tiles), which more than pays for the extra padding
 
 
 class FusedMoE(nn.Module):
@@ -49,6 +51,7 @@ class FusedMoE(nn.Module):
         self.w2 = nn.Parameter(torch.empty(self.E, hidden, I, dtype=dtype, device=device), requires_grad=False)
         self._ws_tokens = 0
         self._ws = None
+        self.pair_tiles = True      # False: 128-row groups at every size (tests, comparisons)
 
     # ---- checkpoint loading (experts.{e}.w1/w2/w3 -> w13 / w2) ----
     def load_expert_weight(self, expert: int, which: str, loaded: torch.Tensor) -> None:
@@ -75,7 +78,7 @@ class FusedMoE(nn.Module):
     def _workspace(self, T: int, device):
         if self._ws is None or self._ws_tokens < T:
             n_pairs = T * self.top_k
-            max_rows = (n_pairs + self.E * (TILE_ROWS - 1) + TILE_ROWS - 1) // TILE_ROWS * TILE_ROWS
+            max_rows = (n_pairs + self.E * (TILE_ROWS_PAIR - 1) + TILE_ROWS_PAIR - 1) // TILE_ROWS_PAIR * TILE_ROWS_PAIR
             max_tiles = max_rows // TILE_ROWS
             i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=device)
             dt = self.w13.dtype
@@ -105,16 +108,18 @@ class FusedMoE(nn.Module):
             return out
         ws = self._workspace(T, x.device)
         E, I = self.E, self.inter_per_rank
-        n_rows = (T * self.top_k + E * (TILE_ROWS - 1) + TILE_ROWS - 1) // TILE_ROWS * TILE_ROWS
-        tile_expert = ws["tile_expert"][: n_rows // TILE_ROWS]
-        ops.moe_align(topk_ids, E, TILE_ROWS, ws["offsets"], ws["cursor"], tile_expert, ws["meta"])
+        tile_rows = TILE_ROWS_PAIR if T * self.top_k >= 512 * E and self.pair_tiles else TILE_ROWS
+        n_rows = (T * self.top_k + E * (tile_rows - 1) + tile_rows - 1) // tile_rows * tile_rows
+        tile_expert = ws["tile_expert"][: n_rows // tile_rows]
+        ops.moe_align(topk_ids, E, tile_rows, ws["offsets"], ws["cursor"], tile_expert, ws["meta"])
         sorted_pos = ws["sorted_pos"][:T]
         ops.moe_scatter(x, topk_ids, topk_w, ws["offsets"], ws["cursor"], ws["a_sorted"], ws["row_scale"],
                         sorted_pos, E)
         a = ws["a_sorted"][:n_rows]
         act = ops.gemm(a, self.w13.view(E * 2 * I, H), out=ws["act"][:n_rows], swiglu=True, tile_expert=tile_expert,
-                       num_m_tiles=ws["meta"][:1], n_per_expert=2 * I, max_ctas=max_ctas)
+                       num_m_tiles=ws["meta"][:1], n_per_expert=2 * I, max_ctas=max_ctas, tile_rows=tile_rows)
         y = ops.gemm(act, self.w2.view(E * H, I), out=ws["y"][:n_rows], row_scale=ws["row_scale"],
-                     tile_expert=tile_expert, num_m_tiles=ws["meta"][:1], n_per_expert=H, max_ctas=max_ctas)
+                     tile_expert=tile_expert, num_m_tiles=ws["meta"][:1], n_per_expert=H, max_ctas=max_ctas,
+                     tile_rows=tile_rows)
         ops.moe_combine(y, sorted_pos, out, self.top_k)
         return out

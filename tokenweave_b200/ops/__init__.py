@@ -84,10 +84,11 @@ def _row_stride(t: torch.Tensor) -> int:
 def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *,
          bias: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None, swiglu: bool = False,
          max_ctas: int = 0, tile_expert: Optional[torch.Tensor] = None,
-         num_m_tiles: Optional[torch.Tensor] = None, n_per_expert: int = 0) -> torch.Tensor:
+         num_m_tiles: Optional[torch.Tensor] = None, n_per_expert: int = 0, tile_rows: int = 128) -> torch.Tensor:
     """``out = a @ w.T`` (+bias, *row_scale); with ``swiglu`` the weight is ``[gate; up]`` and the
-    output is ``silu(a@gate.T) * (a@up.T)``. Grouped mode (``tile_expert`` given): every 128-row tile
-    of ``a`` multiplies the weight block of its expert, ``w`` being ``[E * n_per_expert, K]``."""
+    output is ``silu(a@gate.T) * (a@up.T)``. Grouped mode (``tile_expert`` given): every ``tile_rows``-row
+    tile of ``a`` multiplies the weight block of its expert, ``w`` being ``[E * n_per_expert, K]``;
+    ``tile_rows`` is 128 (single-CTA tiles) or 256 (experts padded to 256 rows: the groups run on CTA pairs)."""
     M, K = a.shape
     rows_b = w.shape[0]
     per_expert = n_per_expert if tile_expert is not None else rows_b
@@ -101,6 +102,15 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
         out.copy_(res)
         return out
     _check_bf16(a, w, out, bias)
+    if tile_expert is not None and tile_rows == 256:
+        if bias is not None:
+            raise ValueError("the grouped GEMM has no bias")
+        _native.call("tw_gemm_bf16_grouped256", a.data_ptr(), _row_stride(a), w.data_ptr(), _row_stride(w), rows_b,
+                     out.data_ptr(), _row_stride(out), _p(row_scale), M, N, K, int(swiglu),
+                     per_expert // 2 if swiglu else 0, _p(tile_expert), _p(num_m_tiles), per_expert, max_ctas,
+                     status_word(a.device).data_ptr(), _stream(),
+                     tag=f"[grouped {M}x{N}x{K}{'+swiglu' if swiglu else ''}]" if _native._timing is not None else "")
+        return out
     _native.call("tw_gemm_bf16", a.data_ptr(), _row_stride(a), w.data_ptr(), _row_stride(w), rows_b,
                  out.data_ptr(), _row_stride(out), _p(bias), _p(row_scale), M, N, K, int(swiglu),
                  per_expert // 2 if swiglu else 0, _p(tile_expert), _p(num_m_tiles), per_expert, max_ctas,

@@ -18,6 +18,7 @@ vp, ll, i32, f32, u64 = C.c_void_p, C.c_longlong, C.c_int, C.c_float, C.c_ulongl
 
 _SIGNATURES = {
     "tw_gemm_bf16": [vp, ll, vp, ll, ll, vp, ll, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp, vp],
+    "tw_gemm_bf16_grouped256": [vp, ll, vp, ll, ll, vp, ll, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp],
     "tw_rmsnorm": [vp, vp, vp, i32, i32, ll, ll, f32, i32, vp],
     "tw_rmsnorm_copy": [vp, vp, vp, i32, i32, ll, ll, f32, i32, vp],
     "tw_add_rmsnorm": [vp, vp, vp, i32, i32, ll, ll, f32, i32, vp],
