@@ -121,7 +121,9 @@ __device__ __forceinline__ void pair_tile_coords(int t, int num_m, int num_n, in
   n_tile = in_group / rows;
 }
 
-template <bool SWIGLU>
+// WIDE is a template argument: the one thread that issues the MMAs sets the pace of the main loop, and the
+// narrow kernel must not carry the wide one's extra instructions.
+template <bool SWIGLU, bool WIDE>
 __global__ void __launch_bounds__(G2_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const Gemm2Params p) {
@@ -132,9 +134,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int b_half_bytes = HALF_N * G2_BK * 2;
   const int stage_bytes = KBPS * (G2_A_BYTES + b_half_bytes);
   const int OUT_COLS = SWIGLU ? BN / 2 : BN;
-  const bool WIDE = BN > 256;                      // two MMAs of BN / 2 columns per k-step, one accumulator
+  // WIDE (BN > 256): two MMAs of BN / 2 columns per k-step, one accumulator
   const int MMA_N = WIDE ? BN / 2 : BN;
-  const int NUM_ACC = WIDE ? 1 : 2;
+  constexpr int NUM_ACC = WIDE ? 1 : 2;
   const uint32_t IDESC = make_idesc_bf16(2 * G2_BM, MMA_N, 0, 0);
 
   extern __shared__ uint8_t smem_raw[];
@@ -365,12 +367,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
-template <bool SWIGLU>
+template <bool SWIGLU, bool WIDE>
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p, int pairs,
                        cudaStream_t stream) {
   const int stage_bytes = p.kb_per_stage * (G2_A_BYTES + (p.bn / 2) * G2_BK * 2);
   const int smem = p.stages * stage_bytes + 256 + 1024;
-  auto kern = gemm_bf16_pair_kernel<SWIGLU>;
+  auto kern = gemm_bf16_pair_kernel<SWIGLU, WIDE>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -477,5 +479,6 @@ extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, lo
   p.status = status;
   int pairs = num_m * num_n;
   if (pairs > pairs_avail) pairs = pairs_avail;
-  return swiglu ? launch_pair<true>(tmA, tmB, p, pairs, stream) : launch_pair<false>(tmA, tmB, p, pairs, stream);
+  if (bn > 256) return launch_pair<false, true>(tmA, tmB, p, pairs, stream);
+  return swiglu ? launch_pair<true, false>(tmA, tmB, p, pairs, stream) : launch_pair<false, false>(tmA, tmB, p, pairs, stream);
 }
