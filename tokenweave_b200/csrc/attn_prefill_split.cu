@@ -20,7 +20,10 @@
 //     two-wide fp32 instructions and the three-input maximum of sm_100.
 // Tried and dropped: softmax steps of 64 keys with S double-buffered per group (Q K^T of the next step
 // then never waits for the softmax). An M = 128 MMA with N = 64 takes as long as one with N = 128, so
-// the Q K^T time doubled and the kernel was 40 % slower.
+// the Q K^T time doubled and the kernel was 40 % slower. Also dropped: every 2nd, 3rd or 4th pair of
+// exponentials as a cubic on the FMA pipe instead of ex2.approx (correct to 8e-5, but 17 to 25 % slower at
+// every share: the softmax warps are bound by issue slots, and the polynomial costs six times the
+// instructions of the MUFU form).
 // Replaces the FlashAttention-2 varlen call the reference makes on Blackwell
 // (vllm/v1/attention/backends/flash_attn.py:713-733, vllm/attention/utils/fa_utils.py:29-34).
 //

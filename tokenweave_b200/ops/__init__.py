@@ -509,8 +509,8 @@ _decode_ws: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 # Decode attention kernel: "tc" (attn_decode_tc.cu: tcgen05; used for grouped-query models with head size 128
 # once a sequence of the step has 256 keys, 1.4 to 1.8 times faster than the SIMT kernel on B200) or "simt"
 # (attn_decode.cu, every other case). TW_DECODE_TC=0 forces "simt". "tcp" is the persistent form of "tc"
-# (one CTA per SM walks the work items; TW_DECODE_TC=persistent): written and compiled, not yet run on a GPU,
-# so nothing selects it by default.
+# (one CTA per SM walks the work items; TW_DECODE_TC=persistent): as fast or faster only for short contexts and
+# models with 8 KV heads per GPU, so nothing selects it by default.
 def _env_decode_variant() -> str:
     v = os.environ.get("TW_DECODE_TC", "1")
     return "tcp" if v == "persistent" else "tc" if v == "1" else "simt"
