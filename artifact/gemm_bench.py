@@ -27,6 +27,9 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, nargs="+", default=[1024, 4096, 8192])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--fp8", action=argparse.BooleanOptionalAction, default=True)
+    ap.add_argument("--fp8-plans", type=int, nargs="*", default=[],
+                    help="also time tw_gemm_fp8 with these plans (kernel * 1000 + tile width; 1 = single-CTA tiles, "
+                         "2 = CTA pairs), one column each")
     ap.add_argument("--square", type=int, nargs="*", default=[8192], help="extra M=N=K problems")
     ap.add_argument("--out", default=os.path.join(RESULTS_DIR, "gemm_bench"))
     args = ap.parse_args()
@@ -70,6 +73,12 @@ def main() -> None:
             wq, w_s = ops.quant_fp8(w)
             f8 = time_us(lambda: ops.gemm_fp8(aq, wq, a_s, w_s, out=out, swiglu=bool(sw)), warmup=3, iters=args.iters)
             row.update(tw_fp8_us=round(f8, 1), tw_fp8_tflops=round(flops / f8 / 1e6, 1))
+            for plan in args.fp8_plans:
+                if sw and plan % 1000 > 256:
+                    continue                                  # the SwiGLU epilogue has no wide tiles
+                t = time_us(lambda: ops.gemm_fp8(aq, wq, a_s, w_s, out=out, swiglu=bool(sw), plan=plan), warmup=3,
+                            iters=args.iters)
+                row[f"tw_fp8_plan{plan}_us"] = round(t, 1)
             if not sw:
                 try:
                     wqt = wq.t()

@@ -415,12 +415,14 @@ def test_quant_fp8(T, H):
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 1280, 1024), (1000, 1000, 208), (4096, 7168, 1024),
                                    (77, 8, 512), (2048, 8192, 3584)])
-def test_gemm_fp8(M, N, K):
+# the library's choice / single-CTA tiles / CTA pairs, 256 and 128 columns wide / CTA pairs, wide tile
+@pytest.mark.parametrize("plan", [0, 1256, 2256, 2128, 2384])
+def test_gemm_fp8(M, N, K, plan):
     a, w = rnd(M, K), rnd(N, K, scale=1 / math.sqrt(K))
     aq, a_s = ops.quant_fp8(a)
     wq, w_s = ops.quant_fp8(w)
     bias = rnd(N)
-    out = ops.gemm_fp8(aq, wq, a_s, w_s, bias=bias)
+    out = ops.gemm_fp8(aq, wq, a_s, w_s, bias=bias, plan=plan)
     # exact products of the same quantised operands: only accumulation order and the final rounding differ
     close(out, ref.gemm_fp8(aq, wq, a_s, w_s, bias))
     # and the quantised result approximates the bf16 product
@@ -428,15 +430,16 @@ def test_gemm_fp8(M, N, K):
     assert (out.float() - full).abs().mean() < 0.05 * full.abs().mean() + 0.02
     # unscaled: sums of products of up to 448 * 448 that cancel; the absolute slack follows the magnitude
     raw = ref.gemm_fp8(aq, wq, None, None)
-    close(ops.gemm_fp8(aq, wq, None, None), raw, atol=1e-4 * raw.float().abs().max().item(), rtol=2e-2)
+    close(ops.gemm_fp8(aq, wq, None, None, plan=plan), raw, atol=1e-4 * raw.float().abs().max().item(), rtol=2e-2)
 
 
 @pytest.mark.parametrize("M,I,K", [(256, 512, 256), (1000, 3584, 1024), (4096, 3584, 8192)])
-def test_gemm_fp8_swiglu(M, I, K):
+@pytest.mark.parametrize("plan", [0, 1256, 2256, 2192])
+def test_gemm_fp8_swiglu(M, I, K, plan):
     a, w = rnd(M, K), rnd(2 * I, K, scale=1 / math.sqrt(K))
     aq, a_s = ops.quant_fp8(a)
     wq, w_s = ops.quant_fp8(w)
-    out = ops.gemm_fp8(aq, wq, a_s, w_s, swiglu=True)
+    out = ops.gemm_fp8(aq, wq, a_s, w_s, swiglu=True, plan=plan)
     assert out.shape == (M, I)
     close(out, ref.gemm_fp8(aq, wq, a_s, w_s, swiglu=True))
 

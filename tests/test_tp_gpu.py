@@ -54,6 +54,11 @@ def _rank(rank, world, path, prompts, mode, expect_path, transport):
             mode, extra = mode[:-3], dict(enable_expert_parallel=True)
         elif mode.endswith("+fp8"):
             mode, extra = mode[:-4], dict(quantization="fp8")
+        elif mode.endswith("+vpe"):
+            # embedding table sharded over the vocabulary: every rank gathers its own rows, zeros elsewhere, and
+            # the sum rides on the first layer's collective (or an all-reduce of its own in the baselines)
+            mode = mode[:-4]
+            os.environ["TW_EMBEDDING_PARALLEL"] = "1"
         if mode == "baseline_custom_ar":
             extra = dict(disable_custom_all_reduce=False)
         logits, llm = _generate(path, prompts, tensor_parallel_size=world,
@@ -97,7 +102,9 @@ def _rank(rank, world, path, prompts, mode, expect_path, transport):
                                                  ("tiny-mixtral", "fused_gemm", "multimem"),
                                                  ("tiny-mixtral", "overlap+ep", "multimem"),
                                                  ("tiny-llama-d128", "overlap+fp8", "multimem"),
-                                                 ("tiny-llama-d128", "baseline_custom_ar", "multimem")])
+                                                 ("tiny-llama-d128", "baseline_custom_ar", "multimem"),
+                                                 ("tiny-llama-d128", "overlap+vpe", "multimem"),
+                                                 ("tiny-llama-d128", "baseline_nccl+vpe", "p2p")])
 def test_tp2_matches_single_gpu(tmp_path, arch, mode, transport):
     _tp_matches_single_gpu(tmp_path, arch, mode, transport, 2)
 

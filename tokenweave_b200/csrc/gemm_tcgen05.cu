@@ -469,11 +469,11 @@ extern "C" int tw_gemm_set_kernel_override(int kind) {
   return 0;
 }
 
-extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
-                                 void* C, long long ldc, const void* bias, const float* row_scale, int M, int N,
-                                 int K, int swiglu, int up_row_offset, int bn, int max_ctas, const int* tile_expert,
-                                 const int* num_m_tiles_dev, int n_per_expert, uint32_t* status,
-                                 cudaStream_t stream);
+extern "C" int tw_gemm_pair(int fp8, const void* A, long long lda, const void* B, long long ldb, long long rows_b,
+                            void* C, long long ldc, const void* bias, const float* row_scale, const float* col_scale,
+                            int M, int N, int K, int swiglu, int up_row_offset, int bn, int max_ctas,
+                            const int* tile_expert, const int* num_m_tiles_dev, int n_per_expert, uint32_t* status,
+                            cudaStream_t stream);
 
 // Shared launcher body. A is [M,K] with row stride lda, B is [rows_b, K] with row stride ldb
 // (rows_b = N, 2*N for SwiGLU, or experts * n_per_expert); strides count elements (2 bytes, or 1 for fp8).
@@ -498,21 +498,21 @@ static int gemm_dispatch(bool fp8, const void* A, long long lda, const void* B, 
   int sms = device_sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
-  // the cost model sees k-blocks: an fp8 problem has K / 128 of them; CTA pairs are bf16-only
-  if (tile_expert != nullptr && group_tile_rows == 256 && !fp8 && sms >= 2)
-    return tw_gemm_bf16_pair(A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, M, N, K, swiglu, up_row_offset, 256, sms,
-                             tile_expert, num_m_tiles_dev, n_per_expert, status, stream);
-  GemmPlan plan = choose_plan(M, N, fp8 ? K / 2 : K, sms, swiglu != 0, tile_expert != nullptr || fp8);
+  if (tile_expert != nullptr && group_tile_rows == 256 && sms >= 2)
+    return tw_gemm_pair(fp8, A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, col_scale, M, N, K, swiglu,
+                        up_row_offset, 256, sms, tile_expert, num_m_tiles_dev, n_per_expert, status, stream);
+  // the cost model sees k-blocks: an fp8 problem has K / 128 of them
+  GemmPlan plan = choose_plan(M, N, fp8 ? K / 2 : K, sms, swiglu != 0, tile_expert != nullptr);
   if (plan_hint > 0) {
     const int kind = plan_hint / 1000, bn = plan_hint % 1000;
-    const bool pair_ok = !fp8 && kind == 2 && tile_expert == nullptr && sms >= 2 && bn % 64 == 0 &&
+    const bool pair_ok = kind == 2 && tile_expert == nullptr && sms >= 2 && bn % 64 == 0 &&
                          (bn <= 256 || (bn <= 512 && !swiglu));
     const bool single_ok = kind == 1 && bn % (swiglu ? 64 : 32) == 0 && bn <= 256;
     if (bn >= 64 && (pair_ok || single_ok)) plan = GemmPlan{pair_ok, bn};
   }
   if (plan.pair)
-    return tw_gemm_bf16_pair(A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, M, N, K, swiglu, up_row_offset, plan.bn,
-                             sms, nullptr, nullptr, 0, status, stream);
+    return tw_gemm_pair(fp8, A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, col_scale, M, N, K, swiglu, up_row_offset,
+                        plan.bn, sms, nullptr, nullptr, 0, status, stream);
   const int BN = plan.bn;
   const int out_cols = swiglu ? BN / 2 : BN;
   const int num_n = (N + out_cols - 1) / out_cols;

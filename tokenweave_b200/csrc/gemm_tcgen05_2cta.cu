@@ -8,11 +8,16 @@
 // No cluster-multicast copy is involved: every CTA issues ordinary tiled TMA loads into its own shared
 // memory; only the completion signal goes to the leader's mbarrier (cta_group::2 form of the copy).
 //
-// Roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only; both CTAs'
-// warp 1 take part in the paired TMEM allocation), warps 2..5 epilogue of the CTA's own 128 rows.
+// Roles per CTA (320 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only; both CTAs'
+// warp 1 take part in the paired TMEM allocation), warps 2..9 epilogue of the CTA's own 128 rows: two
+// warps per 32-row slice of tensor memory (warp w reads lanes 32 (w % 4) ..), one taking the even and one
+// the odd 32-column chunks of the tile, so that a tile with a short K loop (K = 1024: o_proj under 8-way
+// tensor parallelism) is not held up by its own write-back.
 // Barriers: full[s] lives in the leader and counts the bytes of both CTAs; empty[s] and acc_full[a]
 // exist in both CTAs and are signalled by the leader's tcgen05.commit (one commit per CTA);
 // acc_empty[a] lives in the leader and collects one arrival per epilogue warp of both CTAs.
+// FP8: operands are e4m3 bytes, a k-block is 128 elements (the same 128 bytes per row), the MMA is
+// kind::f8f6f4 (K = 32 per instruction) and the epilogue applies acc * row_scale[m] * col_scale[n] + bias[n].
 // Wide tiles (256 < BN <= 512, plain epilogue only): one accumulator of BN columns, two MMAs of BN / 2
 // columns per k-step. A skinny N (the QKV projection under 8-way tensor parallelism has N = 1280) then
 // fits one wave of 256 x 320 tiles where 256-wide tiles need two waves at half occupancy. Each CTA holds
@@ -29,7 +34,8 @@ namespace tw {
 
 constexpr int G2_BM = 128;          // rows per CTA (256 per pair)
 constexpr int G2_BK = 64;
-constexpr int G2_THREADS = 192;
+constexpr int G2_THREADS = 320;
+constexpr int G2_EPI_WARPS = 8;
 constexpr int G2_GROUP_M = 8;       // pair-tiles per rasterisation group
 constexpr int G2_MAX_STAGES = 8;
 constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;
@@ -41,6 +47,7 @@ struct Gemm2Params {
   long long ldc;
   const __nv_bfloat16* bias;
   const float* row_scale;
+  const float* col_scale;         // fp8 only: per-output-channel weight scale (may be null)
   int M, N, K;
   int num_m_tiles, num_n_tiles;   // in 256-row pair tiles
   // grouped mode (mixture of experts): pair tile m belongs to expert tile_expert[m], whose weights start
@@ -94,6 +101,17 @@ __device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t a_desc, u
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_ss_pair_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                ::"r"(bar_cluster_addr)
@@ -123,7 +141,7 @@ __device__ __forceinline__ void pair_tile_coords(int t, int num_m, int num_n, in
 
 // WIDE is a template argument: the one thread that issues the MMAs sets the pace of the main loop, and the
 // narrow kernel must not carry the wide one's extra instructions.
-template <bool SWIGLU, bool WIDE>
+template <bool SWIGLU, bool WIDE, bool FP8>
 __global__ void __launch_bounds__(G2_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const Gemm2Params p) {
@@ -137,7 +155,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   // WIDE (BN > 256): two MMAs of BN / 2 columns per k-step, one accumulator
   const int MMA_N = WIDE ? BN / 2 : BN;
   constexpr int NUM_ACC = WIDE ? 1 : 2;
-  const uint32_t IDESC = make_idesc_bf16(2 * G2_BM, MMA_N, 0, 0);
+  const uint32_t IDESC = FP8 ? make_idesc_e4m3(2 * G2_BM, MMA_N) : make_idesc_bf16(2 * G2_BM, MMA_N, 0, 0);
+  constexpr int BK_ELEMS = FP8 ? 2 * G2_BK : G2_BK;     // elements per k-block: 128 bytes of a row either way
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -161,7 +180,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 8);   // 4 epilogue warps of each CTA
+      mbar_init(&acc_empty[a], 2 * G2_EPI_WARPS);   // the epilogue warps of both CTAs
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -184,7 +203,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (p.num_m_tiles_dev != nullptr) num_m = min(num_m, *p.num_m_tiles_dev);
   const int num_n = p.num_n_tiles;
   const int total_tiles = num_m * num_n;
-  const int num_kb = ((p.K + G2_BK - 1) / G2_BK + KBPS - 1) / KBPS;   // pipeline iterations per tile
+  const int num_kb = ((p.K + BK_ELEMS - 1) / BK_ELEMS + KBPS - 1) / KBPS;   // pipeline iterations per tile
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
@@ -213,7 +232,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * stage_bytes);
           for (int s = 0; s < KBPS; ++s) {
             // a k-block past the end of K reads zeros (out-of-bounds fill) and adds nothing
-            const int kx = (kb * KBPS + s) * G2_BK;
+            const int kx = (kb * KBPS + s) * BK_ELEMS;
             tma_load_2d_pair(sa + s * G2_A_BYTES, &tmA, leader_full, kx, m0);
             if (WIDE) {
               // this CTA's quarter of the B rows of each of the two MMAs (the tensor map's box is BN / 4 rows)
@@ -255,11 +274,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const uint64_t b_desc = make_smem_desc_sw128(sb + s * b_half_bytes, 16, 1024);
 #pragma unroll
             for (int k = 0; k < G2_BK / 16; ++k) {
-              umma_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+              // 32 bytes further along K per instruction: +2 in the descriptor's 16-byte address units
+              if (FP8) umma_ss_pair_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+              else umma_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
               if (WIDE) {
                 // second half of the columns: the next BN / 4 rows of this CTA's B tile (and of the peer's)
                 const uint64_t b2 = make_smem_desc_sw128(sb + s * b_half_bytes + (BN / 4) * G2_BK * 2, 16, 1024);
-                umma_ss_pair(d_tmem + MMA_N, a_desc + 2 * k, b2 + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+                if (FP8) umma_ss_pair_f8(d_tmem + MMA_N, a_desc + 2 * k, b2 + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+                else umma_ss_pair(d_tmem + MMA_N, a_desc + 2 * k, b2 + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
               }
             }
           }
@@ -281,8 +303,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
-    const int q = warp & 3;
+    // ---------------- epilogue (warps 2..9 of both CTAs) ----------------
+    const int q = warp & 3;                  // this warp reads tensor-memory lanes 32 q .. 32 q + 31
+    const int par = (warp - 2) >> 2;         // warps 2..5: even 32-column chunks, warps 6..9: odd ones
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = pair; t < total_tiles && !*abort_flag; t += num_pairs) {
@@ -300,10 +323,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const float rs = (p.row_scale != nullptr && row < p.M) ? p.row_scale[row] : 1.f;
       __nv_bfloat16* crow = p.C + static_cast<long long>(row) * p.ldc + n0;
 #pragma unroll 1
-      for (int c = 0; c < OUT_COLS / 32; ++c) {
+      for (int c = par; c < OUT_COLS / 32; c += 2) {
         uint32_t v[32];
         uint32_t packed[16];
         tmem_ld_32x32(taddr + c * 32, v);
+        const int nc = n0 + c * 32;
         if (SWIGLU) {
           uint32_t u[32];
           tmem_ld_32x32(taddr + BN / 2 + c * 32, u);
@@ -312,16 +336,74 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           for (int j = 0; j < 16; ++j) {
             float g0 = __uint_as_float(v[2 * j]), g1 = __uint_as_float(v[2 * j + 1]);
             float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            if (FP8) {
+              // gate and up rows of the weight carry their own channel scales; the token scale (rs)
+              // de-quantises both, so it goes in before the non-linearity
+              const int n = min(nc + 2 * j, p.N - 2);
+              g0 *= rs;
+              g1 *= rs;
+              if (p.col_scale != nullptr) {
+                g0 *= p.col_scale[n];
+                g1 *= p.col_scale[n + 1];
+                u0 *= p.col_scale[p.up_row_offset + n];
+                u1 *= p.col_scale[p.up_row_offset + n + 1];
+              }
+            }
             packed[j] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0 * rs, g1 / (1.f + __expf(-g1)) * u1 * rs);
           }
+        } else if (FP8) {
+          tmem_wait_ld();
+          if (nc + 32 <= p.N && (p.N & 7) == 0) {
+            // whole chunk in range: channel scales and bias come in as 16-byte vectors (the same addresses
+            // for every thread of the warp, one transaction each)
+            if (p.col_scale != nullptr) {
+              const float4* cs4 = reinterpret_cast<const float4*>(p.col_scale + nc);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 sc = __ldg(cs4 + j);
+                v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) * (rs * sc.x));
+                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) * (rs * sc.y));
+                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) * (rs * sc.z));
+                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) * (rs * sc.w));
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * rs);
+            }
+            if (p.bias != nullptr) {
+              const uint4* b4 = reinterpret_cast<const uint4*>(p.bias + nc);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 bv = __ldg(b4 + j);
+                const uint32_t* bu = reinterpret_cast<const uint32_t*>(&bv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = unpack_bf16x2(bu[e]);
+                  v[8 * j + 2 * e] = __float_as_uint(__uint_as_float(v[8 * j + 2 * e]) + f.x);
+                  v[8 * j + 2 * e + 1] = __float_as_uint(__uint_as_float(v[8 * j + 2 * e + 1]) + f.y);
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int n = nc + j;
+              const float cs = (p.col_scale != nullptr && n < p.N) ? p.col_scale[n] : 1.f;
+              const float bb = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+              v[j] = __float_as_uint(__uint_as_float(v[j]) * rs * cs + bb);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            packed[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
         } else {
           tmem_wait_ld();
           if (p.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const int n = n0 + c * 32 + j;
-              const float b = (n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
-              v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
+              const int n = nc + j;
+              const float bb = (n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+              v[j] = __float_as_uint(__uint_as_float(v[j]) + bb);
             }
           }
 #pragma unroll
@@ -331,7 +413,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (row < p.M) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const int n = n0 + c * 32 + j * 8;
+            const int n = nc + j * 8;
             if (n + 8 <= p.N) {
               *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) =
                   make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
@@ -367,12 +449,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
-template <bool SWIGLU, bool WIDE>
+template <bool SWIGLU, bool WIDE, bool FP8>
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p, int pairs,
                        cudaStream_t stream) {
   const int stage_bytes = p.kb_per_stage * (G2_A_BYTES + (p.bn / 2) * G2_BK * 2);
   const int smem = p.stages * stage_bytes + 256 + 1024;
-  auto kern = gemm_bf16_pair_kernel<SWIGLU, WIDE>;
+  auto kern = gemm_bf16_pair_kernel<SWIGLU, WIDE, FP8>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -415,31 +497,35 @@ extern "C" int tw_gemm_set_pair_kbps(int kbps) {
   return 0;
 }
 
-// Same contract as tw_gemm_bf16. `bn` is the tile width (multiple of 64, <= 256, or up to 512 without SwiGLU),
-// `max_ctas` bounds the SMs used (rounded down to an even number). Grouped mode: tile_expert has one entry per
-// 256-row tile of A (the caller pads every expert to 256 rows).
-extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
-                                 void* C, long long ldc, const void* bias, const float* row_scale, int M, int N,
-                                 int K, int swiglu, int up_row_offset, int bn, int max_ctas, const int* tile_expert,
-                                 const int* num_m_tiles_dev, int n_per_expert, uint32_t* status,
-                                 cudaStream_t stream) {
+// Same contract as tw_gemm_bf16 / tw_gemm_fp8. `bn` is the tile width (multiple of 64, <= 256, or up to 512
+// without SwiGLU), `max_ctas` bounds the SMs used (rounded down to an even number). Grouped mode: tile_expert has
+// one entry per 256-row tile of A (the caller pads every expert to 256 rows). Strides count elements (2 bytes, or 1
+// for fp8).
+extern "C" int tw_gemm_pair(int fp8, const void* A, long long lda, const void* B, long long ldb, long long rows_b,
+                            void* C, long long ldc, const void* bias, const float* row_scale, const float* col_scale,
+                            int M, int N, int K, int swiglu, int up_row_offset, int bn, int max_ctas,
+                            const int* tile_expert, const int* num_m_tiles_dev, int n_per_expert, uint32_t* status,
+                            cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldc % 8) != 0 || bn % 64 != 0 || bn < 64 || bn > 512 ||
-      (bn > 256 && swiglu)) {
-    set_last_error("tw_gemm_bf16_pair: bad strides or tile width (K=%d, bn=%d)", K, bn);
+  const int in_align = fp8 ? 16 : 8;     // 16 bytes of operand elements
+  if ((K % in_align) != 0 || (lda % in_align) != 0 || (ldb % in_align) != 0 || (ldc % 8) != 0 || bn % 64 != 0 ||
+      bn < 64 || bn > 512 || (bn > 256 && swiglu)) {
+    set_last_error("tw_gemm_pair: bad strides or tile width (K=%d, bn=%d)", K, bn);
     return 1;
   }
   int sms = device_sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   int pairs_avail = sms / 2;
   if (pairs_avail < 1) {
-    set_last_error("tw_gemm_bf16_pair: needs at least 2 SMs");
+    set_last_error("tw_gemm_pair: needs at least 2 SMs");
     return 1;
   }
+  const int esz = fp8 ? 1 : 2;
+  const int bk_elems = fp8 ? 2 * G2_BK : G2_BK;
   const int num_m = (M + 2 * G2_BM - 1) / (2 * G2_BM);
   const int out_cols = swiglu ? bn / 2 : bn;
   const int num_n = (N + out_cols - 1) / out_cols;
-  int kbps = (g_pair_kbps == 2 && K >= 256) ? 2 : 1;
+  int kbps = (g_pair_kbps == 2 && K >= 4 * bk_elems) ? 2 : 1;
   // wide tiles: two k-blocks per stage only while three such stages fit (216 KB of pipeline at most)
   if (bn > 256 && (216 * 1024) / (2 * (G2_A_BYTES + (bn / 2) * G2_BK * 2)) < 3) kbps = 1;
   const int stage_bytes = kbps * (G2_A_BYTES + (bn / 2) * G2_BK * 2);
@@ -449,21 +535,24 @@ extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, lo
   CUtensorMap tmA, tmB;
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
-    uint64_t strides[1] = {(uint64_t)lda * 2};
-    uint32_t box[2] = {G2_BK, G2_BM};
-    if (!make_tensor_map_bf16(&tmA, A, 2, dims, strides, box)) return 1;
+    uint64_t strides[1] = {(uint64_t)lda * esz};
+    uint32_t box[2] = {(uint32_t)bk_elems, G2_BM};
+    if (!(fp8 ? make_tensor_map_u8(&tmA, A, 2, dims, strides, box) : make_tensor_map_bf16(&tmA, A, 2, dims, strides, box)))
+      return 1;
   }
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows_b};
-    uint64_t strides[1] = {(uint64_t)ldb * 2};
-    uint32_t box[2] = {G2_BK, (uint32_t)(bn > 256 ? bn / 4 : bn / 2)};     // wide tiles: two loads of a quarter each
-    if (!make_tensor_map_bf16(&tmB, B, 2, dims, strides, box)) return 1;
+    uint64_t strides[1] = {(uint64_t)ldb * esz};
+    uint32_t box[2] = {(uint32_t)bk_elems, (uint32_t)(bn > 256 ? bn / 4 : bn / 2)};   // wide tiles: two loads of a quarter each
+    if (!(fp8 ? make_tensor_map_u8(&tmB, B, 2, dims, strides, box) : make_tensor_map_bf16(&tmB, B, 2, dims, strides, box)))
+      return 1;
   }
   Gemm2Params p;
   p.C = reinterpret_cast<__nv_bfloat16*>(C);
   p.ldc = ldc;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.row_scale = row_scale;
+  p.col_scale = col_scale;
   p.M = M;
   p.N = N;
   p.K = K;
@@ -479,6 +568,21 @@ extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, lo
   p.status = status;
   int pairs = num_m * num_n;
   if (pairs > pairs_avail) pairs = pairs_avail;
-  if (bn > 256) return launch_pair<false, true>(tmA, tmB, p, pairs, stream);
-  return swiglu ? launch_pair<true, false>(tmA, tmB, p, pairs, stream) : launch_pair<false, false>(tmA, tmB, p, pairs, stream);
+  if (fp8) {
+    if (bn > 256) return launch_pair<false, true, true>(tmA, tmB, p, pairs, stream);
+    return swiglu ? launch_pair<true, false, true>(tmA, tmB, p, pairs, stream)
+                  : launch_pair<false, false, true>(tmA, tmB, p, pairs, stream);
+  }
+  if (bn > 256) return launch_pair<false, true, false>(tmA, tmB, p, pairs, stream);
+  return swiglu ? launch_pair<true, false, false>(tmA, tmB, p, pairs, stream)
+                : launch_pair<false, false, false>(tmA, tmB, p, pairs, stream);
+}
+
+extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, long long ldb, long long rows_b,
+                                 void* C, long long ldc, const void* bias, const float* row_scale, int M, int N,
+                                 int K, int swiglu, int up_row_offset, int bn, int max_ctas, const int* tile_expert,
+                                 const int* num_m_tiles_dev, int n_per_expert, uint32_t* status,
+                                 cudaStream_t stream) {
+  return tw_gemm_pair(0, A, lda, B, ldb, rows_b, C, ldc, bias, row_scale, nullptr, M, N, K, swiglu, up_row_offset, bn,
+                      max_ctas, tile_expert, num_m_tiles_dev, n_per_expert, status, stream);
 }

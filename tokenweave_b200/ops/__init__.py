@@ -168,10 +168,11 @@ def rmsnorm_quant_fp8(x: torch.Tensor, weight: torch.Tensor, eps: float, residua
 
 def gemm_fp8(a: torch.Tensor, w: torch.Tensor, a_scale: Optional[torch.Tensor], w_scale: Optional[torch.Tensor],
              out: Optional[torch.Tensor] = None, *, bias: Optional[torch.Tensor] = None, swiglu: bool = False,
-             max_ctas: int = 0) -> torch.Tensor:
+             max_ctas: int = 0, plan: int = 0) -> torch.Tensor:
     """``out[m, n] = (a @ w.T)[m, n] * a_scale[m] * w_scale[n] + bias[n]`` in bf16, ``a`` ``[M, K]`` and ``w``
     ``[N, K]`` being e4m3 (per-token and per-output-channel scales, fp32, either may be None). With
-    ``swiglu`` the weight is ``[gate; up]`` and the result ``silu(gate part) * (up part)``."""
+    ``swiglu`` the weight is ``[gate; up]`` and the result ``silu(gate part) * (up part)``. ``plan``: 0 = the
+    library's cost model, else kernel * 1000 + tile width (1 = single-CTA tiles, 2 = CTA pairs)."""
     M, K = a.shape
     rows_b = w.shape[0]
     N = rows_b // 2 if swiglu else rows_b
@@ -188,7 +189,7 @@ def gemm_fp8(a: torch.Tensor, w: torch.Tensor, a_scale: Optional[torch.Tensor], 
             raise ValueError("scales must be contiguous fp32 vectors of one value per row / output channel")
     _native.call("tw_gemm_fp8", a.data_ptr(), _row_stride(a), w.data_ptr(), _row_stride(w), rows_b, out.data_ptr(),
                  _row_stride(out), _p(bias), _p(a_scale), _p(w_scale), M, N, K, int(swiglu), N if swiglu else 0,
-                 None, None, rows_b, max_ctas, 0, status_word(a.device).data_ptr(), _stream(),
+                 None, None, rows_b, max_ctas, int(plan), status_word(a.device).data_ptr(), _stream(),
                  tag=f"[fp8 {M}x{N}x{K}{'+swiglu' if swiglu else ''}]" if _native._timing is not None else "")
     return out
 
