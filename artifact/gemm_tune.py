@@ -41,8 +41,12 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=8)
     ap.add_argument("--shapes", nargs="*", default=None,
                     help="restrict the run to these weight shapes, each as N,K,swiglu (e.g. 1280,8192,0)")
-    ap.add_argument("--out", default=os.path.join(ROOT, "tokenweave_b200", "gemm_configs", "NVIDIA_B200.json"))
+    ap.add_argument("--fp8", action="store_true", help="tune tw_gemm_fp8 (e4m3 operands) instead of the bf16 GEMM")
+    ap.add_argument("--out", default=None, help="default: tokenweave_b200/gemm_configs/NVIDIA_B200[_fp8].json")
     args = ap.parse_args()
+    if args.out is None:
+        args.out = os.path.join(ROOT, "tokenweave_b200", "gemm_configs",
+                                "NVIDIA_B200_fp8.json" if args.fp8 else "NVIDIA_B200.json")
     from tokenweave_b200 import ops
     from tokenweave_b200.config import resolve_model_config
     from tokenweave_b200.ops import _native
@@ -74,6 +78,8 @@ def main() -> None:
                 continue
             a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
             out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            if args.fp8:
+                (aq, a_s), (wq, w_s) = ops.quant_fp8(a), ops.quant_fp8(w)
             for sms in args.sm_budgets:
                 best = None
                 for kernel in (2, 1):
@@ -81,9 +87,14 @@ def main() -> None:
                     widths = (list(range(512, 63, -64)) if (kernel == 2 and not sw) else
                               range(256, 63, -64) if (kernel == 2 or sw) else range(256, 63, -32))
                     for bn in widths:
-                        lib.tw_gemm_set_kernel_override(kernel)
-                        lib.tw_gemm_set_tile_override(bn)
-                        us = time_us(lambda: ops.gemm(a, w, out=out, swiglu=bool(sw), max_ctas=sms), warmup=2, iters=args.iters)
+                        if args.fp8:
+                            us = time_us(lambda: ops.gemm_fp8(aq, wq, a_s, w_s, out=out, swiglu=bool(sw), max_ctas=sms,
+                                                              plan=kernel * 1000 + bn), warmup=2, iters=args.iters)
+                        else:
+                            lib.tw_gemm_set_kernel_override(kernel)
+                            lib.tw_gemm_set_tile_override(bn)
+                            us = time_us(lambda: ops.gemm(a, w, out=out, swiglu=bool(sw), max_ctas=sms), warmup=2,
+                                         iters=args.iters)
                         # candidates run widest first; a narrower tile must win by 2 % to replace it
                         if best is None or us < best[2] * 0.98:
                             best = (kernel, bn, us)

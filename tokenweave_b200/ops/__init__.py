@@ -189,7 +189,8 @@ def gemm_fp8(a: torch.Tensor, w: torch.Tensor, a_scale: Optional[torch.Tensor], 
             raise ValueError("scales must be contiguous fp32 vectors of one value per row / output channel")
     _native.call("tw_gemm_fp8", a.data_ptr(), _row_stride(a), w.data_ptr(), _row_stride(w), rows_b, out.data_ptr(),
                  _row_stride(out), _p(bias), _p(a_scale), _p(w_scale), M, N, K, int(swiglu), N if swiglu else 0,
-                 None, None, rows_b, max_ctas, int(plan), status_word(a.device).data_ptr(), _stream(),
+                 None, None, rows_b, max_ctas, int(plan) or gemm_table.lookup(M, N, K, swiglu, max_ctas, fp8=True),
+                 status_word(a.device).data_ptr(), _stream(),
                  tag=f"[fp8 {M}x{N}x{K}{'+swiglu' if swiglu else ''}]" if _native._timing is not None else "")
     return out
 

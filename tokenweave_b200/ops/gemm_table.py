@@ -4,7 +4,8 @@ problem shape. The analogue of the reference's per-device tuned config files for
 fused_moe.py:625-674).
 
 ``gemm_configs/<device>.json`` holds ``{"<N>,<K>,<swiglu>": [[M, sms, kernel, bn, microseconds], ...]}``
-written by ``artifact/gemm_tune.py``. A lookup takes the entry with the nearest M (on a log scale)
+written by ``artifact/gemm_tune.py`` (``NVIDIA_B200.json`` for bf16 operands, ``NVIDIA_B200_fp8.json`` for e4m3
+operands). A lookup takes the entry with the nearest M (on a log scale)
 among those measured with the nearest SM budget; shapes that were never tuned fall back to the cost
 model inside the launcher (plan hint 0).
 """
@@ -30,13 +31,14 @@ def _load() -> dict:
         if forced in ("1", "2"):
             from . import _native
             _native.load().tw_gemm_set_kernel_override(int(forced))
-        path = CONFIG_DIR / "NVIDIA_B200.json"
-        if path.exists() and not _disabled:
-            with open(path) as f:
-                raw = json.load(f)
-            for key, rows in raw.items():
-                n, k, sw = key.split(",")
-                _table[(int(n), int(k), int(sw))] = [tuple(r[:4]) for r in rows]
+        for fp8, name in ((0, "NVIDIA_B200.json"), (1, "NVIDIA_B200_fp8.json")):
+            path = CONFIG_DIR / name
+            if path.exists() and not _disabled:
+                with open(path) as f:
+                    raw = json.load(f)
+                for key, rows in raw.items():
+                    n, k, sw = key.split(",")
+                    _table[(int(n), int(k), int(sw), fp8)] = [tuple(r[:4]) for r in rows]
     return _table
 
 
@@ -54,9 +56,9 @@ def set_enabled(on: bool) -> None:
 
 
 @lru_cache(maxsize=4096)
-def lookup(M: int, N: int, K: int, swiglu: bool, max_ctas: int = 0) -> int:
+def lookup(M: int, N: int, K: int, swiglu: bool, max_ctas: int = 0, fp8: bool = False) -> int:
     """Plan hint for the launcher: ``kernel * 1000 + bn`` or 0 (let the cost model decide)."""
-    rows = _load().get((N, K, int(bool(swiglu))))
+    rows = _load().get((N, K, int(bool(swiglu)), int(bool(fp8))))
     if not rows:
         return 0
     sms = max_ctas if max_ctas > 0 else 148
