@@ -22,7 +22,8 @@ import torch  # noqa: E402
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["gemm", "gemm_swiglu", "gemm_fp8", "rmsnorm_quant_fp8", "attn_prefill", "attn_decode", "add_rmsnorm", "rope_kv",
-                                     "moe_router", "fused_local", "sample"])
+                                     "moe_router", "moe_layer", "fused_local", "gemm_rs_norm_local", "ag_gemm_local",
+                                     "sample"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=4096)
@@ -128,6 +129,52 @@ def main() -> None:
         g = (torch.randn(8, H, device=dev) / math.sqrt(H)).to(BF)
         fn = lambda: ops.moe_router(x, g, 2)
         bytes_moved = T * H * 2
+    elif args.case == "moe_layer":
+        # one Mixtral-8x22B MoE layer as a GPU of an 8-way tensor-parallel group sees it: 8 experts, top-2,
+        # hidden 6144, 2048 intermediate columns per expert; router, align, scatter, two grouped GEMMs, combine
+        from tokenweave_b200.layers.moe import FusedMoE
+        from tokenweave_b200.parallel.state import set_single_process
+        set_single_process(torch.device(dev))
+        T, H, I, E = args.tokens, 6144, 2048, 8
+        moe = FusedMoE(E, 2, H, I, dtype=BF, device=dev)
+        moe.gate.data.copy_(torch.randn(E, H, device=dev) / math.sqrt(H))
+        moe.w13.data.copy_(torch.randn(E, 2 * I, H, device=dev) / math.sqrt(H))
+        moe.w2.data.copy_(torch.randn(E, H, I, device=dev) / math.sqrt(I))
+        x = torch.randn(T, H, device=dev).to(BF)
+        out = torch.empty_like(x)
+        fn = lambda: moe(x, out=out)
+        flops = 2 * (2 * T) * H * (3 * I)
+    elif args.case in ("gemm_rs_norm_local", "ag_gemm_local"):
+        # the GEMM fused with its collective on one GPU acting as a world of one (peer transport): the GEMM CTAs
+        # and the communication CTAs run as on several GPUs, the "peers" are this GPU's own buffer
+        from tokenweave_b200.ops import _native
+        T, H, K = args.m, args.hidden, args.k
+        flags = torch.zeros(1024, dtype=torch.int32, device=dev)
+        flagp = torch.tensor([flags.data_ptr()], dtype=torch.int64, device=dev)
+        w_norm = torch.ones(H, device=dev, dtype=BF)
+        stream = torch.cuda.current_stream().cuda_stream
+        if args.case == "gemm_rs_norm_local":      # o_proj / down_proj: [T, K] x [H, K]^T -> reduce-scatter -> norm
+            a = torch.randn(T, K, device=dev).to(BF)
+            w = (torch.randn(H, K, device=dev) / math.sqrt(K)).to(BF)
+            rows, res = torch.zeros(T, H, device=dev, dtype=BF), torch.randn(T, H, device=dev).to(BF)
+            bases = torch.tensor([rows.data_ptr()], dtype=torch.int64, device=dev)
+            fn = lambda: _native.call("tw_gemm_rs_norm", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), T, H, K,
+                                      None, rows.data_ptr(), None, bases.data_ptr(), flagp.data_ptr(), 0, 1, 10 ** 9,
+                                      ops.status_word().data_ptr(), 0, T, res.data_ptr(), res.stride(0),
+                                      w_norm.data_ptr(), 1e-5, 16, 0, stream)
+            flops = 2 * T * H * K
+        else:                                      # qkv_proj / gate_up_proj: all-gather -> [T, H] x [N, H]^T
+            N = args.n
+            rows = torch.randn(T, H, device=dev).to(BF)
+            w = (torch.randn(N, H, device=dev) / math.sqrt(H)).to(BF)
+            c = torch.empty(T, N, device=dev, dtype=BF)
+            bases = torch.tensor([rows.data_ptr()], dtype=torch.int64, device=dev)
+            epoch = torch.zeros(2, dtype=torch.int32, device=dev)
+            fn = lambda: _native.call("tw_ag_gemm", rows.data_ptr(), w.data_ptr(), w.stride(0), N, c.data_ptr(),
+                                      c.stride(0), None, T, N, H, 0, 0, None, bases.data_ptr(), flagp.data_ptr(),
+                                      epoch.data_ptr(), 0, 1, 10 ** 9, ops.status_word().data_ptr(), 0, T, 16, 0,
+                                      stream)
+            flops = 2 * T * N * H
     else:   # fused_local: the fused collective kernel on one GPU acting as a world of one (peer transport)
         from tokenweave_b200.ops import _native
         T, H = args.tokens, args.hidden

@@ -14,8 +14,8 @@
 //               page and 64-column half, straight from the paged cache through the block table
 //   warp 1      MMA issuer; S^T double-buffered in TMEM (2 x 16 columns), O^T in 16 more
 //   warps 2..5  softmax: thread r owns KEY r of the tile (TMEM lane r of S^T: 16 scores, one per
-//               head). The per-head maximum over the tile's keys is a warp reduction plus a
-//               four-way exchange through shared memory; P goes to shared memory as bf16 in the
+//               head). The per-head maximum over the tile's keys is a warp reduction (one
+//               redux.sync.max.f32 per head) plus a four-way exchange through shared memory; P goes to shared memory as bf16 in the
 //               swizzled K-major operand layout (row = head, column = key). In the epilogue the
 //               same thread owns output column d = r (TMEM lane r of O^T).
 // O is rescaled lazily (only when a head's running maximum grew by more than 2^8), as in the prefill
@@ -261,7 +261,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
 #pragma unroll
       for (int g = 0; g < DTC_NH; ++g) {
         s[g] = valid ? __uint_as_float(sv[g]) * p.scale_log2 : -INFINITY;
-        mx[g] = (g < G) ? warp_max(s[g]) : 0.f;
+        mx[g] = (g < G) ? warp_max_redux(s[g]) : 0.f;
       }
       float* xm = xchg + sb * 64;
       if (lane == 0) {
@@ -639,7 +639,7 @@ attn_decode_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmK, const 
 #pragma unroll
         for (int g = 0; g < DTC_NH; ++g) {
           s[g] = valid ? __uint_as_float(sv[g]) * p.scale_log2 : -INFINITY;
-          mx[g] = (g < G) ? warp_max(s[g]) : 0.f;
+          mx[g] = (g < G) ? warp_max_redux(s[g]) : 0.f;
         }
         float* xm = xchg + sb * 64;
         if (lane == 0) {
