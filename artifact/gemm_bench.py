@@ -88,6 +88,18 @@ def main() -> None:
                     row.update(cublaslt_fp8_us=round(lt, 1))
                 except Exception as e:  # library refuses the shape / scaling mode
                     row.update(cublaslt_fp8_us=f"n/a ({type(e).__name__})")
+                # int8 operands, int32 accumulation: tw_gemm_int8 (scales applied in the epilogue, bf16 out) against
+                # the library's plain int8 GEMM (int32 out, no scaling pass counted)
+                ai, ai_s = ops.quant_int8(a)
+                wi, wi_s = ops.quant_int8(w)
+                i8 = time_us(lambda: ops.gemm_int8(ai, wi, ai_s, wi_s, out=out), warmup=3, iters=args.iters)
+                row.update(tw_int8_us=round(i8, 1), tw_int8_tops=round(flops / i8 / 1e6, 1))
+                try:
+                    wit = wi.t()
+                    lt8 = time_us(lambda: torch._int_mm(ai, wit), warmup=3, iters=args.iters)
+                    row.update(cublaslt_int8_us=round(lt8, 1))
+                except Exception as e:
+                    row.update(cublaslt_int8_us=f"n/a ({type(e).__name__})")
         rows.append(row)
         print(" ".join(f"{k}={v}" for k, v in row.items() if k != "peak_source"), flush=True)
         del a, w, out

@@ -1,4 +1,4 @@
-"""quantization="fp8" on the GPU: the decoder linears run the e4m3 tcgen05 GEMM on per-token quantised
+"""quantization="fp8" / "int8" on the GPU: the decoder linears run the 8-bit tcgen05 GEMMs on per-token quantised
 activations; the logits must track the bf16 model's."""
 import pytest
 import torch
@@ -24,10 +24,11 @@ def _first_logits(quant):
     return logits, weights, toks
 
 
-def test_fp8_model_tracks_bf16_model():
+@pytest.mark.parametrize("quant,dtype", [("fp8", torch.float8_e4m3fn), ("int8", torch.int8)])
+def test_fp8_model_tracks_bf16_model(quant, dtype):
     ref, w_ref, _ = _first_logits(None)
-    q, w_q, toks = _first_logits("fp8")
-    assert w_ref == {torch.bfloat16} and w_q == {torch.float8_e4m3fn}
+    q, w_q, toks = _first_logits(quant)
+    assert w_ref == {torch.bfloat16} and w_q == {dtype}
     cos = torch.nn.functional.cosine_similarity(ref, q, dim=-1)
     assert cos.min() > 0.97, cos
     assert all(len(t) == 4 for t in toks)

@@ -191,25 +191,26 @@ def test_preemption_recompute_keeps_outputs():
 
 
 def test_fp8_quantised_model_tracks_the_full_precision_model():
-    """quantization="fp8": every decoder linear runs on e4m3 weights (per-channel scales) and per-token
+    """quantization="fp8" / "int8": every decoder linear runs on 8-bit weights (per-channel scales) and per-token
     quantised activations; logits stay close to the unquantised model's and greedy tokens mostly agree."""
     from tokenweave_b200.layers.linear import _QuantizableLinear
     prompts = _prompts(MODEL_PRESETS["tiny-llama"]["vocab_size"], [48, 9])
     logits = {}
-    for quant in (None, "fp8"):
+    for quant in (None, "fp8", "int8"):
         llm = _engine("tiny-llama", quantization=quant, seed=3)
         r = _runner(llm)
         r.capture_logits = True
         llm.generate(prompts, SamplingParams(temperature=0, max_tokens=1))
         logits[quant] = torch.cat([lg for _, lg in r.captured_logits]).float()
         n_q = sum(1 for m in r.model.modules() if isinstance(m, _QuantizableLinear) and m.weight_scale is not None)
-        assert (n_q > 0) == (quant == "fp8")
-        if quant == "fp8":
-            assert all(m.weight.dtype == torch.float8_e4m3fn for m in r.model.modules()
+        assert (n_q > 0) == (quant is not None)
+        if quant is not None:
+            want = torch.float8_e4m3fn if quant == "fp8" else torch.int8
+            assert all(m.weight.dtype == want for m in r.model.modules()
                        if isinstance(m, _QuantizableLinear) and m.weight_scale is not None)
-    a, b = logits[None], logits["fp8"]
-    cos = torch.nn.functional.cosine_similarity(a, b, dim=-1)
-    assert cos.min() > 0.98, cos
+    for quant in ("fp8", "int8"):
+        cos = torch.nn.functional.cosine_similarity(logits[None], logits[quant], dim=-1)
+        assert cos.min() > 0.98, (quant, cos)
     with pytest.raises(ValueError):
         _engine("tiny-llama", quantization="int3")
 

@@ -444,6 +444,36 @@ def test_gemm_fp8_swiglu(M, I, K, plan):
     close(out, ref.gemm_fp8(aq, wq, a_s, w_s, swiglu=True))
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 1280, 1024), (1000, 1000, 208), (4096, 7168, 1024),
+                                   (77, 8, 512), (2048, 8192, 3584)])
+@pytest.mark.parametrize("plan", [0, 2256, 2128, 2384])
+def test_gemm_int8(M, N, K, plan):
+    """int8 operands on the tensor cores (32-bit integer accumulation): exact against the integer product."""
+    a, w = rnd(M, K), rnd(N, K, scale=1 / math.sqrt(K))
+    aq, a_s = ops.quant_int8(a)
+    wq, w_s = ops.quant_int8(w)
+    bias = rnd(N)
+    out = ops.gemm_int8(aq, wq, a_s, w_s, bias=bias, plan=plan)
+    close(out, ref.gemm_int8(aq, wq, a_s, w_s, bias))
+    full = ref.gemm(a, w).float() + bias.float()
+    assert (out.float() - full).abs().mean() < 0.03 * full.abs().mean() + 0.02
+    # unscaled: the integer sums themselves, exact up to the final rounding to bf16
+    raw = ref.gemm_int8(aq, wq, None, None)
+    got = ops.gemm_int8(aq, wq, None, None, plan=plan)
+    assert torch.equal(got, raw)
+
+
+@pytest.mark.parametrize("M,I,K", [(256, 512, 256), (1000, 3584, 1024)])
+@pytest.mark.parametrize("plan", [0, 2256, 2192])
+def test_gemm_int8_swiglu(M, I, K, plan):
+    a, w = rnd(M, K), rnd(2 * I, K, scale=1 / math.sqrt(K))
+    aq, a_s = ops.quant_int8(a)
+    wq, w_s = ops.quant_int8(w)
+    out = ops.gemm_int8(aq, wq, a_s, w_s, swiglu=True, plan=plan)
+    assert out.shape == (M, I)
+    close(out, ref.gemm_int8(aq, wq, a_s, w_s, swiglu=True))
+
+
 @pytest.mark.parametrize("T,H", [(7, 64), (300, 8192), (33, 5120)])
 def test_int8_quant_and_fused_norm(T, H):
     x = rnd(T, H, scale=3.0)

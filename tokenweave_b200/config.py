@@ -279,7 +279,7 @@ class EngineConfig:
     scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
     tokenweave: TokenWeaveConfig = field(default_factory=TokenWeaveConfig)
     load_format: str = "auto"             # "auto" | "dummy" | "safetensors" | "sharded_state"
-    quantization: Optional[str] = None    # None | "fp8" (e4m3 weights per channel, dynamic per-token activations)
+    quantization: Optional[str] = None    # None | "fp8" | "int8" (8-bit weights per channel, dynamic per-token activations)
     seed: int = 0
     device: str = "auto"                  # "auto" | "cuda" | "cpu"
     enforce_eager: bool = True
@@ -364,8 +364,8 @@ class EngineArgs:
         budget = self.max_num_batched_tokens or (8192 if self.enable_chunked_prefill else max(max_len, 8192))
         if self.quantization is None and model.checkpoint_quantization is not None:
             self.quantization = model.checkpoint_quantization        # an fp8 checkpoint runs on the fp8 GEMMs
-        if self.quantization not in (None, "fp8"):
-            raise ValueError(f"unknown quantization {self.quantization!r} (supported: fp8)")
+        if self.quantization not in (None, "fp8", "int8"):
+            raise ValueError(f"unknown quantization {self.quantization!r} (supported: fp8, int8)")
         if self.quantization and self.tokenweave_mode == "fused_gemm":
             raise ValueError("the fused GEMM+collective kernels take bf16 weights: use tokenweave_mode "
                              "overlap or fuse_only with quantization")

@@ -604,3 +604,24 @@ extern "C" int tw_gemm_fp8(const void* A, long long lda, const void* B, long lon
                        up_row_offset, tile_expert, num_m_tiles_dev, n_per_expert, max_ctas, plan_hint, status,
                        stream);
 }
+
+// int8 x int8 -> bf16 with 32-bit integer accumulation: C = (A * B^T) * row_scale[m] * col_scale[n] + bias[n]
+// (symmetric quantisation; scales fp32, either may be null). Runs on CTA pairs (tcgen05 kind::i8). The counterpart
+// of the reference's CUTLASS int8 scaled-mm (csrc/quantization/cutlass_w8a8/scaled_mm_entry.cu, symmetric case).
+// With `swiglu` B is [gate; up] (2 N rows, the up rows `N` further down) and C = silu(gate part) * (up part).
+extern "C" int tw_gemm_int8(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc,
+                            const void* bias, const float* row_scale, const float* col_scale, int M, int N, int K,
+                            int swiglu, int max_ctas, int plan_hint, uint32_t* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  int sms = device_sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  int bn = 0;
+  if (plan_hint / 1000 == 2) bn = plan_hint % 1000;
+  if (bn > 256 && swiglu) bn = 256;
+  if (bn == 0) {
+    const GemmPlan plan = choose_plan(M, N, K / 2, sms, swiglu != 0, false);
+    bn = plan.pair ? plan.bn : (N > 128 || swiglu ? 256 : 128);
+  }
+  return tw_gemm_pair(2, A, lda, B, ldb, swiglu ? 2LL * N : N, C, ldc, bias, row_scale, col_scale, M, N, K, swiglu,
+                      swiglu ? N : 0, bn, sms, nullptr, nullptr, 0, status, stream);
+}

@@ -18,6 +18,8 @@
 // acc_empty[a] lives in the leader and collects one arrival per epilogue warp of both CTAs.
 // FP8: operands are e4m3 bytes, a k-block is 128 elements (the same 128 bytes per row), the MMA is
 // kind::f8f6f4 (K = 32 per instruction) and the epilogue applies acc * row_scale[m] * col_scale[n] + bias[n].
+// INT8 (KIND 2): the same with signed 8-bit operands, kind::i8 and 32-bit integer accumulators that the epilogue
+// converts to fp32 before scaling (the reference's CUTLASS int8 scaled-mm, csrc/quantization/cutlass_w8a8/).
 // Wide tiles (256 < BN <= 512, plain epilogue only): one accumulator of BN columns, two MMAs of BN / 2
 // columns per k-step. A skinny N (the QKV projection under 8-way tensor parallelism has N = 1280) then
 // fits one wave of 256 x 320 tiles where 256-wide tiles need two waves at half occupancy. Each CTA holds
@@ -112,6 +114,31 @@ __device__ __forceinline__ void umma_ss_pair_f8(uint32_t d_tmem, uint64_t a_desc
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_ss_pair_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptor for kind::i8: signed 8-bit A and B (format 1), 32-bit integer accumulator (format 2),
+// both operands K-major.
+__host__ __device__ constexpr uint32_t make_idesc_s8(int m, int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+constexpr int KIND_BF16 = 0, KIND_E4M3 = 1, KIND_S8 = 2;
+template <int KIND>
+__device__ __forceinline__ void umma_pair_kind(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  if (KIND == KIND_E4M3) umma_ss_pair_f8(d_tmem, a_desc, b_desc, idesc, accumulate);
+  else if (KIND == KIND_S8) umma_ss_pair_i8(d_tmem, a_desc, b_desc, idesc, accumulate);
+  else umma_ss_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                ::"r"(bar_cluster_addr)
@@ -141,7 +168,7 @@ __device__ __forceinline__ void pair_tile_coords(int t, int num_m, int num_n, in
 
 // WIDE is a template argument: the one thread that issues the MMAs sets the pace of the main loop, and the
 // narrow kernel must not carry the wide one's extra instructions.
-template <bool SWIGLU, bool WIDE, bool FP8>
+template <bool SWIGLU, bool WIDE, int KIND>
 __global__ void __launch_bounds__(G2_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const Gemm2Params p) {
@@ -155,7 +182,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   // WIDE (BN > 256): two MMAs of BN / 2 columns per k-step, one accumulator
   const int MMA_N = WIDE ? BN / 2 : BN;
   constexpr int NUM_ACC = WIDE ? 1 : 2;
-  const uint32_t IDESC = FP8 ? make_idesc_e4m3(2 * G2_BM, MMA_N) : make_idesc_bf16(2 * G2_BM, MMA_N, 0, 0);
+  constexpr bool FP8 = KIND != KIND_BF16;            // 8-bit operands (e4m3 or int8): scales in the epilogue
+  const uint32_t IDESC = KIND == KIND_E4M3 ? make_idesc_e4m3(2 * G2_BM, MMA_N)
+                         : KIND == KIND_S8 ? make_idesc_s8(2 * G2_BM, MMA_N)
+                                           : make_idesc_bf16(2 * G2_BM, MMA_N, 0, 0);
   constexpr int BK_ELEMS = FP8 ? 2 * G2_BK : G2_BK;     // elements per k-block: 128 bytes of a row either way
 
   extern __shared__ uint8_t smem_raw[];
@@ -275,13 +305,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll
             for (int k = 0; k < G2_BK / 16; ++k) {
               // 32 bytes further along K per instruction: +2 in the descriptor's 16-byte address units
-              if (FP8) umma_ss_pair_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
-              else umma_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+              umma_pair_kind<KIND>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
               if (WIDE) {
                 // second half of the columns: the next BN / 4 rows of this CTA's B tile (and of the peer's)
                 const uint64_t b2 = make_smem_desc_sw128(sb + s * b_half_bytes + (BN / 4) * G2_BK * 2, 16, 1024);
-                if (FP8) umma_ss_pair_f8(d_tmem + MMA_N, a_desc + 2 * k, b2 + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
-                else umma_ss_pair(d_tmem + MMA_N, a_desc + 2 * k, b2 + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
+                umma_pair_kind<KIND>(d_tmem + MMA_N, a_desc + 2 * k, b2 + 2 * k, IDESC, (kb | s | k) != 0 ? 1u : 0u);
               }
             }
           }
@@ -334,8 +362,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            float g0 = __uint_as_float(v[2 * j]), g1 = __uint_as_float(v[2 * j + 1]);
-            float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            float g0, g1, u0, u1;
+            if (KIND == KIND_S8) {
+              g0 = __int2float_rn(static_cast<int>(v[2 * j])), g1 = __int2float_rn(static_cast<int>(v[2 * j + 1]));
+              u0 = __int2float_rn(static_cast<int>(u[2 * j])), u1 = __int2float_rn(static_cast<int>(u[2 * j + 1]));
+            } else {
+              g0 = __uint_as_float(v[2 * j]), g1 = __uint_as_float(v[2 * j + 1]);
+              u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            }
             if (FP8) {
               // gate and up rows of the weight carry their own channel scales; the token scale (rs)
               // de-quantises both, so it goes in before the non-linearity
@@ -353,6 +387,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
         } else if (FP8) {
           tmem_wait_ld();
+          if (KIND == KIND_S8) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__int2float_rn(static_cast<int>(v[j])));
+          }
           if (nc + 32 <= p.N && (p.N & 7) == 0) {
             // whole chunk in range: channel scales and bias come in as 16-byte vectors (the same addresses
             // for every thread of the warp, one transaction each)
@@ -449,12 +487,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
-template <bool SWIGLU, bool WIDE, bool FP8>
+template <bool SWIGLU, bool WIDE, int KIND>
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p, int pairs,
                        cudaStream_t stream) {
   const int stage_bytes = p.kb_per_stage * (G2_A_BYTES + (p.bn / 2) * G2_BK * 2);
   const int smem = p.stages * stage_bytes + 256 + 1024;
-  auto kern = gemm_bf16_pair_kernel<SWIGLU, WIDE, FP8>;
+  auto kern = gemm_bf16_pair_kernel<SWIGLU, WIDE, KIND>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -497,7 +535,8 @@ extern "C" int tw_gemm_set_pair_kbps(int kbps) {
   return 0;
 }
 
-// Same contract as tw_gemm_bf16 / tw_gemm_fp8. `bn` is the tile width (multiple of 64, <= 256, or up to 512
+// Same contract as tw_gemm_bf16 / tw_gemm_fp8 (`fp8`: 0 bf16 operands, 1 e4m3, 2 signed int8; the 8-bit kinds take
+// row and column scales). `bn` is the tile width (multiple of 64, <= 256, or up to 512
 // without SwiGLU), `max_ctas` bounds the SMs used (rounded down to an even number). Grouped mode: tile_expert has
 // one entry per 256-row tile of A (the caller pads every expert to 256 rows). Strides count elements (2 bytes, or 1
 // for fp8).
@@ -509,7 +548,7 @@ extern "C" int tw_gemm_pair(int fp8, const void* A, long long lda, const void* B
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int in_align = fp8 ? 16 : 8;     // 16 bytes of operand elements
   if ((K % in_align) != 0 || (lda % in_align) != 0 || (ldb % in_align) != 0 || (ldc % 8) != 0 || bn % 64 != 0 ||
-      bn < 64 || bn > 512 || (bn > 256 && swiglu)) {
+      bn < 64 || bn > 512 || (bn > 256 && swiglu) || fp8 < 0 || fp8 > 2) {
     set_last_error("tw_gemm_pair: bad strides or tile width (K=%d, bn=%d)", K, bn);
     return 1;
   }
@@ -568,14 +607,19 @@ extern "C" int tw_gemm_pair(int fp8, const void* A, long long lda, const void* B
   p.status = status;
   int pairs = num_m * num_n;
   if (pairs > pairs_avail) pairs = pairs_avail;
-  if (fp8) {
-    if (bn > 256) return launch_pair<false, true, true>(tmA, tmB, p, pairs, stream);
-    return swiglu ? launch_pair<true, false, true>(tmA, tmB, p, pairs, stream)
-                  : launch_pair<false, false, true>(tmA, tmB, p, pairs, stream);
+  if (fp8 == 2) {
+    if (bn > 256) return launch_pair<false, true, KIND_S8>(tmA, tmB, p, pairs, stream);
+    return swiglu ? launch_pair<true, false, KIND_S8>(tmA, tmB, p, pairs, stream)
+                  : launch_pair<false, false, KIND_S8>(tmA, tmB, p, pairs, stream);
   }
-  if (bn > 256) return launch_pair<false, true, false>(tmA, tmB, p, pairs, stream);
-  return swiglu ? launch_pair<true, false, false>(tmA, tmB, p, pairs, stream)
-                : launch_pair<false, false, false>(tmA, tmB, p, pairs, stream);
+  if (fp8) {
+    if (bn > 256) return launch_pair<false, true, KIND_E4M3>(tmA, tmB, p, pairs, stream);
+    return swiglu ? launch_pair<true, false, KIND_E4M3>(tmA, tmB, p, pairs, stream)
+                  : launch_pair<false, false, KIND_E4M3>(tmA, tmB, p, pairs, stream);
+  }
+  if (bn > 256) return launch_pair<false, true, KIND_BF16>(tmA, tmB, p, pairs, stream);
+  return swiglu ? launch_pair<true, false, KIND_BF16>(tmA, tmB, p, pairs, stream)
+                : launch_pair<false, false, KIND_BF16>(tmA, tmB, p, pairs, stream);
 }
 
 extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, long long ldb, long long rows_b,

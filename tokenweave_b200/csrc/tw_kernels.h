@@ -54,6 +54,9 @@ int tw_gemm_fp8(const void* A, long long lda, const void* B, long long ldb, long
                 long long ldc, const void* bias, const float* row_scale, const float* col_scale, int M, int N,
                 int K, int swiglu, int up_row_offset, const int* tile_expert, const int* num_m_tiles_dev,
                 int n_per_expert, int max_ctas, int plan_hint, uint32_t* status, cudaStream_t stream);
+int tw_gemm_int8(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, const void* bias,
+                 const float* row_scale, const float* col_scale, int M, int N, int K, int swiglu, int max_ctas,
+                 int plan_hint, uint32_t* status, cudaStream_t stream);
 int tw_quant_fp8(const void* x, long long ldx, void* out, long long ldo, float* scales, int T, int H, int dynamic,
                  int max_ctas, cudaStream_t stream);
 int tw_rmsnorm_quant_fp8(const void* x, void* residual, const void* w, void* out, long long ldo, float* scales,

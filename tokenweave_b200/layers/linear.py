@@ -26,9 +26,18 @@ class _QuantizableLinear(nn.Module):
     by an e4m3 weight with one fp32 scale per output channel and every call quantises its input per
     token on the fly (dynamic activation scales) before the fp8 tcgen05 GEMM — the scheme of the
     reference's ``Fp8LinearMethod`` with dynamic activation quantisation
-    (vllm/model_executor/layers/quantization/fp8.py) on its sm100 scaled-mm."""
+    (vllm/model_executor/layers/quantization/fp8.py) on its sm100 scaled-mm. :meth:`quantize_int8_` is the same
+    scheme with symmetric int8 weights and activations and exact integer accumulation (the reference's
+    compressed-tensors W8A8 int8 path on its CUTLASS int8 scaled-mm)."""
 
     weight_scale: Optional[torch.Tensor] = None
+
+    def quantize_int8_(self) -> None:
+        if self.weight_scale is not None:
+            return
+        q, scale = ops.quant_int8(self.weight.data)
+        self.weight = nn.Parameter(q, requires_grad=False)
+        self.weight_scale = scale
 
     def quantize_fp8_(self) -> None:
         if self.weight_scale is not None:
@@ -44,6 +53,12 @@ class _QuantizableLinear(nn.Module):
         if out is None:
             n = self.weight.shape[0] // 2 if swiglu else self.weight.shape[0]
             out = torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
+        if self.weight.dtype == torch.int8:
+            xq, x_scale = ops.quant_int8(x, max_ctas=max_ctas)
+            if row_scale is not None:
+                x_scale = x_scale * row_scale
+            return ops.gemm_int8(xq, self.weight, x_scale, self.weight_scale, out=out, bias=bias, swiglu=swiglu,
+                                 max_ctas=max_ctas)
         xq, x_scale = ops.quant_fp8(x, max_ctas=max_ctas)
         if row_scale is not None:
             x_scale = x_scale * row_scale

@@ -119,24 +119,25 @@ def load_model_weights(model, config: EngineConfig) -> None:
             raise ValueError(f"load_format={fmt!r} needs a checkpoint directory")
         loaded = model.load_weights(dequantized_stream(iter_checkpoint(config.model.path)))
         logger.info("loaded %d tensors from %s", len(loaded), config.model.path)
-    if config.quantization == "fp8":
-        quantize_linears_fp8_(model)
+    if config.quantization in ("fp8", "int8"):
+        quantize_linears_fp8_(model, config.quantization)
 
 
-def quantize_linears_fp8_(model) -> int:
+def quantize_linears_fp8_(model, kind: str = "fp8") -> int:
     """Online fp8 quantisation of a loaded bf16 model: every tensor-parallel linear of the decoder
     layers gets an e4m3 weight with per-output-channel scales (the reference quantises bf16
     checkpoints the same way when ``quantization="fp8"`` meets an unquantised checkpoint,
     vllm/model_executor/layers/quantization/fp8.py). The LM head, the embedding, the MoE router and
-    the expert weights stay bf16. Returns the number of layers converted."""
+    the expert weights stay bf16. ``kind="int8"``: symmetric int8 instead of e4m3. Returns the number of layers
+    converted."""
     from ..layers.linear import _QuantizableLinear
     from ..layers.embedding import ParallelLMHead
     n = 0
     for name, mod in model.named_modules():
         if isinstance(mod, _QuantizableLinear) and not isinstance(mod, ParallelLMHead) and "gate." not in name + ".":
-            mod.quantize_fp8_()
+            mod.quantize_int8_() if kind == "int8" else mod.quantize_fp8_()
             n += 1
-    logger.info("quantised %d linear layers to fp8 (e4m3, per-channel weight scales)", n)
+    logger.info("quantised %d linear layers to %s (per-channel weight scales)", n, kind)
     return n
 
 

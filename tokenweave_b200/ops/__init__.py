@@ -312,6 +312,34 @@ def quant_int8(x: torch.Tensor, scale: Optional[torch.Tensor] = None, out: Optio
     return out, scales
 
 
+def gemm_int8(a: torch.Tensor, w: torch.Tensor, a_scale: Optional[torch.Tensor], w_scale: Optional[torch.Tensor],
+              out: Optional[torch.Tensor] = None, *, bias: Optional[torch.Tensor] = None, swiglu: bool = False,
+              max_ctas: int = 0, plan: int = 0) -> torch.Tensor:
+    """``out[m, n] = (a @ w.T)[m, n] * a_scale[m] * w_scale[n] + bias[n]`` in bf16 for int8 ``a`` ``[M, K]`` and
+    ``w`` ``[N, K]`` (symmetric quantisation, exact 32-bit integer accumulation on the tensor cores; scales fp32,
+    either may be None). With ``swiglu`` the weight is ``[gate; up]`` and the result ``silu(gate part) * (up
+    part)``. ``plan``: 0 = the library's choice, else 2000 + tile width (CTA pairs)."""
+    M, K = a.shape
+    rows_b = w.shape[0]
+    N = rows_b // 2 if swiglu else rows_b
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    if not a.is_cuda:
+        out.copy_(reference.gemm_int8(a, w, a_scale, w_scale, bias, swiglu))
+        return out
+    if a.dtype != torch.int8 or w.dtype != torch.int8:
+        raise TypeError("gemm_int8 takes int8 operands")
+    _check_bf16(out, bias)
+    for s, n in ((a_scale, M), (w_scale, rows_b)):
+        if s is not None and (s.dtype != torch.float32 or s.numel() != n or not s.is_contiguous()):
+            raise ValueError("scales must be contiguous fp32 vectors of one value per row / output channel")
+    _native.call("tw_gemm_int8", a.data_ptr(), _row_stride(a), w.data_ptr(), _row_stride(w), out.data_ptr(),
+                 _row_stride(out), _p(bias), _p(a_scale), _p(w_scale), M, N, K, int(swiglu), max_ctas, int(plan),
+                 status_word(a.device).data_ptr(), _stream(),
+                 tag=f"[int8 {M}x{N}x{K}{'+swiglu' if swiglu else ''}]" if _native._timing is not None else "")
+    return out
+
+
 def rmsnorm_quant_int8(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None,
                        scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, max_ctas: int = 0):
     """``q = int8(rmsnorm(x [+ residual]) * weight / scale)``; with ``residual`` the sum is written back to

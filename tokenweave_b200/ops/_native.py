@@ -29,6 +29,7 @@ _SIGNATURES = {
     "tw_argmax": [vp, ll, vp, i32, i32, vp],
     "tw_sample": [vp, ll, i32, i32, vp, vp, vp],
     "tw_gemm_fp8": [vp, ll, vp, ll, ll, vp, ll, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp, vp],
+    "tw_gemm_int8": [vp, ll, vp, ll, vp, ll, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "tw_quant_fp8": [vp, ll, vp, ll, vp, i32, i32, i32, i32, vp],
     "tw_rmsnorm_quant_fp8": [vp, vp, vp, vp, ll, vp, i32, i32, ll, ll, f32, i32, i32, vp],
     "tw_quant_int8": [vp, ll, vp, ll, vp, i32, i32, i32, i32, vp],

@@ -110,6 +110,23 @@ def gemm_fp8(a: torch.Tensor, w: torch.Tensor, a_scale: Optional[torch.Tensor], 
     return acc.to(torch.bfloat16)
 
 
+def gemm_int8(a: torch.Tensor, w: torch.Tensor, a_scale: Optional[torch.Tensor], w_scale: Optional[torch.Tensor],
+              bias: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
+    """Exact integer product of int8 operands (accumulated in float64, which holds every partial sum exactly),
+    scaled per row and per output channel in fp32 like the kernel's epilogue, rounded once."""
+    acc = (a.double() @ w.double().t()).float()
+    if a_scale is not None:
+        acc = acc * a_scale.float().unsqueeze(-1)
+    if w_scale is not None:
+        acc = acc * w_scale.float().unsqueeze(0)
+    if swiglu:
+        n = acc.shape[1] // 2
+        return (F.silu(acc[:, :n]) * acc[:, n:]).to(torch.bfloat16)
+    if bias is not None:
+        acc = acc + bias.float()
+    return acc.to(torch.bfloat16)
+
+
 ACTIVATION_KINDS = {"silu_and_mul": 0, "gelu_and_mul": 1, "gelu_tanh_and_mul": 2, "mul_and_silu": 3,
                     "fatrelu_and_mul": 4, "gelu_new": 5, "gelu_fast": 6, "quick_gelu": 7, "gelu": 8, "silu": 9}
 
