@@ -50,6 +50,9 @@ class ModelConfig:
     init_std: float = 0.02
     path: Optional[str] = None           # checkpoint directory (None: random init)
     checkpoint_quantization: Optional[str] = None    # "fp8" when the checkpoint's config says its weights are fp8
+    # weight-only integer checkpoints (AWQ, GPTQ): {"method", "bits", "group_size", "zeros_plus_one"}; their packed
+    # tensors are expanded to the model's dtype while loading (models/loader.py)
+    checkpoint_packing: Optional[dict] = None
 
     @property
     def is_moe(self) -> bool:
@@ -99,7 +102,7 @@ class ModelConfig:
             num_experts=cfg.get("num_local_experts", 0), num_experts_per_tok=cfg.get("num_experts_per_tok", 2),
             max_model_len=max_len,
             tie_word_embeddings=cfg.get("tie_word_embeddings", False), dtype=dt, eos_token_id=eos, path=path,
-            checkpoint_quantization=ModelConfig._quant_of(cfg))
+            checkpoint_quantization=ModelConfig._quant_of(cfg), checkpoint_packing=ModelConfig._packing_of(cfg))
 
     @staticmethod
     def _quant_of(cfg: dict) -> Optional[str]:
@@ -111,12 +114,35 @@ class ModelConfig:
             return None
         if method == "fp8":
             return "fp8"
+        if method in ("awq", "gptq"):
+            return None                  # weight-only integers: expanded at load time, see _packing_of
         if method == "compressed-tensors":
             groups = (qc.get("config_groups") or {}).values()
             if groups and all((g.get("weights") or {}).get("type") == "float" and (g.get("weights") or {}).get("num_bits") == 8
                               for g in groups):
                 return "fp8"
-        raise ValueError(f"checkpoint quantised with {method!r}: only fp8 checkpoints are served")
+        raise ValueError(f"checkpoint quantised with {method!r}: fp8, AWQ and GPTQ checkpoints are served")
+
+    @staticmethod
+    def _packing_of(cfg: dict) -> Optional[dict]:
+        """Packing of a weight-only integer checkpoint: AWQ (``quant_method`` awq, ``version`` gemm, 4 bits, the
+        layout vllm/model_executor/layers/quantization/awq.py reads) or GPTQ (4 or 8 bits, with or without
+        activation order, vllm/model_executor/layers/quantization/gptq.py)."""
+        qc = cfg.get("quantization_config") or {}
+        method = str(qc.get("quant_method", "")).lower()
+        if method not in ("awq", "gptq"):
+            return None
+        bits = int(qc.get("bits", qc.get("w_bit", 4)))
+        group = int(qc.get("group_size", qc.get("q_group_size", 128)))
+        if method == "awq":
+            if bits != 4 or str(qc.get("version", "gemm")).lower() != "gemm":
+                raise ValueError("AWQ checkpoints are served in the 4-bit GEMM layout only")
+            return {"method": "awq", "bits": 4, "group_size": group, "zeros_plus_one": False}
+        if bits not in (4, 8):
+            raise ValueError(f"GPTQ checkpoints are served with 4 or 8 bits (got {bits})")
+        # the first GPTQ format stores zero points minus one; "gptq_v2" stores them as they are
+        v2 = str(qc.get("checkpoint_format", "gptq")).lower() == "gptq_v2"
+        return {"method": "gptq", "bits": bits, "group_size": group, "zeros_plus_one": not v2}
 
     @staticmethod
     def from_pretrained(path: str) -> "ModelConfig":

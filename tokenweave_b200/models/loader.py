@@ -10,7 +10,7 @@ from __future__ import annotations
 import glob
 import json
 import os
-from typing import Iterator
+from typing import Iterator, Optional
 
 import torch
 
@@ -61,6 +61,90 @@ def dequantize_fp8(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
         full = s.repeat_interleave(br, 0)[: w.shape[0]].repeat_interleave(bc, 1)[:, : w.shape[1]]
         return w * full
     raise ValueError(f"fp8 scale of shape {tuple(s.shape)} for a weight of shape {tuple(w.shape)}")
+
+
+_AWQ_NIBBLE_TO_COLUMN = (0, 2, 4, 6, 1, 3, 5, 7)     # nibble i of a packed word holds output column 8 c + this
+
+
+def _unpack_columns(packed: torch.Tensor, bits: int, order=None) -> torch.Tensor:
+    """int32 ``[R, C]`` whose words pack ``32 / bits`` values along the columns -> int32 ``[R, C * 32 / bits]``;
+    ``order[i]`` is the column (within its group) that field i of a word holds (default: i)."""
+    per = 32 // bits
+    shifts = torch.arange(per, dtype=torch.int32) * bits
+    vals = (packed.to(torch.int32).unsqueeze(-1) >> shifts) & ((1 << bits) - 1)       # [R, C, per] by field
+    if order is not None:
+        out = torch.empty_like(vals)
+        out[..., list(order)] = vals
+        vals = out
+    return vals.reshape(packed.shape[0], -1)
+
+
+def dequantize_awq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, group_size: int) -> torch.Tensor:
+    """AWQ GEMM layout (4 bits): ``qweight`` int32 ``[K, N / 8]`` and ``qzeros`` int32 ``[K / g, N / 8]`` pack eight
+    output columns per word in the order 0, 2, 4, 6, 1, 3, 5, 7; ``scales`` ``[K / g, N]``. Returns the ``[N, K]``
+    fp32 weight ``(q - z) * s`` (the arithmetic of the reference's ``awq_dequantize``,
+    csrc/quantization/awq/gemm_kernels.cu)."""
+    q = _unpack_columns(qweight, 4, _AWQ_NIBBLE_TO_COLUMN)
+    z = _unpack_columns(qzeros, 4, _AWQ_NIBBLE_TO_COLUMN)
+    g = group_size if group_size > 0 else q.shape[0]
+    z = z.repeat_interleave(g, 0)[: q.shape[0]]
+    s = scales.float().repeat_interleave(g, 0)[: q.shape[0]]
+    return ((q - z).float() * s).t().contiguous()
+
+
+def dequantize_gptq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, g_idx: Optional[torch.Tensor],
+                    bits: int, group_size: int, zeros_plus_one: bool) -> torch.Tensor:
+    """GPTQ layout: ``qweight`` int32 ``[K * bits / 32, N]`` packs consecutive INPUT rows per word, ``qzeros`` int32
+    ``[K / g, N * bits / 32]`` packs consecutive output columns, ``scales`` ``[K / g, N]``, ``g_idx`` ``[K]`` names the
+    group of every input row (activation order; absent: row // group size). Returns the ``[N, K]`` fp32 weight
+    ``(q - z) * s`` (the reference's csrc/quantization/gptq/q_gemm.cu reconstruction)."""
+    q = _unpack_columns(qweight.t().contiguous(), bits).t()                  # [K, N]
+    z = _unpack_columns(qzeros, bits)                                         # [K / g, N]
+    if zeros_plus_one:
+        z = z + 1          # no wrap-around: a stored 15 means 16, as in the reference's kernel
+    K = q.shape[0]
+    if g_idx is None:
+        g = group_size if group_size > 0 else K
+        idx = torch.arange(K) // g
+    else:
+        idx = g_idx.long()
+    return ((q - z[idx]).float() * scales.float()[idx]).t().contiguous()
+
+
+_PACKED_SUFFIXES = (".qweight", ".qzeros", ".scales", ".g_idx")
+
+
+def unpacked_stream(weights: Iterator[tuple[str, torch.Tensor]], packing: Optional[dict]):
+    """Expands the packed tensors of an AWQ / GPTQ checkpoint (``<linear>.qweight / qzeros / scales [/ g_idx]``) into
+    ``<linear>.weight`` in fp32 as soon as a linear's tensors are complete; everything else passes through. The
+    engine then runs the model in its 16-bit dtype (or re-quantises to fp8 / int8 if asked to): weight-only 4-bit
+    GEMMs are not built."""
+    if not packing:
+        yield from weights
+        return
+    need = {"qweight", "qzeros", "scales"} | ({"g_idx"} if packing["method"] == "gptq" else set())
+    parts: dict[str, dict[str, torch.Tensor]] = {}
+
+    def expand(d):
+        if packing["method"] == "awq":
+            return dequantize_awq(d["qweight"], d["qzeros"], d["scales"], packing["group_size"])
+        return dequantize_gptq(d["qweight"], d["qzeros"], d["scales"], d.get("g_idx"), packing["bits"],
+                               packing["group_size"], packing["zeros_plus_one"])
+
+    for name, t in weights:
+        if not name.endswith(_PACKED_SUFFIXES):
+            yield name, t
+            continue
+        stem, kind = name.rsplit(".", 1)
+        d = parts.setdefault(stem, {})
+        d[kind] = t
+        if need <= set(d):
+            yield stem + ".weight", expand(parts.pop(stem))
+    for stem, d in parts.items():            # GPTQ files without g_idx tensors end up here
+        missing = {"qweight", "qzeros", "scales"} - set(d)
+        if missing:
+            raise ValueError(f"{stem}: packed checkpoint lacks {sorted(missing)}")
+        yield stem + ".weight", expand(d)
 
 
 def dequantized_stream(weights: Iterator[tuple[str, torch.Tensor]]) -> Iterator[tuple[str, torch.Tensor]]:
@@ -117,7 +201,8 @@ def load_model_weights(model, config: EngineConfig) -> None:
     else:
         if not config.model.path:
             raise ValueError(f"load_format={fmt!r} needs a checkpoint directory")
-        loaded = model.load_weights(dequantized_stream(iter_checkpoint(config.model.path)))
+        loaded = model.load_weights(dequantized_stream(unpacked_stream(iter_checkpoint(config.model.path),
+                                                                       config.model.checkpoint_packing)))
         logger.info("loaded %d tensors from %s", len(loaded), config.model.path)
     if config.quantization in ("fp8", "int8"):
         quantize_linears_fp8_(model, config.quantization)
