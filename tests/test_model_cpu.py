@@ -247,7 +247,7 @@ def test_fp8_checkpoint_loads_and_matches_online_quantisation(tmp_path):
         logits.append(torch.stack([got[str(i)] for i in range(len(prompts))]))
         llm.shutdown()
     torch.testing.assert_close(logits[0], logits[1], atol=1e-4, rtol=1e-4)
-    bad = dict(hf_config_dict(cfg), quantization_config={"quant_method": "gptq", "bits": 4})
-    save_hf_checkpoint(st, bad, str(tmp_path / "gptq"))
-    with pytest.raises(ValueError, match="only fp8"):
-        _engine(str(tmp_path / "gptq"))
+    bad = dict(hf_config_dict(cfg), quantization_config={"quant_method": "aqlm", "bits": 2})
+    save_hf_checkpoint(st, bad, str(tmp_path / "aqlm"))
+    with pytest.raises(ValueError, match="checkpoints are served"):
+        _engine(str(tmp_path / "aqlm"))
