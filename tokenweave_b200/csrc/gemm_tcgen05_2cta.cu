@@ -16,6 +16,11 @@
 // Barriers: full[s] lives in the leader and counts the bytes of both CTAs; empty[s] and acc_full[a]
 // exist in both CTAs and are signalled by the leader's tcgen05.commit (one commit per CTA);
 // acc_empty[a] lives in the leader and collects one arrival per epilogue warp of both CTAs.
+// Write-back (tiles up to 256 columns): a thread owns one ROW of the accumulator, so direct stores would touch 32
+// different lines per instruction, half a sector each. Instead every epilogue warp packs 32 rows x 32 columns
+// of bf16 into its own 2 KB of shared memory (two buffers, the 64-byte swizzle of the tensor map: no bank
+// conflicts) and one lane sends it with a TMA store, which writes whole sectors, clips the edges of C itself and
+// leaves the warp free to fetch its next chunk. Wide tiles keep the direct stores (no shared memory to spare).
 // FP8: operands are e4m3 bytes, a k-block is 128 elements (the same 128 bytes per row), the MMA is
 // kind::f8f6f4 (K = 32 per instruction) and the epilogue applies acc * row_scale[m] * col_scale[n] + bias[n].
 // INT8 (KIND 2): the same with signed 8-bit operands, kind::i8 and 32-bit integer accumulators that the epilogue
@@ -41,7 +46,8 @@ constexpr int G2_EPI_WARPS = 8;
 constexpr int G2_GROUP_M = 8;       // pair-tiles per rasterisation group
 constexpr int G2_MAX_STAGES = 8;
 constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;
-constexpr int G2_SMEM_BUDGET = 200 * 1024;
+constexpr int G2_SMEM_BUDGET = 192 * 1024;      // pipeline stages of the tiles up to 256 columns wide ...
+constexpr int G2_EPI_STAGE_BYTES = G2_EPI_WARPS * 2 * 2048;   // ... plus two 32 x 32 bf16 staging buffers per epilogue warp
 constexpr int G2_TMEM_COLS = 512;
 
 struct Gemm2Params {
@@ -171,7 +177,7 @@ __device__ __forceinline__ void pair_tile_coords(int t, int num_m, int num_n, in
 template <bool SWIGLU, bool WIDE, int KIND>
 __global__ void __launch_bounds__(G2_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const Gemm2Params p) {
+                      const __grid_constant__ CUtensorMap tmC, const Gemm2Params p) {
   const int BN = p.bn;
   const int HALF_N = BN / 2;                       // B rows held by each CTA
   const int STAGES = p.stages;
@@ -191,7 +197,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * stage_bytes);
+  constexpr bool TMA_EPI = !WIDE;                     // write-back through shared memory and TMA stores
+  uint8_t* epi_stage = smem + STAGES * stage_bytes;   // 1024-byte aligned: the stage sizes are multiples of 4 KB
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + (TMA_EPI ? G2_EPI_STAGE_BYTES : 0));
   uint64_t* empty_bar = full_bar + G2_MAX_STAGES;
   uint64_t* acc_full = empty_bar + G2_MAX_STAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -222,6 +230,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (TMA_EPI) tma_prefetch_desc(&tmC);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -336,6 +345,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int par = (warp - 2) >> 2;         // warps 2..5: even 32-column chunks, warps 6..9: odd ones
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint8_t* my_stage = epi_stage + (warp - 2) * 4096;
+    int sbuf = 0;
     for (int t = pair; t < total_tiles && !*abort_flag; t += num_pairs) {
       int m_tile, n_tile;
       pair_tile_coords(t, num_m, num_n, m_tile, n_tile);
@@ -448,7 +459,25 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           for (int j = 0; j < 16; ++j)
             packed[j] = pack_bf16x2(__uint_as_float(v[2 * j]) * rs, __uint_as_float(v[2 * j + 1]) * rs);
         }
-        if (row < p.M) {
+        if (TMA_EPI) {
+          uint8_t* dst = my_stage + sbuf * 2048;
+          // the store sent from this buffer two chunks ago must have read it
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          // row `lane` of the 32 x 32 block: 64 bytes; its four 16-byte pieces are XOR-swizzled with bits 7..8 of the
+          // row's offset (the 64-byte swizzle of the tensor map), which also spreads a quarter-warp over all banks
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(dst + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, dst, nc, m_tile * 2 * G2_BM + static_cast<int>(rank) * G2_BM + q * 32);
+            tma_store_commit();
+          }
+          sbuf ^= 1;
+        } else if (row < p.M) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int n = nc + j * 8;
@@ -474,6 +503,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 
   // ---------------- tear-down ----------------
+  if (TMA_EPI && warp >= 2 && lane == 0) tma_store_wait_all<0>();   // shared memory stays until the stores have left
   if (*abort_flag) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -488,10 +518,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 }
 
 template <bool SWIGLU, bool WIDE, int KIND>
-static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p, int pairs,
-                       cudaStream_t stream) {
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const Gemm2Params& p,
+                       int pairs, cudaStream_t stream) {
   const int stage_bytes = p.kb_per_stage * (G2_A_BYTES + (p.bn / 2) * G2_BK * 2);
-  const int smem = p.stages * stage_bytes + 256 + 1024;
+  const int smem = p.stages * stage_bytes + (WIDE ? 0 : G2_EPI_STAGE_BYTES) + 256 + 1024;
   auto kern = gemm_bf16_pair_kernel<SWIGLU, WIDE, KIND>;
   static thread_local int configured_dev = -1;
   int dev = 0;
@@ -517,7 +547,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, p);
   if (e != cudaSuccess) {
     set_last_error("gemm pair launch failed: %s", cudaGetErrorString(e));
     return 1;
@@ -571,7 +601,14 @@ extern "C" int tw_gemm_pair(int fp8, const void* A, long long lda, const void* B
   int stages = (bn > 256 ? 216 * 1024 : G2_SMEM_BUDGET) / stage_bytes;
   if (stages > G2_MAX_STAGES) stages = G2_MAX_STAGES;
 
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
+  {
+    // C as the TMA stores of the epilogue see it: 32 x 32 blocks of bf16; rows and columns past M and N are clipped
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+    uint64_t strides[1] = {(uint64_t)ldc * 2};
+    uint32_t box[2] = {32, 32};
+    if (!make_tensor_map_bf16_sw64(&tmC, C, 2, dims, strides, box)) return 1;
+  }
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
     uint64_t strides[1] = {(uint64_t)lda * esz};
@@ -608,18 +645,18 @@ extern "C" int tw_gemm_pair(int fp8, const void* A, long long lda, const void* B
   int pairs = num_m * num_n;
   if (pairs > pairs_avail) pairs = pairs_avail;
   if (fp8 == 2) {
-    if (bn > 256) return launch_pair<false, true, KIND_S8>(tmA, tmB, p, pairs, stream);
-    return swiglu ? launch_pair<true, false, KIND_S8>(tmA, tmB, p, pairs, stream)
-                  : launch_pair<false, false, KIND_S8>(tmA, tmB, p, pairs, stream);
+    if (bn > 256) return launch_pair<false, true, KIND_S8>(tmA, tmB, tmC, p, pairs, stream);
+    return swiglu ? launch_pair<true, false, KIND_S8>(tmA, tmB, tmC, p, pairs, stream)
+                  : launch_pair<false, false, KIND_S8>(tmA, tmB, tmC, p, pairs, stream);
   }
   if (fp8) {
-    if (bn > 256) return launch_pair<false, true, KIND_E4M3>(tmA, tmB, p, pairs, stream);
-    return swiglu ? launch_pair<true, false, KIND_E4M3>(tmA, tmB, p, pairs, stream)
-                  : launch_pair<false, false, KIND_E4M3>(tmA, tmB, p, pairs, stream);
+    if (bn > 256) return launch_pair<false, true, KIND_E4M3>(tmA, tmB, tmC, p, pairs, stream);
+    return swiglu ? launch_pair<true, false, KIND_E4M3>(tmA, tmB, tmC, p, pairs, stream)
+                  : launch_pair<false, false, KIND_E4M3>(tmA, tmB, tmC, p, pairs, stream);
   }
-  if (bn > 256) return launch_pair<false, true, KIND_BF16>(tmA, tmB, p, pairs, stream);
-  return swiglu ? launch_pair<true, false, KIND_BF16>(tmA, tmB, p, pairs, stream)
-                : launch_pair<false, false, KIND_BF16>(tmA, tmB, p, pairs, stream);
+  if (bn > 256) return launch_pair<false, true, KIND_BF16>(tmA, tmB, tmC, p, pairs, stream);
+  return swiglu ? launch_pair<true, false, KIND_BF16>(tmA, tmB, tmC, p, pairs, stream)
+                : launch_pair<false, false, KIND_BF16>(tmA, tmB, tmC, p, pairs, stream);
 }
 
 extern "C" int tw_gemm_bf16_pair(const void* A, long long lda, const void* B, long long ldb, long long rows_b,

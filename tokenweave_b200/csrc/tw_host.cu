@@ -35,7 +35,8 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 static bool make_tensor_map_typed(CUtensorMap* out, CUtensorMapDataType dtype, const void* base, int rank,
-                                  const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+                                  const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                                  CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) {
     set_last_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -64,7 +65,7 @@ static bool make_tensor_map_typed(CUtensorMap* out, CUtensorMapDataType dtype, c
   }
   CUresult r = fn(out, dtype, (cuuint32_t)rank, const_cast<void*>(base),
                   gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_last_error("cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu)",
@@ -78,6 +79,12 @@ static bool make_tensor_map_typed(CUtensorMap* out, CUtensorMapDataType dtype, c
 bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                           const uint64_t* strides_bytes, const uint32_t* box) {
   return make_tensor_map_typed(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, rank, dims, strides_bytes, box);
+}
+
+bool make_tensor_map_bf16_sw64(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                               const uint64_t* strides_bytes, const uint32_t* box) {
+  return make_tensor_map_typed(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, rank, dims, strides_bytes, box,
+                               CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
 bool make_tensor_map_u8(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,

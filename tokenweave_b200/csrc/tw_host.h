@@ -19,6 +19,10 @@ const char* last_error();
 bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                           const uint64_t* strides_bytes, const uint32_t* box);
 
+// The same with the 64-byte swizzle (boxes whose rows are 64 bytes: the write-back blocks of the GEMM epilogue).
+bool make_tensor_map_bf16_sw64(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                               const uint64_t* strides_bytes, const uint32_t* box);
+
 // The same for a tensor of 8-bit elements (fp8 operands).
 bool make_tensor_map_u8(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                         const uint64_t* strides_bytes, const uint32_t* box);
