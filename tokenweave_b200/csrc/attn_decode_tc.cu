@@ -69,6 +69,10 @@ struct DecodeTcParams {
   uint32_t* status;
 };
 
+// GT: query heads per KV head as a compile-time constant (4, 8 or 16), or 0 to read it from the arguments. The
+// softmax costs a few instructions per head, key and tile, all in the 128 threads that own the keys; with the
+// group size known the loops over the 16 columns of S^T shrink to the heads that exist.
+template <int GT>
 __global__ void __launch_bounds__(DTC_THREADS, 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                       const DecodeTcParams p) {
@@ -97,7 +101,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
-  const int G = p.hq / p.hkv;
+  const int G = GT > 0 ? GT : p.hq / p.hkv;
   const int row = p.tok_row[tok];
   const int seq = p.tok_seq[tok];
   const int kv_len = p.tok_kvlen[tok];
@@ -266,14 +270,31 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       float* xm = xchg + sb * 64;
       if (lane == 0) {
 #pragma unroll
-        for (int g = 0; g < DTC_NH; ++g) xm[sw * 16 + g] = mx[g];
+        for (int g4 = 0; g4 < DTC_NH; g4 += 4)
+          if (g4 < G)
+            *reinterpret_cast<float4*>(xm + sw * 16 + g4) = make_float4(mx[g4], mx[g4 + 1], mx[g4 + 2], mx[g4 + 3]);
       }
       dtc_softmax_sync();
       bool rescale = false;
-      float alpha[DTC_NH];
+      float alpha[DTC_NH], mt_all[DTC_NH];
+#pragma unroll
+      for (int g4 = 0; g4 < DTC_NH; g4 += 4) {
+        // the four warps' maxima of four heads: four 16-byte loads
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a, c = a, d = a;
+        if (g4 < G) {
+          a = *reinterpret_cast<const float4*>(xm + g4);
+          b = *reinterpret_cast<const float4*>(xm + 16 + g4);
+          c = *reinterpret_cast<const float4*>(xm + 32 + g4);
+          d = *reinterpret_cast<const float4*>(xm + 48 + g4);
+        }
+        mt_all[g4] = fmaxf(fmaxf(a.x, b.x), fmaxf(c.x, d.x));
+        mt_all[g4 + 1] = fmaxf(fmaxf(a.y, b.y), fmaxf(c.y, d.y));
+        mt_all[g4 + 2] = fmaxf(fmaxf(a.z, b.z), fmaxf(c.z, d.z));
+        mt_all[g4 + 3] = fmaxf(fmaxf(a.w, b.w), fmaxf(c.w, d.w));
+      }
 #pragma unroll
       for (int g = 0; g < DTC_NH; ++g) {
-        const float mt = fmaxf(fmaxf(xm[g], xm[16 + g]), fmaxf(xm[32 + g], xm[48 + g]));
+        const float mt = mt_all[g];
         alpha[g] = 1.f;
         if (g < G) {
           if (j == 0) {
@@ -410,6 +431,7 @@ __device__ __forceinline__ DtpItem dtp_item(const DecodeTcParams& p, int idx) {
   return it;
 }
 
+template <int GT>
 __global__ void __launch_bounds__(DTC_THREADS, 1)
 attn_decode_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                                  const DecodeTcParams p, const int n_items) {
@@ -438,7 +460,7 @@ attn_decode_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmK, const 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int G = p.hq / p.hkv;
+  const int G = GT > 0 ? GT : p.hq / p.hkv;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < DTC_RING; ++i) {
@@ -644,14 +666,31 @@ attn_decode_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmK, const 
         float* xm = xchg + sb * 64;
         if (lane == 0) {
 #pragma unroll
-          for (int g = 0; g < DTC_NH; ++g) xm[sw * 16 + g] = mx[g];
+          for (int g4 = 0; g4 < DTC_NH; g4 += 4)
+            if (g4 < G)
+              *reinterpret_cast<float4*>(xm + sw * 16 + g4) = make_float4(mx[g4], mx[g4 + 1], mx[g4 + 2], mx[g4 + 3]);
         }
         dtc_softmax_sync();
         bool rescale = false;
-        float alpha[DTC_NH];
+        float alpha[DTC_NH], mt_all[DTC_NH];
+#pragma unroll
+        for (int g4 = 0; g4 < DTC_NH; g4 += 4) {
+          // the four warps' maxima of four heads: four 16-byte loads
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a, c = a, d = a;
+          if (g4 < G) {
+            a = *reinterpret_cast<const float4*>(xm + g4);
+            b = *reinterpret_cast<const float4*>(xm + 16 + g4);
+            c = *reinterpret_cast<const float4*>(xm + 32 + g4);
+            d = *reinterpret_cast<const float4*>(xm + 48 + g4);
+          }
+          mt_all[g4] = fmaxf(fmaxf(a.x, b.x), fmaxf(c.x, d.x));
+          mt_all[g4 + 1] = fmaxf(fmaxf(a.y, b.y), fmaxf(c.y, d.y));
+          mt_all[g4 + 2] = fmaxf(fmaxf(a.z, b.z), fmaxf(c.z, d.z));
+          mt_all[g4 + 3] = fmaxf(fmaxf(a.w, b.w), fmaxf(c.w, d.w));
+        }
 #pragma unroll
         for (int g = 0; g < DTC_NH; ++g) {
-          const float mt = fmaxf(fmaxf(xm[g], xm[16 + g]), fmaxf(xm[32 + g], xm[48 + g]));
+          const float mt = mt_all[g];
           alpha[g] = 1.f;
           if (g < G) {
             if (j == 0) {
@@ -784,7 +823,11 @@ extern "C" int tw_attn_decode_tc(const void* q, long long ldq, const void* k_cac
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DTC_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTC_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTC_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTC_SMEM);
     if (e != cudaSuccess) {
       set_last_error("attn_decode_tc: cudaFuncSetAttribute(smem=%d) failed: %s", DTC_SMEM, cudaGetErrorString(e));
       return 1;
@@ -809,7 +852,11 @@ extern "C" int tw_attn_decode_tc(const void* q, long long ldq, const void* k_cac
   p.part_o = part_o;
   p.part_ml = part_ml;
   p.status = status;
-  attn_decode_tc_kernel<<<dim3(n_tok, hkv, splits), DTC_THREADS, DTC_SMEM, stream>>>(tmK, tmV, p);
+  const dim3 grid(n_tok, hkv, splits);
+  const int group = hq / hkv;
+  if (group == 8) attn_decode_tc_kernel<8><<<grid, DTC_THREADS, DTC_SMEM, stream>>>(tmK, tmV, p);
+  else if (group == 4) attn_decode_tc_kernel<4><<<grid, DTC_THREADS, DTC_SMEM, stream>>>(tmK, tmV, p);
+  else attn_decode_tc_kernel<0><<<grid, DTC_THREADS, DTC_SMEM, stream>>>(tmK, tmV, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error("attn_decode_tc launch failed: %s", cudaGetErrorString(e));
@@ -856,8 +903,12 @@ extern "C" int tw_attn_decode_tc_persistent(const void* q, long long ldq, const 
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_persistent_kernel,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_persistent_kernel<0>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, DTP_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_tc_persistent_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTP_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_tc_persistent_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTP_SMEM);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) {
       set_last_error("attn_decode_tc_persistent: device set-up failed: %s", cudaGetErrorString(e));
@@ -890,7 +941,10 @@ extern "C" int tw_attn_decode_tc_persistent(const void* q, long long ldq, const 
   }
   const int cap = max_ctas > 0 ? max_ctas : sm_count;
   const int grid = static_cast<int>(items < cap ? items : cap);
-  attn_decode_tc_persistent_kernel<<<grid, DTC_THREADS, DTP_SMEM, stream>>>(tmK, tmV, p, static_cast<int>(items));
+  const int group = hq / hkv, n_items = static_cast<int>(items);
+  if (group == 8) attn_decode_tc_persistent_kernel<8><<<grid, DTC_THREADS, DTP_SMEM, stream>>>(tmK, tmV, p, n_items);
+  else if (group == 4) attn_decode_tc_persistent_kernel<4><<<grid, DTC_THREADS, DTP_SMEM, stream>>>(tmK, tmV, p, n_items);
+  else attn_decode_tc_persistent_kernel<0><<<grid, DTC_THREADS, DTP_SMEM, stream>>>(tmK, tmV, p, n_items);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error("attn_decode_tc_persistent launch failed: %s", cudaGetErrorString(e));
