@@ -34,8 +34,7 @@ __device__ __forceinline__ float2 moe_ffma2(float2 a, float2 b, float2 c) {
 
 // TPW tokens per warp, persistent CTAs. The gate weight [E, H] lives in shared memory; a warp reads (and converts)
 // every 16 bytes of it once for its TPW tokens, and the multiply-adds are the packed two-wide fp32 form of sm_100:
-// the kernel is bound by instruction issue, and this is 0.9 instructions per multiply-add where one token per warp
-// with scalar FMAs took 2.1.
+// this is about one instruction per multiply-add where one token per warp with scalar FMAs took 2.1.
 template <int E, int TPW>
 __global__ void __launch_bounds__(512)       // 16 warps per SM: 128 registers each for the TPW x E accumulators
 moe_router_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
@@ -59,14 +58,22 @@ moe_router_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 #pragma unroll
     for (int i = 0; i < TPW; ++i)          // tokens past the end re-read the last row; their results are dropped
       xr[i] = reinterpret_cast<const uint4*>(x + static_cast<long long>(min(tb + i, T - 1)) * ldx);
+    // the row pieces of the NEXT step are requested before this step's arithmetic: with 16 warps per SM the loads
+    // of one step alone would leave the memory system idle while the warps multiply
+    uint4 xv[TPW];
+#pragma unroll
+    for (int i = 0; i < TPW; ++i) xv[i] = lane < nvec ? xr[i][lane] : make_uint4(0u, 0u, 0u, 0u);
     for (int v = lane; v < nvec; v += 32) {
       float2 xf[TPW][4];
 #pragma unroll
       for (int i = 0; i < TPW; ++i) {
-        const uint4 xv = xr[i][v];
-        const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv);
+        const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv[i]);
 #pragma unroll
         for (int j = 0; j < 4; ++j) xf[i][j] = unpack_bf16x2(xu[j]);
+      }
+      if (v + 32 < nvec) {
+#pragma unroll
+        for (int i = 0; i < TPW; ++i) xv[i] = xr[i][v + 32];
       }
 #pragma unroll
       for (int e = 0; e < E; ++e) {
@@ -257,7 +264,7 @@ extern "C" int tw_moe_router(const void* x, long long ldx, const void* wg, float
   const int cap = device_sm_count();
   auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
   auto wb = reinterpret_cast<const __nv_bfloat16*>(wg);
-  // tokens per warp: 64 accumulator registers per thread in every case
+  // tokens per warp: at most 64 accumulator registers per thread, room left for the prefetched row pieces
 #define TW_ROUTER_CASE(NE, TPW)                                                                     \
   case NE: {                                                                                        \
     auto kern = moe_router_kernel<NE, TPW>;                                                         \
@@ -270,8 +277,8 @@ extern "C" int tw_moe_router(const void* x, long long ldx, const void* wg, float
   }
   switch (E) {
     TW_ROUTER_CASE(4, 4)
-    TW_ROUTER_CASE(8, 4)
-    TW_ROUTER_CASE(16, 2)
+    TW_ROUTER_CASE(8, 2)
+    TW_ROUTER_CASE(16, 1)
     TW_ROUTER_CASE(32, 1)
     default:
       set_last_error("moe_router: number of experts %d not in {4, 8, 16, 32}", E);
