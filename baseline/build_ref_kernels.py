@@ -80,8 +80,11 @@ def note(line: str) -> None:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("TW_REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("TW_REFERENCE_DIR"),
+                    help="checkout of microsoft/tokenweave (or set TW_REFERENCE_DIR)")
     args = ap.parse_args()
+    if not args.reference or not os.path.isdir(os.path.join(args.reference, "csrc")):
+        ap.error("give the reference checkout with --reference DIR (it must contain csrc/)")
     src = os.path.join(OUT, "src")
     os.makedirs(src, exist_ok=True)
     for name in FILES:

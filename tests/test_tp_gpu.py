@@ -137,6 +137,7 @@ def _graph_rank(rank, world, path, prompts, mode):
     import torch.distributed as dist
     from tokenweave_b200 import LLM, SamplingParams, ops
     err = None
+    os.environ["TW_GRAPH_MIXED_SIGHTS"] = "1"      # the prefill of four prompts is what this test wants captured
     try:
         results = []
         for graphs in (False, True):

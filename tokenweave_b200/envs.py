@@ -42,6 +42,9 @@ _VARS: dict[str, Callable[[], Any]] = {
     "TW_USE_PYNCCL": lambda: os.getenv("TW_USE_PYNCCL", "1") == "1",
     # libnccl for the ctypes binding (parallel/pynccl.py); default: the one torch ships
     "TW_NCCL_SO_PATH": lambda: os.getenv("TW_NCCL_SO_PATH"),
+    # CUDA graphs: sights of a step shape that mixes prefill chunks with decode rows (or prefills several sequences)
+    # before it is captured; decode-only steps and single-sequence prefills are captured on their second sight
+    "TW_GRAPH_MIXED_SIGHTS": lambda: int(os.getenv("TW_GRAPH_MIXED_SIGHTS", "4")),
     # where the artifact scripts write their CSV / JSON results
     "TW_RESULTS_DIR": lambda: os.getenv("TW_RESULTS_DIR", "results"),
     # port range start for rendezvous when none is given

@@ -16,7 +16,7 @@ from typing import Optional
 import numpy as np
 import torch
 
-from .. import ops
+from .. import envs, ops
 from ..config import EngineConfig
 from ..layers.attention import AttentionMetadata, build_attention_metadata
 from ..layers.sampler import Sampler
@@ -222,13 +222,19 @@ class ModelRunner:
         return logits, (ops.argmax(logits) if greedy else None)
 
     def _run_graphed(self, sig, step_in: StepInput, n_logits: int, greedy: bool):
-        """Eager on the first sight of a signature (which also warms every kernel up), capture on the
-        second, replay from then on."""
+        """Eager on the first sight of a signature (which also warms every kernel up), then captured and replayed.
+        A capture costs a device synchronisation plus tens of milliseconds, so it has to pay for itself: steps that
+        are all single-token rows (decode) or one prefill of one sequence repeat for many steps and are captured on
+        their second sight; steps that mix prefill chunks with decode rows rarely come back with the same shape and
+        are captured only after ``TW_GRAPH_MIXED_SIGHTS`` (4) sights (a throughput run with chunked prefill lost 15 % to captures of shapes
+        that were never replayed)."""
         entry = self._graphs.get(sig)
         if entry is None:
             seen = self._graph_seen.get(sig, 0)
             self._graph_seen[sig] = seen + 1
-            if seen == 0 or len(self._graphs) >= 64:
+            metas = [m for m in (step_in.meta, step_in.meta0, step_in.meta1) if m is not None]
+            steady = all(m.num_tiles == 0 or (m.num_single == 0 and m.num_seqs == 1) for m in metas)
+            if seen < (1 if steady else envs.TW_GRAPH_MIXED_SIGHTS) or len(self._graphs) >= 64:
                 return self._forward_and_logits(step_in, n_logits, greedy)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
