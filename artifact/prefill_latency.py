@@ -60,6 +60,8 @@ def run_mode(args, mode: str, world: int, rank: int) -> list[dict]:
                      "attention_ctas": plan.attention_ctas, "mlp_ctas": plan.mlp_ctas, "layers": cfg.num_layers})
         if rank == 0:
             print(f"[{mode}] Input length: {n}, Avg latency (ms): {wall_ms:.3f} (device {dev_ms:.3f})", flush=True)
+            # rows so far, so that a run cut short still leaves its measurements behind
+            write_rows(args.out, f"prefill_{args.model}_tp{world}_{mode}_partial", rows)
     ops.check_status()
     llm.shutdown()
     return rows

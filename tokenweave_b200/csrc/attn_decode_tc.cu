@@ -260,13 +260,18 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       uint32_t sv[16];
       tmem_ld_32x16(t_lane + COL_S + sb * DTC_NH, sv);
       tmem_wait_ld();
-      const bool valid = (t_begin + j) * DTC_BN + r < kv_len;
+      // Scores stay in the MMA's units until the exponent: max commutes with the (positive) scale, and
+      // 2^(s * scale - m) is one FMA and one MUFU. Only a tile that reaches past the context masks keys.
       float s[DTC_NH], mx[DTC_NH];
 #pragma unroll
-      for (int g = 0; g < DTC_NH; ++g) {
-        s[g] = valid ? __uint_as_float(sv[g]) * p.scale_log2 : -INFINITY;
-        mx[g] = (g < G) ? warp_max_redux(s[g]) : 0.f;
+      for (int g = 0; g < DTC_NH; ++g) s[g] = __uint_as_float(sv[g]);
+      if ((t_begin + j + 1) * DTC_BN > kv_len) {            // the same for the whole CTA
+        const bool valid = (t_begin + j) * DTC_BN + r < kv_len;
+#pragma unroll
+        for (int g = 0; g < DTC_NH; ++g) s[g] = valid ? s[g] : -INFINITY;
       }
+#pragma unroll
+      for (int g = 0; g < DTC_NH; ++g) mx[g] = (g < G) ? warp_max_redux(s[g]) : 0.f;
       float* xm = xchg + sb * 64;
       if (lane == 0) {
 #pragma unroll
@@ -275,8 +280,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
             *reinterpret_cast<float4*>(xm + sw * 16 + g4) = make_float4(mx[g4], mx[g4 + 1], mx[g4 + 2], mx[g4 + 3]);
       }
       dtc_softmax_sync();
-      bool rescale = false;
-      float alpha[DTC_NH], mt_all[DTC_NH];
+      float mt_all[DTC_NH];
 #pragma unroll
       for (int g4 = 0; g4 < DTC_NH; g4 += 4) {
         // the four warps' maxima of four heads: four 16-byte loads
@@ -287,22 +291,34 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
           c = *reinterpret_cast<const float4*>(xm + 32 + g4);
           d = *reinterpret_cast<const float4*>(xm + 48 + g4);
         }
-        mt_all[g4] = fmaxf(fmaxf(a.x, b.x), fmaxf(c.x, d.x));
-        mt_all[g4 + 1] = fmaxf(fmaxf(a.y, b.y), fmaxf(c.y, d.y));
-        mt_all[g4 + 2] = fmaxf(fmaxf(a.z, b.z), fmaxf(c.z, d.z));
-        mt_all[g4 + 3] = fmaxf(fmaxf(a.w, b.w), fmaxf(c.w, d.w));
+        mt_all[g4] = fmaxf(fmaxf(a.x, b.x), fmaxf(c.x, d.x)) * p.scale_log2;
+        mt_all[g4 + 1] = fmaxf(fmaxf(a.y, b.y), fmaxf(c.y, d.y)) * p.scale_log2;
+        mt_all[g4 + 2] = fmaxf(fmaxf(a.z, b.z), fmaxf(c.z, d.z)) * p.scale_log2;
+        mt_all[g4 + 3] = fmaxf(fmaxf(a.w, b.w), fmaxf(c.w, d.w)) * p.scale_log2;
       }
+      // The reference maxima move only when a head's maximum grew by more than 2^8 (rare after the first tiles):
+      // one combined test here, the per-head work in the branch. All 128 threads see the same maxima and decide alike.
+      bool rescale = false;
+      float alpha[DTC_NH];
+      if (j == 0) {
 #pragma unroll
-      for (int g = 0; g < DTC_NH; ++g) {
-        const float mt = mt_all[g];
-        alpha[g] = 1.f;
-        if (g < G) {
-          if (j == 0) {
-            m_ref[g] = mt;
-          } else if (mt > m_ref[g] + 8.f) {
-            alpha[g] = dtc_exp2(m_ref[g] - mt);
-            m_ref[g] = mt;
-            rescale = true;         // the same decision in all 128 threads: they all see the same maxima
+        for (int g = 0; g < DTC_NH; ++g)
+          if (g < G) m_ref[g] = mt_all[g];
+      } else {
+        float over = -1.f;
+#pragma unroll
+        for (int g = 0; g < DTC_NH; ++g)
+          if (g < G) over = fmaxf(over, mt_all[g] - m_ref[g]);
+        if (over > 8.f) {
+          rescale = true;
+#pragma unroll
+          for (int g = 0; g < DTC_NH; ++g) {
+            alpha[g] = 1.f;
+            if (g < G && mt_all[g] > m_ref[g] + 8.f) {
+              alpha[g] = dtc_exp2(m_ref[g] - mt_all[g]);
+              m_ref[g] = mt_all[g];
+            }
+            l_part[g] *= alpha[g];
           }
         }
       }
@@ -311,8 +327,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
 #pragma unroll
       for (int g = 0; g < DTC_NH; ++g) {
         if (g < G) {
-          const float pv = dtc_exp2(s[g] - m_ref[g]);
-          l_part[g] = l_part[g] * alpha[g] + pv;
+          const float pv = dtc_exp2(fmaf(s[g], p.scale_log2, -m_ref[g]));
+          l_part[g] += pv;
           *reinterpret_cast<__nv_bfloat16*>(p_buf + g * 128 + ((kc ^ (g & 7)) * 16) + ke * 2) = __float2bfloat16(pv);
         }
       }
@@ -656,13 +672,18 @@ attn_decode_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmK, const 
         uint32_t sv[16];
         tmem_ld_32x16(t_lane + COL_S + sb * DTC_NH, sv);
         tmem_wait_ld();
-        const bool valid = (it.t_begin + j) * DTC_BN + r < it.kv_len;
+        // Scores stay in the MMA's units until the exponent: max commutes with the (positive) scale, and
+        // 2^(s * scale - m) is one FMA and one MUFU. Only a tile that reaches past the context masks keys.
         float s[DTC_NH], mx[DTC_NH];
 #pragma unroll
-        for (int g = 0; g < DTC_NH; ++g) {
-          s[g] = valid ? __uint_as_float(sv[g]) * p.scale_log2 : -INFINITY;
-          mx[g] = (g < G) ? warp_max_redux(s[g]) : 0.f;
+        for (int g = 0; g < DTC_NH; ++g) s[g] = __uint_as_float(sv[g]);
+        if ((it.t_begin + j + 1) * DTC_BN > it.kv_len) {            // the same for the whole CTA
+          const bool valid = (it.t_begin + j) * DTC_BN + r < it.kv_len;
+#pragma unroll
+          for (int g = 0; g < DTC_NH; ++g) s[g] = valid ? s[g] : -INFINITY;
         }
+#pragma unroll
+        for (int g = 0; g < DTC_NH; ++g) mx[g] = (g < G) ? warp_max_redux(s[g]) : 0.f;
         float* xm = xchg + sb * 64;
         if (lane == 0) {
 #pragma unroll
@@ -671,8 +692,7 @@ attn_decode_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmK, const 
               *reinterpret_cast<float4*>(xm + sw * 16 + g4) = make_float4(mx[g4], mx[g4 + 1], mx[g4 + 2], mx[g4 + 3]);
         }
         dtc_softmax_sync();
-        bool rescale = false;
-        float alpha[DTC_NH], mt_all[DTC_NH];
+        float mt_all[DTC_NH];
 #pragma unroll
         for (int g4 = 0; g4 < DTC_NH; g4 += 4) {
           // the four warps' maxima of four heads: four 16-byte loads
@@ -683,32 +703,44 @@ attn_decode_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmK, const 
             c = *reinterpret_cast<const float4*>(xm + 32 + g4);
             d = *reinterpret_cast<const float4*>(xm + 48 + g4);
           }
-          mt_all[g4] = fmaxf(fmaxf(a.x, b.x), fmaxf(c.x, d.x));
-          mt_all[g4 + 1] = fmaxf(fmaxf(a.y, b.y), fmaxf(c.y, d.y));
-          mt_all[g4 + 2] = fmaxf(fmaxf(a.z, b.z), fmaxf(c.z, d.z));
-          mt_all[g4 + 3] = fmaxf(fmaxf(a.w, b.w), fmaxf(c.w, d.w));
+          mt_all[g4] = fmaxf(fmaxf(a.x, b.x), fmaxf(c.x, d.x)) * p.scale_log2;
+          mt_all[g4 + 1] = fmaxf(fmaxf(a.y, b.y), fmaxf(c.y, d.y)) * p.scale_log2;
+          mt_all[g4 + 2] = fmaxf(fmaxf(a.z, b.z), fmaxf(c.z, d.z)) * p.scale_log2;
+          mt_all[g4 + 3] = fmaxf(fmaxf(a.w, b.w), fmaxf(c.w, d.w)) * p.scale_log2;
         }
+        // The reference maxima move only when a head's maximum grew by more than 2^8 (rare after the first tiles):
+        // one combined test here, the per-head work in the branch. All 128 threads see the same maxima and decide alike.
+        bool rescale = false;
+        float alpha[DTC_NH];
+        if (j == 0) {
 #pragma unroll
-        for (int g = 0; g < DTC_NH; ++g) {
-          const float mt = mt_all[g];
-          alpha[g] = 1.f;
-          if (g < G) {
-            if (j == 0) {
-              m_ref[g] = mt;
-            } else if (mt > m_ref[g] + 8.f) {
-              alpha[g] = dtc_exp2(m_ref[g] - mt);
-              m_ref[g] = mt;
-              rescale = true;
+          for (int g = 0; g < DTC_NH; ++g)
+            if (g < G) m_ref[g] = mt_all[g];
+        } else {
+          float over = -1.f;
+#pragma unroll
+          for (int g = 0; g < DTC_NH; ++g)
+            if (g < G) over = fmaxf(over, mt_all[g] - m_ref[g]);
+          if (over > 8.f) {
+            rescale = true;
+#pragma unroll
+            for (int g = 0; g < DTC_NH; ++g) {
+              alpha[g] = 1.f;
+              if (g < G && mt_all[g] > m_ref[g] + 8.f) {
+                alpha[g] = dtc_exp2(m_ref[g] - mt_all[g]);
+                m_ref[g] = mt_all[g];
+              }
+              l_part[g] *= alpha[g];
             }
           }
         }
         uint8_t* p_buf = smem + DTP_OFF_P + sb * DTC_P_BYTES + (r >> 6) * (DTC_NH * 128);
-        const int kc = (r & 63) >> 3, ke = r & 7;
+        const int kc = (r & 63) >> 3, ke = r & 7;     // 16-byte chunk and element of this key inside its 64-key block
 #pragma unroll
         for (int g = 0; g < DTC_NH; ++g) {
           if (g < G) {
-            const float pv = dtc_exp2(s[g] - m_ref[g]);
-            l_part[g] = l_part[g] * alpha[g] + pv;
+            const float pv = dtc_exp2(fmaf(s[g], p.scale_log2, -m_ref[g]));
+            l_part[g] += pv;
             *reinterpret_cast<__nv_bfloat16*>(p_buf + g * 128 + ((kc ^ (g & 7)) * 16) + ke * 2) = __float2bfloat16(pv);
           }
         }
