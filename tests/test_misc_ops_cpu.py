@@ -38,3 +38,36 @@ def test_merge_cpu_is_exact_softmax_merge():
     empty = torch.full((H, 1), -math.inf)
     out2, _ = ref.merge_attn_states(parts[0][0], parts[0][1], parts[1][0], empty)
     assert torch.allclose(out2, parts[0][0], atol=1e-6)
+
+
+def test_gemm_plan_tables_answer_for_tuned_shapes_only():
+    """The tuned plan tables (bf16 and e4m3) give a kernel and a tile width for the linear-layer shapes they were
+    measured on, nothing for shapes far from any measurement, and keep the two operand types apart."""
+    from tokenweave_b200.ops import gemm_table
+    gemm_table.reload()
+    for fp8 in (False, True):
+        plan = gemm_table.lookup(4096, 8192, 1024, False, 0, fp8=fp8)       # o_proj of Llama-3.3-70B at TP = 8
+        assert plan // 1000 in (1, 2) and 64 <= plan % 1000 <= 512 and plan % 1000 % 32 == 0
+        sw = gemm_table.lookup(8192, 3584, 8192, True, 0, fp8=fp8)          # gate / up with the SwiGLU epilogue
+        assert sw // 1000 in (1, 2) and sw % 1000 <= 256                     # no wide tiles with SwiGLU
+        assert gemm_table.lookup(4096, 8200, 1000, False, 0, fp8=fp8) == 0  # never tuned: the cost model decides
+        assert gemm_table.lookup(7, 8192, 1024, False, 0, fp8=fp8) == 0     # too far from any measured M
+    gemm_table.set_enabled(False)
+    try:
+        assert gemm_table.lookup(4096, 8192, 1024, False, 0) == 0
+    finally:
+        gemm_table.set_enabled(True)
+
+
+def test_int8_gemm_reference_is_exact_and_scaled():
+    import torch
+    from tokenweave_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    a = torch.randint(-127, 128, (9, 64), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (5, 64), generator=g, dtype=torch.int8)
+    raw = ops.gemm_int8(a, w, None, None)
+    assert torch.equal(raw.float(), (a.long() @ w.long().t()).float().to(torch.bfloat16).float())
+    a_s, w_s = torch.rand(9) + 0.5, torch.rand(5) + 0.5
+    got = ops.gemm_int8(a, w, a_s, w_s, bias=torch.ones(5, dtype=torch.bfloat16))
+    want = (a.long() @ w.long().t()).float() * a_s[:, None] * w_s[None, :] + 1.0
+    torch.testing.assert_close(got.float(), want, rtol=1e-2, atol=1e-2)
