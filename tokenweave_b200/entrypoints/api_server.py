@@ -205,14 +205,20 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
                 return error(400, "streaming takes a single prompt")
 
             async def sse() -> AsyncIterator[str]:
-                sent = {}
+                sent, sent_tokens = {}, {}
                 try:
                     async for out in engine.generate(prompts[0], sp, rid + "-0", lora_request=lora):
                         for comp in out.outputs:
                             prev = sent.get(comp.index, 0)
                             delta = comp.text[prev:]
                             sent[comp.index] = len(comp.text)
-                            if delta or comp.finish_reason:
+                            # a chunk per batch of new tokens, also when they add no text yet (an incomplete
+                            # multi-byte character, a token outside the tokenizer's table): clients that time the
+                            # stream (time to first token, gaps) see every step
+                            n_prev = sent_tokens.get(comp.index, 0)
+                            new_tokens = len(comp.token_ids) > n_prev
+                            sent_tokens[comp.index] = len(comp.token_ids)
+                            if delta or new_tokens or comp.finish_reason:
                                 chunk = {"id": rid, "object": "text_completion", "created": created, "model": name,
                                          "choices": [{"index": comp.index, "text": delta, "logprobs": None,
                                                       "finish_reason": comp.finish_reason}]}
