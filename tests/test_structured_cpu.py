@@ -267,3 +267,82 @@ def test_constrained_text_is_always_well_formed_utf8():
                 out.decode("utf-8")                 # raises on half a character, overlong forms, surrogates
         assert accepted > 5
     assert DFA(r"[^a]").fullmatch("é") and DFA(r".").fullmatch("😀") and not DFA(r".").fullmatch(b"\xc3")
+
+
+ARITH = '''
+root   ::= expr
+expr   ::= term (("+" | "-") term)*          # sums of terms
+term   ::= number | "(" expr ")"
+number ::= [1-9] [0-9]{0,2}
+'''
+
+
+def _parse_arith(text: str) -> int:
+    """Recursive-descent recogniser of ARITH; returns the deepest parenthesis nesting, raises on a syntax error."""
+    pos, deepest = 0, 0
+
+    def expr(depth: int) -> None:
+        nonlocal pos
+        term(depth)
+        while pos < len(text) and text[pos] in "+-":
+            pos += 1
+            term(depth)
+
+    def term(depth: int) -> None:
+        nonlocal pos, deepest
+        if pos < len(text) and text[pos] == "(":
+            pos += 1
+            deepest = max(deepest, depth + 1)
+            expr(depth + 1)
+            assert pos < len(text) and text[pos] == ")", text
+            pos += 1
+        else:
+            start = pos
+            while pos < len(text) and text[pos].isdigit():
+                pos += 1
+            assert 1 <= pos - start <= 3 and text[start] != "0", text
+
+    expr(0)
+    assert pos == len(text), text
+    return deepest
+
+
+def test_grammar_lowering_accepts_the_bounded_language():
+    from tokenweave_b200.engine.structured import GrammarError, grammar_to_regex
+    d = DFA(grammar_to_regex(ARITH, max_depth=2))
+    for good in ["7", "12+3", "(1+2)-3", "((4))", "1-(2+(3))+999"]:
+        assert d.fullmatch(good.encode()), good
+        assert _parse_arith(good) <= 2
+    for bad in ["", "1+", "()", "01", "1234", "(((5)))", "a", "1 + 2"]:
+        assert not d.fullmatch(bad.encode()), bad
+    assert DFA(grammar_to_regex(ARITH, max_depth=3)).fullmatch(b"(((5)))")
+    # Lark-style colons, single quotes, a start rule by name, comments, repetition bounds, negated classes
+    lark = """start: item (',' item){0,2}
+item: [a-c]+ | '"' [^"]* '"'   # words or quoted text
+"""
+    d2 = DFA(grammar_to_regex(lark))
+    assert d2.fullmatch(b'ab,"x y",c') and not d2.fullmatch(b"a,b,c,a") and not d2.fullmatch(b"d")
+    with pytest.raises(GrammarError):
+        grammar_to_regex("root ::= missing")
+    with pytest.raises(GrammarError):
+        grammar_to_regex('root ::= "(" root ")"')          # no derivation ends within the bound
+    with pytest.raises(GrammarError):
+        grammar_to_regex('root ::= ("a"')
+
+
+def test_grammar_constrained_generation_end_to_end():
+    """Sampled text of a random-weight model must be a sentence of the grammar; the server takes the same field."""
+    from tokenweave_b200 import LLM, SamplingParams
+    llm = LLM("tiny-llama", dtype="float32", device="cpu", block_size=16, max_num_batched_tokens=256, seed=3)
+    outs = llm.generate(["calc: "] * 3, [SamplingParams(temperature=1.0, seed=s, max_tokens=60, guided_grammar=ARITH)
+                                        for s in (1, 2, 3)])
+    for o in outs:
+        text = o.outputs[0].text
+        if o.outputs[0].finish_reason == "stop":
+            assert _parse_arith(text) <= 3, text             # a complete sentence within the nesting bound
+        else:                                                # cut by max_tokens: still a prefix of a sentence
+            assert all(c in "0123456789+-()" for c in text), text
+    assert any(o.outputs[0].finish_reason == "stop" for o in outs)
+    with pytest.raises(ValueError):
+        llm.generate(["x"], SamplingParams(guided_grammar="root ::= nowhere"))
+    llm.shutdown()

@@ -92,7 +92,7 @@ class LLMEngine:
                 sp.guided_choice_token_ids = [list(self.tokenizer.encode(c, add_special_tokens=False))
                                               for c in sp.guided_choice]
                 sp.eos_token_id = self.eos_token_id
-            if (sp.guided_regex or sp.guided_json is not None) and not sp.guided_pattern:
+            if (sp.guided_regex or sp.guided_json is not None or sp.guided_grammar) and not sp.guided_pattern:
                 from . import structured
                 if self.eos_token_id is None:
                     raise ValueError("structured output ends a request through the end-of-sequence token; "

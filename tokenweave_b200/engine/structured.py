@@ -464,6 +464,231 @@ def json_schema_to_regex(schema: Union[str, dict, bool, None], max_depth: int = 
 
 
 # ---- vocabulary trie and token masks ---------------------------------------------------------------------------
+# ---- context-free grammars, lowered to a regular expression of bounded nesting ----------------------------------
+class GrammarError(ValueError):
+    pass
+
+
+class _GrammarParser:
+    """GBNF / EBNF text -> ``{rule: alternatives}`` where an alternative is a list of items and an item is
+    ``("lit", text)``, ``("class", source)``, ``("any",)``, ``("ref", name)``, ``("group", alternatives)`` or
+    ``("rep", item, lo, hi)``. Rules are ``name ::= ...`` (``name: ...`` is accepted too), alternatives are
+    separated by ``|``, items are string literals in double or single quotes, character classes ``[...]``, ``.``,
+    rule names, parenthesised groups, each with an optional ``?`` ``*`` ``+`` or ``{m,n}``; ``#`` starts a comment.
+    A rule ends where the next ``name ::=`` begins."""
+
+    def __init__(self, text: str):
+        self.t = text
+        self.i = 0
+
+    def _ws(self, newlines: bool = True) -> None:
+        while self.i < len(self.t):
+            c = self.t[self.i]
+            if c == "#":
+                while self.i < len(self.t) and self.t[self.i] != "\n":
+                    self.i += 1
+            elif c in " \t\r" or (newlines and c == "\n"):
+                self.i += 1
+            else:
+                return
+
+    def _name(self) -> Optional[str]:
+        j = self.i
+        while j < len(self.t) and (self.t[j].isalnum() or self.t[j] in "_-"):
+            j += 1
+        if j == self.i:
+            return None
+        name, self.i = self.t[self.i:j], j
+        return name
+
+    def _at_rule_start(self) -> bool:
+        save = self.i
+        name = self._name()
+        ok = False
+        if name is not None:
+            self._ws(False)
+            ok = self.t.startswith("::=", self.i) or (self.t.startswith(":", self.i) and not self.t.startswith("::", self.i))
+        self.i = save
+        return ok
+
+    def parse(self) -> dict:
+        rules: dict = {}
+        self._ws()
+        while self.i < len(self.t):
+            name = self._name()
+            if name is None:
+                raise GrammarError(f"rule name expected at offset {self.i}")
+            self._ws(False)
+            if self.t.startswith("::=", self.i):
+                self.i += 3
+            elif self.t.startswith(":", self.i):
+                self.i += 1
+            else:
+                raise GrammarError(f"'::=' expected after rule {name!r}")
+            if name in rules:
+                raise GrammarError(f"rule {name!r} defined twice")
+            rules[name] = self._alternatives(top=True)
+            self._ws()
+        if not rules:
+            raise GrammarError("empty grammar")
+        return rules
+
+    def _alternatives(self, top: bool) -> list:
+        alts, cur = [], []
+        while True:
+            self._ws()
+            if self.i >= len(self.t) or (top and self._at_rule_start()):
+                break
+            c = self.t[self.i]
+            if c == "|":
+                self.i += 1
+                alts.append(cur)
+                cur = []
+                continue
+            if c == ")":
+                if top:
+                    raise GrammarError(f"unbalanced ')' at offset {self.i}")
+                break
+            cur.append(self._postfix(self._item()))
+        alts.append(cur)
+        return alts
+
+    def _item(self):
+        c = self.t[self.i]
+        if c in "\"'":
+            j, out = self.i + 1, []
+            while j < len(self.t) and self.t[j] != c:
+                if self.t[j] == "\\" and j + 1 < len(self.t):
+                    e = self.t[j + 1]
+                    out.append({"n": "\n", "t": "\t", "r": "\r"}.get(e, e))
+                    j += 2
+                else:
+                    out.append(self.t[j])
+                    j += 1
+            if j >= len(self.t):
+                raise GrammarError("unterminated string literal")
+            self.i = j + 1
+            return ("lit", "".join(out))
+        if c == "[":
+            j = self.i + 1
+            if j < len(self.t) and self.t[j] == "^":
+                j += 1
+            if j < len(self.t) and self.t[j] == "]":
+                j += 1
+            while j < len(self.t) and self.t[j] != "]":
+                j += 2 if self.t[j] == "\\" else 1
+            if j >= len(self.t):
+                raise GrammarError("unterminated character class")
+            src, self.i = self.t[self.i:j + 1], j + 1
+            return ("class", src)
+        if c == ".":
+            self.i += 1
+            return ("any",)
+        if c == "(":
+            self.i += 1
+            alts = self._alternatives(top=False)
+            if self.i >= len(self.t) or self.t[self.i] != ")":
+                raise GrammarError("missing ')'")
+            self.i += 1
+            return ("group", alts)
+        name = self._name()
+        if name is None:
+            raise GrammarError(f"unexpected {c!r} at offset {self.i}")
+        return ("ref", name)
+
+    def _postfix(self, item):
+        while self.i < len(self.t):
+            c = self.t[self.i]
+            if c == "?":
+                item, self.i = ("rep", item, 0, 1), self.i + 1
+            elif c == "*":
+                item, self.i = ("rep", item, 0, None), self.i + 1
+            elif c == "+":
+                item, self.i = ("rep", item, 1, None), self.i + 1
+            elif c == "{":
+                j = self.t.find("}", self.i)
+                parts = self.t[self.i + 1:j].split(",") if j > 0 else []
+                if not parts or not parts[0].strip().isdigit() or len(parts) > 2:
+                    raise GrammarError(f"bad repetition at offset {self.i}")
+                lo = int(parts[0])
+                hi = lo if len(parts) == 1 else (int(parts[1]) if parts[1].strip() else None)
+                item, self.i = ("rep", item, lo, hi), j + 1
+            else:
+                break
+        return item
+
+
+def grammar_to_regex(grammar: str, start: Optional[str] = None, max_depth: int = 3) -> str:
+    """Regular expression of the strings a context-free grammar derives with every rule nested in itself at most
+    ``max_depth`` times (the counterpart of the reference's ``guided_grammar``, which hands the grammar to xgrammar's
+    pushdown automaton, vllm/v1/structured_output/backend_xgrammar.py; here the bounded language goes through the
+    same DFA and token-mask machinery as regular expressions and JSON schemas). A derivation that would nest a rule
+    deeper is left out; a grammar whose start rule has no derivation within the bound is an error. The start rule is
+    ``start``, else ``root``, else the first rule."""
+    rules = _GrammarParser(grammar).parse()
+    if start is None:
+        start = "root" if "root" in rules else ("start" if "start" in rules else next(iter(rules)))
+    if start not in rules:
+        raise GrammarError(f"no rule {start!r}")
+
+    def alts_rx(alts, depth: dict) -> Optional[str]:
+        out = []
+        for items in alts:
+            parts = []
+            for it in items:
+                r = item_rx(it, depth)
+                if r is None:
+                    parts = None
+                    break
+                parts.append(r)
+            if parts is not None:
+                out.append("".join(parts))
+        if not out:
+            return None
+        return out[0] if len(out) == 1 else "(" + "|".join(out) + ")"
+
+    def item_rx(it, depth: dict) -> Optional[str]:
+        kind = it[0]
+        if kind == "lit":
+            return regex_escape(it[1])
+        if kind == "class":
+            return it[1]
+        if kind == "any":
+            return "."
+        if kind == "group":
+            r = alts_rx(it[1], depth)
+            return None if r is None else "(" + r + ")"
+        if kind == "ref":
+            name = it[1]
+            if name not in rules:
+                raise GrammarError(f"rule {name!r} is used but not defined")
+            d = depth.get(name, 0)
+            if d > max_depth:
+                return None
+            depth[name] = d + 1
+            r = alts_rx(rules[name], depth)
+            depth[name] = d
+            return None if r is None else "(" + r + ")"
+        _, inner, lo, hi = it
+        r = item_rx(inner, depth)
+        if r is None:
+            return "" if lo == 0 else None            # zero repetitions remain possible
+        if (lo, hi) == (0, 1):
+            return "(" + r + ")?"
+        if (lo, hi) == (0, None):
+            return "(" + r + ")*"
+        if (lo, hi) == (1, None):
+            return "(" + r + ")+"
+        return "(" + r + "){" + str(lo) + ("" if hi == lo else "," + ("" if hi is None else str(hi))) + "}"
+
+    rx = alts_rx(rules[start], {start: 1})
+    if rx is None:
+        raise GrammarError(f"rule {start!r} derives nothing within {max_depth} levels of nesting")
+    if len(rx) > 200_000:
+        raise GrammarError("the grammar unrolls into a regular expression that is too large; lower max_depth")
+    return rx
+
+
 def token_bytes_table(tokenizer, vocab_size: int) -> list[bytes]:
     """UTF-8 bytes every token contributes to the output text (empty for special / unknown tokens)."""
     if hasattr(tokenizer, "token_bytes"):
@@ -580,6 +805,9 @@ def constraint_pattern(sp) -> Optional[str]:
     gj = getattr(sp, "guided_json", None)
     if gj is not None and gj is not False:
         return json_schema_to_regex(gj)
+    gg = getattr(sp, "guided_grammar", None)
+    if gg:
+        return grammar_to_regex(gg)
     return None
 
 

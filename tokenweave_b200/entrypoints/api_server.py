@@ -27,7 +27,7 @@ logger = init_logger(__name__)
 _SAMPLING_FIELDS = ("n", "temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty",
                     "repetition_penalty", "seed", "stop", "stop_token_ids", "max_tokens", "min_tokens", "ignore_eos",
                     "skip_special_tokens", "logit_bias", "allowed_token_ids", "bad_words_token_ids", "guided_choice",
-                    "prompt_logprobs", "guided_regex", "guided_json", "include_stop_str_in_output",
+                    "prompt_logprobs", "guided_regex", "guided_json", "guided_grammar", "include_stop_str_in_output",
                     "truncate_prompt_tokens")
 
 

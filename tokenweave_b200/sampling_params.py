@@ -46,6 +46,8 @@ class SamplingParams:
     # ``{}`` admits any JSON value). The engine lowers both to ``guided_pattern``; see engine/structured.py.
     guided_regex: Optional[str] = None
     guided_json: Union[None, str, dict] = None
+    # a context-free grammar (GBNF / EBNF text); served with every rule nested in itself a bounded number of times
+    guided_grammar: Optional[str] = None
     guided_pattern: Optional[str] = None
 
     def __post_init__(self):
@@ -82,7 +84,8 @@ class SamplingParams:
         return (self.presence_penalty != 0.0 or self.frequency_penalty != 0.0 or self.repetition_penalty != 1.0
                 or bool(self.logit_bias) or self.allowed_token_ids is not None or bool(self.bad_words_token_ids)
                 or self.min_tokens > 0 or bool(self.guided_choice_token_ids)
-                or bool(self.guided_regex) or self.guided_json is not None or bool(self.guided_pattern))
+                or bool(self.guided_regex) or self.guided_json is not None or bool(self.guided_grammar)
+                or bool(self.guided_pattern))
 
     def clone(self) -> "SamplingParams":
         import copy
