@@ -76,3 +76,53 @@ def test_chat_endpoint_with_tools():
             assert c.post("/v1/chat/completions", json={**body, "tool_choice": {"function": {"name": "zzz"}}}).status_code == 400
     finally:
         eng.shutdown()
+
+
+def test_named_parsers_and_reasoning_split():
+    """The spellings of the model families, each alone and through ``auto``; the <think> splitter."""
+    mistral = '[TOOL_CALLS] [{"name": "get_weather", "arguments": {"city": "Paris", "unit": "c"}}]'
+    pythonic = '[get_weather(city="Paris", unit="c"), add(a=1, b=2)]'
+    semis = '{"name": "add", "parameters": {"a": 1, "b": 2}}; {"name": "add", "parameters": {"a": 3, "b": 4}}'
+    hermes = 'sure <tool_call>{"name": "add", "arguments": {"a": 1, "b": 2}}</tool_call>'
+    for text, parser, n in ((mistral, "mistral", 1), (pythonic, "pythonic", 2), (semis, "llama3_json", 2),
+                            (hermes, "hermes", 1)):
+        for p in (parser, "auto"):
+            content, calls = tc.calls_from_text(text, TOOLS, p)
+            assert len(calls) == n and all(c["type"] == "function" for c in calls), (p, text)
+        # another family's parser leaves the text alone
+        other = "hermes" if parser != "hermes" else "mistral"
+        assert tc.calls_from_text(text, TOOLS, other) == (text, [])
+    _, calls = tc.calls_from_text(pythonic, TOOLS, "pythonic")
+    assert json.loads(calls[1]["function"]["arguments"]) == {"a": 1, "b": 2}
+    # not calls: an unknown function, positional arguments, a non-literal argument, a plain list
+    for text in ('[nope(a=1)]', '[add(1, 2)]', '[add(a=x, b=2)]', '[1, 2]'):
+        assert tc.calls_from_text(text, TOOLS, "pythonic") == (text, [])
+    with pytest.raises(ValueError):
+        tc.calls_from_text("x", TOOLS, "xml")
+    assert tc.split_reasoning("<think>two plus two</think> 4") == ("two plus two", "4")
+    assert tc.split_reasoning("carry the one</think>12") == ("carry the one", "12")
+    assert tc.split_reasoning("<think>never finished") == ("never finished", None)
+    assert tc.split_reasoning("no tags") == (None, "no tags")
+
+
+def test_server_options_for_parsers():
+    pytest.importorskip("fastapi")
+    from tokenweave_b200.config import EngineArgs
+    from tokenweave_b200.engine.async_engine import AsyncLLMEngine
+    from tokenweave_b200.entrypoints.api_server import build_app
+    pytest.importorskip("httpx")
+    from starlette.testclient import TestClient
+    eng = AsyncLLMEngine.from_engine_args(EngineArgs(model="tiny-llama", dtype="float32", device="cpu", block_size=16,
+                                                     max_num_batched_tokens=256, seed=1))
+    try:
+        with pytest.raises(ValueError):
+            build_app(eng, "tiny", tool_call_parser="xml")
+        with pytest.raises(ValueError):
+            build_app(eng, "tiny", reasoning_parser="other")
+        with TestClient(build_app(eng, "tiny", tool_call_parser="pythonic", reasoning_parser="deepseek_r1")) as c:
+            r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 6,
+                                                     "temperature": 0})
+            msg = r.json()["choices"][0]["message"]
+            assert r.status_code == 200 and msg["content"] is not None and "reasoning_content" not in msg
+    finally:
+        eng.shutdown()

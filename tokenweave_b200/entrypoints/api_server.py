@@ -69,10 +69,18 @@ def _logprobs_block(comp, tokenizer) -> Optional[dict]:
 
 
 def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
-              lora_modules: Optional[dict] = None):
+              lora_modules: Optional[dict] = None, tool_call_parser: str = "auto",
+              reasoning_parser: Optional[str] = None):
     """``lora_modules`` maps a served adapter name to its directory: a request whose ``model`` field is
     such a name runs through that adapter (``--lora-modules name=path`` of the reference's server,
-    vllm/entrypoints/openai/serving_models.py)."""
+    vllm/entrypoints/openai/serving_models.py). ``tool_call_parser`` names the spelling of tool calls to look
+    for in free text (entrypoints/tool_calls.py); ``reasoning_parser="deepseek_r1"`` moves ``<think>`` blocks of
+    complete (non-streamed, or tool-calling) chat answers into ``reasoning_content``."""
+    from .tool_calls import TOOL_CALL_PARSERS
+    if tool_call_parser not in TOOL_CALL_PARSERS:
+        raise ValueError(f"unknown tool-call parser {tool_call_parser!r}")
+    if reasoning_parser not in (None, "deepseek_r1"):
+        raise ValueError(f"unknown reasoning parser {reasoning_parser!r}")
     from fastapi import FastAPI, Request
     from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
@@ -370,16 +378,24 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
 
         def message_of(comp) -> tuple[dict, Optional[str]]:
             """Assistant message (with tool calls where the text holds some) and the finish reason."""
+            text, reasoning = comp.text, None
+            if reasoning_parser and forced is None:
+                reasoning, text = tc.split_reasoning(text)
             if not tools:
-                return {"role": "assistant", "content": comp.text}, comp.finish_reason
+                msg = {"role": "assistant", "content": text}
+                if reasoning:
+                    msg["reasoning_content"] = reasoning
+                return msg, comp.finish_reason
             if forced is not None:
                 try:
                     calls, content = tc.calls_from_forced(comp.text, tools, tool_choice), None
                 except (ValueError, KeyError, TypeError):      # cut off by max_tokens before the JSON closed
                     calls, content = [], comp.text
             else:
-                content, calls = tc.calls_from_text(comp.text, tools)
+                content, calls = tc.calls_from_text(text or "", tools, tool_call_parser)
             msg = {"role": "assistant", "content": content}
+            if reasoning:
+                msg["reasoning_content"] = reasoning
             if calls:
                 msg["tool_calls"] = calls
             return msg, ("tool_calls" if calls and comp.finish_reason == "stop" else comp.finish_reason)
@@ -445,6 +461,12 @@ def main() -> None:
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--served-model-name", default=None)
     ap.add_argument("--chat-template", default=None, help="a Jinja chat template (file or literal) replacing the tokenizer's")
+    ap.add_argument("--tool-call-parser", default="auto",
+                    help="spelling of tool calls in free text: auto, hermes, llama3_json, mistral, pythonic")
+    ap.add_argument("--enable-auto-tool-choice", action="store_true",
+                    help="accepted for command lines written for the reference's server (tool_choice=auto is always on)")
+    ap.add_argument("--reasoning-parser", default=None, choices=["deepseek_r1"],
+                    help="move <think> ... </think> blocks of chat answers into reasoning_content")
     ap.add_argument("--lora-modules", nargs="*", default=[], metavar="NAME=PATH",
                     help="adapters to serve; a request selects one by its name in the model field (needs --enable-lora)")
     EngineArgs.add_cli_args(ap)
@@ -466,7 +488,8 @@ def main() -> None:
         engine.engine.tokenizer.chat_template = tpl
     import uvicorn
     try:
-        uvicorn.run(build_app(engine, ns.served_model_name, lora_modules), host=ns.host, port=ns.port, log_level="info")
+        uvicorn.run(build_app(engine, ns.served_model_name, lora_modules, ns.tool_call_parser, ns.reasoning_parser),
+                    host=ns.host, port=ns.port, log_level="info")
     finally:
         engine.shutdown()
 
