@@ -27,6 +27,14 @@ def main():
     doc = llm.generate(["JSON: "], SamplingParams(temperature=1.0, seed=2, max_tokens=64, guided_json=schema))[0]
     print("json schema:", json.loads(doc.outputs[0].text))
 
+    grammar = '''
+        root ::= expr
+        expr ::= term (("+" | "-") term)*
+        term ::= [1-9] [0-9]? | "(" expr ")"
+    '''
+    calc = llm.generate(["calc: "], SamplingParams(temperature=1.0, seed=4, max_tokens=40, guided_grammar=grammar))[0]
+    print("grammar    :", calc.outputs[0].text)
+
     pick = llm.generate(["Colour? "], SamplingParams(temperature=1.0, seed=3, max_tokens=8,
                                                     guided_choice=["red", "green", "blue"]))[0]
     print("choice     :", pick.outputs[0].text)
@@ -46,6 +54,13 @@ def main():
     print("spec decode:", len(rep.outputs[0].token_ids), "tokens,", sched.num_accepted_tokens, "of",
           sched.num_draft_tokens, "drafts confirmed")
     llm.shutdown()
+
+    # 8-bit weights and activations (on a GPU: the tcgen05 kind::i8 GEMM; here the reference arithmetic)
+    q = LLM("tiny-llama", dtype="float32", device="cpu", block_size=16, max_num_batched_tokens=256, seed=3,
+            quantization="int8")
+    out = q.generate(["abc"], SamplingParams(temperature=0, max_tokens=4))[0]
+    print("int8 model :", out.outputs[0].token_ids)
+    q.shutdown()
 
 
 if __name__ == "__main__":
