@@ -71,3 +71,19 @@ def test_int8_gemm_reference_is_exact_and_scaled():
     got = ops.gemm_int8(a, w, a_s, w_s, bias=torch.ones(5, dtype=torch.bfloat16))
     want = (a.long() @ w.long().t()).float() * a_s[:, None] * w_s[None, :] + 1.0
     torch.testing.assert_close(got.float(), want, rtol=1e-2, atol=1e-2)
+
+
+def test_report_renders_the_committed_measurements():
+    """artifact/report.py turns the benchmark CSVs into the figure tables (Markdown)."""
+    import os
+    import sys
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "artifact")
+    sys.path.insert(0, root)
+    import report
+    text = report.report(os.path.join(root, "csvs"))
+    assert "fused_microbench_tp8.csv" in text and "vs reference" in text
+    assert "| 65536 | 1879.1 | 2295.2 | 1931.4 | 1.22x | 1.03x |" in text
+    assert "throughput_llama70b_tp8_1024_64.csv" in text and "1.34x" in text
+    rows = [{"model": "m", "tp": "2", "mode": "overlap", "tokens": "8", "latency_ms": "2.0", "device_ms": "1.0"},
+            {"model": "m", "tp": "2", "mode": "no_ar", "tokens": "8", "latency_ms": "1.0", "device_ms": "0.5"}]
+    assert "| 8 | 1.0 | 0.5 | 0.50x |" in report.prefill_table(rows)
