@@ -109,3 +109,54 @@ def test_connector_under_tp2(tmp_path):
         seq.append(int(naive_logits(cfg, st, seq)[-1].argmax()))
     run_ranks(_tp_rank, 2, ckpt, store, p1, p2, seq[len(p2):])
     assert len(_stored(store)) == 2 * 6              # six blocks, one file per rank
+
+
+def test_blocks_travel_through_a_tcp_store(tmp_path):
+    """TcpStoreConnector: the producer engine hosts a key-value store, the consumer connects to it over a socket,
+    finds the producer's blocks and computes only the tail of its prompts."""
+    from tw_testing import free_port
+    from tokenweave_b200.engine.kv_connector import decode_block, encode_block
+    k = torch.randn(2, 16, 2, 8).to(torch.bfloat16)
+    k2, v2 = decode_block(encode_block(k, k + 1))
+    assert torch.equal(k2, k) and torch.equal(v2, k + 1) and k2.dtype == torch.bfloat16
+    with pytest.raises(ValueError):
+        decode_block(encode_block(k, k)[:-4])
+
+    cfg = ModelConfig(name="tiny-llama", **MODEL_PRESETS["tiny-llama"])
+    st = make_hf_state(cfg, seed=33)
+    ckpt = str(tmp_path / "ckpt")
+    save_hf_checkpoint(st, hf_config_dict(cfg), ckpt)
+    port = free_port()
+
+    def tcp(role, host, master):
+        return {"kv_connector": "TcpStoreConnector", "kv_role": role,
+                "kv_connector_extra_config": {"host": host, "port": port, "is_master": master, "timeout_s": 20}}
+
+    g = torch.Generator().manual_seed(1)
+    shared = torch.randint(0, cfg.vocab_size, (100,), generator=g).tolist()
+    p1, p2 = shared + [7, 8, 9], shared + [11, 12, 13, 14, 15]
+    sp = SamplingParams(temperature=0, max_tokens=4, ignore_eos=True)
+    args = dict(dtype="float32", device="cpu", skip_tokenizer_init=True, block_size=16, max_num_batched_tokens=64)
+    producer = LLM(ckpt, kv_transfer_config=tcp("kv_producer", "127.0.0.1", True), **args)
+    try:
+        outs, computed = _prefill_tokens(producer, [p1], sp)
+        assert computed == len(p1) + 3
+        # "localhost" instead of "127.0.0.1": the consumer does not find the store object of this process and
+        # goes through the socket, as an engine on another machine would
+        consumer = LLM(ckpt, kv_transfer_config=tcp("kv_consumer", "localhost", False), **args)
+        try:
+            outs2, computed2 = _prefill_tokens(consumer, [p2, p1], sp)
+            assert computed2 == (len(p2) - 96 + 3) + (len(p1) - 96 + 3)        # six blocks of each prompt came over
+            for out, p in zip(outs2, (p2, p1)):
+                seq = list(p)
+                for _ in range(4):
+                    seq.append(int(naive_logits(cfg, st, seq)[-1].argmax()))
+                assert out.outputs[0].token_ids == seq[len(p):]
+        finally:
+            consumer.shutdown()
+    finally:
+        producer.shutdown()
+    with pytest.raises(ValueError):
+        KVTransferConfig.from_user({"kv_connector": "TcpStoreConnector", "kv_role": "kv_both"})          # no port
+    with pytest.raises(ValueError):
+        KVTransferConfig.from_user({"kv_connector": "Carrier pigeon", "kv_role": "kv_both"})

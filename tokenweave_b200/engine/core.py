@@ -41,8 +41,9 @@ class EngineCore:
         # KV connector: the scheduler side only asks which blocks the store can supply; the workers move the data
         self.kv_transfer = config.kv_transfer
         if self.kv_transfer is not None:
-            from .kv_connector import SharedStorageConnector, kv_fingerprint
-            lookup = SharedStorageConnector(self.kv_transfer, 0, config.parallel.world_size, kv_fingerprint(config))
+            from .kv_connector import kv_fingerprint, make_connector
+            lookup = make_connector(self.kv_transfer, 0, config.parallel.world_size, kv_fingerprint(config),
+                                    host_store=True)
             self.kv.track_published = self.kv_transfer.can_save
             if self.kv_transfer.can_load:
                 self.scheduler.connector = lookup

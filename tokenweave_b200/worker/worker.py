@@ -190,10 +190,10 @@ class Worker:
     # ---- KV connector (engine/kv_connector.py): blocks to / from the external store -------------------------
     def _kv_connector(self):
         if getattr(self, "_connector", None) is None:
-            from ..engine.kv_connector import SharedStorageConnector, kv_fingerprint
+            from ..engine.kv_connector import kv_fingerprint, make_connector
             tp = pstate.get_tp()
-            self._connector = SharedStorageConnector(self.config.kv_transfer, tp.global_rank, tp.global_size,
-                                                     kv_fingerprint(self.config))
+            self._connector = make_connector(self.config.kv_transfer, tp.global_rank, tp.global_size,
+                                             kv_fingerprint(self.config))
         return self._connector
 
     def save_kv_blocks(self, items: list) -> None:
