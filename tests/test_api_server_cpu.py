@@ -179,3 +179,19 @@ def test_score_version_and_stop_string_options(client):
     kept = client.post("/v1/completions", json={**body, "stop": [needle], "include_stop_str_in_output": True}).json()["choices"][0]
     assert cut["finish_reason"] == "stop" and full.startswith(cut["text"]) and needle not in cut["text"]
     assert kept["text"] == cut["text"] + needle
+
+
+def test_api_key_and_cors(engine):
+    from starlette.testclient import TestClient
+    from tokenweave_b200.entrypoints.api_server import build_app
+    with TestClient(build_app(engine, "tiny", api_key="s3cret", allowed_origins=["https://ui.example"])) as c:
+        body = {"prompt": "hi", "max_tokens": 2, "temperature": 0}
+        assert c.get("/health").status_code == 200                        # liveness needs no key
+        assert c.post("/v1/completions", json=body).status_code == 401
+        assert c.post("/v1/completions", json=body, headers={"Authorization": "Bearer wrong"}).status_code == 401
+        ok = c.post("/v1/completions", json=body, headers={"Authorization": "Bearer s3cret"})
+        assert ok.status_code == 200 and ok.json()["choices"][0]["finish_reason"] == "length"
+        assert c.get("/v1/models", headers={"Authorization": "Bearer s3cret"}).status_code == 200
+        pre = c.options("/v1/completions", headers={"Origin": "https://ui.example",
+                                                    "Access-Control-Request-Method": "POST"})
+        assert pre.headers.get("access-control-allow-origin") == "https://ui.example"

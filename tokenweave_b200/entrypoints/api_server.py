@@ -12,6 +12,7 @@ Tensor-parallel serving uses the multiprocess executor (one worker process per G
 """
 import argparse
 import json
+import os
 import time
 import uuid
 from typing import Any, AsyncIterator, Optional
@@ -70,12 +71,15 @@ def _logprobs_block(comp, tokenizer) -> Optional[dict]:
 
 def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
               lora_modules: Optional[dict] = None, tool_call_parser: str = "auto",
-              reasoning_parser: Optional[str] = None):
+              reasoning_parser: Optional[str] = None, api_key: Optional[str] = None,
+              allowed_origins: Optional[list] = None):
     """``lora_modules`` maps a served adapter name to its directory: a request whose ``model`` field is
     such a name runs through that adapter (``--lora-modules name=path`` of the reference's server,
     vllm/entrypoints/openai/serving_models.py). ``tool_call_parser`` names the spelling of tool calls to look
     for in free text (entrypoints/tool_calls.py); ``reasoning_parser="deepseek_r1"`` moves ``<think>`` blocks of
-    complete (non-streamed, or tool-calling) chat answers into ``reasoning_content``."""
+    complete (non-streamed, or tool-calling) chat answers into ``reasoning_content``. ``api_key``: every ``/v1`` route
+    then wants ``Authorization: Bearer <key>`` (``--api-key`` / the ``TW_API_KEY`` variable; the reference's
+    vllm/entrypoints/openai/api_server.py authentication middleware); ``allowed_origins`` switches CORS headers on."""
     from .tool_calls import TOOL_CALL_PARSERS
     if tool_call_parser not in TOOL_CALL_PARSERS:
         raise ValueError(f"unknown tool-call parser {tool_call_parser!r}")
@@ -87,6 +91,20 @@ def build_app(engine: AsyncLLMEngine, served_model_name: Optional[str] = None,
     from ..lora import LoRARequest
 
     app = FastAPI(title="tokenweave_b200")
+    if allowed_origins:
+        from fastapi.middleware.cors import CORSMiddleware
+        app.add_middleware(CORSMiddleware, allow_origins=list(allowed_origins), allow_methods=["*"], allow_headers=["*"])
+    if api_key:
+        import hmac
+
+        @app.middleware("http")
+        async def authenticate(request: Request, call_next):
+            if request.method != "OPTIONS" and request.url.path.startswith("/v1"):
+                given = request.headers.get("Authorization", "")
+                if not hmac.compare_digest(given.encode(), ("Bearer " + api_key).encode()):
+                    return JSONResponse({"error": {"message": "invalid or missing API key", "type": "authentication_error",
+                                                   "code": 401}}, status_code=401)
+            return await call_next(request)
     model_cfg = engine.engine.config.model
     name = served_model_name or model_cfg.name
     tokenizer = engine.engine.tokenizer
@@ -467,6 +485,9 @@ def main() -> None:
                     help="accepted for command lines written for the reference's server (tool_choice=auto is always on)")
     ap.add_argument("--reasoning-parser", default=None, choices=["deepseek_r1"],
                     help="move <think> ... </think> blocks of chat answers into reasoning_content")
+    ap.add_argument("--api-key", default=os.environ.get("TW_API_KEY"),
+                    help="require 'Authorization: Bearer <key>' on the /v1 routes (default: the TW_API_KEY variable)")
+    ap.add_argument("--allowed-origins", nargs="*", default=None, help="origins to answer with CORS headers")
     ap.add_argument("--lora-modules", nargs="*", default=[], metavar="NAME=PATH",
                     help="adapters to serve; a request selects one by its name in the model field (needs --enable-lora)")
     EngineArgs.add_cli_args(ap)
@@ -488,7 +509,8 @@ def main() -> None:
         engine.engine.tokenizer.chat_template = tpl
     import uvicorn
     try:
-        uvicorn.run(build_app(engine, ns.served_model_name, lora_modules, ns.tool_call_parser, ns.reasoning_parser),
+        uvicorn.run(build_app(engine, ns.served_model_name, lora_modules, ns.tool_call_parser, ns.reasoning_parser,
+                              ns.api_key, ns.allowed_origins),
                     host=ns.host, port=ns.port, log_level="info")
     finally:
         engine.shutdown()
