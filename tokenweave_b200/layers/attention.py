@@ -47,6 +47,10 @@ class AttentionMetadata:
 
 def plan_attention(q_lens: Sequence[int], kv_lens: Sequence[int]):
     """Host-side routing: 128-query tiles (longest causal span first) and single-query tokens."""
+    if q_lens and max(q_lens) == 1 and min(q_lens) == 1:
+        # a decode-only step (the common case while serving): one single-query token per sequence, no loop
+        rows = np.arange(len(q_lens), dtype=np.int32)
+        return [], [], rows, rows, np.asarray(kv_lens, dtype=np.int32)
     tile_seq, tile_q0, tok_row, tok_seq, tok_kv = [], [], [], [], []
     row = 0
     for b, (ql, kv) in enumerate(zip(q_lens, kv_lens)):

@@ -155,13 +155,16 @@ class Sampler:
         return ops.sample(logits, packed.pin_memory().to(logits.device, non_blocking=True))
 
     def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams],
-                 generators: Sequence[Optional[torch.Generator]], prompt_tokens=None, output_tokens=None) -> SamplerOutput:
+                 generators: Sequence[Optional[torch.Generator]], prompt_tokens=None, output_tokens=None,
+                 needs_penalties: Optional[Sequence[bool]] = None) -> SamplerOutput:
+        """``needs_penalties``: per request, whether its logits have to be edited (the caller may have cached what
+        ``SamplingParams.needs_penalties`` works out from a dozen fields)."""
         B, V = logits.shape
         want_logprobs = any(sp.logprobs is not None for sp in params)
         # reported log-probabilities are the model's own: taken before penalties, logit bias and masks touch the
         # logits (vllm/v1/sample/sampler.py:36-47 computes its raw_logprobs first as well)
         raw_logprobs = torch.log_softmax(logits.float(), dim=-1) if want_logprobs else None
-        if any(sp.needs_penalties for sp in params):
+        if any(needs_penalties) if needs_penalties is not None else any(sp.needs_penalties for sp in params):
             logits = apply_penalties(logits.clone(), params, prompt_tokens, output_tokens, guided=self._guided)
         if all(sp.greedy for sp in params):
             ids = ops.argmax(logits)

@@ -71,6 +71,15 @@ class _CachedRequest:
     block_ids: list[int]
     generator: Optional[torch.Generator] = None
     lora_id: int = 0
+    # fixed for the life of a request (its sampling parameters do not change once it is with the workers); read
+    # for every request on every step, so not recomputed from the dozen fields behind them each time
+    needs_penalties: bool = False
+    plain_greedy: bool = False        # greedy, no logits edits, no log-probabilities: the argmax kernel suffices
+
+    def __post_init__(self):
+        sp = self.sampling_params
+        self.needs_penalties = bool(sp.needs_penalties)
+        self.plain_greedy = bool(sp.greedy and not self.needs_penalties and sp.logprobs is None)
 
 
 class ModelRunner:
@@ -354,8 +363,7 @@ class ModelRunner:
             return result
         n_logits = len(logits_rows)
         reqs = [self.requests[r] for r in sample_reqs]
-        greedy = bool(reqs) and all(r.sampling_params.greedy and not r.sampling_params.needs_penalties
-                                    and r.sampling_params.logprobs is None for r in reqs)
+        greedy = bool(reqs) and all(r.plain_greedy for r in reqs)
         if n_logits:
             self._rows_host[:n_logits] = torch.as_tensor(logits_rows, dtype=torch.long)
             self._rows_dev[:n_logits].copy_(self._rows_host[:n_logits], non_blocking=True)
@@ -386,9 +394,20 @@ class ModelRunner:
                 from ..layers.sampler import SamplerOutput
                 out = SamplerOutput(greedy_ids)
             else:
+                # the token history is copied only for the requests whose logits it edits (penalties, masks);
+                # everyone else gets its LENGTH (seeded draws depend on the position), not a copy of its tokens:
+                # slicing every prompt on every step cost milliseconds per decode step of a full batch
+                prompts_h, outputs_h = [], []
+                for r in reqs:
+                    n_p = r.num_prompt_tokens
+                    if r.needs_penalties:
+                        prompts_h.append(r.token_ids[:n_p])
+                        outputs_h.append(r.token_ids[n_p:])
+                    else:
+                        prompts_h.append(())
+                        outputs_h.append(range(len(r.token_ids) - n_p))
                 out = self.sampler(logits, [r.sampling_params for r in reqs], [r.generator for r in reqs],
-                                   [r.token_ids[: r.num_prompt_tokens] for r in reqs],
-                                   [r.token_ids[r.num_prompt_tokens:] for r in reqs])
+                                   prompts_h, outputs_h, [r.needs_penalties for r in reqs])
             if ev is not None:
                 ev[1].record()
             if self._status_src is not None:
