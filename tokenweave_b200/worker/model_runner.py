@@ -80,6 +80,21 @@ class _CachedRequest:
         sp = self.sampling_params
         self.needs_penalties = bool(sp.needs_penalties)
         self.plain_greedy = bool(sp.greedy and not self.needs_penalties and sp.logprobs is None)
+        self._blocks_np = np.empty(max(16, 2 * len(self.block_ids)), dtype=np.int32)
+        self._blocks_n = 0
+
+    def block_array(self) -> np.ndarray:
+        """``block_ids`` as an int32 array that grows with the list (block-table rows are filled from it on every
+        step; converting the list each time was a visible share of a decode step's host time)."""
+        n = len(self.block_ids)
+        if n > self._blocks_n:
+            if n > self._blocks_np.size:
+                grown = np.empty(2 * n, dtype=np.int32)
+                grown[:self._blocks_n] = self._blocks_np[:self._blocks_n]
+                self._blocks_np = grown
+            self._blocks_np[self._blocks_n:n] = self.block_ids[self._blocks_n:n]
+            self._blocks_n = n
+        return self._blocks_np[:n]
 
 
 class ModelRunner:
@@ -287,7 +302,7 @@ class ModelRunner:
                 slots[row] = req.block_ids[computed // bs] * bs + computed % bs
                 q_lens.append(1)
                 kv_lens.append(computed + 1)
-                tables[b] = req.block_ids
+                tables[b] = req.block_array()
                 if computed + 1 >= len(req.token_ids):
                     logits_rows.append(row)
                     sample_reqs.append(rid)
@@ -302,11 +317,11 @@ class ModelRunner:
                 spec[rid] = drafts
             pos = np.arange(computed, computed + n_new, dtype=np.int32)
             positions[row:row + n_new] = pos
-            blocks = np.asarray(req.block_ids, dtype=np.int32)
+            blocks = req.block_array()
             slots[row:row + n_new] = blocks[pos // bs] * bs + pos % bs
             q_lens.append(n_new)
             kv_lens.append(computed + n_new)
-            tables[b] = req.block_ids
+            tables[b] = blocks
             if computed + n_base >= len(req.token_ids):
                 # one logits row at the request's last own token, and one after every draft
                 for k in range(len(drafts) + 1):
