@@ -66,3 +66,10 @@ def test_plan_attention_routing():
     assert (tile_seq[0], tile_q0[0]) == (3, 0)            # longest causal span first
     assert tok_row == [300, 301, 302, 303, 304, 305] and tok_seq == [1, 2, 2, 2, 2, 2]
     assert tok_kv == [77, 36, 37, 38, 39, 40]
+    # a decode-only step takes the loop-free path and must say what the loop says for it
+    tile_seq, tile_q0, tok_row, tok_seq, tok_kv = plan_attention([1, 1, 1], [9, 300, 41])
+    assert list(tile_seq) == [] and list(tile_q0) == []
+    assert list(tok_row) == [0, 1, 2] and list(tok_seq) == [0, 1, 2] and list(tok_kv) == [9, 300, 41]
+    # one two-token row (a verified draft) in the batch: back to the general path
+    _, _, tok_row, tok_seq, tok_kv = plan_attention([1, 2], [9, 31])
+    assert list(tok_row) == [0, 1, 2] and list(tok_seq) == [0, 1, 1] and list(tok_kv) == [9, 30, 31]
