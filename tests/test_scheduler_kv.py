@@ -244,3 +244,28 @@ def test_priority_policy_orders_admission_and_preemption():
     assert victims and victims[0] == "2" and "1" not in victims and "3" not in victims
     with pytest.raises(ValueError):
         Scheduler(SchedulerConfig(64, 8, True, 1024, "lottery"), kv).add_request(req(9, 4))
+
+
+def test_long_prefill_threshold_lets_short_requests_in():
+    """With a cap on the new tokens of one request per step a long prompt shares the budget from the first step."""
+    kv = KVCacheManager(64, 16, False)
+    s = Scheduler(SchedulerConfig(64, 8, True, 1024, "fcfs", 24), kv)
+    s.add_request(req(0, 100))
+    s.add_request(req(1, 30))
+    out, _ = run_step(s)
+    assert [(x.request.request_id, x.num_new_tokens) for x in out.scheduled] == [("0", 24), ("1", 24)]
+    out, touched = run_step(s)
+    # both continue under the cap; request 1 finishes its prompt with its last six tokens and emits a token
+    assert [(x.request.request_id, x.num_new_tokens) for x in out.scheduled] == [("0", 24), ("1", 6)]
+    assert [r.request_id for r in touched] == ["1"]
+    steps = 2
+    while s.has_unfinished_requests() and steps < 40:
+        run_step(s)
+        steps += 1
+    assert not s.has_unfinished_requests() and kv.pool.num_free == 63      # everything finished, blocks returned
+    # without chunked prefill the cap is ignored (a prompt is scheduled whole or not at all)
+    kv2 = KVCacheManager(64, 16, False)
+    s2 = Scheduler(SchedulerConfig(128, 8, False, 1024, "fcfs", 24), kv2)
+    s2.add_request(req(0, 100))
+    out, _ = run_step(s2)
+    assert [(x.request.request_id, x.num_new_tokens) for x in out.scheduled] == [("0", 100)]

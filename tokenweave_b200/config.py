@@ -268,6 +268,9 @@ class SchedulerConfig:
     enable_chunked_prefill: bool = True
     max_model_len: int = 8192
     policy: str = "fcfs"                  # "fcfs" | "priority" (lower value first, arrival order among equals)
+    # > 0: a request gets at most this many new tokens per step, so that one long prompt does not take a whole
+    # step's budget and shorter requests behind it start sooner (vllm/v1/core/sched/scheduler.py:181-184, 333-336)
+    long_prefill_token_threshold: int = 0
 
 
 @dataclass
@@ -350,6 +353,7 @@ class EngineArgs:
     max_num_seqs: int = 256
     enable_chunked_prefill: bool = True
     scheduling_policy: str = "fcfs"       # "fcfs" | "priority": requests carry a priority, lower values run first
+    long_prefill_token_threshold: int = 0     # > 0: cap on the new tokens of one request per step
     enforce_eager: bool = True
     enable_expert_parallel: bool = False
     disable_custom_all_reduce: bool = True
@@ -407,7 +411,7 @@ class EngineArgs:
                                     data_parallel_rank=self.data_parallel_rank,
                                     pipeline_parallel_size=self.pipeline_parallel_size),
             scheduler=SchedulerConfig(budget, self.max_num_seqs, self.enable_chunked_prefill, max_len,
-                                      self.scheduling_policy),
+                                      self.scheduling_policy, max(0, int(self.long_prefill_token_threshold))),
             tokenweave=TokenWeaveConfig(mode=self.tokenweave_mode, config_path=self.tokenweave_config,
                                         overlap_threshold=self.tokenweave_threshold,
                                         transport=self.tokenweave_transport,

@@ -107,6 +107,7 @@ class Scheduler:
         out = SchedulerOutput(step_id=self._step)
         self._step += 1
         budget = self.config.max_num_batched_tokens
+        cap = self.config.long_prefill_token_threshold
         preempted: list[Request] = []
 
         # running requests first (decode tokens and prefill continuations)
@@ -114,6 +115,8 @@ class Scheduler:
         while i < len(self.running) and budget > 0:
             req = self.running[i]
             n = min(req.num_tokens - req.num_computed_tokens, budget)
+            if 0 < cap < n and self.config.enable_chunked_prefill:
+                n = cap
             if not self.config.enable_chunked_prefill and n < req.num_tokens - req.num_computed_tokens:
                 i += 1
                 continue
@@ -169,6 +172,8 @@ class Scheduler:
                 n_ext = len(ext_hashes) * self.kv.block_size
                 remaining = req.num_tokens - req.num_computed_tokens - n_cached - n_ext
                 n = min(remaining, budget)
+                if 0 < cap < n and self.config.enable_chunked_prefill:
+                    n = cap
                 if n < remaining and not self.config.enable_chunked_prefill:
                     break
                 req.num_computed_tokens += n_cached
