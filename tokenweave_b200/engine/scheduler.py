@@ -210,11 +210,29 @@ class Scheduler:
         sampled = dict(zip(result.req_ids, result.sampled_token_ids))
         touched: list[Request] = []
         self.last_emitted = 0              # tokens appended to outputs by this step
+        spec_on = self.spec.enabled
         for s in sched.scheduled:
             req = s.request
             if req.status.finished:
                 continue
             tok = sampled.get(req.request_id)
+            if not s.spec_token_ids and type(tok) is int and not spec_on:
+                # the common decode step (one sampled token, no drafts): the general path below without its
+                # temporaries and helper calls
+                req.num_computed_tokens = s.num_computed_tokens + s.num_new_tokens
+                if req.num_computed_tokens < req.num_tokens:
+                    self.kv.cache_full_blocks(req)
+                    continue
+                req.output_token_ids.append(tok)
+                self.last_emitted += 1
+                if req.first_token_time is None:
+                    req.first_token_time = time.monotonic()
+                stop = self._stop_decision(req)
+                self.kv.cache_full_blocks(req)
+                if stop is not None:
+                    self._stop_running(req, *stop)
+                touched.append(req)
+                continue
             toks = [int(t) for t in tok] if isinstance(tok, (list, tuple)) else ([] if tok is None else [int(tok)])
             # drafts that the model did not confirm leave no valid KV behind: they are not "computed"
             rejected = 0
